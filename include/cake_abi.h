@@ -1,0 +1,193 @@
+/* C ABI of libcake_b200.so: the sm_100a backend for the two kernel targets of tpu-cake's
+ * schedule dialect -- the K-sharded BF16 matmul followed by a reduce-scatter, and Inkling
+ * ragged paged attention (RPA).
+ *
+ * Conventions
+ *   - Every function returns an int32_t status: 0 = CAKE_OK, negative = error. A textual
+ *     description of the last error on the calling thread is returned by cake_last_error().
+ *   - The caller owns every device buffer it passes in. The library owns only its handles
+ *     and the symmetric receive slots it allocates for the peer-to-peer strategy.
+ *   - One process drives one GPU (the current CUDA device at create time). Multi-GPU runs
+ *     use one process per GPU; receive slots are shared between processes with CUDA IPC
+ *     handles that the host exchanges over its own channel (torch.distributed, MPI, ...).
+ *   - Enqueue calls are asynchronous and ordered on the CUDA stream passed in (a
+ *     cudaStream_t cast to void*; NULL = the legacy default stream).
+ *   - Handles are not thread-safe.
+ *   - No function falls back to a CPU implementation.
+ */
+#ifndef CAKE_ABI_H_
+#define CAKE_ABI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CAKE_OK 0
+#define CAKE_ERR_INVALID_ARGUMENT (-1)
+#define CAKE_ERR_CUDA (-2)
+#define CAKE_ERR_UNSUPPORTED (-3)
+#define CAKE_ERR_TIMEOUT (-4)   /* a bounded device-side wait ran out; see cake_status */
+#define CAKE_ERR_DEVICE_CHECK (-5) /* a device-side index check failed; see cake_status */
+#define CAKE_ERR_STATE (-6)
+
+#define CAKE_MAX_WORLD 8
+
+#define CAKE_DTYPE_F32 0
+#define CAKE_DTYPE_BF16 1
+
+/* ---------------------------------------------------------------- general */
+
+/* ABI version of the loaded library. */
+int32_t cake_abi_version(void);
+
+/* Last error message of the calling thread (never NULL). */
+const char* cake_last_error(void);
+
+/* Device-written status word of the most recent kernels of a handle family.
+ * code: 0 = ok, 1 = bounded wait on a shared-memory barrier ran out, 2 = bounded wait on a
+ * peer arrival counter ran out, 3 = page index out of range, 4 = sequence metadata out of range.
+ * detail0..2 carry coordinates (block, tile / sequence, stage / page slot). */
+typedef struct cake_status {
+  int32_t code;
+  int32_t detail0;
+  int32_t detail1;
+  int32_t detail2;
+} cake_status;
+
+/* ---------------------------------------------------------------- symmetric memory helpers
+ * Replaces the remote-DMA scratch the reference allocates inside its Pallas ring kernel
+ * (src/tpu_cake/pallas_lowering.py:276-326): receive slots live in ordinary device memory
+ * allocated here with cudaMalloc so that they can be exported to peer processes. */
+int32_t cake_symm_alloc(size_t bytes, void** out_ptr);           /* zero-filled */
+int32_t cake_symm_free(void* ptr);
+int32_t cake_ipc_export(void* ptr, uint8_t handle_out[64]);
+int32_t cake_ipc_open(const uint8_t handle[64], void** out_ptr);
+int32_t cake_ipc_close(void* ptr);
+
+/* ---------------------------------------------------------------- matmul + reduce-scatter
+ * Replaces PallasMatmulPlan.build()'s executable (src/tpu_cake/pallas_lowering.py:417-476):
+ * the per-device local contraction (_matmul_kernel, :44-50,429-444) followed by the
+ * reduce-scatter over the mesh axis (lax.psum_scatter, :459-464, or the Pallas ring, :117-326).
+ */
+
+#define CAKE_RS_LOCAL_PARTIAL 0 /* write the partial, laid out owner-major; the host runs the
+                                   library collective (NCCL reduce-scatter) on it */
+#define CAKE_RS_P2P_OWNER_PUSH 1 /* epilogue pushes each partial tile to its owner GPU; a second
+                                    kernel sums the W slots in rank order */
+
+typedef struct cake_matmul_rs_desc {
+  int64_t m;            /* rows of lhs and of the partial */
+  int64_t n;            /* columns of rhs and of the partial */
+  int64_t k_local;      /* this rank's share of the contraction dimension */
+  int32_t world;        /* mesh size W (1..CAKE_MAX_WORLD) */
+  int32_t rank;         /* this process's position on the mesh axis */
+  int32_t scatter_dim;  /* 0 = scatter rows (M), 1 = scatter columns (N) */
+  int32_t out_dtype;    /* CAKE_DTYPE_* of the reduced local output */
+  int32_t transport_dtype; /* CAKE_DTYPE_* of partial sums crossing the link (world > 1) */
+  int32_t strategy;     /* CAKE_RS_* (ignored when world == 1) */
+  int32_t tile_m;       /* 128 */
+  int32_t tile_n;       /* 64, 128 or 256 */
+  int32_t rhs_layout;   /* 0 = rhs is [k_local, n] row-major (the reference layout),
+                           1 = rhs is [n, k_local] row-major (pre-transposed) */
+  int32_t reserved;
+} cake_matmul_rs_desc;
+
+typedef struct cake_matmul_rs cake_matmul_rs;
+
+int32_t cake_matmul_rs_create(const cake_matmul_rs_desc* desc, cake_matmul_rs** out);
+int32_t cake_matmul_rs_destroy(cake_matmul_rs* plan);
+
+/* Bytes of the partial buffer for CAKE_RS_LOCAL_PARTIAL (m * n * transport size). */
+size_t cake_matmul_rs_partial_bytes(const cake_matmul_rs* plan);
+
+/* CAKE_RS_P2P_OWNER_PUSH: bytes of this rank's receive slots / arrival counters. */
+size_t cake_matmul_rs_slot_bytes(const cake_matmul_rs* plan);
+size_t cake_matmul_rs_flag_bytes(const cake_matmul_rs* plan);
+
+/* CAKE_RS_P2P_OWNER_PUSH: slot and counter buffers of every rank (entry [rank] is this rank's own
+ * allocation, the others are IPC mappings). Must be called once before the first enqueue. */
+int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void* const* flags);
+
+/* lhs: bf16 [m, k_local]; rhs: bf16 per rhs_layout; out: world == 1 or P2P: the reduced local
+ * output [m/W, n] or [m, n/W] in out_dtype; LOCAL_PARTIAL with world > 1: the owner-major partial
+ * [W][out_rows][out_cols] in transport_dtype. */
+int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void* rhs, void* out,
+                               void* stream);
+
+/* Same computation with HOST buffers: copies lhs and rhs to device staging buffers owned by the
+ * plan, enqueues, copies the local output back and synchronises the stream. world == 1 or P2P. */
+int32_t cake_matmul_rs_run_host(cake_matmul_rs* plan, const void* lhs_host, const void* rhs_host,
+                                void* out_host, void* stream);
+
+/* Reads (and clears) the device status word; synchronises the stream first. */
+int32_t cake_matmul_rs_status(cake_matmul_rs* plan, void* stream, cake_status* out);
+
+/* Number of kernels the last enqueue launched (for launch accounting). */
+int32_t cake_matmul_rs_launches_per_enqueue(const cake_matmul_rs* plan);
+
+/* ---------------------------------------------------------------- ragged paged attention
+ * Replaces FusedRpaPlan.invoke / OwnedRpaDecodeCorePlan.build
+ * (src/tpu_cake/rpa_lowering.py:232-273,900-963), whose device code is _owned_rpa_kernel_loop
+ * (src/tpu_cake/rpa_owned_kernel.py:85-960), and gives the prototype op
+ * tpu_schedule.ragged_paged_attention (src/tpu_cake/dialects/tpu_schedule.py:2003-2103) a lowering.
+ */
+
+#define CAKE_RPA_CACHE_SEPARATE 0 /* key_cache, value_cache: [pages, page_size, kv_heads, head_dim] */
+#define CAKE_RPA_CACHE_FUSED 1    /* [pages, page_size, 2*kv_heads/2, 2, head_dim_padded]; head h's K at
+                                     interleaved index 2h, V at 2h+1 */
+#define CAKE_RPA_TABLE_2D 0       /* page_table[num_seqs, max_pages], token t -> page_table[s, t/ps] */
+#define CAKE_RPA_TABLE_FLAT 1     /* page_indices flat; sequence s starts at cu_kv_lens[s] / ps */
+
+typedef struct cake_rpa_desc {
+  int32_t num_seqs;
+  int32_t num_q_tokens;   /* sum of query lengths (== num_seqs for pure decode) */
+  int32_t q_heads;
+  int32_t kv_heads;
+  int32_t head_dim;       /* 128 */
+  int32_t head_dim_padded;/* fused cache only; == head_dim for the separate layout */
+  int32_t page_size;      /* tokens per page: 1, 2, 4, 8, 16 or 32 */
+  int32_t cache_layout;   /* CAKE_RPA_CACHE_* */
+  int32_t table_layout;   /* CAKE_RPA_TABLE_* */
+  int32_t max_pages_per_seq; /* row pitch of the 2-D page table */
+  int64_t total_pages;
+  float sm_scale;
+  int32_t bias_mode;      /* 0 = none, 1 = dense f32 bias[q_heads, bias_extent] indexed by key
+                             position (prototype op), 2 = relative bias: states[tokens, q_heads, R]
+                             (bf16) x projection[R, extent] (bf16) at distance kv_len-1-pos */
+  int32_t bias_extent;
+  int32_t rel_dim;        /* R for bias_mode 2 */
+  int32_t update_cache;   /* 1 = first write new_k/new_v of each sequence at position kv_len-1 */
+  int32_t kv_chunk_tokens;/* split-KV chunk; 0 = library default */
+  int32_t reserved;
+} cake_rpa_desc;
+
+typedef struct cake_rpa cake_rpa;
+
+int32_t cake_rpa_create(const cake_rpa_desc* desc, cake_rpa** out);
+int32_t cake_rpa_destroy(cake_rpa* plan);
+
+/* Scratch the decode needs for split-KV partial results (bytes, device memory). */
+size_t cake_rpa_workspace_bytes(const cake_rpa* plan);
+
+/* Pure decode (one query token per sequence).
+ * q, out: bf16 [num_seqs, q_heads, head_dim] (out may alias q);
+ * new_k, new_v: bf16 [num_seqs, kv_heads, head_dim] or NULL when update_cache == 0;
+ * cache0: key cache (separate) or fused cache; cache1: value cache or NULL;
+ * kv_lens: i32 [num_seqs]; page_table: i32 per table_layout; cu_kv_lens: i32 [num_seqs+1] (flat
+ * layout) or NULL; bias0 / bias1 per bias_mode or NULL. */
+int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k, const void* new_v,
+                                void* cache0, void* cache1, const int32_t* kv_lens,
+                                const int32_t* page_table, const int32_t* cu_kv_lens,
+                                const void* bias0, const void* bias1, void* out, void* workspace,
+                                void* stream);
+
+int32_t cake_rpa_status(cake_rpa* plan, void* stream, cake_status* out);
+int32_t cake_rpa_launches_per_enqueue(const cake_rpa* plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CAKE_ABI_H_ */

@@ -1,0 +1,809 @@
+// K-sharded BF16 matmul followed by a reduce-scatter, for sm_100a.
+//
+// What it replaces: the local contraction `_matmul_kernel` (src/tpu_cake/pallas_lowering.py:44-50,
+// launched :429-444) and the collective that follows it (lax.psum_scatter :459-464, or the
+// bidirectional Pallas ring :117-326). The reference materialises the f32 partial [M,N] in HBM
+// between the two; here the epilogue of the contraction writes every partial tile straight to the
+// GPU that owns it, and a second small kernel sums the W received copies in rank order.
+//
+// cake_matmul_rs_sm100<BN, B_KMAJOR>: persistent, warp-specialised.
+//   warp 0    TMA producer: A tile 128x64 and B tile 64xBN (bf16) per stage into 128B-swizzled smem
+//   warp 1    owns TMEM; one lane issues tcgen05.mma (M=128, N=BN, K=16), f32 accumulators in TMEM,
+//             two accumulator buffers so the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2-5 epilogue: tcgen05.ld -> convert -> swizzled smem staging -> 128-byte row segments to
+//             the owner's memory (local or peer), then a release-add on the owner's arrival counter
+// cake_reduce_slots_sm100: waits (bounded) for the W arrival counters, then out = sum over source
+//   ranks in fixed order (deterministic), cast to the output dtype.
+#include <cuda_bf16.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <new>
+
+#include "cake_host.h"
+#include "cake_ptx.cuh"
+
+namespace cake {
+
+constexpr int kTileM = 128;
+constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kABytes = kTileM * kBlockK * 2;
+constexpr uint32_t kStagingBytesPerWarp = 32 * 128;
+constexpr long long kBarrierBudgetCycles = 4000000000ll;  // about two seconds of SM clock
+constexpr unsigned long long kPeerBudgetNs = 20000000000ull;  // 20 s
+
+template <int BN>
+struct GemmCfg {
+  static constexpr uint32_t kBBytes = BN * kBlockK * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
+  static constexpr uint32_t kSmemBytes =
+      kStages * kStageBytes + 4 * kStagingBytesPerWarp + 256 /*barriers*/ + 1024 /*alignment*/;
+};
+
+struct MatmulParams {
+  int32_t m, n, k_local;
+  int32_t m_tiles, n_tiles, k_blocks;
+  int32_t world, rank, scatter_dim;
+  int32_t out_rows, out_cols;  // shape of one owner's local output
+  int32_t store_f32;           // destination element type: 1 = f32, 0 = bf16
+  int32_t vec_ok;              // 16-byte pieces never straddle owners or bounds
+  int32_t count_arrivals;      // peer-to-peer strategy: signal the owner's counter per tile
+  int32_t region_order;        // visit owner regions starting at rank+1 (own region last)
+  void* dest[CAKE_MAX_WORLD];  // per-owner base of the [out_rows, out_cols] destination
+  unsigned long long* arrive[CAKE_MAX_WORLD];  // per-owner counter written by this rank
+  int32_t* status;
+};
+
+__device__ __forceinline__ void record_status(int32_t* status, int code, int d0, int d1, int d2) {
+  if (status && atomicCAS(status, 0, code) == 0) {
+    status[1] = d0;
+    status[2] = d1;
+    status[3] = d2;
+  }
+}
+
+// Bounded mbarrier wait that also gives up when another role of this CTA has aborted.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity,
+                                              volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (true) {
+    for (int i = 0; i < 32; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag) return false;
+    if (clock64() - start > kBarrierBudgetCycles) return false;
+  }
+}
+
+// Grouped rasterisation: consecutive tile ids walk 8 row-tiles down before moving one column-tile
+// right, so the CTAs of one wave share A rows and B columns in L2.
+__device__ __forceinline__ void raster(int t, int mt_count, int nt_count, int& mi, int& ni) {
+  const int group_sz = 8 * nt_count;
+  const int g = t / group_sz;
+  const int first_m = g * 8;
+  const int gm = min(8, mt_count - first_m);
+  const int r = t - g * group_sz;
+  mi = first_m + r % gm;
+  ni = r / gm;
+}
+
+template <int BN>
+__device__ __forceinline__ void tile_coords(const MatmulParams& p, int t, int& mt, int& nt) {
+  if (p.region_order) {
+    if (p.scatter_dim == 0) {
+      const int m_tiles_r = p.out_rows / kTileM;
+      const int per_region = m_tiles_r * p.n_tiles;
+      const int j = t / per_region;
+      const int owner = (p.rank + 1 + j) % p.world;
+      int mi, ni;
+      raster(t - j * per_region, m_tiles_r, p.n_tiles, mi, ni);
+      mt = owner * m_tiles_r + mi;
+      nt = ni;
+    } else {
+      const int n_tiles_r = p.out_cols / BN;
+      const int per_region = p.m_tiles * n_tiles_r;
+      const int j = t / per_region;
+      const int owner = (p.rank + 1 + j) % p.world;
+      int mi, ni;
+      raster(t - j * per_region, p.m_tiles, n_tiles_r, mi, ni);
+      mt = mi;
+      nt = owner * n_tiles_r + ni;
+    }
+  } else {
+    raster(t, p.m_tiles, p.n_tiles, mt, nt);
+  }
+}
+
+// Destination of element (r, c) of the partial: which owner, and where in its local output.
+__device__ __forceinline__ char* dest_addr(const MatmulParams& p, int r, int c, int elem_bytes) {
+  int owner, lr, lc;
+  if (p.scatter_dim == 0) {
+    owner = r / p.out_rows;
+    lr = r - owner * p.out_rows;
+    lc = c;
+  } else {
+    owner = c / p.out_cols;
+    lr = r;
+    lc = c - owner * p.out_cols;
+  }
+  return static_cast<char*>(p.dest[owner]) +
+         (static_cast<size_t>(lr) * p.out_cols + lc) * static_cast<size_t>(elem_bytes);
+}
+
+template <int BN, bool B_KMAJOR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    cake_matmul_rs_sm100(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, const MatmulParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* staging = smem + STAGES * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 4 * kStagingBytesPerWarp);
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;      // [2]
+  uint64_t* drain_bar = tmem_empty + 2;      // [1]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tmem_full[b]), 1);
+      mbar_init(smem_u32(&tmem_empty[b]), 4);
+    }
+    mbar_init(smem_u32(drain_bar), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_base_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mt, nt;
+        tile_coords<BN>(p, t, mt, nt);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!wait_or_abort(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
+            if (!*abort_flag) record_status(p.status, 1, blockIdx.x, t, 100 + stage);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&full_bar[stage]);
+          const uint32_t a_dst = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t b_dst = a_dst + kABytes;
+          mbar_arrive_expect_tx(full, Cfg::kStageBytes);
+          tma_load_2d(a_dst, &tmap_a, full, kb * kBlockK, mt * kTileM);
+          if (B_KMAJOR) {
+            tma_load_2d(b_dst, &tmap_b, full, kb * kBlockK, nt * BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) {
+              tma_load_2d(b_dst + j * (64 * kBlockK * 2), &tmap_b, full, nt * BN + j * 64,
+                          kb * kBlockK);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Let copies already in flight land before the CTA's shared memory is released.
+        for (int s = 0; s < STAGES; ++s) {
+          const uint32_t par = (s < stage) ? phase : (phase ^ 1);
+          mbar_wait_bounded(smem_u32(&full_bar[s]), par, 200000000ll);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(kTileM, BN, 0, B_KMAJOR ? 0 : 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!wait_or_abort(smem_u32(&tmem_empty[buf]), acc_phase ^ 1, abort_flag)) {
+          if (!*abort_flag) record_status(p.status, 1, blockIdx.x, t, 200 + buf);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!wait_or_abort(smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            if (!*abort_flag) record_status(p.status, 1, blockIdx.x, t, 300 + stage);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            // A (K-major): 8-row groups 1024 B apart; a K step of 16 elements is 32 B inside the
+            // 128-byte swizzle row.
+            const uint64_t a_desc = umma_desc_sw128(a_addr + kk * 32, 16, 1024);
+            // B as [N,K] (K-major): same as A. B as [K,N] (MN-major): 64-column blocks 8192 B
+            // apart (leading offset), 8-deep K groups 1024 B apart (stride offset); a K step of
+            // 16 is two such groups.
+            const uint64_t b_desc = B_KMAJOR ? umma_desc_sw128(b_addr + kk * 32, 16, 1024)
+                                             : umma_desc_sw128(b_addr + kk * 2048, 8192, 1024);
+            tcgen05_mma_bf16(tmem_d, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          tcgen05_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tcgen05_commit(smem_u32(&tmem_full[buf]));
+      }
+      // Drain: every MMA issued above has retired before TMEM is released.
+      tcgen05_commit(smem_u32(drain_bar));
+      mbar_wait_bounded(smem_u32(drain_bar), 0, kBarrierBudgetCycles);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps 2..5
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* my_stage = staging + (warp - 2) * kStagingBytesPerWarp;
+    const int elem_bytes = p.store_f32 ? 4 : 2;
+    const int cols_per_chunk = p.store_f32 ? 32 : 64;  // 128 bytes per row per chunk
+    const int epp = 16 / elem_bytes;                   // elements per 16-byte piece
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      int mt, nt;
+      tile_coords<BN>(p, t, mt, nt);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      // The decision is made warp-uniform: tcgen05.ld below is a warp-collective instruction.
+      if (!__all_sync(0xffffffffu, wait_or_abort(smem_u32(&tmem_full[buf]), acc_phase, abort_flag))) {
+        if (!*abort_flag && lane == 0) record_status(p.status, 1, blockIdx.x, t, 400 + buf);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      const int row0 = mt * kTileM + q * 32;
+      const int num_chunks = BN / cols_per_chunk;
+      for (int ch = 0; ch < num_chunks; ++ch) {
+        uint4 pieces[8];
+        if (p.store_f32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + ch * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            pieces[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(t_row + ch * 64 + h * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]),
+                                                                __uint_as_float(v[8 * j + 2 * e + 1]));
+                w[e] = *reinterpret_cast<const uint32_t*>(&b2);
+              }
+              pieces[h * 4 + j] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+        if (ch == num_chunks - 1) {
+          // The accumulator buffer is fully read: hand it back to the MMA warp.
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty[buf]));
+        }
+        // Transpose through swizzled smem so that global stores are 128-byte row segments.
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = pieces[j];
+        }
+        __syncwarp();
+        const int pj = lane & 7;
+        const int c = nt * BN + ch * cols_per_chunk + pj * epp;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = i * 4 + (lane >> 3);
+          const int r = row0 + rr;
+          const uint4 val = *reinterpret_cast<const uint4*>(my_stage + rr * 128 + ((pj ^ (rr & 7)) << 4));
+          if (r < p.m) {
+            if (p.vec_ok) {
+              if (c < p.n) *reinterpret_cast<uint4*>(dest_addr(p, r, c, elem_bytes)) = val;
+            } else if (p.store_f32) {
+              const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+              for (int e = 0; e < 4; ++e)
+                if (c + e < p.n)
+                  *reinterpret_cast<uint32_t*>(dest_addr(p, r, c + e, 4)) = w[e];
+            } else {
+              const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+              for (int e = 0; e < 8; ++e)
+                if (c + e < p.n)
+                  *reinterpret_cast<uint16_t*>(dest_addr(p, r, c + e, 2)) =
+                      static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
+            }
+          }
+        }
+        __syncwarp();
+      }
+      if (p.count_arrivals) {
+        // Each epilogue warp publishes its own 32 rows: no CTA-wide barrier, so a warp that has
+        // given up on a wait can never leave the others stuck at one.
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_system();
+          const int r_lo = row0, r_hi = min(row0 + 32, p.m);
+          const int c_lo = nt * BN, c_hi = min(c_lo + BN, p.n);
+          if (r_hi > r_lo && c_hi > c_lo) {
+            if (p.scatter_dim == 0) {
+              for (int o = r_lo / p.out_rows; o <= (r_hi - 1) / p.out_rows; ++o) {
+                const int rows = min(r_hi, (o + 1) * p.out_rows) - max(r_lo, o * p.out_rows);
+                red_release_sys_add_u64(p.arrive[o],
+                                        static_cast<unsigned long long>(rows) * (c_hi - c_lo));
+              }
+            } else {
+              for (int o = c_lo / p.out_cols; o <= (c_hi - 1) / p.out_cols; ++o) {
+                const int cols = min(c_hi, (o + 1) * p.out_cols) - max(c_lo, o * p.out_cols);
+                red_release_sys_add_u64(p.arrive[o],
+                                        static_cast<unsigned long long>(cols) * (r_hi - r_lo));
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+// out[i] = sum over source ranks (fixed order) of slot[src][i]; waits for every source's arrival
+// counter to reach `expected` first. The wait is bounded; on expiry nothing is written and the
+// status word records which source was late.
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256)
+    cake_reduce_slots_sm100(const TIn* __restrict__ slots, TOut* __restrict__ out, size_t elems,
+                            int world, const unsigned long long* arrive,
+                            unsigned long long expected, int32_t* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const unsigned long long start = global_timer_ns();
+    for (int src = 0; src < world && ok; ++src) {
+      while (ld_acquire_sys_u64(arrive + src) < expected) {
+        if (global_timer_ns() - start > kPeerBudgetNs) {
+          record_status(status, 2, blockIdx.x, src, 0);
+          ok = 0;
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  constexpr int V = 16 / sizeof(TIn);  // elements per 16-byte load
+  const size_t groups = elems / V;
+  for (size_t g = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; g < groups;
+       g += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] = 0.f;
+    for (int src = 0; src < world; ++src) {
+      const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(slots + src * elems) + g);
+      if (sizeof(TIn) == 4) {
+        acc[0] += __uint_as_float(raw.x);
+        acc[1] += __uint_as_float(raw.y);
+        acc[2] += __uint_as_float(raw.z);
+        acc[3] += __uint_as_float(raw.w);
+      } else {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] += __uint_as_float(w[e] << 16);
+          acc[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      if (sizeof(TOut) == 4) {
+        reinterpret_cast<float*>(out)[g * V + e] = acc[e];
+      } else {
+        reinterpret_cast<__nv_bfloat16*>(out)[g * V + e] = __float2bfloat16_rn(acc[e]);
+      }
+    }
+  }
+  // Tail (elems not a multiple of V).
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (size_t i = groups * V; i < elems; ++i) {
+      float a = 0.f;
+      for (int src = 0; src < world; ++src) {
+        const TIn v = slots[src * elems + i];
+        a += sizeof(TIn) == 4 ? *reinterpret_cast<const float*>(&v)
+                              : __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&v)) << 16);
+      }
+      if (sizeof(TOut) == 4) reinterpret_cast<float*>(out)[i] = a;
+      else reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(a);
+    }
+  }
+}
+
+// bf16 [rows, cols] -> [cols, rows]; used only when the caller asks the library to consume the
+// reference's [K,N] rhs through the K-major operand path.
+__global__ void cake_transpose_bf16(const uint16_t* __restrict__ in, uint16_t* __restrict__ out,
+                                    int rows, int cols) {
+  __shared__ uint16_t tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[i][threadIdx.x] = in[static_cast<size_t>(r) * cols + c];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) out[static_cast<size_t>(c) * rows + r] = tile[threadIdx.x][i];
+  }
+}
+
+}  // namespace cake
+
+// ====================================================================================== host
+
+struct cake_matmul_rs {
+  cake_matmul_rs_desc d;
+  int device = 0;
+  int sm_count = 0;
+  int64_t out_rows = 0, out_cols = 0;
+  size_t tsize = 4;  // bytes per transported element
+  size_t osize = 4;  // bytes per output element
+  bool rhs_via_transpose = false;
+  void* rhs_t = nullptr;  // [n, k_local] scratch when rhs_via_transpose
+  void* slots[CAKE_MAX_WORLD] = {};
+  void* flags[CAKE_MAX_WORLD] = {};
+  bool bound = false;
+  unsigned long long epoch = 0;
+  cake::StatusWord status;
+  // tensor-map cache
+  const void* last_lhs = nullptr;
+  const void* last_rhs = nullptr;
+  CUtensorMap tmap_a, tmap_b;
+  // staging for run_host
+  void* h_lhs = nullptr;
+  void* h_rhs = nullptr;
+  void* h_out = nullptr;
+  int launches = 0;
+};
+
+namespace {
+
+using cake::fail;
+
+template <int BN, bool KM>
+int32_t launch_gemm(const cake_matmul_rs* plan, const cake::MatmulParams& p, int grid,
+                    cudaStream_t stream) {
+  auto kernel = cake::cake_matmul_rs_sm100<BN, KM>;
+  static bool configured = false;
+  if (!configured) {
+    CAKE_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       cake::GemmCfg<BN>::kSmemBytes));
+    configured = true;
+  }
+  kernel<<<grid, cake::kGemmThreads, cake::GemmCfg<BN>::kSmemBytes, stream>>>(plan->tmap_a,
+                                                                              plan->tmap_b, p);
+  CAKE_CUDA_TRY(cudaGetLastError());
+  return CAKE_OK;
+}
+
+int32_t encode_maps(cake_matmul_rs* plan, const void* lhs, const void* rhs_kmajor_or_mn) {
+  const cake_matmul_rs_desc& d = plan->d;
+  const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(d.k_local), static_cast<uint64_t>(d.m)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(d.k_local) * 2};
+    const uint32_t box[2] = {cake::kBlockK, cake::kTileM};
+    int32_t rc = cake::encode_tensor_map(&plan->tmap_a, lhs, 2, dims, strides, box, true);
+    if (rc) return rc;
+  }
+  if (kmajor) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(d.k_local), static_cast<uint64_t>(d.n)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(d.k_local) * 2};
+    const uint32_t box[2] = {cake::kBlockK, static_cast<uint32_t>(d.tile_n)};
+    return cake::encode_tensor_map(&plan->tmap_b, rhs_kmajor_or_mn, 2, dims, strides, box, true);
+  }
+  const uint64_t dims[2] = {static_cast<uint64_t>(d.n), static_cast<uint64_t>(d.k_local)};
+  const uint64_t strides[1] = {static_cast<uint64_t>(d.n) * 2};
+  const uint32_t box[2] = {64, cake::kBlockK};
+  return cake::encode_tensor_map(&plan->tmap_b, rhs_kmajor_or_mn, 2, dims, strides, box, true);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t cake_matmul_rs_create(const cake_matmul_rs_desc* desc, cake_matmul_rs** out) {
+  if (!desc || !out) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_create: null argument");
+  const cake_matmul_rs_desc& d = *desc;
+  if (d.m <= 0 || d.n <= 0 || d.k_local <= 0 || d.m > INT32_MAX || d.n > INT32_MAX ||
+      d.k_local > INT32_MAX)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "matmul shape must be positive and fit int32: m=%lld n=%lld k_local=%lld",
+                (long long)d.m, (long long)d.n, (long long)d.k_local);
+  if (d.world < 1 || d.world > CAKE_MAX_WORLD || d.rank < 0 || d.rank >= d.world)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "bad mesh: world=%d rank=%d", d.world, d.rank);
+  if (d.scatter_dim != 0 && d.scatter_dim != 1)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "scatter_dim must be 0 (M) or 1 (N), got %d", d.scatter_dim);
+  if ((d.out_dtype != CAKE_DTYPE_F32 && d.out_dtype != CAKE_DTYPE_BF16) ||
+      (d.transport_dtype != CAKE_DTYPE_F32 && d.transport_dtype != CAKE_DTYPE_BF16))
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "out_dtype / transport_dtype must be CAKE_DTYPE_F32 or CAKE_DTYPE_BF16");
+  if (d.tile_m != 128)
+    return fail(CAKE_ERR_UNSUPPORTED, "tile_m must be 128 on sm_100a (UMMA M), got %d", d.tile_m);
+  if (d.tile_n != 64 && d.tile_n != 128 && d.tile_n != 256)
+    return fail(CAKE_ERR_UNSUPPORTED, "tile_n must be 64, 128 or 256, got %d", d.tile_n);
+  if (d.k_local % 8 != 0)
+    return fail(CAKE_ERR_UNSUPPORTED, "k_local must be a multiple of 8 (16-byte TMA row pitch), got %lld",
+                (long long)d.k_local);
+  if (d.rhs_layout == 0 && d.n % 8 != 0)
+    return fail(CAKE_ERR_UNSUPPORTED, "n must be a multiple of 8 for a [k,n] rhs, got %lld", (long long)d.n);
+  if (d.rhs_layout != 0 && d.rhs_layout != 1)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rhs_layout must be 0 or 1");
+  const int64_t scattered = d.scatter_dim == 0 ? d.m : d.n;
+  if (scattered % d.world != 0)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "scatter dimension %lld is not divisible by world %d",
+                (long long)scattered, d.world);
+  if (d.world > 1 && d.strategy != CAKE_RS_LOCAL_PARTIAL && d.strategy != CAKE_RS_P2P_OWNER_PUSH)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "unknown reduce-scatter strategy %d", d.strategy);
+
+  cake_matmul_rs* plan = new (std::nothrow) cake_matmul_rs();
+  if (!plan) return fail(CAKE_ERR_CUDA, "out of host memory");
+  plan->d = d;
+  cudaError_t e = cudaGetDevice(&plan->device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&plan->sm_count, cudaDevAttrMultiProcessorCount, plan->device);
+  int major = 0;
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, plan->device);
+  if (e != cudaSuccess) {
+    delete plan;
+    return fail(CAKE_ERR_CUDA, "no usable CUDA device: %s", cudaGetErrorString(e));
+  }
+  if (major != 10) {
+    delete plan;
+    return fail(CAKE_ERR_UNSUPPORTED, "libcake_b200 needs an sm_100 GPU, found compute capability %d.x", major);
+  }
+  plan->out_rows = d.scatter_dim == 0 ? d.m / d.world : d.m;
+  plan->out_cols = d.scatter_dim == 1 ? d.n / d.world : d.n;
+  plan->osize = d.out_dtype == CAKE_DTYPE_F32 ? 4 : 2;
+  plan->tsize = d.world == 1 ? plan->osize : (d.transport_dtype == CAKE_DTYPE_F32 ? 4 : 2);
+  const char* env = getenv("CAKE_MATMUL_TRANSPOSE_RHS");
+  plan->rhs_via_transpose = d.rhs_layout == 0 && env && env[0] == '1';
+  int32_t rc = plan->status.ensure();
+  if (rc == CAKE_OK && plan->rhs_via_transpose) {
+    e = cudaMalloc(&plan->rhs_t, static_cast<size_t>(d.n) * d.k_local * 2);
+    if (e != cudaSuccess) rc = fail(CAKE_ERR_CUDA, "cudaMalloc(rhs_t) failed: %s", cudaGetErrorString(e));
+  }
+  if (rc != CAKE_OK) {
+    cake_matmul_rs_destroy(plan);
+    return rc;
+  }
+  *out = plan;
+  return CAKE_OK;
+}
+
+int32_t cake_matmul_rs_destroy(cake_matmul_rs* plan) {
+  if (!plan) return CAKE_OK;
+  plan->status.release();
+  if (plan->rhs_t) cudaFree(plan->rhs_t);
+  if (plan->h_lhs) cudaFree(plan->h_lhs);
+  if (plan->h_rhs) cudaFree(plan->h_rhs);
+  if (plan->h_out) cudaFree(plan->h_out);
+  delete plan;
+  return CAKE_OK;
+}
+
+size_t cake_matmul_rs_partial_bytes(const cake_matmul_rs* plan) {
+  return plan ? static_cast<size_t>(plan->d.m) * plan->d.n * plan->tsize : 0;
+}
+
+size_t cake_matmul_rs_slot_bytes(const cake_matmul_rs* plan) {
+  if (!plan || plan->d.world == 1) return 0;
+  // two parities x W sources x one local output in the transport dtype
+  return 2ull * plan->d.world * plan->out_rows * plan->out_cols * plan->tsize;
+}
+
+size_t cake_matmul_rs_flag_bytes(const cake_matmul_rs* plan) {
+  if (!plan || plan->d.world == 1) return 0;
+  return sizeof(unsigned long long) * CAKE_MAX_WORLD;
+}
+
+int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void* const* flags) {
+  if (!plan || !slots || !flags) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_bind_peers: null argument");
+  for (int r = 0; r < plan->d.world; ++r) {
+    if (!slots[r] || !flags[r]) return fail(CAKE_ERR_INVALID_ARGUMENT, "missing slot/flag pointer for rank %d", r);
+    plan->slots[r] = slots[r];
+    plan->flags[r] = flags[r];
+  }
+  plan->bound = true;
+  return CAKE_OK;
+}
+
+int32_t cake_matmul_rs_launches_per_enqueue(const cake_matmul_rs* plan) { return plan ? plan->launches : 0; }
+
+int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void* rhs, void* out,
+                               void* stream_v) {
+  if (!plan || !lhs || !rhs || !out) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_enqueue: null argument");
+  const cake_matmul_rs_desc& d = plan->d;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "lhs, rhs and out must be 16-byte aligned");
+  const bool p2p = d.world > 1 && d.strategy == CAKE_RS_P2P_OWNER_PUSH;
+  if (p2p && !plan->bound) return fail(CAKE_ERR_STATE, "cake_matmul_rs_bind_peers must be called before enqueue");
+  int launches = 0;
+
+  const void* rhs_used = rhs;
+  if (plan->rhs_via_transpose) {
+    dim3 grid((d.n + 31) / 32, (d.k_local + 31) / 32), block(32, 8);
+    cake::cake_transpose_bf16<<<grid, block, 0, stream>>>(static_cast<const uint16_t*>(rhs),
+                                                          static_cast<uint16_t*>(plan->rhs_t),
+                                                          (int)d.k_local, (int)d.n);
+    CAKE_CUDA_TRY(cudaGetLastError());
+    rhs_used = plan->rhs_t;
+    ++launches;
+  }
+  if (lhs != plan->last_lhs || rhs_used != plan->last_rhs) {
+    int32_t rc = encode_maps(plan, lhs, rhs_used);
+    if (rc) return rc;
+    plan->last_lhs = lhs;
+    plan->last_rhs = rhs_used;
+  }
+
+  cake::MatmulParams p;
+  memset(&p, 0, sizeof(p));
+  p.m = (int)d.m;
+  p.n = (int)d.n;
+  p.k_local = (int)d.k_local;
+  p.m_tiles = (int)((d.m + cake::kTileM - 1) / cake::kTileM);
+  p.n_tiles = (int)((d.n + d.tile_n - 1) / d.tile_n);
+  p.k_blocks = (int)((d.k_local + cake::kBlockK - 1) / cake::kBlockK);
+  p.world = d.world;
+  p.rank = d.rank;
+  p.scatter_dim = d.scatter_dim;
+  p.out_rows = (int)plan->out_rows;
+  p.out_cols = (int)plan->out_cols;
+  p.store_f32 = plan->tsize == 4;
+  const int epp = 16 / (int)plan->tsize;
+  p.vec_ok = (plan->out_cols % epp == 0) && (d.n % epp == 0);
+  p.count_arrivals = p2p;
+  p.status = plan->status.dev;
+  const size_t chunk_elems = static_cast<size_t>(plan->out_rows) * plan->out_cols;
+  unsigned long long parity = 0;
+  if (d.world == 1) {
+    p.dest[0] = out;
+  } else if (!p2p) {
+    for (int o = 0; o < d.world; ++o) p.dest[o] = static_cast<char*>(out) + o * chunk_elems * plan->tsize;
+  } else {
+    plan->epoch += 1;
+    parity = plan->epoch & 1ull;
+    for (int o = 0; o < d.world; ++o) {
+      p.dest[o] = static_cast<char*>(plan->slots[o]) + (parity * d.world + d.rank) * chunk_elems * plan->tsize;
+      p.arrive[o] = static_cast<unsigned long long*>(plan->flags[o]) + d.rank;
+    }
+  }
+  if (d.world > 1) {
+    const bool aligned = d.scatter_dim == 0 ? (plan->out_rows % cake::kTileM == 0)
+                                            : (plan->out_cols % d.tile_n == 0);
+    p.region_order = aligned ? 1 : 0;
+  }
+  const int num_tiles = p.m_tiles * p.n_tiles;
+  const int grid = num_tiles < plan->sm_count ? num_tiles : plan->sm_count;
+  const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
+  int32_t rc;
+  if (d.tile_n == 256) rc = kmajor ? launch_gemm<256, true>(plan, p, grid, stream) : launch_gemm<256, false>(plan, p, grid, stream);
+  else if (d.tile_n == 128) rc = kmajor ? launch_gemm<128, true>(plan, p, grid, stream) : launch_gemm<128, false>(plan, p, grid, stream);
+  else rc = kmajor ? launch_gemm<64, true>(plan, p, grid, stream) : launch_gemm<64, false>(plan, p, grid, stream);
+  if (rc) return rc;
+  ++launches;
+
+  if (p2p) {
+    const unsigned long long expected = plan->epoch * chunk_elems;
+    const char* my_slots = static_cast<const char*>(plan->slots[d.rank]) + parity * d.world * chunk_elems * plan->tsize;
+    const unsigned long long* my_flags = static_cast<const unsigned long long*>(plan->flags[d.rank]);
+    const size_t groups = chunk_elems / (16 / plan->tsize);
+    int rgrid = (int)((groups + 255) / 256);
+    if (rgrid > plan->sm_count * 8) rgrid = plan->sm_count * 8;
+    if (rgrid < 1) rgrid = 1;
+    if (plan->tsize == 4 && plan->osize == 4)
+      cake::cake_reduce_slots_sm100<float, float><<<rgrid, 256, 0, stream>>>((const float*)my_slots, (float*)out, chunk_elems, d.world, my_flags, expected, plan->status.dev);
+    else if (plan->tsize == 4)
+      cake::cake_reduce_slots_sm100<float, __nv_bfloat16><<<rgrid, 256, 0, stream>>>((const float*)my_slots, (__nv_bfloat16*)out, chunk_elems, d.world, my_flags, expected, plan->status.dev);
+    else if (plan->osize == 4)
+      cake::cake_reduce_slots_sm100<__nv_bfloat16, float><<<rgrid, 256, 0, stream>>>((const __nv_bfloat16*)my_slots, (float*)out, chunk_elems, d.world, my_flags, expected, plan->status.dev);
+    else
+      cake::cake_reduce_slots_sm100<__nv_bfloat16, __nv_bfloat16><<<rgrid, 256, 0, stream>>>((const __nv_bfloat16*)my_slots, (__nv_bfloat16*)out, chunk_elems, d.world, my_flags, expected, plan->status.dev);
+    CAKE_CUDA_TRY(cudaGetLastError());
+    ++launches;
+  }
+  plan->launches = launches;
+  return CAKE_OK;
+}
+
+int32_t cake_matmul_rs_run_host(cake_matmul_rs* plan, const void* lhs_host, const void* rhs_host,
+                                void* out_host, void* stream_v) {
+  if (!plan || !lhs_host || !rhs_host || !out_host) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_run_host: null argument");
+  const cake_matmul_rs_desc& d = plan->d;
+  if (d.world > 1 && d.strategy != CAKE_RS_P2P_OWNER_PUSH)
+    return fail(CAKE_ERR_UNSUPPORTED, "run_host needs world == 1 or the peer-to-peer strategy");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const size_t lhs_bytes = static_cast<size_t>(d.m) * d.k_local * 2;
+  const size_t rhs_bytes = static_cast<size_t>(d.n) * d.k_local * 2;
+  const size_t out_bytes = static_cast<size_t>(plan->out_rows) * plan->out_cols * plan->osize;
+  if (!plan->h_lhs) CAKE_CUDA_TRY(cudaMalloc(&plan->h_lhs, lhs_bytes));
+  if (!plan->h_rhs) CAKE_CUDA_TRY(cudaMalloc(&plan->h_rhs, rhs_bytes));
+  if (!plan->h_out) CAKE_CUDA_TRY(cudaMalloc(&plan->h_out, out_bytes));
+  CAKE_CUDA_TRY(cudaMemcpyAsync(plan->h_lhs, lhs_host, lhs_bytes, cudaMemcpyHostToDevice, stream));
+  CAKE_CUDA_TRY(cudaMemcpyAsync(plan->h_rhs, rhs_host, rhs_bytes, cudaMemcpyHostToDevice, stream));
+  int32_t rc = cake_matmul_rs_enqueue(plan, plan->h_lhs, plan->h_rhs, plan->h_out, stream_v);
+  if (rc) return rc;
+  CAKE_CUDA_TRY(cudaMemcpyAsync(out_host, plan->h_out, out_bytes, cudaMemcpyDeviceToHost, stream));
+  CAKE_CUDA_TRY(cudaStreamSynchronize(stream));
+  return CAKE_OK;
+}
+
+int32_t cake_matmul_rs_status(cake_matmul_rs* plan, void* stream_v, cake_status* out) {
+  if (!plan || !out) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_status: null argument");
+  int32_t rc = plan->status.read_and_clear(static_cast<cudaStream_t>(stream_v), out);
+  if (rc) return rc;
+  if (out->code == 1 || out->code == 2)
+    return fail(CAKE_ERR_TIMEOUT, "device-side bounded wait ran out: code=%d block=%d tile/src=%d where=%d",
+                out->code, out->detail0, out->detail1, out->detail2);
+  return CAKE_OK;
+}
+
+}  // extern "C"
