@@ -117,6 +117,14 @@ int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void
 int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void* rhs, void* out,
                                void* stream);
 
+/* CAKE_RS_P2P_OWNER_PUSH only: the two halves of cake_matmul_rs_enqueue as separate calls, so a
+ * host that drives several mesh positions in one process (a test that emulates W ranks on one GPU,
+ * a single-process multi-GPU driver) can enqueue every position's push before any reduction and
+ * never has one launch wait on a later one. */
+int32_t cake_matmul_rs_enqueue_push(cake_matmul_rs* plan, const void* lhs, const void* rhs,
+                                    void* stream);
+int32_t cake_matmul_rs_enqueue_reduce(cake_matmul_rs* plan, void* out, void* stream);
+
 /* Same computation with HOST buffers: copies lhs and rhs to device staging buffers owned by the
  * plan, enqueues, copies the local output back and synchronises the stream. world == 1 or P2P. */
 int32_t cake_matmul_rs_run_host(cake_matmul_rs* plan, const void* lhs_host, const void* rhs_host,

@@ -1,0 +1,216 @@
+"""GPU parity of cake_matmul_rs_sm100 / cake_reduce_slots_sm100 against the CPU oracle, through
+the C ABI."""
+
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import matmul_rs as oracle
+from tests.helpers import BF16, bf16_to_torch, bits_to_bf16
+from tpu_cake_b200 import _native, cuda_lowering, workloads
+
+pytestmark = pytest.mark.gpu
+
+PATTERNS = ("constant", "one-hot-stripes", "signed-periodic", "block-diagonal", "low-rank")
+
+
+def run_single(lhs: np.ndarray, rhs: np.ndarray, device, *, tile_n=256, output_dtype="f32") -> np.ndarray:
+    m, k = lhs.shape
+    n = rhs.shape[1]
+    plan = cuda_lowering.plan_distributed_matmul(mesh_size=1, m=m, k=k, n=n, tile_n=tile_n, output_dtype=output_dtype)
+    executable, _ = plan.build()
+    try:
+        out = torch.full(plan.output_local_shape, float("nan"), dtype=torch.float32 if output_dtype == "f32" else torch.bfloat16, device=device)
+        executable(bf16_to_torch(lhs, device), bf16_to_torch(rhs, device), out)
+        assert executable.status() == (0, 0, 0, 0)
+        assert executable.launches_per_call == 1
+        return out.float().cpu().numpy()
+    finally:
+        executable.close()
+
+
+def test_reference_inputs_local_problem_meets_reference_tolerance(cuda_device):
+    """mesh 8, 128 x 1024 x 1024 (the reference's CPU-runnable case): every rank's local
+    contraction, summed in rank order on the host, against numpy on the exact bf16 inputs with the
+    reference's allclose(1e-3, 1e-3)."""
+    lhs, rhs = workloads.distributed_matmul_inputs(8, 128, 1024, 1024)
+    expected = oracle.matmul_reference(lhs.astype(np.float32), rhs.astype(np.float32))
+    total = np.zeros_like(expected)
+    for rank in range(8):
+        lhs_r, rhs_r = workloads.shard_matmul_inputs(lhs, rhs, 8, rank)
+        partial = run_single(lhs_r, rhs_r, cuda_device, tile_n=128)
+        reference_partial = oracle.local_partials(lhs.astype(np.float32), rhs.astype(np.float32), 8)[rank]
+        assert np.allclose(partial, reference_partial, atol=1e-3, rtol=1e-3)
+        total += partial
+    assert np.allclose(total, expected, atol=1e-3, rtol=1e-3)
+    whole = run_single(lhs, rhs, cuda_device)
+    assert np.allclose(whole, expected, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("pattern", PATTERNS)
+def test_structured_patterns_are_exact_on_device(cuda_device, golden_dir, pattern):
+    """The reference's closed-form operand patterns have exactly representable products: the
+    f32-accumulating tensor-core path must reproduce them bit for bit."""
+    vectors = np.load(golden_dir / "matmul_structured_patterns.npz")
+    lhs = bits_to_bf16(vectors[f"{pattern}/lhs_bf16_bits"])
+    rhs = bits_to_bf16(vectors[f"{pattern}/rhs_bf16_bits"])
+    actual = run_single(lhs, rhs, cuda_device, tile_n=64)
+    np.testing.assert_array_equal(actual, vectors[f"{pattern}/product_f32"])
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 256), (1, 8, 8), (200, 136, 264), (257, 72, 40), (384, 1000, 520)])
+@pytest.mark.parametrize("tile_n", (64, 128, 256))
+def test_ragged_shapes_and_tiles(cuda_device, shape, tile_n):
+    m, k, n = shape
+    generator = np.random.default_rng(m * 1000 + n)
+    lhs = generator.normal(size=(m, k)).astype(np.float32).astype(BF16)
+    rhs = generator.normal(size=(k, n)).astype(np.float32).astype(BF16)
+    expected = oracle.matmul_reference(lhs.astype(np.float32), rhs.astype(np.float32))
+    actual = run_single(lhs, rhs, cuda_device, tile_n=tile_n)
+    assert np.allclose(actual, expected, atol=1e-3, rtol=1e-3)
+    rounded = run_single(lhs, rhs, cuda_device, tile_n=tile_n, output_dtype="bf16")
+    np.testing.assert_array_equal(rounded, oracle.quantize_bf16(actual))
+
+
+def test_repeat_runs_are_bit_identical(cuda_device):
+    lhs, rhs = workloads.distributed_matmul_inputs(1, 512, 2048, 768)
+    first = run_single(lhs, rhs, cuda_device)
+    second = run_single(lhs, rhs, cuda_device)
+    np.testing.assert_array_equal(first, second)
+
+
+def _emulated_ranks(lhs, rhs, world, device, *, scatter_dimension, transport, output_dtype, strategy, tile_n):
+    """Runs every mesh position's kernels on one GPU: all pushes first, then all reductions, so no
+    launch ever waits on a later one."""
+    lib = _native.load()
+    m, k = lhs.shape
+    n = rhs.shape[1]
+    stream = torch.cuda.current_stream(device).cuda_stream
+    handles, operands = [], []
+    for rank in range(world):
+        desc = _native.MatmulRsDesc(
+            m=m, n=n, k_local=k // world, world=world, rank=rank, scatter_dim=scatter_dimension,
+            out_dtype=_native.CAKE_DTYPE_F32 if output_dtype == "f32" else _native.CAKE_DTYPE_BF16,
+            transport_dtype=_native.CAKE_DTYPE_F32 if transport == "f32" else _native.CAKE_DTYPE_BF16,
+            strategy=strategy, tile_m=128, tile_n=tile_n, rhs_layout=0, reserved=0,
+        )
+        handle = ctypes.c_void_p()
+        _native.check(lib.cake_matmul_rs_create(ctypes.byref(desc), ctypes.byref(handle)))
+        handles.append(handle)
+        lhs_r, rhs_r = workloads.shard_matmul_inputs(lhs, rhs, world, rank)
+        operands.append((bf16_to_torch(lhs_r, device), bf16_to_torch(rhs_r, device)))
+    out_rows = m // world if scatter_dimension == 0 else m
+    out_cols = n // world if scatter_dimension == 1 else n
+    torch_out = torch.float32 if output_dtype == "f32" else torch.bfloat16
+    results = []
+    try:
+        if strategy == _native.CAKE_RS_P2P_OWNER_PUSH:
+            slots, flags = [], []
+            for handle in handles:
+                slot, flag = ctypes.c_void_p(), ctypes.c_void_p()
+                _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_slot_bytes(handle), ctypes.byref(slot)))
+                _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_flag_bytes(handle), ctypes.byref(flag)))
+                slots.append(slot.value)
+                flags.append(flag.value)
+            array = ctypes.c_void_p * world
+            for handle in handles:
+                _native.check(lib.cake_matmul_rs_bind_peers(handle, array(*slots), array(*flags)))
+            for repeat in range(3):  # exercises both slot parities and the monotonic counters
+                outs = [torch.full((out_rows, out_cols), float("nan"), dtype=torch_out, device=device) for _ in range(world)]
+                for handle, (lhs_d, rhs_d) in zip(handles, operands):
+                    _native.check(lib.cake_matmul_rs_enqueue_push(handle, lhs_d.data_ptr(), rhs_d.data_ptr(), stream))
+                for handle, out in zip(handles, outs):
+                    _native.check(lib.cake_matmul_rs_enqueue_reduce(handle, out.data_ptr(), stream))
+                torch.cuda.synchronize(device)
+                results.append([out.float().cpu().numpy() for out in outs])
+            for handle in handles:
+                word = _native.CakeStatus()
+                _native.check(lib.cake_matmul_rs_status(handle, stream, ctypes.byref(word)))
+                assert word.code == 0
+            for pointer in slots + flags:
+                lib.cake_symm_free(pointer)
+        else:
+            tdtype = torch.float32 if transport == "f32" else torch.bfloat16
+            partials = []
+            for handle, (lhs_d, rhs_d) in zip(handles, operands):
+                partial = torch.full((world, out_rows, out_cols), float("nan"), dtype=tdtype, device=device)
+                _native.check(lib.cake_matmul_rs_enqueue(handle, lhs_d.data_ptr(), rhs_d.data_ptr(), partial.data_ptr(), stream))
+                partials.append(partial)
+            torch.cuda.synchronize(device)
+            total = torch.zeros((world, out_rows, out_cols), dtype=torch.float32, device=device)
+            for partial in partials:  # rank order, like the oracle
+                total += partial.float()
+            results.append([total[r].cpu().numpy() for r in range(world)])
+    finally:
+        for handle in handles:
+            lib.cake_matmul_rs_destroy(handle)
+    return results
+
+
+@pytest.mark.parametrize("scatter_dimension", (0, 1))
+@pytest.mark.parametrize("transport, output_dtype", [("f32", "f32"), ("bf16", "bf16"), ("bf16", "f32")])
+def test_p2p_owner_push_all_ranks_on_one_gpu(cuda_device, scatter_dimension, transport, output_dtype):
+    """mesh 8 on 128 x 1024 x 1024 with the reference's inputs, both scatter dimensions (the
+    reference scatters N; the large configuration scatters M, 16 rows per rank, so every 128-row
+    tile is split between 8 owners)."""
+    world = 8
+    lhs, rhs = workloads.distributed_matmul_inputs(world, 128, 1024, 1024)
+    expected = oracle.matmul_reduce_scatter(
+        lhs.astype(np.float32), rhs.astype(np.float32), world=world, scatter_dimension=scatter_dimension,
+        transport_dtype=transport, out_dtype=output_dtype,
+    )
+    runs = _emulated_ranks(lhs, rhs, world, cuda_device, scatter_dimension=scatter_dimension, transport=transport,
+                           output_dtype=output_dtype, strategy=_native.CAKE_RS_P2P_OWNER_PUSH, tile_n=128)
+    full = oracle.matmul_reference(lhs.astype(np.float32), rhs.astype(np.float32))
+    for outputs in runs:
+        for rank in range(world):
+            if transport == "f32":
+                assert np.allclose(outputs[rank], expected[rank], atol=1e-3, rtol=1e-3)
+            else:
+                # bf16 transport: partials are rounded once before the f32 sum; compare with the
+                # oracle that rounds the same way (one bf16 ulp of the partial magnitude).
+                assert oracle.relative_l2_error(outputs[rank], expected[rank]) < 4e-3
+        assembled = np.concatenate(outputs, axis=scatter_dimension)
+        assert oracle.relative_l2_error(assembled, full) < 1e-2
+    for later in runs[1:]:
+        for rank in range(world):
+            np.testing.assert_array_equal(later[rank], runs[0][rank])
+
+
+@pytest.mark.parametrize("world, scatter_dimension, tile_n", [(2, 0, 256), (4, 1, 64), (8, 1, 128)])
+def test_owner_major_partial_layout_for_library_collective(cuda_device, world, scatter_dimension, tile_n):
+    lhs, rhs = workloads.distributed_matmul_inputs(world, 256, 1024, 512)
+    expected = oracle.matmul_reduce_scatter(lhs.astype(np.float32), rhs.astype(np.float32), world=world, scatter_dimension=scatter_dimension)
+    outputs = _emulated_ranks(lhs, rhs, world, cuda_device, scatter_dimension=scatter_dimension, transport="f32",
+                              output_dtype="f32", strategy=_native.CAKE_RS_LOCAL_PARTIAL, tile_n=tile_n)[0]
+    for rank in range(world):
+        assert np.allclose(outputs[rank], expected[rank], atol=1e-3, rtol=1e-3)
+
+
+def test_large_configuration_properties(cuda_device):
+    """8192 x 16384 x 8192 at one mesh position (the benchmark workload): sampled rows against the
+    oracle, and the row-sum identity C 1 = A (B 1) over the whole output."""
+    m, k, n = 8192, 16384, 8192
+    generator = torch.Generator(device=cuda_device).manual_seed(20261125)
+    lhs = (torch.randn((m, k), generator=generator, device=cuda_device) * k**-0.5).to(torch.bfloat16)
+    rhs = (torch.randn((k, n), generator=generator, device=cuda_device) * k**-0.5).to(torch.bfloat16)
+    plan = cuda_lowering.plan_distributed_matmul(mesh_size=1, m=m, k=k, n=n, output_dtype="bf16")
+    executable, _ = plan.build()
+    out = executable(lhs, rhs)
+    assert executable.status() == (0, 0, 0, 0)
+    rows = np.array([0, 1, 127, 128, 4095, 4096, 8191, 5000, 6001, 77], dtype=np.int64)
+    lhs_rows = lhs[torch.from_numpy(rows).to(cuda_device)].float().cpu().numpy()
+    rhs_host = rhs.float().cpu().numpy()
+    expected = oracle.matmul_reference(lhs_rows, rhs_host)
+    actual = out[torch.from_numpy(rows).to(cuda_device)].float().cpu().numpy()
+    assert oracle.max_abs_error(actual, expected) < 2e-2
+    assert oracle.relative_l2_error(actual, expected) < 1e-2
+    row_sums = out.double().sum(dim=1).cpu().numpy()
+    identity_sums = (lhs.double() @ rhs.double().sum(dim=1)).cpu().numpy()
+    # bf16 rounding of 8192 outputs of magnitude ~1/128 each: absolute error well under 1e-2.
+    assert np.max(np.abs(row_sums - identity_sums)) < 2e-2
+    executable.close()

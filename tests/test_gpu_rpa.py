@@ -1,0 +1,275 @@
+"""GPU parity of the ragged-paged-attention decode kernels against the CPU oracle, through the
+C ABI. Tolerance (the build's contract for bf16 outputs of f32-accumulated attention):
+max-abs <= 2e-2 and relative-L2 <= 1e-2; page-table and length indexing must be exact, which the
+edge cases below check by construction (poisoned unused pages, permuted tables, boundary lengths)."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import matmul_rs as metrics
+from oracle import rpa as oracle
+from tests.helpers import BF16, bits_to_bf16, to_device, torch_to_bf16
+from tests.test_oracle_golden import fused_inputs
+from tpu_cake_b200 import rpa_cuda_lowering, workloads
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-2
+REL_L2 = 1e-2
+
+
+def assert_close(actual: np.ndarray, expected: np.ndarray) -> None:
+    assert np.isfinite(actual).all()
+    assert metrics.max_abs_error(actual, expected) <= MAX_ABS
+    assert metrics.relative_l2_error(actual, expected) <= REL_L2
+
+
+def fused_plan(inputs, **overrides) -> rpa_cuda_lowering.CudaFusedRpaPlan:
+    shapes = [None if value is None else tuple(np.asarray(value).shape) for value in inputs]
+    fields = dict(
+        name="inkling_fused_rpa", schedule_sha256="0" * 64, query_shape=shapes[0], key_shape=shapes[1], value_shape=shapes[2],
+        fused_cache_shape=shapes[3], kv_lengths_shape=shapes[4], page_indices_shape=shapes[5],
+        cumulative_query_lengths_shape=shapes[6], cumulative_kv_lengths_shape=shapes[7], distribution_shape=shapes[8],
+        relative_states_shape=shapes[9], relative_projection_shape=shapes[10], output_shape=shapes[0],
+        softmax_scale=1.0 / shapes[0][2],
+    )
+    fields.update(overrides)
+    return rpa_cuda_lowering.CudaFusedRpaPlan(**fields)
+
+
+def run_fused(plan, inputs, device):
+    executable = plan.build(device)
+    try:
+        device_inputs = tuple(None if value is None else to_device(np.asarray(value), device) for value in inputs)
+        output, cache = plan.run_preflighted(executable, *device_inputs)
+        assert executable.status() == (0, 0, 0, 0)
+        return torch_to_bf16(output), torch_to_bf16(cache)
+    finally:
+        executable.close()
+
+
+@pytest.mark.parametrize("seed", (0, 7))
+def test_reference_fused_vectors(cuda_device, golden_dir, seed):
+    """The reference's own toy inputs (head_dim 32 padded to 128, page 16, flat page indices,
+    relative bias, scale 1/head_dim): output within its allclose(0.02, 0.02), cache bit-exact."""
+    vectors = np.load(golden_dir / "rpa_reference_vectors.npz")
+    inputs = fused_inputs(vectors, seed)
+    output, cache = run_fused(fused_plan(inputs), inputs, cuda_device)
+    expected = bits_to_bf16(vectors[f"fused/seed{seed}/output_bf16_bits"]).astype(np.float32)
+    assert np.allclose(output.astype(np.float32), expected, rtol=0.02, atol=0.02)
+    assert_close(output.astype(np.float32), expected)
+    np.testing.assert_array_equal(cache.view(np.uint16), vectors[f"fused/seed{seed}/updated_cache_bf16_bits"])
+
+
+def test_kernel_is_told_apart_from_every_oracle_mutation(cuda_device, golden_dir):
+    vectors = np.load(golden_dir / "rpa_reference_vectors.npz")
+    inputs = fused_inputs(vectors, 0)
+    output, cache = run_fused(fused_plan(inputs), inputs, cuda_device)
+    good_cache = vectors["fused/seed0/updated_cache_bf16_bits"]
+    for mutation in oracle.MUTATIONS:
+        wrong = bits_to_bf16(vectors[f"fused/seed0/mutation/{mutation}/output_bf16_bits"]).astype(np.float32)
+        wrong_cache_equal = bool(vectors[f"fused/seed0/mutation/{mutation}/cache_equal"])
+        passes = np.allclose(output.astype(np.float32), wrong, rtol=0.02, atol=0.02) and wrong_cache_equal
+        assert not passes, mutation
+    np.testing.assert_array_equal(cache.view(np.uint16), good_cache)
+
+
+def random_case(seed, *, num_seqs, q_heads, kv_heads, page_size, lengths, pool_pages, poison=True):
+    generator = np.random.default_rng(seed)
+    dim = 128
+    query = generator.normal(size=(num_seqs, q_heads, dim)).astype(np.float32).astype(BF16)
+    key_cache = generator.normal(size=(pool_pages, page_size, kv_heads, dim)).astype(np.float32).astype(BF16)
+    value_cache = generator.normal(size=(pool_pages, page_size, kv_heads, dim)).astype(np.float32).astype(BF16)
+    lengths = np.asarray(lengths, dtype=np.int32)
+    pages_per_seq = -(-lengths.astype(np.int64) // page_size)
+    max_pages = int(pages_per_seq.max())
+    permutation = generator.permutation(pool_pages)
+    table = np.zeros((num_seqs, max_pages), dtype=np.int32)
+    cursor = 0
+    used = np.zeros(pool_pages, dtype=bool)
+    for s in range(num_seqs):
+        count = int(pages_per_seq[s])
+        table[s, :count] = permutation[cursor : cursor + count]
+        used[permutation[cursor : cursor + count]] = True
+        cursor += count
+    assert cursor <= pool_pages
+    if poison:
+        # Pages no sequence owns, and token slots past each sequence's length, hold NaN: any read
+        # of them that reaches the arithmetic shows up in the output.
+        key_cache[~used] = np.nan
+        value_cache[~used] = np.nan
+        for s in range(num_seqs):
+            tail = int(lengths[s]) % page_size
+            if tail:
+                last = table[s, int(pages_per_seq[s]) - 1]
+                key_cache[last, tail:] = np.nan
+                value_cache[last, tail:] = np.nan
+    return query, key_cache, value_cache, table, lengths
+
+
+def run_separate(case, device, *, fused, chunk=0, bias=None, scale=None):
+    query, key_cache, value_cache, table, lengths = case
+    dim = query.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(dim)
+    plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+        name="paged", schedule_sha256="0" * 64, query_shape=query.shape, cache_shape=key_cache.shape,
+        page_table_shape=table.shape, bias_shape=None if bias is None else bias.shape, softmax_scale=scale,
+        kv_chunk_tokens=chunk, cache_layout="fused" if fused else "separate",
+    )
+    executable = plan.build(device)
+    try:
+        if fused:
+            caches = (to_device(oracle.fused_cache_from_separate(key_cache, value_cache), device), None)
+        else:
+            caches = (to_device(key_cache, device), to_device(value_cache, device))
+        out = plan.invoke(executable, to_device(query, device), caches[0], caches[1], to_device(table, device),
+                          to_device(lengths, device), None if bias is None else to_device(bias, device))
+        assert executable.status() == (0, 0, 0, 0)
+        again = plan.invoke(executable, to_device(query, device), caches[0], caches[1], to_device(table, device),
+                            to_device(lengths, device), None if bias is None else to_device(bias, device))
+        torch.cuda.synchronize(device)
+        assert torch.equal(out.view(torch.uint16), again.view(torch.uint16)), "repeat run must be bit-identical"
+        return torch_to_bf16(out).astype(np.float32)
+    finally:
+        executable.close()
+
+
+def expected_for(case, *, bias=None, scale=None):
+    query, key_cache, value_cache, table, lengths = case
+    scale = scale if scale is not None else 1.0 / math.sqrt(query.shape[2])
+    # NaN poison lives only where the oracle never reads (it slices to the sequence length).
+    return oracle.rpa_separate(query, key_cache, value_cache, table, lengths, bias, scale=scale)
+
+
+@pytest.mark.parametrize("fused", (False, True))
+@pytest.mark.parametrize(
+    "q_heads, kv_heads, page_size, lengths",
+    [
+        (4, 4, 16, [1, 15, 16, 17]),            # one query head per KV head; page_size - 1, == , + 1
+        (8, 2, 16, [31, 32, 33, 511, 512, 513]),  # stage (32) and chunk (512) boundaries
+        (32, 8, 16, [128, 700, 2047, 3000]),     # the decode configuration's head layout
+        (64, 8, 32, [1024, 33, 1500, 2500]),     # the sharded configuration's head layout
+        (16, 1, 8, [7, 8, 9, 100]),              # 16 query heads on one KV head
+        (8, 4, 1, [1, 2, 31, 33, 200]),          # one token per page (the reference surface's page size)
+        (8, 4, 2, [3, 64, 65]),
+        (8, 4, 4, [5, 127, 130]),
+    ],
+)
+def test_decode_edge_cases(cuda_device, fused, q_heads, kv_heads, page_size, lengths):
+    pool = sum(-(-length // page_size) for length in lengths) + 7
+    case = random_case(11, num_seqs=len(lengths), q_heads=q_heads, kv_heads=kv_heads, page_size=page_size,
+                       lengths=lengths, pool_pages=pool)
+    actual = run_separate(case, cuda_device, fused=fused)
+    assert_close(actual, expected_for(case))
+
+
+@pytest.mark.parametrize("chunk", (32, 64, 256, 1024))
+def test_split_kv_chunk_sizes_agree(cuda_device, chunk):
+    case = random_case(5, num_seqs=3, q_heads=8, kv_heads=2, page_size=16, lengths=[1000, 31, 257], pool_pages=100)
+    actual = run_separate(case, cuda_device, fused=True, chunk=chunk)
+    assert_close(actual, expected_for(case))
+
+
+def test_dense_bias_and_reference_scale(cuda_device):
+    """The prototype op's semantics: scale 1/head_dim and a dense bias indexed by key position
+    (the reference's separate-cache oracle)."""
+    case = random_case(3, num_seqs=4, q_heads=8, kv_heads=2, page_size=16, lengths=[17, 33, 65, 127], pool_pages=32)
+    bias = np.random.default_rng(9).normal(scale=0.5, size=(8, 128)).astype(np.float32)
+    actual = run_separate(case, cuda_device, fused=False, bias=bias, scale=1.0 / 128)
+    assert_close(actual, expected_for(case, bias=bias, scale=1.0 / 128))
+
+
+def test_batch_permutation_invariance_and_state_isolation(cuda_device):
+    """Reordering sequences reorders outputs and nothing else; changing one sequence's pages leaves
+    every other sequence's output bit-identical (the reference's semantic properties)."""
+    lengths = [100, 37, 513, 64, 1]
+    case = random_case(21, num_seqs=5, q_heads=8, kv_heads=2, page_size=16, lengths=lengths, pool_pages=80, poison=False)
+    base = run_separate(case, cuda_device, fused=True)
+    order = np.array([3, 0, 4, 2, 1])
+    query, key_cache, value_cache, table, lens = case
+    permuted = (query[order], key_cache, value_cache, table[order], lens[order])
+    np.testing.assert_array_equal(run_separate(permuted, cuda_device, fused=True), base[order])
+    changed_key = key_cache.copy()
+    changed_key[table[2, 0]] = changed_key[table[2, 0]] * np.asarray(-1.0, dtype=BF16)
+    other = run_separate((query, changed_key, value_cache, table, lens), cuda_device, fused=True)
+    for s in (0, 1, 3, 4):
+        np.testing.assert_array_equal(other[s], base[s])
+    assert not np.array_equal(other[2], base[2])
+
+
+def test_output_may_alias_query(cuda_device):
+    case = random_case(2, num_seqs=3, q_heads=8, kv_heads=2, page_size=16, lengths=[40, 600, 1100], pool_pages=120)
+    query, key_cache, value_cache, table, lengths = case
+    expected = expected_for(case)
+    plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+        name="alias", schedule_sha256="0" * 64, query_shape=query.shape, cache_shape=key_cache.shape,
+        page_table_shape=table.shape, bias_shape=None, softmax_scale=1.0 / math.sqrt(128),
+    )
+    executable = plan.build(cuda_device)
+    buffer = to_device(query, cuda_device)
+    plan.invoke(executable, buffer, to_device(key_cache, cuda_device), to_device(value_cache, cuda_device),
+                to_device(table, cuda_device), to_device(lengths, cuda_device), out=buffer)
+    assert executable.status() == (0, 0, 0, 0)
+    assert_close(torch_to_bf16(buffer).astype(np.float32), expected)
+    executable.close()
+
+
+def test_out_of_range_page_is_reported_not_faulted(cuda_device):
+    case = random_case(4, num_seqs=2, q_heads=8, kv_heads=2, page_size=16, lengths=[40, 50], pool_pages=16, poison=False)
+    query, key_cache, value_cache, table, lengths = case
+    table = table.copy()
+    table[1, 1] = 10_000
+    plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+        name="bad-page", schedule_sha256="0" * 64, query_shape=query.shape, cache_shape=key_cache.shape,
+        page_table_shape=table.shape, bias_shape=None, softmax_scale=0.1,
+    )
+    executable = plan.build(cuda_device)
+    plan.invoke(executable, to_device(query, cuda_device), to_device(key_cache, cuda_device), to_device(value_cache, cuda_device),
+                to_device(table, cuda_device), to_device(lengths, cuda_device))
+    from tpu_cake_b200 import _native
+
+    with pytest.raises(_native.CakeError) as raised:
+        executable.status()
+    assert raised.value.code == _native.CAKE_ERR_DEVICE_CHECK
+    assert executable.status() == (0, 0, 0, 0)  # cleared; the context is still usable
+    executable.close()
+
+
+def test_decode_configuration_full_size(cuda_device):
+    """64 sequences, KV lengths uniform in [128, 8192], 32 / 8 heads, page 16, pool of 65536 pages:
+    a sample of sequences (shortest, longest, and a few between) against the oracle."""
+    config = workloads.DECODE_64
+    lengths, table = workloads.decode_metadata(config)
+    generator = torch.Generator(device=cuda_device).manual_seed(64)
+    shape = (config.total_pages, config.page_size, config.kv_heads, 2, config.head_dim)
+    cache = torch.empty(shape, dtype=torch.bfloat16, device=cuda_device)
+    for start in range(0, config.total_pages, 8192):
+        cache[start : start + 8192] = torch.randn((8192, *shape[1:]), generator=generator, device=cuda_device).to(torch.bfloat16)
+    query = torch.randn((config.num_seqs, config.q_heads, config.head_dim), generator=generator, device=cuda_device).to(torch.bfloat16)
+    plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+        name=config.name, schedule_sha256="0" * 64, query_shape=tuple(query.shape),
+        cache_shape=(config.total_pages, config.page_size, config.kv_heads, config.head_dim),
+        page_table_shape=table.shape, bias_shape=None, softmax_scale=config.softmax_scale, cache_layout="fused",
+    )
+    executable = plan.build(cuda_device)
+    out = plan.invoke(executable, query, cache, None, to_device(table, cuda_device), to_device(lengths, cuda_device))
+    assert executable.status() == (0, 0, 0, 0)
+    actual = torch_to_bf16(out).astype(np.float32)
+    order = np.argsort(lengths)
+    sample = [int(order[0]), int(order[-1]), int(order[31]), 0, 17, 63]
+    query_host = torch_to_bf16(query)
+    for s in sample:
+        count = -(-int(lengths[s]) // config.page_size)
+        pages = torch.from_numpy(table[s, :count].astype(np.int64)).to(cuda_device)
+        rows = torch_to_bf16(cache[pages])  # [count, ps, kv_heads, 2, dim]
+        expected = oracle.rpa_separate(
+            query_host[s : s + 1], rows[:, :, :, 0, :], rows[:, :, :, 1, :], np.arange(count, dtype=np.int32)[None, :],
+            lengths[s : s + 1], None, scale=config.softmax_scale,
+        )
+        assert_close(actual[s : s + 1], expected)
+    executable.close()

@@ -47,6 +47,8 @@ EXPORTED_SYMBOLS = (
     "cake_matmul_rs_flag_bytes",
     "cake_matmul_rs_bind_peers",
     "cake_matmul_rs_enqueue",
+    "cake_matmul_rs_enqueue_push",
+    "cake_matmul_rs_enqueue_reduce",
     "cake_matmul_rs_run_host",
     "cake_matmul_rs_status",
     "cake_matmul_rs_launches_per_enqueue",
@@ -164,6 +166,10 @@ def load() -> ctypes.CDLL:
     lib.cake_matmul_rs_bind_peers.argtypes = [vp, ctypes.POINTER(vp), ctypes.POINTER(vp)]
     lib.cake_matmul_rs_enqueue.restype = i32
     lib.cake_matmul_rs_enqueue.argtypes = [vp, vp, vp, vp, vp]
+    lib.cake_matmul_rs_enqueue_push.restype = i32
+    lib.cake_matmul_rs_enqueue_push.argtypes = [vp, vp, vp, vp]
+    lib.cake_matmul_rs_enqueue_reduce.restype = i32
+    lib.cake_matmul_rs_enqueue_reduce.argtypes = [vp, vp, vp]
     lib.cake_matmul_rs_run_host.restype = i32
     lib.cake_matmul_rs_run_host.argtypes = [vp, vp, vp, vp, vp]
     lib.cake_matmul_rs_status.restype = i32

@@ -675,9 +675,16 @@ int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void
 
 int32_t cake_matmul_rs_launches_per_enqueue(const cake_matmul_rs* plan) { return plan ? plan->launches : 0; }
 
-int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void* rhs, void* out,
-                               void* stream_v) {
-  if (!plan || !lhs || !rhs || !out) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_enqueue: null argument");
+}  // extern "C"
+
+namespace {
+constexpr int kPhasePush = 1;    // contraction + epilogue stores / pushes
+constexpr int kPhaseReduce = 2;  // slot reduction (peer-to-peer strategy only)
+
+int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, void* out,
+                     void* stream_v, int phases) {
+  if (!plan || !out) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_enqueue: null argument");
+  if ((phases & kPhasePush) && (!lhs || !rhs)) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_enqueue: null operand");
   const cake_matmul_rs_desc& d = plan->d;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs) |
@@ -685,7 +692,14 @@ int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void
     return fail(CAKE_ERR_INVALID_ARGUMENT, "lhs, rhs and out must be 16-byte aligned");
   const bool p2p = d.world > 1 && d.strategy == CAKE_RS_P2P_OWNER_PUSH;
   if (p2p && !plan->bound) return fail(CAKE_ERR_STATE, "cake_matmul_rs_bind_peers must be called before enqueue");
+  if (!p2p && phases != (kPhasePush | kPhaseReduce))
+    return fail(CAKE_ERR_STATE, "separate push / reduce phases exist only for the peer-to-peer strategy");
+  if (p2p && !(phases & kPhasePush) && plan->epoch == 0)
+    return fail(CAKE_ERR_STATE, "reduce phase enqueued before any push phase");
   int launches = 0;
+  const size_t chunk_elems = static_cast<size_t>(plan->out_rows) * plan->out_cols;
+  unsigned long long parity = plan->epoch & 1ull;
+  if (phases & kPhasePush) {
 
   const void* rhs_used = rhs;
   if (plan->rhs_via_transpose) {
@@ -722,8 +736,6 @@ int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void
   p.vec_ok = (plan->out_cols % epp == 0) && (d.n % epp == 0);
   p.count_arrivals = p2p;
   p.status = plan->status.dev;
-  const size_t chunk_elems = static_cast<size_t>(plan->out_rows) * plan->out_cols;
-  unsigned long long parity = 0;
   if (d.world == 1) {
     p.dest[0] = out;
   } else if (!p2p) {
@@ -750,8 +762,9 @@ int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void
   else rc = kmajor ? launch_gemm<64, true>(plan, p, grid, stream) : launch_gemm<64, false>(plan, p, grid, stream);
   if (rc) return rc;
   ++launches;
+  }  // push phase
 
-  if (p2p) {
+  if (p2p && (phases & kPhaseReduce)) {
     const unsigned long long expected = plan->epoch * chunk_elems;
     const char* my_slots = static_cast<const char*>(plan->slots[d.rank]) + parity * d.world * chunk_elems * plan->tsize;
     const unsigned long long* my_flags = static_cast<const unsigned long long*>(plan->flags[d.rank]);
@@ -772,6 +785,24 @@ int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void
   }
   plan->launches = launches;
   return CAKE_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void* rhs, void* out,
+                               void* stream) {
+  return enqueue_impl(plan, lhs, rhs, out, stream, kPhasePush | kPhaseReduce);
+}
+
+int32_t cake_matmul_rs_enqueue_push(cake_matmul_rs* plan, const void* lhs, const void* rhs,
+                                    void* stream) {
+  // `out` is not written by the push phase of the peer-to-peer strategy; pass a non-null dummy.
+  return enqueue_impl(plan, lhs, rhs, reinterpret_cast<void*>(16), stream, kPhasePush);
+}
+
+int32_t cake_matmul_rs_enqueue_reduce(cake_matmul_rs* plan, void* out, void* stream) {
+  return enqueue_impl(plan, nullptr, nullptr, out, stream, kPhaseReduce);
 }
 
 int32_t cake_matmul_rs_run_host(cake_matmul_rs* plan, const void* lhs_host, const void* rhs_host,

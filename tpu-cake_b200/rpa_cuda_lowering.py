@@ -1,0 +1,341 @@
+"""CUDA backend lowering of Inkling ragged paged attention (pure decode).
+
+Mirror of the reference's RPA backend (src/tpu_cake/rpa_lowering.py):
+  - ``CudaFusedRpaPlan`` has the tensor-contract fields of ``FusedRpaPlan`` (:131-170) and its
+    ``preflight`` / ``invoke`` / ``run_preflighted`` methods (:228-288). ``invoke`` runs the
+    sm_100a kernels instead of handing the inputs to a pinned external JAX kernel.
+  - ``preflight_decode_metadata`` is the integer validation of ``_preflight_decode_metadata``
+    (:71-128), same checks, same messages.
+  - ``CudaPagedAttentionPlan`` lowers the prototype op ``tpu_schedule.ragged_paged_attention``
+    (separate K / V caches, 2-D page table, dense bias;
+    src/tpu_cake/dialects/tpu_schedule.py:2003-2103), which has no lowering in the reference.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _native
+from .identity import text_sha256
+
+FUSED_INPUT_NAMES = (
+    "queries",
+    "keys",
+    "values",
+    "fused_cache",
+    "kv_lengths",
+    "page_indices",
+    "cumulative_query_lengths",
+    "cumulative_kv_lengths",
+    "distribution",
+    "relative_states",
+    "relative_projection",
+)
+
+
+def preflight_decode_metadata(inputs: tuple, input_shapes: tuple[tuple[int, ...], ...]) -> None:
+    """Rejects decode metadata the kernel must not be run on. Integer arithmetic in int64 on the
+    host; raises ValueError with the reference's messages."""
+    lengths = np.asarray(_to_host(inputs[4]), dtype=np.int64)
+    page_indices = np.asarray(_to_host(inputs[5]), dtype=np.int64)
+    cu_q = np.asarray(_to_host(inputs[6]), dtype=np.int64)
+    cu_kv = np.asarray(_to_host(inputs[7]), dtype=np.int64)
+    distribution = np.asarray(_to_host(inputs[8]), dtype=np.int64)
+    count = input_shapes[4][0]
+    if distribution.shape != (3,) or np.any(distribution != count):
+        raise ValueError(
+            "Inkling fused RPA adapter accepts decode-only distribution "
+            f"{(count,) * 3}, got {tuple(int(v) for v in distribution)}"
+        )
+    if cu_q.shape != (count + 1,) or np.any(cu_q != np.arange(count + 1)):
+        raise ValueError("Inkling fused RPA adapter requires one query token per sequence")
+    if np.any(lengths <= 0):
+        raise ValueError("Inkling fused RPA requires positive KV lengths")
+    total_pages, page_size = input_shapes[3][0], input_shapes[3][1]
+    if np.any(lengths > total_pages * page_size):
+        raise ValueError("fused RPA KV length exceeds total cache capacity")
+    padded = -(-lengths // page_size) * page_size
+    expected_cu_kv = np.zeros(count + 1, dtype=np.int64)
+    np.cumsum(padded, out=expected_cu_kv[1:])
+    if cu_kv.shape != expected_cu_kv.shape or np.any(cu_kv != expected_cu_kv):
+        raise ValueError("fused RPA cumulative KV lengths must be page-aligned")
+    needed = int(expected_cu_kv[-1]) // page_size
+    if needed > page_indices.size:
+        raise ValueError("fused RPA page table cannot cover all KV lengths")
+    used = page_indices[:needed]
+    if np.any(used < 0) or np.any(used >= total_pages):
+        raise ValueError("fused RPA page index is outside the fused cache")
+    per_sequence: list[np.ndarray] = []
+    for s in range(count):
+        pages = page_indices[int(cu_kv[s]) // page_size : int(cu_kv[s + 1]) // page_size]
+        if np.unique(pages).size != pages.size:
+            raise ValueError("fused RPA page table aliases logical pages within one sequence")
+        per_sequence.append(pages)
+    writes = []
+    for s in range(count):
+        last = int(lengths[s]) - 1
+        page = int(page_indices[int(cu_kv[s]) // page_size + last // page_size])
+        writes.append((page, last % page_size))
+    if len(set(writes)) != len(writes):
+        raise ValueError("fused RPA decode updates collide in the physical cache")
+    for writer, (page, _slot) in enumerate(writes):
+        for reader, pages in enumerate(per_sequence):
+            if reader != writer and page in pages:
+                raise ValueError("fused RPA active write page is shared across sequences")
+
+
+def _to_host(value):
+    if isinstance(value, torch.Tensor):
+        return value.detach().cpu().numpy()
+    return value
+
+
+class RpaDecodeExecutable:
+    """Owns one native decode plan and its split-KV workspace on the current GPU."""
+
+    def __init__(self, desc: _native.RpaDesc, device: torch.device):
+        self._lib = _native.load()
+        self.device = device
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _native.check(self._lib.cake_rpa_create(ctypes.byref(desc), ctypes.byref(handle)))
+        self._handle = handle
+        self.workspace = torch.empty(self._lib.cake_rpa_workspace_bytes(handle), dtype=torch.uint8, device=device)
+
+    def enqueue(self, q, new_k, new_v, cache0, cache1, kv_lens, page_table, cu_kv_lens, bias0, bias1, out) -> None:
+        def ptr(t):
+            return None if t is None else t.data_ptr()
+
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _native.check(
+            self._lib.cake_rpa_decode_enqueue(
+                self._handle, ptr(q), ptr(new_k), ptr(new_v), ptr(cache0), ptr(cache1), ptr(kv_lens),
+                ptr(page_table), ptr(cu_kv_lens), ptr(bias0), ptr(bias1), ptr(out), self.workspace.data_ptr(), stream,
+            )
+        )
+
+    def status(self) -> tuple[int, int, int, int]:
+        word = _native.CakeStatus()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _native.check(self._lib.cake_rpa_status(self._handle, stream, ctypes.byref(word)))
+        return (word.code, word.detail0, word.detail1, word.detail2)
+
+    @property
+    def launches_per_call(self) -> int:
+        return int(self._lib.cake_rpa_launches_per_enqueue(self._handle))
+
+    def close(self) -> None:
+        if self._handle:
+            torch.cuda.synchronize(self.device)
+            self._lib.cake_rpa_destroy(self._handle)
+            self._handle = None
+
+
+def _require(tensor: torch.Tensor, shape: tuple[int, ...], dtype: torch.dtype, name: str, device: torch.device) -> None:
+    if not isinstance(tensor, torch.Tensor) or tuple(tensor.shape) != tuple(shape) or tensor.dtype != dtype:
+        got = (tuple(tensor.shape), tensor.dtype) if isinstance(tensor, torch.Tensor) else type(tensor)
+        raise ValueError(f"{name} must be a {dtype} tensor of shape {tuple(shape)}, got {got}")
+    if tensor.device != device or not tensor.is_contiguous():
+        raise ValueError(f"{name} must be contiguous on {device}")
+
+
+@dataclass(frozen=True)
+class CudaFusedRpaPlan:
+    name: str
+    schedule_sha256: str
+    query_shape: tuple[int, ...]
+    key_shape: tuple[int, ...]
+    value_shape: tuple[int, ...]
+    fused_cache_shape: tuple[int, ...]
+    kv_lengths_shape: tuple[int, ...]
+    page_indices_shape: tuple[int, ...]
+    cumulative_query_lengths_shape: tuple[int, ...]
+    cumulative_kv_lengths_shape: tuple[int, ...]
+    distribution_shape: tuple[int, ...]
+    relative_states_shape: tuple[int, ...] | None
+    relative_projection_shape: tuple[int, ...] | None
+    output_shape: tuple[int, ...]
+    softmax_scale: float
+    causal: int = 1
+    softmax_dtype: str = "float32"
+    sliding_window: int = 0
+    kv_chunk_tokens: int = 0
+    update_cache: bool = True
+    execution_scope: str = "local-shard-caller-owned-sharding"
+
+    def __post_init__(self) -> None:
+        tokens, q_heads, dim = self.query_shape
+        pages, page_size, combined, pack, dim_padded = self.fused_cache_shape
+        if pack != 2:
+            raise ValueError("fused cache must interleave K and V with pack = 2")
+        kv_heads = self.key_shape[1]
+        if combined * pack != 2 * kv_heads or self.value_shape != self.key_shape:
+            raise ValueError("fused cache head axis must hold K and V of every KV head")
+        if self.key_shape != (tokens, kv_heads, dim) or self.output_shape != self.query_shape:
+            raise ValueError("new key / value and output shapes must match the query tokens")
+        if self.kv_lengths_shape != (tokens,) or self.cumulative_kv_lengths_shape != (tokens + 1,):
+            raise ValueError("decode needs one KV length per query token (tokens == sequences)")
+        if self.sliding_window != 0:
+            raise ValueError("sliding-window attention is not lowered by the CUDA backend")
+        if self.softmax_dtype != "float32":
+            raise ValueError("softmax runs in float32")
+        if (self.relative_states_shape is None) != (self.relative_projection_shape is None):
+            raise ValueError("relative states and projection come together")
+
+    @property
+    def input_shapes(self) -> tuple[tuple[int, ...] | None, ...]:
+        return (
+            self.query_shape, self.key_shape, self.value_shape, self.fused_cache_shape, self.kv_lengths_shape,
+            self.page_indices_shape, self.cumulative_query_lengths_shape, self.cumulative_kv_lengths_shape,
+            self.distribution_shape, self.relative_states_shape, self.relative_projection_shape,
+        )
+
+    def render_executable_source(self) -> str:
+        lines = ["# cake-b200 lowered fused ragged paged attention (decode)", f"name = {self.name!r}",
+                 f"schedule_sha256 = {self.schedule_sha256!r}",
+                 "kernels = ('cake_rpa_plan_sm100', 'cake_rpa_cache_update_sm100', 'cake_rpa_decode_sm100', 'cake_rpa_combine_sm100')"]
+        for name, shape in zip(FUSED_INPUT_NAMES, self.input_shapes, strict=True):
+            lines.append(f"{name}_shape = {shape}")
+        lines += [f"softmax_scale = {self.softmax_scale!r}", f"causal = {self.causal}", f"sliding_window = {self.sliding_window}",
+                  f"kv_chunk_tokens = {self.kv_chunk_tokens}", f"update_cache = {self.update_cache}", "abi_version = 1"]
+        return "\n".join(lines) + "\n"
+
+    def source_sha256(self) -> str:
+        return text_sha256(self.render_executable_source())
+
+    def preflight(self, *inputs) -> None:
+        self._validate_signature(inputs)
+        preflight_decode_metadata(inputs, self.input_shapes)
+
+    def _validate_signature(self, inputs: tuple) -> None:
+        if len(inputs) != len(FUSED_INPUT_NAMES):
+            raise ValueError(f"fused RPA takes {len(FUSED_INPUT_NAMES)} inputs, got {len(inputs)}")
+        for name, value, shape in zip(FUSED_INPUT_NAMES, inputs, self.input_shapes, strict=True):
+            if shape is None:
+                if value is not None:
+                    raise ValueError(f"{name} must be None for a plan without relative bias")
+                continue
+            if tuple(value.shape) != tuple(shape):
+                raise ValueError(f"{name} has shape {tuple(value.shape)}, plan expects {tuple(shape)}")
+
+    def build(self, device: torch.device | None = None) -> RpaDecodeExecutable:
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        tokens, q_heads, dim = self.query_shape
+        pages, page_size, _, _, dim_padded = self.fused_cache_shape
+        with_bias = self.relative_states_shape is not None
+        desc = _native.RpaDesc(
+            num_seqs=tokens, num_q_tokens=tokens, q_heads=q_heads, kv_heads=self.key_shape[1], head_dim=dim,
+            head_dim_padded=dim_padded, page_size=page_size, cache_layout=_native.CAKE_RPA_CACHE_FUSED,
+            table_layout=_native.CAKE_RPA_TABLE_FLAT, max_pages_per_seq=self.page_indices_shape[0], total_pages=pages,
+            sm_scale=self.softmax_scale, bias_mode=2 if with_bias else 0,
+            bias_extent=self.relative_projection_shape[1] if with_bias else 0,
+            rel_dim=self.relative_states_shape[2] if with_bias else 0, update_cache=1 if self.update_cache else 0,
+            kv_chunk_tokens=self.kv_chunk_tokens, reserved=0,
+        )
+        return RpaDecodeExecutable(desc, device)
+
+    def invoke(self, executable: RpaDecodeExecutable, *inputs) -> tuple[torch.Tensor, torch.Tensor]:
+        """Runs the decode on device tensors. Returns (output, updated cache); the cache tensor is
+        updated in place and returned (the reference aliases it, tpu_schedule.py:2336-2339); the
+        output is a new tensor."""
+        self._validate_signature(inputs)
+        q, k, v, cache, lens, pages, _cu_q, cu_kv, _dist, states, projection = inputs
+        device = executable.device
+        bf16, i32 = torch.bfloat16, torch.int32
+        _require(q, self.query_shape, bf16, "queries", device)
+        _require(k, self.key_shape, bf16, "keys", device)
+        _require(v, self.value_shape, bf16, "values", device)
+        _require(cache, self.fused_cache_shape, bf16, "fused_cache", device)
+        _require(lens, self.kv_lengths_shape, i32, "kv_lengths", device)
+        _require(pages, self.page_indices_shape, i32, "page_indices", device)
+        _require(cu_kv, self.cumulative_kv_lengths_shape, i32, "cumulative_kv_lengths", device)
+        if states is not None:
+            _require(states, self.relative_states_shape, bf16, "relative_states", device)
+            _require(projection, self.relative_projection_shape, bf16, "relative_projection", device)
+        out = torch.empty(self.output_shape, dtype=bf16, device=device)
+        executable.enqueue(q, k if self.update_cache else None, v if self.update_cache else None, cache, None,
+                           lens, pages, cu_kv, states, projection, out)
+        return out, cache
+
+    def run_preflighted(self, executable: RpaDecodeExecutable, *inputs) -> tuple[torch.Tensor, torch.Tensor]:
+        self.preflight(*inputs)
+        return self.invoke(executable, *inputs)
+
+
+@dataclass(frozen=True)
+class CudaPagedAttentionPlan:
+    """Decode over separate K / V caches with a [B, max_pages] page table and an optional dense
+    bias [q_heads, extent] indexed by key position."""
+
+    name: str
+    schedule_sha256: str
+    query_shape: tuple[int, int, int]
+    cache_shape: tuple[int, int, int, int]  # [pages, page_size, kv_heads, head_dim], same for K and V
+    page_table_shape: tuple[int, int]
+    bias_shape: tuple[int, int] | None
+    softmax_scale: float
+    kv_chunk_tokens: int = 0
+    cache_layout: str = "separate"  # or "fused": one [pages, page_size, kv_heads, 2, head_dim] tensor
+
+    def __post_init__(self) -> None:
+        batch, q_heads, dim = self.query_shape
+        if self.cache_shape[3] != dim or q_heads % self.cache_shape[2]:
+            raise ValueError("cache head_dim must equal the query's and q_heads must be a multiple of kv_heads")
+        if self.page_table_shape[0] != batch:
+            raise ValueError("page table needs one row per sequence")
+        if self.bias_shape is not None and (self.bias_shape[0] != q_heads or self.bias_shape[1] < self.page_table_shape[1] * self.cache_shape[1]):
+            raise ValueError("bias must cover q_heads x (max_pages * page_size) key positions (tpu_schedule.py:2098-2101)")
+        if self.cache_layout not in ("separate", "fused"):
+            raise ValueError("cache_layout must be 'separate' or 'fused'")
+
+    def render_executable_source(self) -> str:
+        return (
+            "# cake-b200 lowered ragged paged attention (decode, 2-D page table)\n"
+            f"name = {self.name!r}\nschedule_sha256 = {self.schedule_sha256!r}\nquery_shape = {self.query_shape}\n"
+            f"cache_shape = {self.cache_shape}\ncache_layout = {self.cache_layout!r}\npage_table_shape = {self.page_table_shape}\n"
+            f"bias_shape = {self.bias_shape}\nsoftmax_scale = {self.softmax_scale!r}\nkv_chunk_tokens = {self.kv_chunk_tokens}\nabi_version = 1\n"
+        )
+
+    def source_sha256(self) -> str:
+        return text_sha256(self.render_executable_source())
+
+    def build(self, device: torch.device | None = None) -> RpaDecodeExecutable:
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        batch, q_heads, dim = self.query_shape
+        pages, page_size, kv_heads, _ = self.cache_shape
+        desc = _native.RpaDesc(
+            num_seqs=batch, num_q_tokens=batch, q_heads=q_heads, kv_heads=kv_heads, head_dim=dim, head_dim_padded=dim,
+            page_size=page_size,
+            cache_layout=_native.CAKE_RPA_CACHE_FUSED if self.cache_layout == "fused" else _native.CAKE_RPA_CACHE_SEPARATE,
+            table_layout=_native.CAKE_RPA_TABLE_2D, max_pages_per_seq=self.page_table_shape[1], total_pages=pages,
+            sm_scale=self.softmax_scale, bias_mode=1 if self.bias_shape is not None else 0,
+            bias_extent=self.bias_shape[1] if self.bias_shape is not None else 0, rel_dim=0, update_cache=0,
+            kv_chunk_tokens=self.kv_chunk_tokens, reserved=0,
+        )
+        return RpaDecodeExecutable(desc, device)
+
+    def invoke(self, executable: RpaDecodeExecutable, query, key_cache, value_cache, page_table, sequence_lengths, bias=None, out=None):
+        device = executable.device
+        _require(query, self.query_shape, torch.bfloat16, "query", device)
+        if self.cache_layout == "fused":
+            pages, page_size, kv_heads, dim = self.cache_shape
+            _require(key_cache, (pages, page_size, kv_heads, 2, dim), torch.bfloat16, "fused cache", device)
+            if value_cache is not None:
+                raise ValueError("value_cache must be None for the fused cache layout")
+        else:
+            _require(key_cache, self.cache_shape, torch.bfloat16, "key_cache", device)
+            _require(value_cache, self.cache_shape, torch.bfloat16, "value_cache", device)
+        _require(page_table, self.page_table_shape, torch.int32, "page_table", device)
+        _require(sequence_lengths, (self.query_shape[0],), torch.int32, "sequence_lengths", device)
+        if self.bias_shape is not None:
+            _require(bias, self.bias_shape, torch.float32, "bias", device)
+        elif bias is not None:
+            raise ValueError("plan was lowered without a bias")
+        if out is None:
+            out = torch.empty(self.query_shape, dtype=torch.bfloat16, device=device)
+        executable.enqueue(query, None, None, key_cache, value_cache, sequence_lengths, page_table, None, bias, None, out)
+        return out

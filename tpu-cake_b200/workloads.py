@@ -1,0 +1,108 @@
+"""Seeded synthetic inputs for the hot-path configurations.
+
+Matmul inputs follow the reference's recipe exactly (src/tpu_cake/runner.py:439-456): one
+generator seeded from the workload identity draws lhs then rhs as float32 normals, which are then
+rounded to bfloat16. The attention configurations have no generator in the reference (its
+workloads are fixed toy shapes, src/tpu_cake/workloads/inkling_rpa.py:76-84,413-468); the ones
+here are seeded the same way (``semantic_seed(config, "inputs")``) and stand in for the serving
+traces such kernels are normally measured on.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import ml_dtypes
+import numpy as np
+
+from .identity import semantic_seed, semantic_sha256, workload_rng
+
+BF16 = np.dtype(ml_dtypes.bfloat16)
+
+
+def distributed_matmul_workload_identity(mesh_size: int, m: int, k: int, n: int) -> str:
+    return semantic_sha256("distributed-matmul-workload", str(mesh_size), str(m), str(k), str(n))
+
+
+def distributed_matmul_inputs(mesh_size: int, m: int, k: int, n: int, *, scale: float = 1.0) -> tuple[np.ndarray, np.ndarray]:
+    """Global lhs [m, k] and rhs [k, n] as bfloat16 arrays. ``scale`` = 1 is the reference recipe;
+    the large configuration uses K**-0.5 so that outputs stay O(1)."""
+    generator = workload_rng(distributed_matmul_workload_identity(mesh_size, m, k, n), "device-run", "attempt-0", "inputs")
+    lhs = generator.normal(size=(m, k)).astype(np.float32)
+    rhs = generator.normal(size=(k, n)).astype(np.float32)
+    if scale != 1.0:
+        lhs *= np.float32(scale)
+        rhs *= np.float32(scale)
+    return lhs.astype(BF16), rhs.astype(BF16)
+
+
+def shard_matmul_inputs(lhs: np.ndarray, rhs: np.ndarray, mesh_size: int, rank: int) -> tuple[np.ndarray, np.ndarray]:
+    """This rank's K block: lhs columns / rhs rows (src/tpu_cake/pallas_lowering.py:466-472)."""
+    step = lhs.shape[1] // mesh_size
+    return (
+        np.ascontiguousarray(lhs[:, rank * step : (rank + 1) * step]),
+        np.ascontiguousarray(rhs[rank * step : (rank + 1) * step, :]),
+    )
+
+
+@dataclass(frozen=True)
+class DecodeConfig:
+    """A pure-decode attention scenario: one query token per sequence."""
+
+    name: str
+    num_seqs: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    page_size: int
+    total_pages: int
+    min_kv_len: int
+    max_kv_len: int
+    length_distribution: str  # "uniform" or "log-uniform"
+
+    @property
+    def softmax_scale(self) -> float:
+        return 1.0 / math.sqrt(self.head_dim)
+
+
+DECODE_64 = DecodeConfig("rpa-decode-64seq", 64, 32, 8, 128, 16, 65536, 128, 8192, "uniform")
+DECODE_SHARDED_256 = DecodeConfig("rpa-decode-sharded-256seq", 256, 64, 8, 128, 32, 262144, 1024, 32768, "log-uniform")
+
+
+def decode_metadata(config: DecodeConfig) -> tuple[np.ndarray, np.ndarray]:
+    """(kv_lens int32 [S], page_table int32 [S, max_pages]) from the config's seed. Pages are the
+    first sum(ceil(len/page_size)) entries of a seeded permutation of the pool, dealt per sequence;
+    unused table entries are 0."""
+    generator = np.random.default_rng(semantic_seed(config.name, "inputs"))
+    if config.length_distribution == "uniform":
+        lengths = generator.integers(config.min_kv_len, config.max_kv_len + 1, size=config.num_seqs)
+    elif config.length_distribution == "log-uniform":
+        draws = generator.uniform(math.log(config.min_kv_len), math.log(config.max_kv_len), size=config.num_seqs)
+        lengths = np.minimum(np.floor(np.exp(draws)).astype(np.int64), config.max_kv_len)
+    else:
+        raise ValueError(f"unknown length distribution {config.length_distribution}")
+    lengths = lengths.astype(np.int32)
+    pages_per_seq = -(-lengths.astype(np.int64) // config.page_size)
+    needed = int(pages_per_seq.sum())
+    if needed > config.total_pages:
+        raise ValueError(f"{config.name}: needs {needed} pages, pool has {config.total_pages}")
+    permutation = generator.permutation(config.total_pages)[:needed].astype(np.int32)
+    max_pages = -(-config.max_kv_len // config.page_size)
+    table = np.zeros((config.num_seqs, max_pages), dtype=np.int32)
+    cursor = 0
+    for s, count in enumerate(pages_per_seq):
+        table[s, :count] = permutation[cursor : cursor + count]
+        cursor += int(count)
+    return lengths, table
+
+
+def decode_algorithmic_bytes(kv_lens: np.ndarray, q_heads: int, kv_heads: int, head_dim: int, page_size: int, *, elem_bytes: int = 2) -> int:
+    """Bytes a decode step must move: K and V of every valid token once per KV head, the query read
+    and the output write, one page-table entry per page and one length per sequence. Page padding
+    beyond kv_len is not counted."""
+    lens = np.asarray(kv_lens, dtype=np.int64)
+    kv = int(lens.sum()) * kv_heads * head_dim * elem_bytes * 2
+    q_and_o = lens.size * q_heads * head_dim * elem_bytes * 2
+    table = int((-(-lens // page_size)).sum()) * 4 + 8 * lens.size
+    return kv + q_and_o + table
