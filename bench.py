@@ -1,0 +1,472 @@
+"""Benchmark of the hot path on N B200s of one node.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      (the CPU path on host cores)
+
+Headline: the large K-sharded BF16 matmul + reduce-scatter, A[8192,16384] x B[16384,8192], K split
+over the N ranks, result reduce-scattered along M into bf16 [8192/N, 8192] per GPU. One step = one
+pass of cake_matmul_rs_sm100 (+ cake_reduce_slots_sm100 when N > 1). The total work is fixed, so
+scaling is "strong". A second object, "rpa_decode", reports the ragged-paged-attention decode
+(HBM-bound): 64 sequences on one GPU, or the 256-sequence configuration with KV heads sharded over
+the ranks and outputs all-gathered.
+
+Timing: CUDA events on the stream the kernels are launched on, one event pair per step, a write of
+a buffer larger than L2 between steps, barrier + synchronize on both sides of the timed region,
+maximum over ranks. Clocks and throttle reasons are sampled with nvidia-smi during the region.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import __graft_entry__  # noqa: E402
+
+M, K, N = 8192, 16384, 8192
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (None until a capture of that kernel and workload exists).
+MEASURED_TRAFFIC_BYTES = {"matmul_n1": None, "rpa_decode_64": None}
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    QUERY = (
+        "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.process: subprocess.Popen | None = None
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            self.process = None
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            out, _ = self.process.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+            out, _ = self.process.communicate()
+        clocks, maxima, reasons = [], [], set()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 7:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(self.NAMES, parts[3:]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(maxima) if maxima else None,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }
+
+
+def reduce_max(mesh, value: float) -> float:
+    if mesh.world == 1:
+        return value
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=mesh.device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=mesh.group)
+    return float(t.item())
+
+
+def timed_steps(mesh, step, steps: int, warmup: int, flush) -> tuple[float, list[float]]:
+    """Runs ``warmup`` untimed and ``steps`` timed calls of ``step``; returns (total ms = max over
+    ranks of the sum of per-step device times, this rank's per-step ms)."""
+    import torch
+
+    for _ in range(warmup):
+        flush()
+        step()
+    mesh.barrier()
+    torch.cuda.synchronize(mesh.device)
+    pairs = []
+    for _ in range(steps):
+        flush()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        step()
+        stop.record()
+        pairs.append((start, stop))
+    torch.cuda.synchronize(mesh.device)
+    mesh.barrier()
+    per_step = [a.elapsed_time(b) for a, b in pairs]
+    return reduce_max(mesh, sum(per_step)), per_step
+
+
+def cpu_matmul_sample(rows: int, threads: int) -> dict:
+    """Times the oracle (numpy float32 matmul on bf16-valued inputs) on ``rows`` lhs rows of the
+    headline shape; all host threads numpy's BLAS uses."""
+    from oracle import matmul_rs
+
+    generator = np.random.default_rng(0)
+    lhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(rows, K)).astype(np.float32))
+    rhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(K, N)).astype(np.float32))
+    matmul_rs.matmul_reference(lhs[:64], rhs)
+    best = float("inf")
+    for _ in range(2):
+        started = time.perf_counter()
+        matmul_rs.matmul_reference(lhs, rhs)
+        best = min(best, time.perf_counter() - started)
+    return {
+        "value": 2.0 * rows * K * N / best / 1e12,
+        "unit": "TFLOP/s",
+        "cores": threads,
+        "kind": "port",
+        "sample": f"{rows} of {M} lhs rows of the {M}x{K}x{N} product, numpy float32 matmul, best of 2",
+        "seconds": best,
+    }
+
+
+def cpu_rpa_sample(lengths: np.ndarray, table: np.ndarray, config, sequences: int, threads: int) -> dict:
+    from oracle import rpa
+    from tpu_cake_b200 import workloads
+
+    generator = np.random.default_rng(1)
+    order = np.argsort(lengths)[:: max(1, len(lengths) // sequences)][:sequences]
+    total_bytes, seconds = 0, 0.0
+    for s in order:
+        count = -(-int(lengths[s]) // config.page_size)
+        keys = generator.standard_normal((count, config.page_size, config.kv_heads, config.head_dim), dtype=np.float32)
+        values = generator.standard_normal((count, config.page_size, config.kv_heads, config.head_dim), dtype=np.float32)
+        query = generator.standard_normal((1, config.q_heads, config.head_dim), dtype=np.float32)
+        started = time.perf_counter()
+        rpa.rpa_separate(query, keys, values, np.arange(count, dtype=np.int32)[None, :], lengths[s : s + 1], None, scale=config.softmax_scale)
+        seconds += time.perf_counter() - started
+        total_bytes += workloads.decode_algorithmic_bytes(lengths[s : s + 1], config.q_heads, config.kv_heads, config.head_dim, config.page_size)
+    return {
+        "value": total_bytes / seconds / 1e9,
+        "unit": "GB/s",
+        "cores": threads,
+        "kind": "port",
+        "sample": f"{len(order)} of {len(lengths)} sequences of {config.name}, numpy oracle, algorithmic bf16 bytes / wall time",
+        "seconds": seconds,
+    }
+
+
+# ----------------------------------------------------------------------------------------- ours
+
+
+def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
+    import torch
+
+    from tpu_cake_b200 import cuda_lowering
+
+    world = mesh.world
+    strategy = {
+        "p2p_bf16": cuda_lowering.MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE_BF16_TRANSPORT,
+        "p2p_f32": cuda_lowering.MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE,
+        "nccl": cuda_lowering.MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER,
+    }[args.strategy]
+    plan = cuda_lowering.plan_distributed_matmul(
+        mesh_size=world, m=M, k=K, n=N, scatter_dimension=0, output_dtype="bf16", tile_n=256,
+        collective_implementation=strategy if world > 1 else None,
+    )
+    executable, _ = plan.build(mesh=mesh)
+    k_local = K // world
+    generator = torch.Generator(device=mesh.device).manual_seed(20261125)
+    lhs_full = (torch.randn((M, K), generator=generator, device=mesh.device) * K**-0.5).to(torch.bfloat16)
+    lhs = lhs_full[:, mesh.rank * k_local : (mesh.rank + 1) * k_local].contiguous()
+    del lhs_full
+    rhs_full = (torch.randn((K, N), generator=generator, device=mesh.device) * K**-0.5).to(torch.bfloat16)
+    rhs = rhs_full[mesh.rank * k_local : (mesh.rank + 1) * k_local].contiguous()
+    del rhs_full
+    out = torch.empty(plan.output_local_shape, dtype=torch.bfloat16, device=mesh.device)
+    flush_buffer = torch.empty(256 << 20, dtype=torch.uint8, device=mesh.device)
+
+    def flush():
+        flush_buffer.fill_(1)
+
+    def step():
+        executable(lhs, rhs, out)
+
+    sampler = ClockSampler(mesh.device.index)
+    sampler.start()
+    total_ms, per_step = timed_steps(mesh, step, args.steps, args.warmup, flush)
+    clocks = sampler.stop()
+    executable.status()
+    launches = executable.launches_per_call * args.steps
+    flops_total = 2.0 * M * N * K
+    ms_per_step = total_ms / args.steps
+    value = flops_total / (ms_per_step * 1e-3) / 1e12
+
+    # Roofline of the dominant kernel: at N = 1 the step is exactly one cake_matmul_rs_sm100
+    # launch; at N > 1 the event pair also spans the slot reduction, so the figure is conservative.
+    kernel_ms = statistics.mean(per_step)
+    achieved = (flops_total / world) / (kernel_ms * 1e-3) / 1e12
+    peak = float(peaks["bf16_tflops"])
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+        "traffic": MEASURED_TRAFFIC_BYTES["matmul_n1"] if world == 1 else None,
+        "peak_source": f"{peak_kind}: cuBLAS bf16 burst", "frac_of_sustained": achieved / float(peaks["bf16_tflops_sustained"]),
+        "kernel": "cake_matmul_rs_sm100<256>", "kernel_ms": kernel_ms,
+    }
+
+    # End to end through the C ABI with host buffers (pinned): H2D of both operands, the kernels,
+    # D2H of the local output, inside the timed region.
+    e2e = None
+    if strategy is not cuda_lowering.MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER or world == 1:
+        lhs_host = lhs.cpu().view(torch.uint16).pin_memory().numpy()
+        rhs_host = rhs.cpu().view(torch.uint16).pin_memory().numpy()
+        out_host = torch.empty(plan.output_local_shape, dtype=torch.uint16).pin_memory().numpy()
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            executable.run_host(lhs_host, rhs_host, out_host)
+        mesh.barrier()
+        torch.cuda.synchronize(mesh.device)
+        started = time.perf_counter()
+        for _ in range(e2e_steps):
+            executable.run_host(lhs_host, rhs_host, out_host)
+        torch.cuda.synchronize(mesh.device)
+        elapsed = reduce_max(mesh, time.perf_counter() - started)
+        mesh.barrier()
+        executable.status()
+        e2e = {
+            "value": flops_total / (elapsed / e2e_steps) / 1e12, "unit": "TFLOP/s",
+            "h2d_bytes_per_step": int(lhs_host.nbytes + rhs_host.nbytes), "d2h_bytes_per_step": int(out_host.nbytes),
+            "ms_per_step": elapsed / e2e_steps * 1e3, "steps": e2e_steps, "api": "cake_matmul_rs_run_host",
+        }
+    executable.close()
+    del lhs, rhs, out, flush_buffer
+    torch.cuda.empty_cache()
+    return {
+        "value": value, "ms_per_step": ms_per_step, "roofline": roofline, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": launches, "strategy": args.strategy if world > 1 else "single",
+    }
+
+
+def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
+    import torch
+
+    from tpu_cake_b200 import rpa_cuda_lowering, workloads
+
+    world = mesh.world
+    config = workloads.DECODE_64 if world == 1 else workloads.DECODE_SHARDED_256
+    lengths, table = workloads.decode_metadata(config)
+    local_kv = config.kv_heads // world
+    local_q = config.q_heads // world
+    generator = torch.Generator(device=mesh.device).manual_seed(1000 + mesh.rank)
+    shape = (config.total_pages, config.page_size, local_kv, 2, config.head_dim)
+    cache = torch.empty(shape, dtype=torch.bfloat16, device=mesh.device)
+    block = 4096
+    for start in range(0, config.total_pages, block):
+        stop = min(config.total_pages, start + block)
+        cache[start:stop] = torch.randn((stop - start, *shape[1:]), generator=generator, device=mesh.device).to(torch.bfloat16)
+    query = torch.randn((config.num_seqs, local_q, config.head_dim), generator=generator, device=mesh.device).to(torch.bfloat16)
+    table_d = torch.from_numpy(table).to(mesh.device)
+    lengths_d = torch.from_numpy(lengths).to(mesh.device)
+    plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+        name=config.name, schedule_sha256="0" * 64, query_shape=(config.num_seqs, local_q, config.head_dim),
+        cache_shape=(config.total_pages, config.page_size, local_kv, config.head_dim), page_table_shape=table.shape,
+        bias_shape=None, softmax_scale=config.softmax_scale, cache_layout="fused", kv_chunk_tokens=args.kv_chunk,
+    )
+    executable = plan.build(mesh.device)
+    out = torch.empty_like(query)
+    gathered = torch.empty((world, config.num_seqs, local_q, config.head_dim), dtype=torch.bfloat16, device=mesh.device) if world > 1 else None
+    flush_buffer = torch.empty(256 << 20, dtype=torch.uint8, device=mesh.device)
+
+    def flush():
+        flush_buffer.fill_(1)
+
+    def step():
+        plan.invoke(executable, query, cache, None, table_d, lengths_d, out=out)
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(gathered, out, group=mesh.group)
+
+    steps = max(args.steps, 10)
+    total_ms, per_step = timed_steps(mesh, step, steps, max(args.warmup, 3), flush)
+    executable.status()
+    bytes_total = workloads.decode_algorithmic_bytes(lengths, config.q_heads, config.kv_heads, config.head_dim, config.page_size)
+    ms_per_step = total_ms / steps
+    value = bytes_total / (ms_per_step * 1e-3) / 1e9
+    achieved = (bytes_total / world) / (statistics.mean(per_step) * 1e-3) / 1e9
+    peak = float(peaks["hbm_gbs"])
+    result = {
+        "metric": "rpa_decode_hbm_gbs", "value": value, "unit": "GB/s", "ms_per_step": ms_per_step, "steps": steps,
+        "config": {
+            "workload": config.name, "num_seqs": config.num_seqs, "q_heads": config.q_heads, "kv_heads": config.kv_heads,
+            "head_dim": config.head_dim, "page_size": config.page_size, "total_pages": config.total_pages,
+            "kv_tokens": int(lengths.astype(np.int64).sum()), "sharding": f"kv_heads/{world}" if world > 1 else "none",
+            "collective": "nccl all_gather of outputs" if world > 1 else "none", "l2": "256 MiB flush between steps",
+        },
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": MEASURED_TRAFFIC_BYTES["rpa_decode_64"] if world == 1 else None,
+            "peak_source": f"{peak_kind}: device copy bandwidth", "kernel": "cake_rpa_decode_sm100 (+plan, combine)",
+            "algorithmic_bytes": bytes_total // world,
+        },
+        "gpu_launches": executable.launches_per_call * steps,
+    }
+    # End to end: per-step inputs (queries, lengths, page table) come from pinned host memory and the
+    # outputs go back; the KV pool is resident state, as in serving.
+    q_host = query.cpu().pin_memory()
+    table_host = table_d.cpu().pin_memory()
+    lengths_host = lengths_d.cpu().pin_memory()
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    e2e_steps = 10
+    mesh.barrier()
+    torch.cuda.synchronize(mesh.device)
+    started = time.perf_counter()
+    for _ in range(e2e_steps):
+        query.copy_(q_host, non_blocking=True)
+        table_d.copy_(table_host, non_blocking=True)
+        lengths_d.copy_(lengths_host, non_blocking=True)
+        step()
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.synchronize(mesh.device)
+    elapsed = reduce_max(mesh, time.perf_counter() - started)
+    result["e2e"] = {
+        "value": bytes_total / (elapsed / e2e_steps) / 1e9, "unit": "GB/s",
+        "h2d_bytes_per_step": int(q_host.nbytes + table_host.nbytes + lengths_host.nbytes), "d2h_bytes_per_step": int(out_host.nbytes),
+        "ms_per_step": elapsed / e2e_steps * 1e3,
+    }
+    if world == 1 and mesh.rank == 0 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_rpa_sample(lengths, table, config, 8, os.cpu_count() or 1)
+    executable.close()
+    return result
+
+
+def run_ours(args) -> None:
+    import torch
+
+    __graft_entry__.load_package()
+    from tpu_cake_b200.mesh import ProcessMesh
+
+    mesh = ProcessMesh.from_environment()
+    if mesh.world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {mesh.world}: launch with torch.distributed.run")
+    peaks, peak_kind = measured_peaks()
+    matmul = bench_matmul(mesh, args, peaks, peak_kind)
+    rpa = None if args.no_rpa else bench_rpa(mesh, args, peaks, peak_kind)
+    line = {
+        "metric": "matmul_reduce_scatter_tflops", "value": matmul["value"], "unit": "TFLOP/s", "n_gpus": mesh.world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": matmul["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": f"K-sharded bf16 matmul {M}x{K}x{N} + reduce-scatter along M to bf16 [{M // mesh.world},{N}] per GPU",
+            "m": M, "k": K, "n": N, "mesh": mesh.world, "accumulate": "f32", "collective": matmul["strategy"],
+            "l2": "256 MiB flush between steps",
+        },
+        "roofline": matmul["roofline"], "e2e": matmul["e2e"], "gpu_launches": matmul["gpu_launches"], "clocks": matmul["clocks"],
+    }
+    if mesh.rank == 0 and mesh.world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_matmul_sample(args.cpu_rows, os.cpu_count() or 1)
+    if rpa is not None:
+        line["rpa_decode"] = rpa
+        line["gpu_launches"] += rpa["gpu_launches"]
+    if mesh.rank == 0:
+        print(json.dumps(line), flush=True)
+    if mesh.world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------ reference
+
+
+def run_reference(args) -> None:
+    """The reference's CPU path for the same metric and config. The reference's own JAX program
+    cannot run on this machine (jax and xDSL are not installed and cannot be), so this arm times the
+    oracle port, which restates the numpy oracle the reference itself checks against; each step is a
+    bounded sample of the workload."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = args.cpu_rows
+    from oracle import matmul_rs
+
+    generator = np.random.default_rng(0)
+    lhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(rows, K)).astype(np.float32))
+    rhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(K, N)).astype(np.float32))
+    for _ in range(min(args.warmup, 3)):
+        matmul_rs.matmul_reference(lhs, rhs)
+    steps = min(args.steps, 10)
+    started = time.perf_counter()
+    for _ in range(steps):
+        matmul_rs.matmul_reference(lhs, rhs)
+    elapsed = time.perf_counter() - started
+    value = 2.0 * rows * K * N * steps / elapsed / 1e12
+    sample = f"{rows} of {M} lhs rows of the {M}x{K}x{N} product per step, numpy float32 matmul on bf16-valued inputs"
+    line = {
+        "impl": "reference", "metric": "matmul_reduce_scatter_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"K-sharded bf16 matmul {M}x{K}x{N} + reduce-scatter along M", "m": M, "k": K, "n": N, "mesh": args.gpus},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--strategy", choices=("p2p_bf16", "p2p_f32", "nccl"), default="p2p_bf16")
+    parser.add_argument("--kv-chunk", type=int, default=0)
+    parser.add_argument("--cpu-rows", type=int, default=1024)
+    parser.add_argument("--no-rpa", action="store_true")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
