@@ -68,11 +68,12 @@ class ClockSampler:
     def start(self) -> None:
         try:
             self.process = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
         except OSError:
             self.process = None
+        time.sleep(0.3)  # let nvidia-smi start sampling before the GPU work begins
 
     def stop(self) -> dict:
         if self.process is None:
@@ -149,16 +150,19 @@ def cpu_matmul_sample(rows: int, threads: int) -> dict:
     rhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(K, N)).astype(np.float32))
     matmul_rs.matmul_reference(lhs[:64], rhs)
     best = float("inf")
-    for _ in range(2):
+    repeats = 0
+    budget_started = time.perf_counter()
+    while repeats < 3 or (time.perf_counter() - budget_started < 10.0 and repeats < 20):
         started = time.perf_counter()
         matmul_rs.matmul_reference(lhs, rhs)
         best = min(best, time.perf_counter() - started)
+        repeats += 1
     return {
         "value": 2.0 * rows * K * N / best / 1e12,
         "unit": "TFLOP/s",
         "cores": threads,
         "kind": "port",
-        "sample": f"{rows} of {M} lhs rows of the {M}x{K}x{N} product, numpy float32 matmul, best of 2",
+        "sample": f"{rows} of {M} lhs rows of the {M}x{K}x{N} product, numpy float32 matmul, best of {repeats}",
         "seconds": best,
     }
 
@@ -368,7 +372,7 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
         "ms_per_step": elapsed / e2e_steps * 1e3,
     }
     if world == 1 and mesh.rank == 0 and not args.no_cpu_baseline:
-        result["cpu_baseline"] = cpu_rpa_sample(lengths, table, config, 8, os.cpu_count() or 1)
+        result["cpu_baseline"] = cpu_rpa_sample(lengths, table, config, 32, os.cpu_count() or 1)
     executable.close()
     return result
 
@@ -456,7 +460,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--strategy", choices=("p2p_bf16", "p2p_f32", "nccl"), default="p2p_bf16")
     parser.add_argument("--kv-chunk", type=int, default=0)
-    parser.add_argument("--cpu-rows", type=int, default=1024)
+    parser.add_argument("--cpu-rows", type=int, default=8192)
     parser.add_argument("--no-rpa", action="store_true")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
