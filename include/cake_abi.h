@@ -192,6 +192,39 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
                                 const void* bias0, const void* bias1, void* out, void* workspace,
                                 void* stream);
 
+/* Decode for hosts that may not allocate device memory. No counterpart in the reference: its
+ * kernels get their scratch from the JAX runtime.
+ *
+ * Who needs it: a plugin inside a serving engine that owns the only device allocator and hands the
+ * plugin fixed input and output buffers, or a serving loop whose memory pool is frozen after
+ * start-up (an allocation there is refused, or stalls the whole device mid-request). Such a host
+ * cannot provide the split-KV workspace cake_rpa_decode_enqueue asks for, and cannot call
+ * cake_rpa_create either (it allocates a status word). This one call needs neither: it takes the
+ * descriptor directly, keeps its scratch in an array built into the library
+ * (CAKE_RPA_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the process exits), and
+ * calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Arguments are those of cake_rpa_decode_enqueue without the workspace. status_device is an
+ * optional caller-owned device buffer of 4 int32 (zeroed by the caller) that receives the
+ * cake_status fields if a device-side check fails; pass NULL to ignore.
+ *
+ * Limits and rules:
+ *   - A shape whose scratch would exceed CAKE_RPA_STATIC_SCRATCH_BYTES is rejected with
+ *     CAKE_ERR_UNSUPPORTED (the message states the bytes needed). The need grows with
+ *     (page-table extent * page_size / kv_chunk_tokens + num_seqs) * q_heads * 520 bytes.
+ *   - The first call on each device looks up the array's device address (one-time set-up); make
+ *     that first call before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps the previous call's contents. Every
+ *     call rewrites what it later reads, so calls that run one after another are independent, but
+ *     two calls whose kernels overlap on the GPU (different streams) race on it: serialise them. */
+#define CAKE_RPA_STATIC_SCRATCH_BYTES (16u << 20)
+int32_t cake_rpa_decode_static_scratch(const cake_rpa_desc* desc, const void* q, const void* new_k,
+                                       const void* new_v, void* cache0, void* cache1,
+                                       const int32_t* kv_lens, const int32_t* page_table,
+                                       const int32_t* cu_kv_lens, const void* bias0,
+                                       const void* bias1, void* out, int32_t* status_device,
+                                       void* stream);
+
 int32_t cake_rpa_status(cake_rpa* plan, void* stream, cake_status* out);
 int32_t cake_rpa_launches_per_enqueue(const cake_rpa* plan);
 

@@ -742,3 +742,102 @@ int32_t cake_rpa_status(cake_rpa* plan, void* stream_v, cake_status* out) {
 }
 
 }  // extern "C"
+
+// ====================================================================================== no-allocation variant
+//
+// cake_rpa_decode_static_scratch: the same decode, for hosts that are not allowed to allocate
+// device memory -- a plugin running inside a serving engine that hands it fixed input / output
+// buffers and owns the only allocator, or a loop whose memory pool is frozen after start-up, where
+// a cudaMalloc would either be refused or would synchronise the whole device in the middle of
+// serving. Such a host has nowhere to get the split-KV workspace from, so this variant keeps it in
+// the array below, which is part of the library image: every GPU that loads the library holds
+// CAKE_RPA_STATIC_SCRATCH_BYTES of it until the process exits.
+//
+// In host code the array's name is only a stand-in for the symbol, not a device address, so the
+// address the kernels receive is looked up with cudaGetSymbolAddress, once per device, with that
+// device current.
+
+__device__ __align__(256) unsigned char g_cake_rpa_static_scratch[CAKE_RPA_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_address[kMaxDevices] = {};
+
+// Derives the sizes cake_rpa_create would derive, into a caller-provided (stack) plan; validates
+// the descriptor; touches no allocator.
+int32_t rpa_prepare_without_allocation(const cake_rpa_desc& d, cake_rpa* plan) {
+  if (d.num_seqs <= 0 || d.q_heads <= 0 || d.kv_heads <= 0 || d.total_pages <= 0 || d.total_pages >= INT32_MAX)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa (static scratch): num_seqs, q_heads, kv_heads, total_pages out of range");
+  if (d.num_q_tokens != d.num_seqs)
+    return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): only pure decode is lowered");
+  if (d.q_heads % d.kv_heads != 0 || d.q_heads / d.kv_heads > 16)
+    return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): q_heads must be 1..16 times kv_heads");
+  if (d.head_dim <= 0 || d.head_dim > 128 || d.head_dim % 8 != 0)
+    return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): head_dim must be a multiple of 8 up to 128");
+  if (d.cache_layout == CAKE_RPA_CACHE_FUSED ? d.head_dim_padded != 128
+                                             : (d.cache_layout != CAKE_RPA_CACHE_SEPARATE || d.head_dim != 128))
+    return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): cache rows must be 128 elements wide");
+  int log2_ps = -1;
+  for (int i = 0; i <= 5; ++i)
+    if (d.page_size == (1 << i)) log2_ps = i;
+  if (log2_ps < 0) return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): page_size must be a power of two up to 32");
+  if ((d.table_layout != CAKE_RPA_TABLE_2D && d.table_layout != CAKE_RPA_TABLE_FLAT) || d.max_pages_per_seq <= 0)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa (static scratch): bad page-table layout or extent");
+  if (d.bias_mode < 0 || d.bias_mode > 2 || (d.bias_mode != 0 && d.bias_extent <= 0) || (d.bias_mode == 2 && d.rel_dim <= 0))
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa (static scratch): bad bias description");
+  const int chunk = d.kv_chunk_tokens == 0 ? 512 : d.kv_chunk_tokens;
+  if (chunk < cake::kStageTokens || chunk % cake::kStageTokens != 0)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa (static scratch): kv_chunk_tokens must be a positive multiple of %d", cake::kStageTokens);
+  plan->d = d;
+  plan->log2_ps = log2_ps;
+  plan->chunk_tokens = chunk;
+  const int64_t table_pages = d.table_layout == CAKE_RPA_TABLE_2D
+                                  ? static_cast<int64_t>(d.num_seqs) * d.max_pages_per_seq
+                                  : static_cast<int64_t>(d.max_pages_per_seq);
+  plan->max_items = (table_pages * d.page_size / chunk + d.num_seqs) * d.kv_heads;
+  const int group = d.q_heads / d.kv_heads;
+  plan->off_item_base = 256;
+  plan->off_part_ml = align_up(plan->off_item_base + sizeof(int32_t) * (d.num_seqs + 1), 256);
+  plan->off_part_o = align_up(plan->off_part_ml + sizeof(float) * 2 * group * plan->max_items, 256);
+  plan->ws_bytes = plan->off_part_o + sizeof(float) * 128 * group * plan->max_items;
+  return CAKE_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t cake_rpa_decode_static_scratch(const cake_rpa_desc* desc, const void* q,
+                                                  const void* new_k, const void* new_v,
+                                                  void* cache0, void* cache1, const int32_t* kv_lens,
+                                                  const int32_t* page_table,
+                                                  const int32_t* cu_kv_lens, const void* bias0,
+                                                  const void* bias1, void* out,
+                                                  int32_t* status_device, void* stream) {
+  if (!desc) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_rpa_decode_static_scratch: null descriptor");
+  cake_rpa plan;  // on the stack: no handle, nothing to destroy
+  int32_t rc = rpa_prepare_without_allocation(*desc, &plan);
+  if (rc) return rc;
+  if (plan.ws_bytes > CAKE_RPA_STATIC_SCRATCH_BYTES)
+    return fail(CAKE_ERR_UNSUPPORTED,
+                "rpa (static scratch): this shape needs %zu bytes of split-KV scratch, the built-in array holds %u; "
+                "use cake_rpa_decode_enqueue with a caller-provided workspace, or a larger kv_chunk_tokens",
+                plan.ws_bytes, static_cast<unsigned>(CAKE_RPA_STATIC_SCRATCH_BYTES));
+  int device = 0, major = 0;
+  CAKE_CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): device ordinal %d out of range", device);
+  if (!g_static_scratch_address[device]) {
+    // First call on this device: one-time set-up (do it before any stream capture begins).
+    CAKE_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10) return fail(CAKE_ERR_UNSUPPORTED, "libcake_b200 needs an sm_100 GPU, found compute capability %d.x", major);
+    void* address = nullptr;
+    CAKE_CUDA_TRY(cudaGetSymbolAddress(&address, g_cake_rpa_static_scratch));
+    if (!address) return fail(CAKE_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the static scratch");
+    g_static_scratch_address[device] = address;
+  }
+  CAKE_CUDA_TRY(cudaDeviceGetAttribute(&plan.sm_count, cudaDevAttrMultiProcessorCount, device));
+  plan.status.dev = status_device;  // caller-owned, may be null; never freed here
+  rc = cake_rpa_decode_enqueue(&plan, q, new_k, new_v, cache0, cache1, kv_lens, page_table, cu_kv_lens,
+                               bias0, bias1, out, g_static_scratch_address[device], stream);
+  plan.status.dev = nullptr;
+  return rc;
+}
