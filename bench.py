@@ -291,6 +291,10 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
 
     world = mesh.world
     config = workloads.DECODE_64 if world == 1 else workloads.DECODE_SHARDED_256
+    if args.rpa_pool_pages:
+        import dataclasses
+
+        config = dataclasses.replace(config, total_pages=args.rpa_pool_pages)
     lengths, table = workloads.decode_metadata(config)
     local_kv = config.kv_heads // world
     local_q = config.q_heads // world
@@ -387,8 +391,13 @@ def run_ours(args) -> None:
     if mesh.world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {mesh.world}: launch with torch.distributed.run")
     peaks, peak_kind = measured_peaks()
-    matmul = bench_matmul(mesh, args, peaks, peak_kind)
     rpa = None if args.no_rpa else bench_rpa(mesh, args, peaks, peak_kind)
+    if args.only_rpa:
+        # Profiling aid: only the attention kernels run (small enough for an ncu capture).
+        if mesh.rank == 0:
+            print(json.dumps(rpa), flush=True)
+        return
+    matmul = bench_matmul(mesh, args, peaks, peak_kind)
     line = {
         "metric": "matmul_reduce_scatter_tflops", "value": matmul["value"], "unit": "TFLOP/s", "n_gpus": mesh.world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": matmul["ms_per_step"], "higher_is_better": True,
@@ -462,6 +471,9 @@ def main() -> None:
     parser.add_argument("--kv-chunk", type=int, default=0)
     parser.add_argument("--cpu-rows", type=int, default=8192)
     parser.add_argument("--no-rpa", action="store_true")
+    parser.add_argument("--only-rpa", action="store_true", help="run only the attention part (profiling aid)")
+    parser.add_argument("--rpa-pool-pages", type=int, default=0,
+                        help="shrink the KV page pool (same sequences and lengths; for captures that must hold little memory)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
     if args.warmup < 3:
