@@ -9,7 +9,7 @@
 //
 // Kernels
 //   cake_rpa_plan_sm100      one CTA: per-sequence chunk counts -> exclusive prefix (work-item
-//                            table) and reset of the work counter
+//                            table), reset of the work counter and of the arrival counters
 //   cake_rpa_cache_update_sm100  optional: writes each sequence's new K/V at position kv_len-1
 //   cake_rpa_decode_sm100    persistent; every WARP is an independent worker with its own
 //                            3-stage shared-memory ring. A work item is (sequence, KV head,
@@ -19,8 +19,9 @@
 //                            once per KV head). QK^T and PV run on mma.sync m16n8k16 with the
 //                            query-head group padded to 16 rows; online softmax in f32 with
 //                            quad shuffles.
-//   cake_rpa_combine_sm100   merges split-KV partials (m, l, o) of a (sequence, KV head) in
-//                            chunk order and writes bf16.
+//                            Split-KV partials (m, l, o) of a (sequence, KV head) are merged, in
+//                            chunk order, by whichever warp publishes the last chunk; loads run
+//                            ahead into the next work item so the ring never drains.
 #include <cuda_bf16.h>
 #include <math.h>
 #include <string.h>
@@ -32,9 +33,15 @@
 
 namespace cake {
 
-constexpr int kRpaWarps = 4;
+#ifndef CAKE_RPA_WARPS
+#define CAKE_RPA_WARPS 6
+#endif
+#ifndef CAKE_RPA_STAGES
+#define CAKE_RPA_STAGES 2
+#endif
+constexpr int kRpaWarps = CAKE_RPA_WARPS;
 constexpr int kRpaThreads = kRpaWarps * 32;
-constexpr int kRpaStages = 3;
+constexpr int kRpaStages = CAKE_RPA_STAGES;
 constexpr int kStageTokens = 32;
 constexpr int kRowBytes = 256;                                // one token of one head: 128 bf16
 constexpr int kStageBytes = kStageTokens * 2 * kRowBytes;     // K and V: 16 KiB
@@ -62,7 +69,9 @@ struct RpaParams {
   const __nv_bfloat16* rel_proj;    // mode 2: [rel_dim, bias_extent]
   int32_t rel_dim;
   int32_t* work_counter;
+  int32_t* arrive;     // [num_seqs * kv_heads] chunks published per (sequence, KV head)
   int32_t* item_base;  // [num_seqs + 1] exclusive prefix of per-sequence chunk counts
+  int32_t* item_seq;   // [sum of chunk counts] sequence of every (sequence, chunk) pair
   float* part_o;       // [max_items][group][128]
   float* part_ml;      // [max_items][group][2]
   int32_t max_items;
@@ -85,6 +94,7 @@ __global__ void __launch_bounds__(256) cake_rpa_plan_sm100(RpaParams p) {
     *p.work_counter = 0;
     p.item_base[0] = 0;
   }
+  for (int i = threadIdx.x; i < p.num_seqs * p.kv_heads; i += blockDim.x) p.arrive[i] = 0;
   __syncthreads();
   for (int base = 0; base < p.num_seqs; base += 256) {
     const int s = base + threadIdx.x;
@@ -103,7 +113,12 @@ __global__ void __launch_bounds__(256) cake_rpa_plan_sm100(RpaParams p) {
       s_scan[threadIdx.x] += v;
       __syncthreads();
     }
-    if (s < p.num_seqs) p.item_base[s + 1] = s_carry + s_scan[threadIdx.x];
+    if (s < p.num_seqs) {
+      const int end = s_carry + s_scan[threadIdx.x];
+      p.item_base[s + 1] = end;
+      if (static_cast<long long>(end) * p.kv_heads <= p.max_items)
+        for (int c = end - chunks; c < end; ++c) p.item_seq[c] = s;
+    }
     __syncthreads();
     if (threadIdx.x == 255) s_carry += s_scan[255];
     __syncthreads();
@@ -193,6 +208,81 @@ __device__ __forceinline__ uint32_t rpa_smem_off(int t, int c16, int kv, int pag
   return off ^ (((off >> 7) & 7u) << 4);
 }
 
+// One unit of work of a warp: KV tokens [tok0, tok0 + ntok) of one (sequence, KV head).
+struct RpaItem {
+  int id, s, h, n_chunks, len, tok0;
+};
+
+// Claims the next work item from the global queue and decodes it (warp-uniform). Returns false
+// when the queue is exhausted.
+__device__ __forceinline__ bool rpa_fetch_item(const RpaParams& p, int total_items, int lane,
+                                               RpaItem& it) {
+  int id = 0;
+  if (lane == 0) id = atomicAdd(p.work_counter, 1);
+  id = __shfl_sync(0xffffffffu, id, 0);
+  if (id >= total_items) return false;
+  if (id >= p.max_items) {
+    if (lane == 0) rpa_record(p.status, 4, id, p.max_items, 1);
+    return false;
+  }
+  const int cs = id / p.kv_heads;
+  const int lo = p.item_seq[cs];
+  const int base = p.item_base[lo];
+  it.id = id;
+  it.s = lo;
+  it.h = id - cs * p.kv_heads;
+  it.n_chunks = p.item_base[lo + 1] - base;
+  it.len = p.kv_lens[lo];
+  it.tok0 = (cs - base) * p.chunk_tokens;
+  return true;
+}
+
+__device__ __forceinline__ int rpa_item_tokens(const RpaParams& p, const RpaItem& it) {
+  return min(p.chunk_tokens, it.len - it.tok0);
+}
+
+// Issues the TMA loads of stage `st` of item `it` into the ring slot at `stage_smem`: one box per
+// page (K and V of one KV head). Page ids are read from the page table 32 at a time (one per
+// lane, `window_pages`, for the item-relative page window `window`) and handed to the issuing
+// lanes by shuffle, so a stage does not wait on a table read of its own.
+__device__ __forceinline__ void rpa_issue_stage(const RpaParams& p, const CUtensorMap* tmap_k,
+                                                const CUtensorMap* tmap_v, const RpaItem& it, int st,
+                                                uint32_t stage_smem, uint32_t bar, int lane,
+                                                int& window, int& window_pages) {
+  const int ps = p.page_size;
+  const int pages_per_stage = kStageTokens >> p.log2_ps;
+  const int ntok = rpa_item_tokens(p, it);
+  const int rem = ntok - st * kStageTokens;
+  const int npages = min(pages_per_stage, (rem + ps - 1) >> p.log2_ps);
+  const int first = st * pages_per_stage;  // first page of the stage, relative to the item
+  if ((first >> 5) != window) {
+    window = first >> 5;
+    const int rel = window * 32 + lane;
+    int page = p.total_pages;  // an out-of-bounds coordinate: the TMA unit fills the box with zeros
+    if (rel < ((ntok + ps - 1) >> p.log2_ps)) {
+      const int page_slot = (it.tok0 >> p.log2_ps) + rel;
+      page = rpa_page_lookup(p, it.s, page_slot);
+      if (page < 0 || page >= p.total_pages) {
+        rpa_record(p.status, 3, it.s, page_slot, page);
+        page = p.total_pages;
+      }
+    }
+    window_pages = page;
+  }
+  const int page = __shfl_sync(0xffffffffu, window_pages, (first + lane) & 31);
+  if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(npages * ps * 512));
+  __syncwarp();
+  if (lane < npages) {
+    const uint32_t dst = stage_smem + lane * ps * 512;
+    if (p.fused) {
+      tma_load_5d(dst, tmap_k, bar, 0, 0, 0, 2 * it.h, page);
+    } else {
+      tma_load_5d(dst, tmap_k, bar, 0, 0, 0, it.h, page);
+      tma_load_5d(dst + ps * 256, tmap_v, bar, 0, 0, 0, it.h, page);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kRpaThreads, 1)
     cake_rpa_decode_sm100(const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_v, const RpaParams p) {
@@ -215,39 +305,25 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
   __syncwarp();
 
   const int ps = p.page_size;
-  const int pages_per_stage = kStageTokens >> p.log2_ps;
   const int total_items = p.item_base[p.num_seqs] * p.kv_heads;
   const int row0 = lane >> 2;
   const int row1 = row0 + 8;
   const int quad = lane & 3;
-  uint32_t phase_bits = 0;
-  bool alive = true;
+
+  // The warp streams stages through its ring continuously: `consume_pos` counts stages computed,
+  // `issue_pos` stages whose loads were issued; loads run ahead across the boundary into the next
+  // work item so the ring never drains between items.
+  RpaItem cur, nxt;
+  bool nxt_fetched = false, have_nxt = false;
+  int cur_issued = 0, nxt_issued = 0;
+  int cur_window = -1, nxt_window = -1, cur_pages = 0, nxt_pages = 0;
+  uint32_t issue_pos = 0, consume_pos = 0;
+  bool alive = rpa_fetch_item(p, total_items, lane, cur);
 
   while (alive) {
-    int item = 0;
-    if (lane == 0) item = atomicAdd(p.work_counter, 1);
-    item = __shfl_sync(0xffffffffu, item, 0);
-    if (item >= total_items) break;
-    if (item >= p.max_items) {
-      if (lane == 0) rpa_record(p.status, 4, item, p.max_items, 1);
-      break;
-    }
-    const int cs = item / p.kv_heads;
-    const int h = item - cs * p.kv_heads;
-    // Largest s with item_base[s] <= cs.
-    int lo = 0, hi = p.num_seqs;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (p.item_base[mid] <= cs) lo = mid; else hi = mid;
-    }
-    const int s = lo;
-    const int chunk = cs - p.item_base[s];
-    const int n_chunks = p.item_base[s + 1] - p.item_base[s];
-    const int len = p.kv_lens[s];
-    const int tok0 = chunk * p.chunk_tokens;
-    const int ntok = min(p.chunk_tokens, len - tok0);
+    const int h = cur.h, s = cur.s, len = cur.len, tok0 = cur.tok0;
+    const int ntok = rpa_item_tokens(p, cur);
     const int nstages = (ntok + kStageTokens - 1) / kStageTokens;
-    const int first_page_slot = tok0 >> p.log2_ps;
 
     // ---- query fragments (A operand, 16 x 128, rows >= group are zero)
     uint32_t qa[8][4];
@@ -270,50 +346,55 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
     float m_run[2] = {kNegBig, kNegBig};
     float l_run[2] = {0.f, 0.f};
 
-    // Issues the TMA loads of stage `st` of this item into ring slot st % kRpaStages.
-    auto issue = [&](int st) {
-      const int slot = st % kRpaStages;
-      const int rem = ntok - st * kStageTokens;
-      const int npages = min(pages_per_stage, (rem + ps - 1) >> p.log2_ps);
-      const uint32_t bar = smem_u32(&bars[slot]);
-      if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(npages * ps * 512));
-      __syncwarp();
-      if (lane < npages) {
-        const int page_slot = first_page_slot + st * pages_per_stage + lane;
-        int page = rpa_page_lookup(p, s, page_slot);
-        if (page < 0 || page >= p.total_pages) {
-          // Out-of-range page: recorded; the TMA unit fills out-of-bounds boxes with zeros.
-          rpa_record(p.status, 3, s, page_slot, page);
-          page = p.total_pages;
-        }
-        const uint32_t dst = smem_u32(ring + slot * kStageBytes + lane * ps * 512);
-        if (p.fused) {
-          tma_load_5d(dst, &tmap_k, bar, 0, 0, 0, 2 * h, page);
-        } else {
-          tma_load_5d(dst, &tmap_k, bar, 0, 0, 0, h, page);
-          tma_load_5d(dst + ps * 256, &tmap_v, bar, 0, 0, 0, h, page);
-        }
-      }
-    };
-
-    // Ring slots are refilled only after every lane finished reading them (generic proxy) and a
-    // proxy fence orders those reads before the async-proxy writes of the next TMA.
-    for (int st = 0; st < min(kRpaStages - 1, nstages); ++st) issue(st);
-
     for (int st = 0; st < nstages; ++st) {
-      if (st + kRpaStages - 1 < nstages) {
-        fence_proxy_async_smem();
-        issue(st + kRpaStages - 1);
+      // ---- top up the ring. A slot is refilled only after every lane finished reading it
+      // (__syncwarp at the end of the previous stage) and a proxy fence orders those generic-proxy
+      // reads before the async-proxy writes of the new TMA.
+      fence_proxy_async_smem();
+      auto top_up = [&]() {
+      while (issue_pos - consume_pos < static_cast<uint32_t>(kRpaStages)) {
+        const uint32_t slot = issue_pos % kRpaStages;
+        const uint32_t stage_smem = smem_u32(ring + slot * kStageBytes);
+        const uint32_t bar = smem_u32(&bars[slot]);
+        if (cur_issued < nstages) {
+          rpa_issue_stage(p, &tmap_k, &tmap_v, cur, cur_issued, stage_smem, bar, lane, cur_window, cur_pages);
+          ++cur_issued;
+          ++issue_pos;
+          continue;
+        }
+        if (!nxt_fetched || !have_nxt) break;
+        const int nxt_stages = (rpa_item_tokens(p, nxt) + kStageTokens - 1) / kStageTokens;
+        if (nxt_issued >= nxt_stages) break;
+        rpa_issue_stage(p, &tmap_k, &tmap_v, nxt, nxt_issued, stage_smem, bar, lane, nxt_window, nxt_pages);
+        ++nxt_issued;
+        ++issue_pos;
       }
-      const int slot = st % kRpaStages;
-      const bool arrived = mbar_wait_bounded(smem_u32(&bars[slot]), (phase_bits >> slot) & 1u,
-                                             kRpaBarrierBudget);
+      };
+      top_up();
+      if (!nxt_fetched) {
+        // Claim the next item now: its queue and table reads overlap the wait for this stage's
+        // data, and the ring can then run ahead into it without stalling.
+        nxt_fetched = true;
+        nxt_issued = 0;
+        nxt_window = -1;
+        have_nxt = rpa_fetch_item(p, total_items, lane, nxt);
+        if (have_nxt && lane < 2 * p.group) {
+          // Pull the next item's query rows toward L2 so its fragment loads do not stall.
+          const char* qptr = reinterpret_cast<const char*>(
+              p.q + (static_cast<size_t>(nxt.s) * p.q_heads + nxt.h * p.group + (lane >> 1)) * p.head_dim);
+          if ((lane & 1) * 128 < p.head_dim * 2)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(qptr + (lane & 1) * 128));
+        }
+        top_up();  // a short item may leave room to run ahead into the one just claimed
+      }
+      const uint32_t slot = consume_pos % kRpaStages;
+      const uint32_t parity = (consume_pos / kRpaStages) & 1u;
+      const bool arrived = mbar_wait_bounded(smem_u32(&bars[slot]), parity, kRpaBarrierBudget);
       if (!__all_sync(0xffffffffu, arrived)) {
-        if (lane == 0) rpa_record(p.status, 1, blockIdx.x, item, st);
+        if (lane == 0) rpa_record(p.status, 1, blockIdx.x, cur.id, st);
         alive = false;
         break;
       }
-      phase_bits ^= 1u << slot;
       const uint32_t sbase = smem_u32(ring + slot * kStageBytes);
       const int valid = min(kStageTokens, ntok - st * kStageTokens);
       const int n16 = (valid + 15) >> 4;  // 16-token groups to process (1 or 2)
@@ -431,20 +512,16 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
         }
       }
       __syncwarp();
+      ++consume_pos;
     }
-    if (!alive) {
-      // Let loads already issued for this item land before shared memory is released.
-      for (int s2 = 0; s2 < kRpaStages; ++s2)
-        mbar_wait_bounded(smem_u32(&bars[s2]), (phase_bits >> s2) & 1u, 100000000ll);
-      break;
-    }
+    if (!alive) break;
 
     // ---- finish the item: row sums across the quad, then output or partial
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
-    if (n_chunks == 1) {
+    if (cur.n_chunks == 1) {
       const float inv0 = 1.f / l_run[0], inv1 = 1.f / l_run[1];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
@@ -459,8 +536,8 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
         }
       }
     } else {
-      float* po = p.part_o + static_cast<size_t>(item) * p.group * 128;
-      float* pml = p.part_ml + static_cast<size_t>(item) * p.group * 2;
+      float* po = p.part_o + static_cast<size_t>(cur.id) * p.group * 128;
+      float* pml = p.part_ml + static_cast<size_t>(cur.id) * p.group * 2;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int d = i * 8 + quad * 2;
@@ -471,34 +548,83 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
         if (row0 < p.group) *reinterpret_cast<float2*>(pml + row0 * 2) = make_float2(m_run[0], l_run[0]);
         if (row1 < p.group) *reinterpret_cast<float2*>(pml + row1 * 2) = make_float2(m_run[1], l_run[1]);
       }
+      // Publish the partial; the warp that publishes the last chunk of this (sequence, KV head)
+      // merges all of them, always in chunk order, so the result does not depend on who merges.
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) {
+        __threadfence();  // cumulative over the other lanes' stores, ordered before it by the warp sync
+        last = atomicAdd(p.arrive + s * p.kv_heads + h, 1) == cur.n_chunks - 1;
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
+        __threadfence();
+        const size_t first_item = static_cast<size_t>(cur.id / p.kv_heads - tok0 / p.chunk_tokens) * p.kv_heads + h;
+        const int n = cur.n_chunks;
+        for (int r = 0; r < p.group; ++r) {
+          // Lane c reads chunk c's (m, l); the running maximum and the sum come from shuffles.
+          float m = kNegBig;
+          for (int c0 = 0; c0 < n; c0 += 32) {
+            const int c = c0 + lane;
+            if (c < n) m = fmaxf(m, __ldcg(p.part_ml + ((first_item + static_cast<size_t>(c) * p.kv_heads) * p.group + r) * 2));
+          }
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+          float l = 0.f;
+          float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int c0 = 0; c0 < n; c0 += 32) {
+            const int c = c0 + lane;
+            float w = 0.f;
+            if (c < n) {
+              const float2 ml = __ldcg(reinterpret_cast<const float2*>(
+                  p.part_ml + ((first_item + static_cast<size_t>(c) * p.kv_heads) * p.group + r) * 2));
+              w = exp2f(ml.x - m);
+              l += ml.y * w;
+            }
+            const int cnt = min(32, n - c0);
+#pragma unroll 4
+            for (int jj = 0; jj < cnt; ++jj) {  // fixed chunk order; independent loads pipeline
+              const float wj = __shfl_sync(0xffffffffu, w, jj);
+              const size_t row = (first_item + static_cast<size_t>(c0 + jj) * p.kv_heads) * p.group + r;
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + row * 128) + lane);
+              o.x += v.x * wj;
+              o.y += v.y * wj;
+              o.z += v.z * wj;
+              o.w += v.w * wj;
+            }
+          }
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+          const float inv = 1.f / l;
+          if (lane * 4 < p.head_dim) {
+            uint2 packed;
+            packed.x = pack_bf16(o.x * inv, o.y * inv);
+            packed.y = pack_bf16(o.z * inv, o.w * inv);
+            *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(s) * p.q_heads + h * p.group + r) * p.head_dim + lane * 4) = packed;
+          }
+        }
+      }
     }
-  }
-}
 
-// One CTA per (sequence, KV head); thread d owns output column d of every query head in the group.
-__global__ void __launch_bounds__(128) cake_rpa_combine_sm100(const RpaParams p) {
-  const int s = blockIdx.x / p.kv_heads;
-  const int h = blockIdx.x - s * p.kv_heads;
-  const int base = p.item_base[s];
-  const int n_chunks = p.item_base[s + 1] - base;
-  if (n_chunks <= 1) return;
-  const int d = threadIdx.x;
-  for (int r = 0; r < p.group; ++r) {
-    float m = kNegBig;
-    for (int c = 0; c < n_chunks; ++c) {
-      const size_t item = static_cast<size_t>(base + c) * p.kv_heads + h;
-      m = fmaxf(m, p.part_ml[(item * p.group + r) * 2]);
+    // ---- next item (already claimed and partly in flight if the ring ran ahead)
+    if (!nxt_fetched) {
+      nxt_issued = 0;
+      nxt_window = -1;
+      have_nxt = rpa_fetch_item(p, total_items, lane, nxt);
     }
-    float l = 0.f, o = 0.f;
-    for (int c = 0; c < n_chunks; ++c) {
-      const size_t item = static_cast<size_t>(base + c) * p.kv_heads + h;
-      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + (item * p.group + r) * 2);
-      const float w = exp2f(ml.x - m);
-      l += ml.y * w;
-      o += p.part_o[(item * p.group + r) * 128 + d] * w;
-    }
-    if (d < p.head_dim)
-      p.out[(static_cast<size_t>(s) * p.q_heads + h * p.group + r) * p.head_dim + d] = __float2bfloat16_rn(o / l);
+    if (!have_nxt) break;
+    cur = nxt;
+    cur_issued = nxt_issued;
+    cur_window = nxt_window;
+    cur_pages = nxt_pages;
+    nxt_fetched = false;
+    have_nxt = false;
+  }
+
+  if (!alive) {
+    // A wait ran out: let loads already issued land before shared memory is released.
+    for (uint32_t pos = consume_pos; pos < issue_pos; ++pos)
+      mbar_wait_bounded(smem_u32(&bars[pos % kRpaStages]), (pos / kRpaStages) & 1u, 100000000ll);
   }
 }
 
@@ -512,7 +638,7 @@ struct cake_rpa {
   int log2_ps = 0;
   int chunk_tokens = 0;
   int64_t max_items = 0;
-  size_t off_item_base = 0, off_part_o = 0, off_part_ml = 0, ws_bytes = 0;
+  size_t off_item_base = 0, off_item_seq = 0, off_arrive = 0, off_part_o = 0, off_part_ml = 0, ws_bytes = 0;
   cake::StatusWord status;
   const void* last_c0 = nullptr;
   const void* last_c1 = nullptr;
@@ -524,6 +650,17 @@ namespace {
 using cake::fail;
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Workspace: [work counter | item_base | item_seq | arrival counters | partial (m,l) | partial o].
+void rpa_layout_workspace(cake_rpa* plan, int group) {
+  const cake_rpa_desc& d = plan->d;
+  plan->off_item_base = 256;
+  plan->off_item_seq = align_up(plan->off_item_base + sizeof(int32_t) * (d.num_seqs + 1), 256);
+  plan->off_arrive = align_up(plan->off_item_seq + sizeof(int32_t) * (plan->max_items / d.kv_heads + 1), 256);
+  plan->off_part_ml = align_up(plan->off_arrive + sizeof(int32_t) * d.num_seqs * d.kv_heads, 256);
+  plan->off_part_o = align_up(plan->off_part_ml + sizeof(float) * 2 * group * plan->max_items, 256);
+  plan->ws_bytes = plan->off_part_o + sizeof(float) * 128 * group * plan->max_items;
+}
 
 int32_t rpa_encode_maps(cake_rpa* plan, const void* c0, const void* c1) {
   const cake_rpa_desc& d = plan->d;
@@ -614,10 +751,7 @@ int32_t cake_rpa_create(const cake_rpa_desc* desc, cake_rpa** out) {
   const int64_t token_bound = table_pages * d.page_size;
   plan->max_items = (token_bound / chunk + d.num_seqs) * d.kv_heads;
   const int group = d.q_heads / d.kv_heads;
-  plan->off_item_base = 256;
-  plan->off_part_ml = align_up(plan->off_item_base + sizeof(int32_t) * (d.num_seqs + 1), 256);
-  plan->off_part_o = align_up(plan->off_part_ml + sizeof(float) * 2 * group * plan->max_items, 256);
-  plan->ws_bytes = plan->off_part_o + sizeof(float) * 128 * group * plan->max_items;
+  rpa_layout_workspace(plan, group);
   int32_t rc = plan->status.ensure();
   if (rc) {
     delete plan;
@@ -657,8 +791,8 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   if ((reinterpret_cast<uintptr_t>(cache0) | reinterpret_cast<uintptr_t>(cache1) |
        reinterpret_cast<uintptr_t>(workspace)) & 255)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: caches and workspace must be 256-byte aligned");
-  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 3)
-    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: q and out must be 4-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: q and out must be 16-byte aligned");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (cache0 != plan->last_c0 || cache1 != plan->last_c1) {
     int32_t rc = rpa_encode_maps(plan, cache0, cache1);
@@ -698,6 +832,8 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   char* ws = static_cast<char*>(workspace);
   p.work_counter = reinterpret_cast<int32_t*>(ws);
   p.item_base = reinterpret_cast<int32_t*>(ws + plan->off_item_base);
+  p.arrive = reinterpret_cast<int32_t*>(ws + plan->off_arrive);
+  p.item_seq = reinterpret_cast<int32_t*>(ws + plan->off_item_seq);
   p.part_ml = reinterpret_cast<float*>(ws + plan->off_part_ml);
   p.part_o = reinterpret_cast<float*>(ws + plan->off_part_o);
   p.max_items = static_cast<int32_t>(plan->max_items > INT32_MAX ? INT32_MAX : plan->max_items);
@@ -722,9 +858,6 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   }
   cake::cake_rpa_decode_sm100<<<plan->sm_count, cake::kRpaThreads, cake::kRpaSmemBytes, stream>>>(
       plan->tmap_k, plan->tmap_v, p);
-  CAKE_CUDA_TRY(cudaGetLastError());
-  ++launches;
-  cake::cake_rpa_combine_sm100<<<d.num_seqs * d.kv_heads, 128, 0, stream>>>(p);
   CAKE_CUDA_TRY(cudaGetLastError());
   ++launches;
   plan->launches = launches;
@@ -797,10 +930,7 @@ int32_t rpa_prepare_without_allocation(const cake_rpa_desc& d, cake_rpa* plan) {
                                   : static_cast<int64_t>(d.max_pages_per_seq);
   plan->max_items = (table_pages * d.page_size / chunk + d.num_seqs) * d.kv_heads;
   const int group = d.q_heads / d.kv_heads;
-  plan->off_item_base = 256;
-  plan->off_part_ml = align_up(plan->off_item_base + sizeof(int32_t) * (d.num_seqs + 1), 256);
-  plan->off_part_o = align_up(plan->off_part_ml + sizeof(float) * 2 * group * plan->max_items, 256);
-  plan->ws_bytes = plan->off_part_o + sizeof(float) * 128 * group * plan->max_items;
+  rpa_layout_workspace(plan, group);
   return CAKE_OK;
 }
 

@@ -52,7 +52,10 @@ class ProcessMesh:
         if self.world > 1:
             import torch.distributed as dist
 
-            dist.barrier(group=self.group, device_ids=[self.device.index])
+            if self.device.type == "cuda":
+                dist.barrier(group=self.group, device_ids=[self.device.index])
+            else:
+                dist.barrier(group=self.group)
 
     def all_gather_bytes(self, payload: bytes) -> list[bytes]:
         """Every rank contributes the same number of bytes; returns all contributions by rank."""
