@@ -75,7 +75,7 @@ def test_matmul_create_rejects_bad_descriptors(overrides, code, fragment):
     [
         ({"num_q_tokens": 9}, _native.CAKE_ERR_UNSUPPORTED, "pure decode"),
         ({"q_heads": 6, "kv_heads": 4}, _native.CAKE_ERR_INVALID_ARGUMENT, "multiple of kv_heads"),
-        ({"q_heads": 68, "kv_heads": 2}, _native.CAKE_ERR_UNSUPPORTED, "at most 16"),
+        ({"q_heads": 36, "kv_heads": 2}, _native.CAKE_ERR_UNSUPPORTED, "at most 8"),
         ({"head_dim": 256, "head_dim_padded": 256}, _native.CAKE_ERR_UNSUPPORTED, "head_dim"),
         ({"page_size": 24}, _native.CAKE_ERR_UNSUPPORTED, "page_size"),
         ({"cache_layout": 0, "head_dim": 64}, _native.CAKE_ERR_UNSUPPORTED, "head_dim 128"),

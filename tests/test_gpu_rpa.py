@@ -154,7 +154,7 @@ def expected_for(case, *, bias=None, scale=None):
         (8, 2, 16, [31, 32, 33, 511, 512, 513]),  # stage (32) and chunk (512) boundaries
         (32, 8, 16, [128, 700, 2047, 3000]),     # the decode configuration's head layout
         (64, 8, 32, [1024, 33, 1500, 2500]),     # the sharded configuration's head layout
-        (16, 1, 8, [7, 8, 9, 100]),              # 16 query heads on one KV head
+        (8, 1, 8, [7, 8, 9, 100]),               # 8 query heads on one KV head
         (8, 4, 1, [1, 2, 31, 33, 200]),          # one token per page (the reference surface's page size)
         (8, 4, 2, [3, 64, 65]),
         (8, 4, 4, [5, 127, 130]),

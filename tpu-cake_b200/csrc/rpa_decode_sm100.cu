@@ -8,20 +8,22 @@
 // inkling_fused_rpa_reference (:471-589).
 //
 // Kernels
-//   cake_rpa_plan_sm100      one CTA: per-sequence chunk counts -> exclusive prefix (work-item
-//                            table), reset of the work counter and of the arrival counters
+//   cake_rpa_plan_sm100      one CTA: cuts every sequence into chunks and builds the work-item
+//                            table (full chunks first, remainders last); resets the work counter
 //   cake_rpa_cache_update_sm100  optional: writes each sequence's new K/V at position kv_len-1
-//   cake_rpa_decode_sm100    persistent; every WARP is an independent worker with its own
-//                            3-stage shared-memory ring. A work item is (sequence, KV head,
+//   cake_rpa_decode_sm100    persistent; every WARP (6 per CTA) is an independent worker with its
+//                            own 2-stage shared-memory ring of 32-token stages. A work item is (sequence, KV head,
 //                            chunk of the KV range). Pages are gathered through the page table
 //                            with one TMA box per page (128-byte swizzle, never multicast); all
 //                            query heads of the KV head share the page (GQA: each page is read
-//                            once per KV head). QK^T and PV run on mma.sync m16n8k16 with the
-//                            query-head group padded to 16 rows; online softmax in f32 with
-//                            quad shuffles.
-//                            Split-KV partials (m, l, o) of a (sequence, KV head) are merged, in
-//                            chunk order, by whichever warp publishes the last chunk; loads run
-//                            ahead into the next work item so the ring never drains.
+//                            once per KV head). The MMAs are issued with the KV side as the
+//                            16-row operand and the query-head group (up to 8 heads) as the
+//                            8-wide operand: S^T = K Q^T and O^T = V^T P^T on mma.sync m16n8k16,
+//                            P^T obtained from the S^T accumulators with movmatrix; online softmax
+//                            in f32 with warp shuffles.
+//                            Loads run ahead into the next work item so the ring never drains.
+//   cake_rpa_combine_sm100   one warp per (sequence, KV head): merges the split-KV partials
+//                            (m, l, o) in chunk order and writes bf16.
 #include <cuda_bf16.h>
 #include <math.h>
 #include <string.h>
@@ -42,10 +44,16 @@ namespace cake {
 constexpr int kRpaWarps = CAKE_RPA_WARPS;
 constexpr int kRpaThreads = kRpaWarps * 32;
 constexpr int kRpaStages = CAKE_RPA_STAGES;
-constexpr int kStageTokens = 32;
+#ifndef CAKE_RPA_STAGE_TOKENS
+#define CAKE_RPA_STAGE_TOKENS 32
+#endif
+constexpr int kStageTokens = CAKE_RPA_STAGE_TOKENS;  // 16 or 32
+constexpr int kGroups16 = kStageTokens / 16;
+static_assert(kStageTokens == 16 || kStageTokens == 32, "stage is one or two 16-token MMA groups");
 constexpr int kRowBytes = 256;                                // one token of one head: 128 bf16
 constexpr int kStageBytes = kStageTokens * 2 * kRowBytes;     // K and V: 16 KiB
-constexpr int kRpaSmemBytes = kRpaWarps * kRpaStages * kStageBytes + 1024 + 256;
+constexpr int kQBufBytes = 8 * kRowBytes;                     // staged query rows of one work item
+constexpr int kRpaSmemBytes = kRpaWarps * (kRpaStages * kStageBytes + kQBufBytes) + 1024 + 256;
 constexpr long long kRpaBarrierBudget = 2000000000ll;
 constexpr float kNegBig = -1.0e30f;
 
@@ -57,6 +65,7 @@ struct RpaParams {
   const int32_t* cu_kv_lens;
   int32_t num_seqs, q_heads, kv_heads, group, head_dim;
   int32_t page_size, log2_ps;
+  int32_t box_tokens, log2_box;  // tokens per TMA box: min(page_size, stage tokens)
   int32_t table_layout, max_pages_per_seq, table_len;
   int32_t total_pages;
   int32_t fused;
@@ -69,9 +78,9 @@ struct RpaParams {
   const __nv_bfloat16* rel_proj;    // mode 2: [rel_dim, bias_extent]
   int32_t rel_dim;
   int32_t* work_counter;
-  int32_t* arrive;     // [num_seqs * kv_heads] chunks published per (sequence, KV head)
-  int32_t* item_base;  // [num_seqs + 1] exclusive prefix of per-sequence chunk counts
-  int32_t* item_seq;   // [sum of chunk counts] sequence of every (sequence, chunk) pair
+  int32_t* tail_cs;    // [num_seqs] queue index of the sequence's remainder chunk, -1 if none
+  int32_t* item_base;  // [num_seqs + 1] first full chunk of every sequence; [num_seqs] = total pairs
+  int4* item_desc;     // [sum of chunk counts] {sequence, first token, kv_len, first pair of the sequence}
   float* part_o;       // [max_items][group][128]
   float* part_ml;      // [max_items][group][2]
   int32_t max_items;
@@ -86,43 +95,78 @@ __device__ __forceinline__ void rpa_record(int32_t* status, int code, int d0, in
   }
 }
 
+// Builds the work-item table. Every sequence is cut into chunks of chunk_tokens; the full chunks of
+// all sequences come first in the queue and the shorter remainders last, so the kernel's tail is made
+// of small items. item_base[s] = index of the sequence's first full chunk, tail_cs[s] = index of its
+// remainder chunk (-1 if none), item_base[num_seqs] = total number of (sequence, chunk) pairs.
 __global__ void __launch_bounds__(256) cake_rpa_plan_sm100(RpaParams p) {
-  __shared__ int s_scan[256];
-  __shared__ int s_carry;
-  if (threadIdx.x == 0) {
-    s_carry = 0;
-    *p.work_counter = 0;
-    p.item_base[0] = 0;
+  __shared__ int s_full[256];
+  __shared__ int s_tail[256];
+  __shared__ int s_carry_full, s_carry_tail, s_total_full;
+  const int tid = threadIdx.x;
+  int local_full = 0;
+  for (int s = tid; s < p.num_seqs; s += 256) {
+    const int len = p.kv_lens[s];
+    if (len > 0) local_full += len / p.chunk_tokens;
+    if (len < 0) rpa_record(p.status, 4, s, len, 0);
   }
-  for (int i = threadIdx.x; i < p.num_seqs * p.kv_heads; i += blockDim.x) p.arrive[i] = 0;
+  s_full[tid] = local_full;
+  if (tid == 0) {
+    s_carry_full = 0;
+    s_carry_tail = 0;
+    *p.work_counter = 0;
+  }
   __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if (tid < off) s_full[tid] += s_full[tid + off];
+    __syncthreads();
+  }
+  if (tid == 0) s_total_full = s_full[0];
+  __syncthreads();
+  const int total_full = s_total_full;
   for (int base = 0; base < p.num_seqs; base += 256) {
-    const int s = base + threadIdx.x;
-    int chunks = 0;
+    const int s = base + tid;
+    int nf = 0, ht = 0, len = 0;
     if (s < p.num_seqs) {
-      const int len = p.kv_lens[s];
-      if (len > 0) chunks = (len + p.chunk_tokens - 1) / p.chunk_tokens;
-      if (len < 0) rpa_record(p.status, 4, s, len, 0);
+      len = p.kv_lens[s];
+      if (len > 0) {
+        nf = len / p.chunk_tokens;
+        ht = (len - nf * p.chunk_tokens) > 0 ? 1 : 0;
+      }
     }
-    s_scan[threadIdx.x] = chunks;
+    __syncthreads();
+    s_full[tid] = nf;
+    s_tail[tid] = ht;
     __syncthreads();
     for (int off = 1; off < 256; off <<= 1) {
-      int v = 0;
-      if (threadIdx.x >= off) v = s_scan[threadIdx.x - off];
+      int a = 0, b = 0;
+      if (tid >= off) {
+        a = s_full[tid - off];
+        b = s_tail[tid - off];
+      }
       __syncthreads();
-      s_scan[threadIdx.x] += v;
+      s_full[tid] += a;
+      s_tail[tid] += b;
       __syncthreads();
     }
     if (s < p.num_seqs) {
-      const int end = s_carry + s_scan[threadIdx.x];
-      p.item_base[s + 1] = end;
-      if (static_cast<long long>(end) * p.kv_heads <= p.max_items)
-        for (int c = end - chunks; c < end; ++c) p.item_seq[c] = s;
+      const int first_full = s_carry_full + s_full[tid] - nf;
+      const int tail_pos = total_full + s_carry_tail + s_tail[tid] - ht;
+      p.item_base[s] = first_full;
+      p.tail_cs[s] = ht ? tail_pos : -1;
+      if (static_cast<long long>(first_full + nf) * p.kv_heads <= p.max_items)
+        for (int c = 0; c < nf; ++c) p.item_desc[first_full + c] = make_int4(s, c * p.chunk_tokens, len, first_full);
+      if (ht && static_cast<long long>(tail_pos + 1) * p.kv_heads <= p.max_items)
+        p.item_desc[tail_pos] = make_int4(s, nf * p.chunk_tokens, len, first_full);
     }
     __syncthreads();
-    if (threadIdx.x == 255) s_carry += s_scan[255];
+    if (tid == 255) {
+      s_carry_full += s_full[255];
+      s_carry_tail += s_tail[255];
+    }
     __syncthreads();
   }
+  if (tid == 0) p.item_base[p.num_seqs] = total_full + s_carry_tail;
 }
 
 // Logical page slot -> physical page for token `tok` of sequence `s`.
@@ -200,45 +244,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Byte offset inside a stage of the 16-byte chunk `c16` (0..15) of token `t`'s K (kv=0) or V
 // (kv=1) row, including the 128-byte swizzle the TMA applied (address bits [7,10) xor into
 // [4,7); the stage base is 1024-byte aligned).
-__device__ __forceinline__ uint32_t rpa_smem_off(int t, int c16, int kv, int page_size, int log2_ps) {
-  const int pg = t >> log2_ps;
-  const int tp = t & (page_size - 1);
-  uint32_t off = static_cast<uint32_t>(pg * page_size * 512 + kv * page_size * 256 +
-                                       (c16 >> 3) * page_size * 128 + tp * 128 + (c16 & 7) * 16);
+__device__ __forceinline__ uint32_t rpa_smem_off(int t, int c16, int kv, int box_tokens, int log2_box) {
+  const int pg = t >> log2_box;
+  const int tp = t & (box_tokens - 1);
+  uint32_t off = static_cast<uint32_t>(pg * box_tokens * 512 + kv * box_tokens * 256 +
+                                       (c16 >> 3) * box_tokens * 128 + tp * 128 + (c16 & 7) * 16);
   return off ^ (((off >> 7) & 7u) << 4);
 }
 
 // One unit of work of a warp: KV tokens [tok0, tok0 + ntok) of one (sequence, KV head).
 struct RpaItem {
-  int id, s, h, n_chunks, len, tok0;
+  int id, s, h, len, tok0, first_cs;  // first_cs: index of the sequence's first (sequence, chunk) pair
 };
-
-// Claims the next work item from the global queue and decodes it (warp-uniform). Returns false
-// when the queue is exhausted.
-__device__ __forceinline__ bool rpa_fetch_item(const RpaParams& p, int total_items, int lane,
-                                               RpaItem& it) {
-  int id = 0;
-  if (lane == 0) id = atomicAdd(p.work_counter, 1);
-  id = __shfl_sync(0xffffffffu, id, 0);
-  if (id >= total_items) return false;
-  if (id >= p.max_items) {
-    if (lane == 0) rpa_record(p.status, 4, id, p.max_items, 1);
-    return false;
-  }
-  const int cs = id / p.kv_heads;
-  const int lo = p.item_seq[cs];
-  const int base = p.item_base[lo];
-  it.id = id;
-  it.s = lo;
-  it.h = id - cs * p.kv_heads;
-  it.n_chunks = p.item_base[lo + 1] - base;
-  it.len = p.kv_lens[lo];
-  it.tok0 = (cs - base) * p.chunk_tokens;
-  return true;
-}
 
 __device__ __forceinline__ int rpa_item_tokens(const RpaParams& p, const RpaItem& it) {
   return min(p.chunk_tokens, it.len - it.tok0);
+}
+
+__device__ __forceinline__ int rpa_item_chunks(const RpaParams& p, const RpaItem& it) {
+  return (it.len + p.chunk_tokens - 1) / p.chunk_tokens;
 }
 
 // Issues the TMA loads of stage `st` of item `it` into the ring slot at `stage_smem`: one box per
@@ -250,11 +274,12 @@ __device__ __forceinline__ void rpa_issue_stage(const RpaParams& p, const CUtens
                                                 uint32_t stage_smem, uint32_t bar, int lane,
                                                 int& window, int& window_pages) {
   const int ps = p.page_size;
-  const int pages_per_stage = kStageTokens >> p.log2_ps;
+  const int tb = p.box_tokens;                       // one box = tb tokens of one page
+  const int boxes_per_stage = kStageTokens >> p.log2_box;
   const int ntok = rpa_item_tokens(p, it);
   const int rem = ntok - st * kStageTokens;
-  const int npages = min(pages_per_stage, (rem + ps - 1) >> p.log2_ps);
-  const int first = st * pages_per_stage;  // first page of the stage, relative to the item
+  const int nboxes = min(boxes_per_stage, (rem + tb - 1) >> p.log2_box);
+  const int first = (st * kStageTokens) >> p.log2_ps;  // first page of the stage, relative to the item
   if ((first >> 5) != window) {
     window = first >> 5;
     const int rel = window * 32 + lane;
@@ -269,16 +294,71 @@ __device__ __forceinline__ void rpa_issue_stage(const RpaParams& p, const CUtens
     }
     window_pages = page;
   }
-  const int page = __shfl_sync(0xffffffffu, window_pages, (first + lane) & 31);
-  if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(npages * ps * 512));
+  // Box `lane` of the stage: with pages no larger than a stage it is page first + lane; with larger
+  // pages the stage is a single box somewhere inside page `first`.
+  const int tok_in_item = st * kStageTokens + lane * tb;
+  const int page = __shfl_sync(0xffffffffu, window_pages, (tok_in_item >> p.log2_ps) & 31);
+  const int tok_off = tok_in_item & (ps - 1);
+  if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(nboxes * tb * 512));
   __syncwarp();
-  if (lane < npages) {
-    const uint32_t dst = stage_smem + lane * ps * 512;
+  if (lane < nboxes) {
+    const uint32_t dst = stage_smem + lane * tb * 512;
     if (p.fused) {
-      tma_load_5d(dst, tmap_k, bar, 0, 0, 0, 2 * it.h, page);
+      tma_load_5d(dst, tmap_k, bar, 0, tok_off, 0, 2 * it.h, page);
     } else {
-      tma_load_5d(dst, tmap_k, bar, 0, 0, 0, it.h, page);
-      tma_load_5d(dst + ps * 256, tmap_v, bar, 0, 0, 0, it.h, page);
+      tma_load_5d(dst, tmap_k, bar, 0, tok_off, 0, it.h, page);
+      tma_load_5d(dst + tb * 256, tmap_v, bar, 0, tok_off, 0, it.h, page);
+    }
+  }
+}
+
+// Merges the split-KV partials of one (sequence, KV head) in chunk order and writes bf16 output.
+// Lane c reads chunk c's (m, l).
+__device__ __forceinline__ void rpa_merge(const RpaParams& p, int s, int h, int n, int first_full, int tail, int lane) {
+  const int n_full = n - (tail >= 0 ? 1 : 0);
+  // Partial row of chunk c and query row r: chunk c is the c-th full chunk or the remainder.
+  auto row_of = [&](int c, int r) {
+    const size_t cs = c < n_full ? static_cast<size_t>(first_full + c) : static_cast<size_t>(tail);
+    return (cs * p.kv_heads + h) * p.group + r;
+  };
+  for (int r = 0; r < p.group; ++r) {
+    float m = kNegBig;
+    for (int c0 = 0; c0 < n; c0 += 32) {
+      const int c = c0 + lane;
+      if (c < n) m = fmaxf(m, __ldcg(p.part_ml + row_of(c, r) * 2));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float l = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = 0; c0 < n; c0 += 32) {
+      const int c = c0 + lane;
+      float w = 0.f;
+      if (c < n) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + row_of(c, r) * 2));
+        w = exp2f(ml.x - m);
+        l += ml.y * w;
+      }
+      const int cnt = min(32, n - c0);
+#pragma unroll 4
+      for (int jj = 0; jj < cnt; ++jj) {  // fixed chunk order; the loads are independent and pipeline
+        const float wj = __shfl_sync(0xffffffffu, w, jj);
+        const size_t row = row_of(c0 + jj, r);
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + row * 128) + lane);
+        o.x += v.x * wj;
+        o.y += v.y * wj;
+        o.z += v.z * wj;
+        o.w += v.w * wj;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    const float inv = 1.f / l;
+    if (lane * 4 < p.head_dim) {
+      uint2 packed;
+      packed.x = pack_bf16(o.x * inv, o.y * inv);
+      packed.y = pack_bf16(o.z * inv, o.w * inv);
+      *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(s) * p.q_heads + h * p.group + r) * p.head_dim + lane * 4) = packed;
     }
   }
 }
@@ -292,7 +372,8 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   uint8_t* ring = smem + warp * kRpaStages * kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRpaWarps * kRpaStages * kStageBytes) +
+  uint8_t* qbuf = smem + kRpaWarps * kRpaStages * kStageBytes + warp * kQBufBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRpaWarps * (kRpaStages * kStageBytes + kQBufBytes)) +
                    warp * kRpaStages;
   if (lane == 0) {
     for (int s = 0; s < kRpaStages; ++s) mbar_init(smem_u32(&bars[s]), 1);
@@ -302,47 +383,118 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
       prefetch_tensormap(&tmap_v);
     }
   }
+  // The query staging buffer holds 8 rows x 128 bf16; rows beyond the group and columns beyond
+  // head_dim are never written again, so they stay zero.
+  for (int i = lane; i < kQBufBytes / 16; i += 32)
+    *reinterpret_cast<uint4*>(qbuf + i * 16) = make_uint4(0u, 0u, 0u, 0u);
   __syncwarp();
 
-  const int ps = p.page_size;
   const int total_items = p.item_base[p.num_seqs] * p.kv_heads;
-  const int row0 = lane >> 2;
-  const int row1 = row0 + 8;
-  const int quad = lane & 3;
+  const int trow = lane >> 2;        // token (QK^T) or head-dim row (PV) this thread holds, +8 for c2/c3
+  const int qrow = (lane & 3) * 2;   // query rows qrow, qrow + 1 of the accumulator fragments
+
+  // Per-lane pieces of the ldmatrix addresses (stage-relative), fixed for the whole kernel. With
+  // boxes of at least 8 tokens the 128-byte swizzle reduces to xor-ing the 16-byte chunk index
+  // with (token & 7) == (lane & 7).
+  const bool fast_addr = p.box_tokens >= 8;
+  const int tb = p.box_tokens;
+  const int tok_k = (lane & 7) + ((lane >> 3) & 1) * 8;  // K fragments: matrices (tok 0-7 | 8-15) x (chunk c | c+1)
+  const int tok_v = (lane & 7) + (lane >> 4) * 8;        // V fragments: matrices (tok 0-7) x (c | c+1), (tok 8-15) x (c | c+1)
+  uint32_t rowk[kGroups16], rowv[kGroups16];
+#pragma unroll
+  for (int g = 0; g < kGroups16; ++g) {
+    const int tk = g * 16 + tok_k, tv = g * 16 + tok_v;
+    rowk[g] = static_cast<uint32_t>((tk >> p.log2_box) * tb * 512 + (tk & (tb - 1)) * 128);
+    rowv[g] = static_cast<uint32_t>((tv >> p.log2_box) * tb * 512 + tb * 256 + (tv & (tb - 1)) * 128);
+  }
+  const uint32_t dhi = static_cast<uint32_t>(tb * 128);      // second 64-element half of a row
+  const uint32_t yk = static_cast<uint32_t>(((lane >> 4) ^ (lane & 7)) << 4);
+  const uint32_t yv = static_cast<uint32_t>((((lane >> 3) & 1) ^ (lane & 7)) << 4);
 
   // The warp streams stages through its ring continuously: `consume_pos` counts stages computed,
   // `issue_pos` stages whose loads were issued; loads run ahead across the boundary into the next
   // work item so the ring never drains between items.
+  //
+  // Everything that costs a round trip to L2 is split into steps taken one per stage iteration, so
+  // the round trip overlaps a stage of work instead of stalling the warp:
+  //   next-item pipeline  ni_state 0 -> 1 queue atomic issued -> 2 descriptor load issued ->
+  //                       3 item decoded, query rows being copied to smem  (4 = queue empty)
   RpaItem cur, nxt;
-  bool nxt_fetched = false, have_nxt = false;
+  int ni_state = 0, ni_raw = 0;
+  int4 ni_desc = make_int4(0, 0, 0, 0);
   int cur_issued = 0, nxt_issued = 0;
   int cur_window = -1, nxt_window = -1, cur_pages = 0, nxt_pages = 0;
   uint32_t issue_pos = 0, consume_pos = 0;
-  bool alive = rpa_fetch_item(p, total_items, lane, cur);
 
-  while (alive) {
+  auto step_next_item = [&]() {
+    if (ni_state == 0) {
+      if (lane == 0) ni_raw = atomicAdd(p.work_counter, 1);
+      ni_state = 1;
+    } else if (ni_state == 1) {
+      const int id = __shfl_sync(0xffffffffu, ni_raw, 0);
+      if (id >= total_items) {
+        ni_state = 4;
+      } else if (id >= p.max_items) {
+        if (lane == 0) rpa_record(p.status, 4, id, p.max_items, 1);
+        ni_state = 4;
+      } else {
+        nxt.id = id;
+        ni_desc = __ldg(p.item_desc + id / p.kv_heads);
+        ni_state = 2;
+      }
+    } else if (ni_state == 2) {
+      nxt.s = ni_desc.x;
+      nxt.tok0 = ni_desc.y;
+      nxt.len = ni_desc.z;
+      nxt.first_cs = ni_desc.w;
+      nxt.h = nxt.id % p.kv_heads;
+      nxt_issued = 0;
+      nxt_window = -1;
+      // Copy the item's query rows into the staging buffer (16-byte pieces, XOR-swizzled by row).
+      const int pieces = p.head_dim >> 3;
+      const __nv_bfloat16* qsrc = p.q + (static_cast<size_t>(nxt.s) * p.q_heads + nxt.h * p.group) * p.head_dim;
+      for (int i = lane; i < p.group * pieces; i += 32) {
+        const int r = i / pieces, ck = i - r * pieces;
+        const uint32_t dst = smem_u32(qbuf + r * 256 + ((ck ^ (r & 7)) << 4));
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(qsrc + r * p.head_dim + ck * 8) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      ni_state = 3;
+    }
+  };
+  while (ni_state < 3) step_next_item();  // cold start: claim and decode the first item
+  bool alive = true;
+
+  while (ni_state == 3 && alive) {
+    // ---- switch to the claimed item; its query rows are (or are about to be) in the staging buffer
+    cur = nxt;
+    cur_issued = nxt_issued;
+    cur_window = nxt_window;
+    cur_pages = nxt_pages;
+    ni_state = 0;
     const int h = cur.h, s = cur.s, len = cur.len, tok0 = cur.tok0;
     const int ntok = rpa_item_tokens(p, cur);
     const int nstages = (ntok + kStageTokens - 1) / kStageTokens;
+    const int n_chunks = rpa_item_chunks(p, cur);
 
-    // ---- query fragments (A operand, 16 x 128, rows >= group are zero)
-    uint32_t qa[8][4];
+    // ---- query fragments as the B operand: S^T[token, query row] = K[token, :] . Q[query row, :]
+    uint32_t qb[8][2];
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncwarp();
     {
-      const size_t qrow0 = (static_cast<size_t>(s) * p.q_heads + h * p.group + row0) * p.head_dim;
-      const size_t qrow1 = (static_cast<size_t>(s) * p.q_heads + h * p.group + row1) * p.head_dim;
+      const int r = lane & 7;
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const int k = ks * 16 + quad * 2;
-        qa[ks][0] = (row0 < p.group && k < p.head_dim) ? *reinterpret_cast<const uint32_t*>(p.q + qrow0 + k) : 0u;
-        qa[ks][1] = (row1 < p.group && k < p.head_dim) ? *reinterpret_cast<const uint32_t*>(p.q + qrow1 + k) : 0u;
-        qa[ks][2] = (row0 < p.group && k + 8 < p.head_dim) ? *reinterpret_cast<const uint32_t*>(p.q + qrow0 + k + 8) : 0u;
-        qa[ks][3] = (row1 < p.group && k + 8 < p.head_dim) ? *reinterpret_cast<const uint32_t*>(p.q + qrow1 + k + 8) : 0u;
+      for (int k2 = 0; k2 < 4; ++k2) {  // one x4 load covers two 16-wide k steps
+        const int ck = k2 * 4 + (lane >> 3);
+        ldmatrix_x4(smem_u32(qbuf + r * 256 + ((ck ^ r) << 4)), qb[2 * k2][0], qb[2 * k2][1], qb[2 * k2 + 1][0],
+                    qb[2 * k2 + 1][1]);
       }
     }
+    __syncwarp();
 
-    float oacc[16][4];
+    float oacc[8][4];  // O^T: tile i holds head-dim rows i*16 + trow (+8) x query rows qrow, qrow+1
 #pragma unroll
-    for (int i = 0; i < 16; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+    for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
     float m_run[2] = {kNegBig, kNegBig};
     float l_run[2] = {0.f, 0.f};
 
@@ -351,7 +503,6 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
       // (__syncwarp at the end of the previous stage) and a proxy fence orders those generic-proxy
       // reads before the async-proxy writes of the new TMA.
       fence_proxy_async_smem();
-      auto top_up = [&]() {
       while (issue_pos - consume_pos < static_cast<uint32_t>(kRpaStages)) {
         const uint32_t slot = issue_pos % kRpaStages;
         const uint32_t stage_smem = smem_u32(ring + slot * kStageBytes);
@@ -362,31 +513,19 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
           ++issue_pos;
           continue;
         }
-        if (!nxt_fetched || !have_nxt) break;
+        if (ni_state != 3) break;
         const int nxt_stages = (rpa_item_tokens(p, nxt) + kStageTokens - 1) / kStageTokens;
         if (nxt_issued >= nxt_stages) break;
         rpa_issue_stage(p, &tmap_k, &tmap_v, nxt, nxt_issued, stage_smem, bar, lane, nxt_window, nxt_pages);
         ++nxt_issued;
         ++issue_pos;
       }
-      };
-      top_up();
-      if (!nxt_fetched) {
-        // Claim the next item now: its queue and table reads overlap the wait for this stage's
-        // data, and the ring can then run ahead into it without stalling.
-        nxt_fetched = true;
-        nxt_issued = 0;
-        nxt_window = -1;
-        have_nxt = rpa_fetch_item(p, total_items, lane, nxt);
-        if (have_nxt && lane < 2 * p.group) {
-          // Pull the next item's query rows toward L2 so its fragment loads do not stall.
-          const char* qptr = reinterpret_cast<const char*>(
-              p.q + (static_cast<size_t>(nxt.s) * p.q_heads + nxt.h * p.group + (lane >> 1)) * p.head_dim);
-          if ((lane & 1) * 128 < p.head_dim * 2)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(qptr + (lane & 1) * 128));
-        }
-        top_up();  // a short item may leave room to run ahead into the one just claimed
-      }
+      // ---- one step of each bookkeeping pipeline; their memory traffic overlaps this stage
+      step_next_item();
+#ifdef CAKE_RPA_SYNC_FETCH
+      while (ni_state < 3) step_next_item();
+#endif
+
       const uint32_t slot = consume_pos % kRpaStages;
       const uint32_t parity = (consume_pos / kRpaStages) & 1u;
       const bool arrived = mbar_wait_bounded(smem_u32(&bars[slot]), parity, kRpaBarrierBudget);
@@ -397,117 +536,128 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
       }
       const uint32_t sbase = smem_u32(ring + slot * kStageBytes);
       const int valid = min(kStageTokens, ntok - st * kStageTokens);
-      const int n16 = (valid + 15) >> 4;  // 16-token groups to process (1 or 2)
+      const int n16 = (valid + 15) >> 4;  // 16-token groups to process
 
       // Zero V rows between the last valid token and the end of its 16-token group: their
       // contents are stale or uninitialised and 0 * NaN would poison the accumulator.
       if (valid < n16 * 16) {
         for (int t = valid; t < n16 * 16; ++t) {
           if (lane < 16) {
-            const uint32_t off = rpa_smem_off(t, lane, 1, ps, p.log2_ps);
+            const uint32_t off = rpa_smem_off(t, lane, 1, p.box_tokens, p.log2_box);
             asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sbase + off), "r"(0u) : "memory");
           }
         }
         __syncwarp();
       }
 
-      // ---- S = Q K^T for up to 32 tokens
-      float sacc[4][4];
+      // ---- S^T = K Q^T: per 16-token group one accumulator tile [16 tokens x 8 query rows]
+      float sacc[kGroups16][4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
-#pragma unroll
-      for (int g16 = 0; g16 < 2; ++g16) {
-        if (g16 < n16) {
-          const int t = g16 * 16 + (lane & 7) + ((lane >> 4) << 3);
+      for (int g = 0; g < kGroups16; ++g) {
+        sacc[g][0] = sacc[g][1] = sacc[g][2] = sacc[g][3] = 0.f;
+        if (g < n16) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            uint32_t b0, b1, b2, b3;
-            ldmatrix_x4(sbase + rpa_smem_off(t, ks * 2 + ((lane >> 3) & 1), 0, ps, p.log2_ps), b0, b1, b2, b3);
-            mma_bf16_16816(sacc[g16 * 2], qa[ks], b0, b1);
-            mma_bf16_16816(sacc[g16 * 2 + 1], qa[ks], b2, b3);
+            uint32_t a[4];
+            const uint32_t addr = fast_addr
+                ? sbase + rowk[g] + (ks >> 2) * dhi + ((static_cast<uint32_t>((ks & 3) * 32)) ^ yk)
+                : sbase + rpa_smem_off(g * 16 + tok_k, ks * 2 + (lane >> 4), 0, p.box_tokens, p.log2_box);
+            ldmatrix_x4(addr, a[0], a[1], a[2], a[3]);
+            mma_bf16_16816(sacc[g], a, qb[ks][0], qb[ks][1]);
           }
         }
       }
 
-      // ---- scale, bias, mask, online softmax (rows row0 and row1 of this thread)
+      // ---- scale, bias, mask (log2 domain); thread holds tokens trow, trow+8 of each group and
+      //      query rows qrow (c0, c2) and qrow+1 (c1, c3)
       const int pos_base = tok0 + st * kStageTokens;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int g = 0; g < kGroups16; ++g) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int tk = j * 8 + quad * 2 + (e & 1);
-          const int row = (e < 2) ? row0 : row1;
-          float v = sacc[j][e] * p.scale_log2;
-          const int pos = pos_base + tk;
-          if (p.bias_mode != 0 && row < p.group && tk < valid) {
-            const int head = h * p.group + row;
-            float b = 0.f;
-            if (p.bias_mode == 1) {
-              if (pos < p.bias_extent) b = p.bias[static_cast<size_t>(head) * p.bias_extent + pos];
-            } else {
-              const int dist = len - 1 - pos;
-              if (dist < p.bias_extent) {
-                const __nv_bfloat16* st_row = p.rel_states + (static_cast<size_t>(s) * p.q_heads + head) * p.rel_dim;
-                for (int r = 0; r < p.rel_dim; ++r)
-                  b += __bfloat162float(st_row[r]) *
-                       __bfloat162float(p.rel_proj[static_cast<size_t>(r) * p.bias_extent + dist]);
+          const int tk = g * 16 + trow + (e >> 1) * 8;
+          float v = sacc[g][e] * p.scale_log2;
+          if (p.bias_mode != 0) {
+            const int row = qrow + (e & 1);
+            const int pos = pos_base + tk;
+            if (row < p.group && tk < valid) {
+              const int head = h * p.group + row;
+              float b = 0.f;
+              if (p.bias_mode == 1) {
+                if (pos < p.bias_extent) b = p.bias[static_cast<size_t>(head) * p.bias_extent + pos];
+              } else {
+                const int dist = len - 1 - pos;
+                if (dist < p.bias_extent) {
+                  const __nv_bfloat16* st_row = p.rel_states + (static_cast<size_t>(s) * p.q_heads + head) * p.rel_dim;
+                  for (int r = 0; r < p.rel_dim; ++r)
+                    b += __bfloat162float(st_row[r]) *
+                         __bfloat162float(p.rel_proj[static_cast<size_t>(r) * p.bias_extent + dist]);
+                }
               }
+              v += b * 1.4426950408889634f;
             }
-            v += b * 1.4426950408889634f;
           }
-          sacc[j][e] = (tk < valid) ? v : kNegBig;
+          sacc[g][e] = (tk < valid) ? v : kNegBig;
         }
       }
+      // ---- online softmax per query row: maxima over this thread's tokens, then over the 8 lanes
+      //      that share the query-row pair (lane bits 2..4)
       float mx0 = kNegBig, mx1 = kNegBig;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        mx0 = fmaxf(mx0, fmaxf(sacc[j][0], sacc[j][1]));
-        mx1 = fmaxf(mx1, fmaxf(sacc[j][2], sacc[j][3]));
+      for (int g = 0; g < kGroups16; ++g) {
+        mx0 = fmaxf(mx0, fmaxf(sacc[g][0], sacc[g][2]));
+        mx1 = fmaxf(mx1, fmaxf(sacc[g][1], sacc[g][3]));
       }
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
       const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+      const bool rescale = (mn0 != m_run[0]) || (mn1 != m_run[1]);
       const float al0 = exp2f(m_run[0] - mn0), al1 = exp2f(m_run[1] - mn1);
       m_run[0] = mn0;
       m_run[1] = mn1;
       float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        sacc[j][0] = exp2f(sacc[j][0] - mn0);
-        sacc[j][1] = exp2f(sacc[j][1] - mn0);
-        sacc[j][2] = exp2f(sacc[j][2] - mn1);
-        sacc[j][3] = exp2f(sacc[j][3] - mn1);
-        sum0 += sacc[j][0] + sacc[j][1];
-        sum1 += sacc[j][2] + sacc[j][3];
+      for (int g = 0; g < kGroups16; ++g) {
+        sacc[g][0] = exp2f(sacc[g][0] - mn0);
+        sacc[g][1] = exp2f(sacc[g][1] - mn1);
+        sacc[g][2] = exp2f(sacc[g][2] - mn0);
+        sacc[g][3] = exp2f(sacc[g][3] - mn1);
+        sum0 += sacc[g][0] + sacc[g][2];
+        sum1 += sacc[g][1] + sacc[g][3];
       }
       l_run[0] = l_run[0] * al0 + sum0;
       l_run[1] = l_run[1] * al1 + sum1;
+      if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        oacc[i][0] *= al0;
-        oacc[i][1] *= al0;
-        oacc[i][2] *= al1;
-        oacc[i][3] *= al1;
+        for (int i = 0; i < 8; ++i) {
+          oacc[i][0] *= al0;
+          oacc[i][1] *= al1;
+          oacc[i][2] *= al0;
+          oacc[i][3] *= al1;
+        }
       }
 
-      // ---- O += P V
+      // ---- O^T += V^T P^T: P^T fragments come from the S^T accumulators through a warp-level
+      //      8x8 transpose (movmatrix)
 #pragma unroll
-      for (int g16 = 0; g16 < 2; ++g16) {
-        if (g16 < n16) {
-          uint32_t pa[4];
-          pa[0] = pack_bf16(sacc[g16 * 2][0], sacc[g16 * 2][1]);
-          pa[1] = pack_bf16(sacc[g16 * 2][2], sacc[g16 * 2][3]);
-          pa[2] = pack_bf16(sacc[g16 * 2 + 1][0], sacc[g16 * 2 + 1][1]);
-          pa[3] = pack_bf16(sacc[g16 * 2 + 1][2], sacc[g16 * 2 + 1][3]);
-          const int t = g16 * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      for (int g = 0; g < kGroups16; ++g) {
+        if (g < n16) {
+          uint32_t pb0, pb1;
+          const uint32_t lo = pack_bf16(sacc[g][0], sacc[g][1]);
+          const uint32_t hi = pack_bf16(sacc[g][2], sacc[g][3]);
+          asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(lo));
+          asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(hi));
 #pragma unroll
-          for (int nd = 0; nd < 8; ++nd) {
-            uint32_t v0, v1, v2, v3;
-            ldmatrix_x4_trans(sbase + rpa_smem_off(t, nd * 2 + (lane >> 4), 1, ps, p.log2_ps), v0, v1, v2, v3);
-            mma_bf16_16816(oacc[nd * 2], pa, v0, v1);
-            mma_bf16_16816(oacc[nd * 2 + 1], pa, v2, v3);
+          for (int dt = 0; dt < 8; ++dt) {
+            uint32_t a[4];
+            const uint32_t addr = fast_addr
+                ? sbase + rowv[g] + (dt >> 2) * dhi + ((static_cast<uint32_t>((dt & 3) * 32)) ^ yv)
+                : sbase + rpa_smem_off(g * 16 + tok_v, dt * 2 + ((lane >> 3) & 1), 1, p.box_tokens, p.log2_box);
+            ldmatrix_x4_trans(addr, a[0], a[1], a[2], a[3]);
+            mma_bf16_16816(oacc[dt], a, pb0, pb1);
           }
         }
       }
@@ -516,116 +666,70 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
     }
     if (!alive) break;
 
-    // ---- finish the item: row sums across the quad, then output or partial
-    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
-    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
-    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
-    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
-    if (cur.n_chunks == 1) {
-      const float inv0 = 1.f / l_run[0], inv1 = 1.f / l_run[1];
+    // ---- finish the item: row sums over the 8 lanes of each query-row pair, then output or partial
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int d = i * 8 + quad * 2;
-        if (d < p.head_dim) {
-          if (row0 < p.group)
-            *reinterpret_cast<uint32_t*>(p.out + (static_cast<size_t>(s) * p.q_heads + h * p.group + row0) * p.head_dim + d) =
-                pack_bf16(oacc[i][0] * inv0, oacc[i][1] * inv0);
-          if (row1 < p.group)
-            *reinterpret_cast<uint32_t*>(p.out + (static_cast<size_t>(s) * p.q_heads + h * p.group + row1) * p.head_dim + d) =
-                pack_bf16(oacc[i][2] * inv1, oacc[i][3] * inv1);
+    for (int off = 4; off < 32; off <<= 1) {
+      l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], off);
+      l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], off);
+    }
+    if (n_chunks == 1) {
+      const float inv0 = 1.f / l_run[0], inv1 = 1.f / l_run[1];
+      __nv_bfloat16* o0 = p.out + (static_cast<size_t>(s) * p.q_heads + h * p.group + qrow) * p.head_dim;
+      __nv_bfloat16* o1 = o0 + p.head_dim;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int d = i * 16 + trow;
+        if (qrow < p.group) {
+          if (d < p.head_dim) o0[d] = __float2bfloat16_rn(oacc[i][0] * inv0);
+          if (d + 8 < p.head_dim) o0[d + 8] = __float2bfloat16_rn(oacc[i][2] * inv0);
+        }
+        if (qrow + 1 < p.group) {
+          if (d < p.head_dim) o1[d] = __float2bfloat16_rn(oacc[i][1] * inv1);
+          if (d + 8 < p.head_dim) o1[d + 8] = __float2bfloat16_rn(oacc[i][3] * inv1);
         }
       }
     } else {
-      float* po = p.part_o + static_cast<size_t>(cur.id) * p.group * 128;
-      float* pml = p.part_ml + static_cast<size_t>(cur.id) * p.group * 2;
+      float* po = p.part_o + (static_cast<size_t>(cur.id) * p.group + qrow) * 128;
+      float* pml = p.part_ml + (static_cast<size_t>(cur.id) * p.group + qrow) * 2;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int d = i * 8 + quad * 2;
-        if (row0 < p.group) *reinterpret_cast<float2*>(po + row0 * 128 + d) = make_float2(oacc[i][0], oacc[i][1]);
-        if (row1 < p.group) *reinterpret_cast<float2*>(po + row1 * 128 + d) = make_float2(oacc[i][2], oacc[i][3]);
-      }
-      if (quad == 0) {
-        if (row0 < p.group) *reinterpret_cast<float2*>(pml + row0 * 2) = make_float2(m_run[0], l_run[0]);
-        if (row1 < p.group) *reinterpret_cast<float2*>(pml + row1 * 2) = make_float2(m_run[1], l_run[1]);
-      }
-      // Publish the partial; the warp that publishes the last chunk of this (sequence, KV head)
-      // merges all of them, always in chunk order, so the result does not depend on who merges.
-      __syncwarp();
-      int last = 0;
-      if (lane == 0) {
-        __threadfence();  // cumulative over the other lanes' stores, ordered before it by the warp sync
-        last = atomicAdd(p.arrive + s * p.kv_heads + h, 1) == cur.n_chunks - 1;
-      }
-      last = __shfl_sync(0xffffffffu, last, 0);
-      if (last) {
-        __threadfence();
-        const size_t first_item = static_cast<size_t>(cur.id / p.kv_heads - tok0 / p.chunk_tokens) * p.kv_heads + h;
-        const int n = cur.n_chunks;
-        for (int r = 0; r < p.group; ++r) {
-          // Lane c reads chunk c's (m, l); the running maximum and the sum come from shuffles.
-          float m = kNegBig;
-          for (int c0 = 0; c0 < n; c0 += 32) {
-            const int c = c0 + lane;
-            if (c < n) m = fmaxf(m, __ldcg(p.part_ml + ((first_item + static_cast<size_t>(c) * p.kv_heads) * p.group + r) * 2));
-          }
-#pragma unroll
-          for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-          float l = 0.f;
-          float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int c0 = 0; c0 < n; c0 += 32) {
-            const int c = c0 + lane;
-            float w = 0.f;
-            if (c < n) {
-              const float2 ml = __ldcg(reinterpret_cast<const float2*>(
-                  p.part_ml + ((first_item + static_cast<size_t>(c) * p.kv_heads) * p.group + r) * 2));
-              w = exp2f(ml.x - m);
-              l += ml.y * w;
-            }
-            const int cnt = min(32, n - c0);
-#pragma unroll 4
-            for (int jj = 0; jj < cnt; ++jj) {  // fixed chunk order; independent loads pipeline
-              const float wj = __shfl_sync(0xffffffffu, w, jj);
-              const size_t row = (first_item + static_cast<size_t>(c0 + jj) * p.kv_heads) * p.group + r;
-              const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + row * 128) + lane);
-              o.x += v.x * wj;
-              o.y += v.y * wj;
-              o.z += v.z * wj;
-              o.w += v.w * wj;
-            }
-          }
-#pragma unroll
-          for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
-          const float inv = 1.f / l;
-          if (lane * 4 < p.head_dim) {
-            uint2 packed;
-            packed.x = pack_bf16(o.x * inv, o.y * inv);
-            packed.y = pack_bf16(o.z * inv, o.w * inv);
-            *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(s) * p.q_heads + h * p.group + r) * p.head_dim + lane * 4) = packed;
-          }
+      for (int i = 0; i < 8; ++i) {
+        const int d = i * 16 + trow;
+        if (qrow < p.group) {
+          po[d] = oacc[i][0];
+          po[d + 8] = oacc[i][2];
+        }
+        if (qrow + 1 < p.group) {
+          po[128 + d] = oacc[i][1];
+          po[128 + d + 8] = oacc[i][3];
         }
       }
+      if (trow == 0) {
+        if (qrow < p.group) *reinterpret_cast<float2*>(pml) = make_float2(m_run[0], l_run[0]);
+        if (qrow + 1 < p.group) *reinterpret_cast<float2*>(pml + 2) = make_float2(m_run[1], l_run[1]);
+      }
+      // cake_rpa_combine_sm100 merges the partials of each (sequence, KV head) after this kernel.
     }
 
-    // ---- next item (already claimed and partly in flight if the ring ran ahead)
-    if (!nxt_fetched) {
-      nxt_issued = 0;
-      nxt_window = -1;
-      have_nxt = rpa_fetch_item(p, total_items, lane, nxt);
-    }
-    if (!have_nxt) break;
-    cur = nxt;
-    cur_issued = nxt_issued;
-    cur_window = nxt_window;
-    cur_pages = nxt_pages;
-    nxt_fetched = false;
-    have_nxt = false;
+    while (ni_state < 3) step_next_item();  // short items may not have finished claiming the next one
   }
 
   if (!alive) {
     // A wait ran out: let loads already issued land before shared memory is released.
+    asm volatile("cp.async.wait_all;" ::: "memory");
     for (uint32_t pos = consume_pos; pos < issue_pos; ++pos)
       mbar_wait_bounded(smem_u32(&bars[pos % kRpaStages]), (pos / kRpaStages) & 1u, 100000000ll);
   }
+}
+
+// One warp per (sequence, KV head): merges its split-KV partials in chunk order.
+__global__ void __launch_bounds__(128) cake_rpa_combine_sm100(const RpaParams p) {
+  const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (pair >= p.num_seqs * p.kv_heads) return;
+  const int s = pair / p.kv_heads;
+  const int h = pair - s * p.kv_heads;
+  const int len = p.kv_lens[s];
+  const int n = len > 0 ? (len + p.chunk_tokens - 1) / p.chunk_tokens : 0;
+  if (n > 1) rpa_merge(p, s, h, n, p.item_base[s], p.tail_cs[s], threadIdx.x & 31);
 }
 
 }  // namespace cake
@@ -638,7 +742,7 @@ struct cake_rpa {
   int log2_ps = 0;
   int chunk_tokens = 0;
   int64_t max_items = 0;
-  size_t off_item_base = 0, off_item_seq = 0, off_arrive = 0, off_part_o = 0, off_part_ml = 0, ws_bytes = 0;
+  size_t off_item_base = 0, off_item_desc = 0, off_tail = 0, off_part_o = 0, off_part_ml = 0, ws_bytes = 0;
   cake::StatusWord status;
   const void* last_c0 = nullptr;
   const void* last_c1 = nullptr;
@@ -651,13 +755,13 @@ using cake::fail;
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Workspace: [work counter | item_base | item_seq | arrival counters | partial (m,l) | partial o].
+// Workspace: [work counter | item_base | item_desc | tail_cs | partial (m,l) | partial o].
 void rpa_layout_workspace(cake_rpa* plan, int group) {
   const cake_rpa_desc& d = plan->d;
   plan->off_item_base = 256;
-  plan->off_item_seq = align_up(plan->off_item_base + sizeof(int32_t) * (d.num_seqs + 1), 256);
-  plan->off_arrive = align_up(plan->off_item_seq + sizeof(int32_t) * (plan->max_items / d.kv_heads + 1), 256);
-  plan->off_part_ml = align_up(plan->off_arrive + sizeof(int32_t) * d.num_seqs * d.kv_heads, 256);
+  plan->off_item_desc = align_up(plan->off_item_base + sizeof(int32_t) * (d.num_seqs + 1), 256);
+  plan->off_tail = align_up(plan->off_item_desc + 16 * (plan->max_items / d.kv_heads + 1), 256);
+  plan->off_part_ml = align_up(plan->off_tail + sizeof(int32_t) * d.num_seqs, 256);
   plan->off_part_o = align_up(plan->off_part_ml + sizeof(float) * 2 * group * plan->max_items, 256);
   plan->ws_bytes = plan->off_part_o + sizeof(float) * 128 * group * plan->max_items;
 }
@@ -665,11 +769,12 @@ void rpa_layout_workspace(cake_rpa* plan, int group) {
 int32_t rpa_encode_maps(cake_rpa* plan, const void* c0, const void* c1) {
   const cake_rpa_desc& d = plan->d;
   const uint64_t ps = d.page_size;
+  const uint32_t tb = static_cast<uint32_t>(d.page_size < cake::kStageTokens ? d.page_size : cake::kStageTokens);
   if (d.cache_layout == CAKE_RPA_CACHE_FUSED) {
     const uint64_t heads2 = 2ull * d.kv_heads;
     const uint64_t dims[5] = {64, ps, 2, heads2, static_cast<uint64_t>(d.total_pages)};
     const uint64_t strides[4] = {heads2 * 256, 128, 256, ps * heads2 * 256};
-    const uint32_t box[5] = {64, static_cast<uint32_t>(ps), 2, 2, 1};
+    const uint32_t box[5] = {64, tb, 2, 2, 1};
     int32_t rc = cake::encode_tensor_map(&plan->tmap_k, c0, 5, dims, strides, box, true);
     if (rc) return rc;
     plan->tmap_v = plan->tmap_k;
@@ -678,7 +783,7 @@ int32_t rpa_encode_maps(cake_rpa* plan, const void* c0, const void* c1) {
   const uint64_t hk = d.kv_heads;
   const uint64_t dims[5] = {64, ps, 2, hk, static_cast<uint64_t>(d.total_pages)};
   const uint64_t strides[4] = {hk * 256, 128, 256, ps * hk * 256};
-  const uint32_t box[5] = {64, static_cast<uint32_t>(ps), 2, 1, 1};
+  const uint32_t box[5] = {64, tb, 2, 1, 1};
   int32_t rc = cake::encode_tensor_map(&plan->tmap_k, c0, 5, dims, strides, box, true);
   if (rc) return rc;
   return cake::encode_tensor_map(&plan->tmap_v, c1, 5, dims, strides, box, true);
@@ -697,8 +802,8 @@ int32_t cake_rpa_create(const cake_rpa_desc* desc, cake_rpa** out) {
                 d.num_q_tokens, d.num_seqs);
   if (d.q_heads % d.kv_heads != 0)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: q_heads %d must be a multiple of kv_heads %d", d.q_heads, d.kv_heads);
-  if (d.q_heads / d.kv_heads > 16)
-    return fail(CAKE_ERR_UNSUPPORTED, "rpa: at most 16 query heads per KV head, got %d", d.q_heads / d.kv_heads);
+  if (d.q_heads / d.kv_heads > 8)
+    return fail(CAKE_ERR_UNSUPPORTED, "rpa: at most 8 query heads per KV head, got %d", d.q_heads / d.kv_heads);
   if (d.head_dim <= 0 || d.head_dim > 128 || d.head_dim % 8 != 0)
     return fail(CAKE_ERR_UNSUPPORTED, "rpa: head_dim must be a multiple of 8 up to 128, got %d", d.head_dim);
   if (d.cache_layout == CAKE_RPA_CACHE_FUSED) {
@@ -814,6 +919,8 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   p.head_dim = d.head_dim;
   p.page_size = d.page_size;
   p.log2_ps = plan->log2_ps;
+  p.box_tokens = d.page_size < cake::kStageTokens ? d.page_size : cake::kStageTokens;
+  p.log2_box = plan->log2_ps < (cake::kStageTokens == 16 ? 4 : 5) ? plan->log2_ps : (cake::kStageTokens == 16 ? 4 : 5);
   p.table_layout = d.table_layout;
   p.max_pages_per_seq = d.max_pages_per_seq;
   p.table_len = d.max_pages_per_seq;
@@ -832,8 +939,8 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   char* ws = static_cast<char*>(workspace);
   p.work_counter = reinterpret_cast<int32_t*>(ws);
   p.item_base = reinterpret_cast<int32_t*>(ws + plan->off_item_base);
-  p.arrive = reinterpret_cast<int32_t*>(ws + plan->off_arrive);
-  p.item_seq = reinterpret_cast<int32_t*>(ws + plan->off_item_seq);
+  p.tail_cs = reinterpret_cast<int32_t*>(ws + plan->off_tail);
+  p.item_desc = reinterpret_cast<int4*>(ws + plan->off_item_desc);
   p.part_ml = reinterpret_cast<float*>(ws + plan->off_part_ml);
   p.part_o = reinterpret_cast<float*>(ws + plan->off_part_o);
   p.max_items = static_cast<int32_t>(plan->max_items > INT32_MAX ? INT32_MAX : plan->max_items);
@@ -858,6 +965,9 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   }
   cake::cake_rpa_decode_sm100<<<plan->sm_count, cake::kRpaThreads, cake::kRpaSmemBytes, stream>>>(
       plan->tmap_k, plan->tmap_v, p);
+  CAKE_CUDA_TRY(cudaGetLastError());
+  ++launches;
+  cake::cake_rpa_combine_sm100<<<(d.num_seqs * d.kv_heads + 3) / 4, 128, 0, stream>>>(p);
   CAKE_CUDA_TRY(cudaGetLastError());
   ++launches;
   plan->launches = launches;
@@ -904,8 +1014,8 @@ int32_t rpa_prepare_without_allocation(const cake_rpa_desc& d, cake_rpa* plan) {
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa (static scratch): num_seqs, q_heads, kv_heads, total_pages out of range");
   if (d.num_q_tokens != d.num_seqs)
     return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): only pure decode is lowered");
-  if (d.q_heads % d.kv_heads != 0 || d.q_heads / d.kv_heads > 16)
-    return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): q_heads must be 1..16 times kv_heads");
+  if (d.q_heads % d.kv_heads != 0 || d.q_heads / d.kv_heads > 8)
+    return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): q_heads must be 1..8 times kv_heads");
   if (d.head_dim <= 0 || d.head_dim > 128 || d.head_dim % 8 != 0)
     return fail(CAKE_ERR_UNSUPPORTED, "rpa (static scratch): head_dim must be a multiple of 8 up to 128");
   if (d.cache_layout == CAKE_RPA_CACHE_FUSED ? d.head_dim_padded != 128
