@@ -30,6 +30,11 @@ int32_t fail(int32_t code, const char* fmt, ...);
 int32_t encode_tensor_map(CUtensorMap* out, const void* base, uint32_t rank, const uint64_t* dims,
                           const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
 
+// Same, with the element size given: 2 = bfloat16, 4 = float32.
+int32_t encode_tensor_map_typed(CUtensorMap* out, const void* base, uint32_t rank, const uint64_t* dims,
+                                const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128,
+                                int elem_bytes);
+
 // Device status word helpers (4 x int32 in device memory).
 struct StatusWord {
   int32_t* dev = nullptr;

@@ -35,6 +35,12 @@ static EncodeTiledFn resolve_encoder() {
 
 int32_t encode_tensor_map(CUtensorMap* out, const void* base, uint32_t rank, const uint64_t* dims,
                           const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+  return encode_tensor_map_typed(out, base, rank, dims, strides_bytes, box, swizzle128, 2);
+}
+
+int32_t encode_tensor_map_typed(CUtensorMap* out, const void* base, uint32_t rank, const uint64_t* dims,
+                                const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128,
+                                int elem_bytes) {
   EncodeTiledFn fn = resolve_encoder();
   if (!fn) return fail(CAKE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t gdims[5];
@@ -47,7 +53,7 @@ int32_t encode_tensor_map(CUtensorMap* out, const void* base, uint32_t rank, con
     estr[i] = 1;
     if (i + 1 < rank) gstrides[i] = strides_bytes[i];
   }
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdims,
+  CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdims,
                   gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -30,7 +30,7 @@ constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 constexpr uint32_t kABytes = kTileM * kBlockK * 2;
-constexpr uint32_t kStagingBytesPerWarp = 32 * 128;
+constexpr uint32_t kStagingBytesPerWarp = 2 * 32 * 128;  // two 32-row x 128-byte chunks per epilogue warp
 constexpr long long kBarrierBudgetCycles = 4000000000ll;  // about two seconds of SM clock
 constexpr unsigned long long kPeerBudgetNs = 20000000000ull;  // 20 s
 
@@ -52,6 +52,7 @@ struct MatmulParams {
   int32_t store_f32;           // destination element type: 1 = f32, 0 = bf16
   int32_t vec_ok;              // 16-byte pieces never straddle owners or bounds
   int32_t count_arrivals;      // peer-to-peer strategy: signal the owner's counter per tile
+  int32_t tma_store;           // epilogue chunks leave shared memory as TMA tensor stores
   int32_t region_order;        // visit owner regions starting at rank+1 (own region last)
   void* dest[CAKE_MAX_WORLD];  // per-owner base of the [out_rows, out_cols] destination
   unsigned long long* arrive[CAKE_MAX_WORLD];  // per-owner counter written by this rank
@@ -135,10 +136,17 @@ __device__ __forceinline__ char* dest_addr(const MatmulParams& p, int r, int c, 
          (static_cast<size_t>(lr) * p.out_cols + lc) * static_cast<size_t>(elem_bytes);
 }
 
+// One tensor map per owner: its [out_rows, out_cols] destination (own output, owner-major partial or
+// a peer's receive slot), boxes of 32 rows x 128 bytes, 128-byte swizzle.
+struct OwnerMaps {
+  CUtensorMap m[CAKE_MAX_WORLD];
+};
+
 template <int BN, bool B_KMAJOR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     cake_matmul_rs_sm100(const __grid_constant__ CUtensorMap tmap_a,
-                         const __grid_constant__ CUtensorMap tmap_b, const MatmulParams p) {
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ OwnerMaps owner_maps, const MatmulParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
 
@@ -283,7 +291,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else {
     // ------------------------------------------------------------------ epilogue warps 2..5
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    uint8_t* my_stage = staging + (warp - 2) * kStagingBytesPerWarp;
+    uint8_t* my_stage_base = staging + (warp - 2) * kStagingBytesPerWarp;
+    int chunk_count = 0;  // chunks this warp has staged so far (selects the staging half)
     const int elem_bytes = p.store_f32 ? 4 : 2;
     const int cols_per_chunk = p.store_f32 ? 32 : 64;  // 128 bytes per row per chunk
     const int epp = 16 / elem_bytes;                   // elements per 16-byte piece
@@ -339,10 +348,42 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&tmem_empty[buf]));
         }
-        // Transpose through swizzled smem so that global stores are 128-byte row segments.
+        // Transpose through swizzled smem (the layout of a 128-byte-swizzled TMA box) so that the
+        // chunk leaves as 128-byte row segments.
+        uint8_t* my_stage = my_stage_base + (chunk_count & 1) * (32 * 128);
+        if (p.tma_store && chunk_count >= 2) {
+          // The staging half is reused every second chunk: its previous store must have read it.
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+        }
+        ++chunk_count;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = pieces[j];
+        }
+        if (p.tma_store) {
+          fence_proxy_async_smem();  // generic-proxy writes above -> visible to the TMA engine
+          __syncwarp();
+          const int r = row0;
+          const int c = nt * BN + ch * cols_per_chunk;
+          if (lane == 0 && r < p.m && c < p.n) {
+            int owner, lr, lc;
+            if (p.scatter_dim == 0) {
+              owner = r / p.out_rows;
+              lr = r - owner * p.out_rows;
+              lc = c;
+            } else {
+              owner = c / p.out_cols;
+              lr = r;
+              lc = c - owner * p.out_cols;
+            }
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&owner_maps.m[owner])), "r"(smem_u32(my_stage)),
+                         "r"(lc), "r"(lr)
+                         : "memory");
+          }
+          if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          continue;
         }
         __syncwarp();
         const int pj = lane & 7;
@@ -376,6 +417,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // given up on a wait can never leave the others stuck at one.
         __syncwarp();
         if (lane == 0) {
+          if (p.tma_store) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores performed
           __threadfence_system();
           const int r_lo = row0, r_hi = min(row0 + 32, p.m);
           const int c_lo = nt * BN, c_hi = min(c_lo + BN, p.n);
@@ -399,6 +441,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
 
+  // Shared memory must outlive every tensor store that still reads it.
+  if (p.tma_store && warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
@@ -517,6 +561,8 @@ struct cake_matmul_rs {
   const void* last_lhs = nullptr;
   const void* last_rhs = nullptr;
   CUtensorMap tmap_a, tmap_b;
+  cake::OwnerMaps owner_maps[2];  // per slot parity (index 0 also serves the non-peer modes)
+  const void* owner_maps_base[2] = {nullptr, nullptr};
   // staging for run_host
   void* h_lhs = nullptr;
   void* h_rhs = nullptr;
@@ -530,7 +576,7 @@ using cake::fail;
 
 template <int BN, bool KM>
 int32_t launch_gemm(const cake_matmul_rs* plan, const cake::MatmulParams& p, int grid,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, int maps_index) {
   auto kernel = cake::cake_matmul_rs_sm100<BN, KM>;
   static bool configured = false;
   if (!configured) {
@@ -538,8 +584,8 @@ int32_t launch_gemm(const cake_matmul_rs* plan, const cake::MatmulParams& p, int
                                        cake::GemmCfg<BN>::kSmemBytes));
     configured = true;
   }
-  kernel<<<grid, cake::kGemmThreads, cake::GemmCfg<BN>::kSmemBytes, stream>>>(plan->tmap_a,
-                                                                              plan->tmap_b, p);
+  kernel<<<grid, cake::kGemmThreads, cake::GemmCfg<BN>::kSmemBytes, stream>>>(
+      plan->tmap_a, plan->tmap_b, plan->owner_maps[maps_index], p);
   CAKE_CUDA_TRY(cudaGetLastError());
   return CAKE_OK;
 }
@@ -748,6 +794,23 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
       p.arrive[o] = static_cast<unsigned long long*>(plan->flags[o]) + d.rank;
     }
   }
+  // Tensor stores need 16-byte row pitch, and chunks (32 rows x 128 bytes) that never straddle owners.
+  const int chunk_cols = 128 / (int)plan->tsize;
+  const bool tma_ok = (plan->out_cols * plan->tsize) % 16 == 0 &&
+                      (d.world == 1 || (d.scatter_dim == 0 ? plan->out_rows % 32 == 0 : plan->out_cols % chunk_cols == 0));
+  const int maps_index = p2p ? (int)parity : 0;
+  p.tma_store = tma_ok ? 1 : 0;
+  if (tma_ok && plan->owner_maps_base[maps_index] != p.dest[0]) {
+    for (int o = 0; o < d.world; ++o) {
+      const uint64_t dims[2] = {static_cast<uint64_t>(plan->out_cols), static_cast<uint64_t>(plan->out_rows)};
+      const uint64_t strides[1] = {static_cast<uint64_t>(plan->out_cols) * plan->tsize};
+      const uint32_t box[2] = {static_cast<uint32_t>(chunk_cols), 32};
+      int32_t mrc = cake::encode_tensor_map_typed(&plan->owner_maps[maps_index].m[o], p.dest[o], 2, dims, strides, box, true,
+                                                  plan->tsize == 4 ? 4 : 2);
+      if (mrc) return mrc;
+    }
+    plan->owner_maps_base[maps_index] = p.dest[0];
+  }
   if (d.world > 1) {
     const bool aligned = d.scatter_dim == 0 ? (plan->out_rows % cake::kTileM == 0)
                                             : (plan->out_cols % d.tile_n == 0);
@@ -757,9 +820,9 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
   const int grid = num_tiles < plan->sm_count ? num_tiles : plan->sm_count;
   const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
   int32_t rc;
-  if (d.tile_n == 256) rc = kmajor ? launch_gemm<256, true>(plan, p, grid, stream) : launch_gemm<256, false>(plan, p, grid, stream);
-  else if (d.tile_n == 128) rc = kmajor ? launch_gemm<128, true>(plan, p, grid, stream) : launch_gemm<128, false>(plan, p, grid, stream);
-  else rc = kmajor ? launch_gemm<64, true>(plan, p, grid, stream) : launch_gemm<64, false>(plan, p, grid, stream);
+  if (d.tile_n == 256) rc = kmajor ? launch_gemm<256, true>(plan, p, grid, stream, maps_index) : launch_gemm<256, false>(plan, p, grid, stream, maps_index);
+  else if (d.tile_n == 128) rc = kmajor ? launch_gemm<128, true>(plan, p, grid, stream, maps_index) : launch_gemm<128, false>(plan, p, grid, stream, maps_index);
+  else rc = kmajor ? launch_gemm<64, true>(plan, p, grid, stream, maps_index) : launch_gemm<64, false>(plan, p, grid, stream, maps_index);
   if (rc) return rc;
   ++launches;
   }  // push phase
