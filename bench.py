@@ -251,6 +251,38 @@ def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
         "kernel": "cake_matmul_rs_sm100<256>", "kernel_ms": kernel_ms,
     }
 
+    # How much of the step is communication that the contraction does not hide: the same kernel,
+    # tiles and transport dtype with the partial left in local memory ("pushes disabled"), and the
+    # two halves of the peer-to-peer step timed separately.
+    phases = None
+    if world > 1 and strategy is not cuda_lowering.MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER:
+        twin = cuda_lowering.MatmulRsExecutable(plan, mesh, contraction_only=True)
+        only_ms, _ = timed_steps(mesh, lambda: twin(lhs, rhs), args.steps, 3, flush)
+        twin.close()
+        push_ms, reduce_ms = 0.0, 0.0
+        mesh.barrier()
+        for _ in range(args.steps):
+            flush()
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            e0.record()
+            executable.push(lhs, rhs)
+            e1.record()
+            executable.reduce(out)
+            e2.record()
+            torch.cuda.synchronize(mesh.device)
+            push_ms += e0.elapsed_time(e1)
+            reduce_ms += e1.elapsed_time(e2)
+        mesh.barrier()
+        executable.status()
+        only_ms /= args.steps
+        phases = {
+            "contraction_only_ms": only_ms,
+            "push_kernel_ms": reduce_max(mesh, push_ms / args.steps),
+            "reduce_kernel_ms": reduce_max(mesh, reduce_ms / args.steps),
+            "exposed_communication": max(0.0, (ms_per_step - only_ms) / ms_per_step),
+            "link_egress_bytes_per_gpu": plan.collective_resources.remote_payload_bytes,
+        }
+
     # End to end through the C ABI with host buffers (pinned): H2D of both operands, the kernels,
     # D2H of the local output, inside the timed region.
     e2e = None
@@ -280,7 +312,7 @@ def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
     torch.cuda.empty_cache()
     return {
         "value": value, "ms_per_step": ms_per_step, "roofline": roofline, "e2e": e2e, "clocks": clocks,
-        "gpu_launches": launches, "strategy": args.strategy if world > 1 else "single",
+        "gpu_launches": launches, "strategy": args.strategy if world > 1 else "single", "phases": phases,
     }
 
 
@@ -409,6 +441,8 @@ def run_ours(args) -> None:
         },
         "roofline": matmul["roofline"], "e2e": matmul["e2e"], "gpu_launches": matmul["gpu_launches"], "clocks": matmul["clocks"],
     }
+    if matmul["phases"] is not None:
+        line["communication"] = matmul["phases"]
     if mesh.rank == 0 and mesh.world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_matmul_sample(args.cpu_rows, os.cpu_count() or 1)
     if rpa is not None:
@@ -470,6 +504,7 @@ def main() -> None:
     parser.add_argument("--strategy", choices=("p2p_bf16", "p2p_f32", "nccl"), default="p2p_bf16")
     parser.add_argument("--kv-chunk", type=int, default=0)
     parser.add_argument("--cpu-rows", type=int, default=8192)
+    parser.add_argument("--k", type=int, default=K, help="contraction extent (experiments only; the headline uses the default)")
     parser.add_argument("--no-rpa", action="store_true")
     parser.add_argument("--only-rpa", action="store_true", help="run only the attention part (profiling aid)")
     parser.add_argument("--rpa-pool-pages", type=int, default=0,
@@ -478,6 +513,7 @@ def main() -> None:
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    globals()["K"] = args.k
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -293,6 +293,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint8_t* my_stage_base = staging + (warp - 2) * kStagingBytesPerWarp;
     int chunk_count = 0;  // chunks this warp has staged so far (selects the staging half)
+    unsigned long long sent[CAKE_MAX_WORLD];  // lane 0: elements pushed to each owner so far
+#pragma unroll
+    for (int o = 0; o < CAKE_MAX_WORLD; ++o) sent[o] = 0;
     const int elem_bytes = p.store_f32 ? 4 : 2;
     const int cols_per_chunk = p.store_f32 ? 32 : 64;  // 128 bytes per row per chunk
     const int epp = 16 / elem_bytes;                   // elements per 16-byte piece
@@ -412,31 +415,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         __syncwarp();
       }
-      if (p.count_arrivals) {
-        // Each epilogue warp publishes its own 32 rows: no CTA-wide barrier, so a warp that has
-        // given up on a wait can never leave the others stuck at one.
-        __syncwarp();
-        if (lane == 0) {
-          if (p.tma_store) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores performed
-          __threadfence_system();
-          const int r_lo = row0, r_hi = min(row0 + 32, p.m);
-          const int c_lo = nt * BN, c_hi = min(c_lo + BN, p.n);
-          if (r_hi > r_lo && c_hi > c_lo) {
-            if (p.scatter_dim == 0) {
-              for (int o = r_lo / p.out_rows; o <= (r_hi - 1) / p.out_rows; ++o) {
-                const int rows = min(r_hi, (o + 1) * p.out_rows) - max(r_lo, o * p.out_rows);
-                red_release_sys_add_u64(p.arrive[o],
-                                        static_cast<unsigned long long>(rows) * (c_hi - c_lo));
-              }
-            } else {
-              for (int o = c_lo / p.out_cols; o <= (c_hi - 1) / p.out_cols; ++o) {
-                const int cols = min(c_hi, (o + 1) * p.out_cols) - max(c_lo, o * p.out_cols);
-                red_release_sys_add_u64(p.arrive[o],
-                                        static_cast<unsigned long long>(cols) * (r_hi - r_lo));
-              }
+      if (p.count_arrivals && lane == 0) {
+        // Tally what this warp has sent to each owner; the owners are told once, after the last
+        // tile (a system-scope fence per tile would stall the pushes behind a link round trip).
+        const int r_lo = row0, r_hi = min(row0 + 32, p.m);
+        const int c_lo = nt * BN, c_hi = min(c_lo + BN, p.n);
+        if (r_hi > r_lo && c_hi > c_lo) {
+          if (p.scatter_dim == 0) {
+            for (int o = r_lo / p.out_rows; o <= (r_hi - 1) / p.out_rows; ++o) {
+              const int rows = min(r_hi, (o + 1) * p.out_rows) - max(r_lo, o * p.out_rows);
+              sent[o] += static_cast<unsigned long long>(rows) * (c_hi - c_lo);
+            }
+          } else {
+            for (int o = c_lo / p.out_cols; o <= (c_hi - 1) / p.out_cols; ++o) {
+              const int cols = min(c_hi, (o + 1) * p.out_cols) - max(c_lo, o * p.out_cols);
+              sent[o] += static_cast<unsigned long long>(cols) * (r_hi - r_lo);
             }
           }
         }
+      }
+    }
+    if (p.count_arrivals) {
+      // Publish: every store of this warp has been performed (tensor stores: group complete; plain
+      // stores: ordered by the warp sync), one system-scope fence, then one release-add per owner.
+      // Each epilogue warp publishes for itself: no CTA-wide barrier, so a warp that has given up
+      // on a wait can never leave the others stuck at one.
+      __syncwarp();
+      if (lane == 0) {
+        if (p.tma_store) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        __threadfence_system();
+        for (int o = 0; o < p.world; ++o)
+          if (sent[o] != 0) red_release_sys_add_u64(p.arrive[o], sent[o]);
       }
     }
   }
@@ -447,6 +456,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tcgen05_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 // out[i] = sum over source ranks (fixed order) of slot[src][i]; waits for every source's arrival
@@ -482,8 +496,16 @@ __global__ void __launch_bounds__(256)
     float acc[V];
 #pragma unroll
     for (int e = 0; e < V; ++e) acc[e] = 0.f;
-    for (int src = 0; src < world; ++src) {
-      const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(slots + src * elems) + g);
+    // All sources' loads are issued before any is used (independent, so they overlap); the sum
+    // itself runs in rank order.
+    uint4 raw_all[CAKE_MAX_WORLD];
+#pragma unroll
+    for (int src = 0; src < CAKE_MAX_WORLD; ++src)
+      if (src < world) raw_all[src] = __ldcg(reinterpret_cast<const uint4*>(slots + src * elems) + g);
+#pragma unroll
+    for (int src = 0; src < CAKE_MAX_WORLD; ++src) {
+      if (src >= world) break;
+      const uint4 raw = raw_all[src];
       if (sizeof(TIn) == 4) {
         acc[0] += __uint_as_float(raw.x);
         acc[1] += __uint_as_float(raw.y);
@@ -498,13 +520,23 @@ __global__ void __launch_bounds__(256)
         }
       }
     }
+    if (sizeof(TOut) == 4) {
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
-      if (sizeof(TOut) == 4) {
-        reinterpret_cast<float*>(out)[g * V + e] = acc[e];
-      } else {
-        reinterpret_cast<__nv_bfloat16*>(out)[g * V + e] = __float2bfloat16_rn(acc[e]);
-      }
+      for (int e = 0; e < V; e += 4)
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + g * V + e) =
+            make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
+    } else if (V == 8) {
+      uint4 packed;
+      packed.x = pack2_bf16(acc[0], acc[1]);
+      packed.y = pack2_bf16(acc[2], acc[3]);
+      packed.z = pack2_bf16(acc[4], acc[5]);
+      packed.w = pack2_bf16(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + g * V) = packed;
+    } else {
+      uint2 packed;
+      packed.x = pack2_bf16(acc[0], acc[1]);
+      packed.y = pack2_bf16(acc[2], acc[3]);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + g * V) = packed;
     }
   }
   // Tail (elems not a multiple of V).

@@ -232,12 +232,16 @@ class MatmulRsExecutable:
     stream. Fails loudly if libcake_b200.so is not built or the GPU is not sm_100.
     """
 
-    def __init__(self, plan: CudaMatmulRsPlan, mesh: ProcessMesh):
+    def __init__(self, plan: CudaMatmulRsPlan, mesh: ProcessMesh, *, contraction_only: bool = False):
+        """``contraction_only`` builds the same contraction with the same tiles and transport dtype
+        but leaves the partial in local memory (owner-major) and runs no collective: the
+        "pushes disabled" twin used to measure how much communication time is exposed."""
         self.plan = plan
         self.mesh = mesh
         self._lib = _native.load()
         strategy = plan.collective_implementation
-        self._p2p = mesh.world > 1 and strategy is not MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER
+        self._contraction_only = contraction_only
+        self._p2p = mesh.world > 1 and strategy is not MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER and not contraction_only
         desc = _native.MatmulRsDesc(
             m=plan.partial_local_shape[0],
             n=plan.partial_local_shape[1],
@@ -272,7 +276,7 @@ class MatmulRsExecutable:
             )
         elif mesh.world > 1:
             self._partial = torch.empty(
-                (mesh.world,) + plan.output_local_shape, dtype=torch.float32, device=mesh.device
+                (mesh.world,) + plan.output_local_shape, dtype=_TORCH_DTYPE[plan.transport_dtype], device=mesh.device
             )
 
     # -- device call
@@ -289,6 +293,8 @@ class MatmulRsExecutable:
             import torch.distributed as dist
 
             _native.check(self._lib.cake_matmul_rs_enqueue(self._handle, lhs.data_ptr(), rhs.data_ptr(), self._partial.data_ptr(), stream))
+            if self._contraction_only:
+                return self._partial
             if plan.output_dtype == "f32":
                 dist.reduce_scatter_tensor(out, self._partial, group=self.mesh.group)
             else:
@@ -297,6 +303,20 @@ class MatmulRsExecutable:
                 out.copy_(reduced)
             return out
         _native.check(self._lib.cake_matmul_rs_enqueue(self._handle, lhs.data_ptr(), rhs.data_ptr(), out.data_ptr(), stream))
+        return out
+
+    # -- the two halves of a peer-to-peer call, for phase timing
+    def push(self, lhs: torch.Tensor, rhs: torch.Tensor) -> None:
+        if not self._p2p:
+            raise ValueError("push / reduce exist only for the peer-to-peer strategies")
+        stream = torch.cuda.current_stream(self.mesh.device).cuda_stream
+        _native.check(self._lib.cake_matmul_rs_enqueue_push(self._handle, lhs.data_ptr(), rhs.data_ptr(), stream))
+
+    def reduce(self, out: torch.Tensor) -> torch.Tensor:
+        if not self._p2p:
+            raise ValueError("push / reduce exist only for the peer-to-peer strategies")
+        stream = torch.cuda.current_stream(self.mesh.device).cuda_stream
+        _native.check(self._lib.cake_matmul_rs_enqueue_reduce(self._handle, out.data_ptr(), stream))
         return out
 
     # -- host call (the end-to-end path: host buffers in, host buffer out)
