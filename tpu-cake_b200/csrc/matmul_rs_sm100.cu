@@ -53,7 +53,7 @@ struct MatmulParams {
   int32_t vec_ok;              // 16-byte pieces never straddle owners or bounds
   int32_t count_arrivals;      // peer-to-peer strategy: signal the owner's counter per tile
   int32_t tma_store;           // epilogue chunks leave shared memory as TMA tensor stores
-  int32_t region_order;        // visit owner regions starting at rank+1 (own region last)
+  int32_t region_order;        // consecutive tiles go to consecutive owners, starting at rank+1
   void* dest[CAKE_MAX_WORLD];  // per-owner base of the [out_rows, out_cols] destination
   unsigned long long* arrive[CAKE_MAX_WORLD];  // per-owner counter written by this rank
   int32_t* status;
@@ -98,20 +98,18 @@ __device__ __forceinline__ void tile_coords(const MatmulParams& p, int t, int& m
   if (p.region_order) {
     if (p.scatter_dim == 0) {
       const int m_tiles_r = p.out_rows / kTileM;
-      const int per_region = m_tiles_r * p.n_tiles;
-      const int j = t / per_region;
+      const int j = t % p.world;
       const int owner = (p.rank + 1 + j) % p.world;
       int mi, ni;
-      raster(t - j * per_region, m_tiles_r, p.n_tiles, mi, ni);
+      raster(t / p.world, m_tiles_r, p.n_tiles, mi, ni);
       mt = owner * m_tiles_r + mi;
       nt = ni;
     } else {
       const int n_tiles_r = p.out_cols / BN;
-      const int per_region = p.m_tiles * n_tiles_r;
-      const int j = t / per_region;
+      const int j = t % p.world;
       const int owner = (p.rank + 1 + j) % p.world;
       int mi, ni;
-      raster(t - j * per_region, p.m_tiles, n_tiles_r, mi, ni);
+      raster(t / p.world, p.m_tiles, n_tiles_r, mi, ni);
       mt = mi;
       nt = owner * n_tiles_r + ni;
     }
