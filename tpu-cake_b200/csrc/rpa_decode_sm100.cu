@@ -22,7 +22,7 @@
 //                            P^T obtained from the S^T accumulators with movmatrix; online softmax
 //                            in f32 with warp shuffles.
 //                            Loads run ahead into the next work item so the ring never drains.
-//   cake_rpa_combine_sm100   one warp per (sequence, KV head): merges the split-KV partials
+//   cake_rpa_combine_sm100   one warp per (sequence, query head): merges the split-KV partials
 //                            (m, l, o) in chunk order and writes bf16.
 #include <cuda_bf16.h>
 #include <math.h>
@@ -314,14 +314,14 @@ __device__ __forceinline__ void rpa_issue_stage(const RpaParams& p, const CUtens
 
 // Merges the split-KV partials of one (sequence, KV head) in chunk order and writes bf16 output.
 // Lane c reads chunk c's (m, l).
-__device__ __forceinline__ void rpa_merge(const RpaParams& p, int s, int h, int n, int first_full, int tail, int lane) {
+__device__ __forceinline__ void rpa_merge(const RpaParams& p, int s, int h, int r, int n, int first_full, int tail, int lane) {
   const int n_full = n - (tail >= 0 ? 1 : 0);
   // Partial row of chunk c and query row r: chunk c is the c-th full chunk or the remainder.
   auto row_of = [&](int c, int r) {
     const size_t cs = c < n_full ? static_cast<size_t>(first_full + c) : static_cast<size_t>(tail);
     return (cs * p.kv_heads + h) * p.group + r;
   };
-  for (int r = 0; r < p.group; ++r) {
+  {
     float m = kNegBig;
     for (int c0 = 0; c0 < n; c0 += 32) {
       const int c = c0 + lane;
@@ -721,15 +721,17 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
   }
 }
 
-// One warp per (sequence, KV head): merges its split-KV partials in chunk order.
+// One warp per (sequence, KV head, query row): merges its split-KV partials in chunk order.
 __global__ void __launch_bounds__(128) cake_rpa_combine_sm100(const RpaParams p) {
-  const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (pair >= p.num_seqs * p.kv_heads) return;
+  const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= p.num_seqs * p.kv_heads * p.group) return;
+  const int pair = unit / p.group;
+  const int r = unit - pair * p.group;
   const int s = pair / p.kv_heads;
   const int h = pair - s * p.kv_heads;
   const int len = p.kv_lens[s];
   const int n = len > 0 ? (len + p.chunk_tokens - 1) / p.chunk_tokens : 0;
-  if (n > 1) rpa_merge(p, s, h, n, p.item_base[s], p.tail_cs[s], threadIdx.x & 31);
+  if (n > 1) rpa_merge(p, s, h, r, n, p.item_base[s], p.tail_cs[s], threadIdx.x & 31);
 }
 
 }  // namespace cake
@@ -967,7 +969,7 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
       plan->tmap_k, plan->tmap_v, p);
   CAKE_CUDA_TRY(cudaGetLastError());
   ++launches;
-  cake::cake_rpa_combine_sm100<<<(d.num_seqs * d.kv_heads + 3) / 4, 128, 0, stream>>>(p);
+  cake::cake_rpa_combine_sm100<<<(d.num_seqs * d.q_heads + 3) / 4, 128, 0, stream>>>(p);
   CAKE_CUDA_TRY(cudaGetLastError());
   ++launches;
   plan->launches = launches;
