@@ -40,8 +40,9 @@ import __graft_entry__  # noqa: E402
 M, K, N = 8192, 16384, 8192
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (None until a capture of that kernel and workload exists).
-MEASURED_TRAFFIC_BYTES = {"matmul_n1": None, "rpa_decode_64": None}
+# profiles/: cake_matmul_rs_sm100<256> on 8192x16384x8192 (2.909 GB read + 0.134 GB written) and
+# cake_rpa_decode_sm100 on the 64-sequence decode configuration (1.090 GB read + 0.011 GB written).
+MEASURED_TRAFFIC_BYTES = {"matmul_n1": 3_043_610_488, "rpa_decode_64": 1_101_872_264}
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -361,6 +362,20 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
             dist.all_gather_into_tensor(gathered, out, group=mesh.group)
 
     steps = max(args.steps, 10)
+    launch_mode = "stream"
+    if world == 1 and not args.no_graph:
+        # The step is three short kernels: replaying them from a CUDA graph removes the launch gaps.
+        step()
+        torch.cuda.synchronize(mesh.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            plan.invoke(executable, query, cache, None, table_d, lengths_d, out=out)
+        eager_step = step
+
+        def step():
+            graph.replay()
+
+        launch_mode = "cuda-graph"
     total_ms, per_step = timed_steps(mesh, step, steps, max(args.warmup, 3), flush)
     executable.status()
     bytes_total = workloads.decode_algorithmic_bytes(lengths, config.q_heads, config.kv_heads, config.head_dim, config.page_size)
@@ -375,6 +390,7 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
             "head_dim": config.head_dim, "page_size": config.page_size, "total_pages": config.total_pages,
             "kv_tokens": int(lengths.astype(np.int64).sum()), "sharding": f"kv_heads/{world}" if world > 1 else "none",
             "collective": "nccl all_gather of outputs" if world > 1 else "none", "l2": "256 MiB flush between steps",
+            "launch": launch_mode,
         },
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -506,6 +522,7 @@ def main() -> None:
     parser.add_argument("--cpu-rows", type=int, default=8192)
     parser.add_argument("--k", type=int, default=K, help="contraction extent (experiments only; the headline uses the default)")
     parser.add_argument("--no-rpa", action="store_true")
+    parser.add_argument("--no-graph", action="store_true", help="launch the attention step kernel by kernel instead of replaying a CUDA graph")
     parser.add_argument("--only-rpa", action="store_true", help="run only the attention part (profiling aid)")
     parser.add_argument("--rpa-pool-pages", type=int, default=0,
                         help="shrink the KV page pool (same sequences and lengths; for captures that must hold little memory)")
