@@ -214,3 +214,26 @@ def test_large_configuration_properties(cuda_device):
     # bf16 rounding of 8192 outputs of magnitude ~1/128 each: absolute error well under 1e-2.
     assert np.max(np.abs(row_sums - identity_sums)) < 2e-2
     executable.close()
+
+
+@pytest.mark.parametrize("mesh_size, strategy", [(1, "nccl_reduce_scatter"), (8, "p2p_fused_epilogue"), (4, "nccl_reduce_scatter")])
+def test_runner_writes_a_complete_bundle(cuda_device, tmp_path, mesh_size, strategy):
+    """run-matmul on the reference's CPU-runnable shape: ledger reaches TIMED, artifacts exist and
+    the saved output passes the reference's tolerance against the saved oracle."""
+    from tpu_cake_b200 import runner
+    from tpu_cake_b200.run_ledger import RunLedger, RunState
+
+    out = tmp_path / "run"
+    result = runner.run_distributed_matmul(out, mesh_size=mesh_size, m=128, k=1024, n=1024, warmup_iterations=1,
+                                           measured_iterations=3, collective_strategy=strategy)
+    assert result.passed and result.median_ns > 0 and len(result.samples_ns) == 3
+    assert result.execution == ("one-process-per-gpu" if mesh_size == 1 else "emulated-on-one-gpu")
+    for name in ("invocation.json", "distributed.mlir", "physical.mlir", "lowered_cuda.py", "cost_model.json",
+                 "kernel_manifest.json", "lhs.npy", "rhs.npy", "output.npy", "oracle.npy", "ledger.sqlite", "result.json"):
+        assert (out / name).exists(), name
+    with RunLedger(out / "ledger.sqlite") as ledger:
+        states = [event.state for event in ledger.history(result.run_id)]
+    assert states == [RunState.CREATED, RunState.VERIFIED, RunState.LOWERED, RunState.COMPILED, RunState.CORRECT, RunState.TIMED]
+    assert np.allclose(np.load(out / "output.npy"), np.load(out / "oracle.npy"), atol=1e-3, rtol=1e-3)
+    with pytest.raises(FileExistsError):
+        runner.run_distributed_matmul(out, mesh_size=mesh_size, m=128, k=1024, n=1024, warmup_iterations=0, measured_iterations=1)

@@ -1,0 +1,125 @@
+"""Schedule -> physical kernel -> CUDA plan, the IR verifiers (mutation tests in the reference's
+"fail closed" style) and the cost model's known answers."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from tpu_cake_b200 import cost_model, cuda_lowering, dialects, ir, schedule_lowering, workloads
+
+
+def physical(mesh=8, m=128, k=1024, n=1024, **kwargs):
+    return schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(mesh_size=mesh, m=m, k=k, n=n), **kwargs)
+
+
+def test_schedule_lowers_to_the_sixteen_operation_kernel():
+    module = physical()
+    kernel = module.ops[0]
+    assert [op.name for op in kernel.body.ops] == list(cuda_lowering._PHYSICAL_MATMUL_OPS)
+    assert kernel.properties["target"] == "b200"
+    matmul = kernel.body.ops[11]
+    assert (matmul.properties["tile_m"], matmul.properties["tile_k"], matmul.properties["tile_n"]) == (128, 128, 1024)
+    collective = kernel.body.ops[12]
+    assert collective.properties["group_size"] == 8 and collective.properties["split_dimension"] == 1
+    assert collective.properties["collective_plan"] == "axis:t" and "implementation" not in collective.properties
+
+
+def test_canonical_text_is_stable_and_ignores_names_and_locations():
+    first = workloads.distributed_matmul_schedule(mesh_size=8, m=128, k=1024, n=1024)
+    second = workloads.distributed_matmul_schedule(mesh_size=8, m=128, k=1024, n=1024)
+    second.ops[0].properties["sym_name"] = "renamed"
+    second.ops[0].body.ops[0].location = ir.SourceLocation("elsewhere.py", 9, 9)
+    assert ir.schedule_sha256(first) == ir.schedule_sha256(second)
+    other = workloads.distributed_matmul_schedule(mesh_size=4, m=128, k=1024, n=1024)
+    assert ir.schedule_sha256(first) != ir.schedule_sha256(other)
+    text = ir.canonical_text(physical())
+    assert '"tpu_schedule.mxu_matmul"' in text and 'role = "alloc0"' in text and "lhs_tile" not in text
+
+
+def test_lowered_plan_matches_reference_fields():
+    module = physical(tile=schedule_lowering.MatmulTile(128, 256), collective_implementation=dialects.CollectiveImplementation.P2P_OWNER_PUSH)
+    plan = cuda_lowering.lower_physical_matmul_to_cuda(module)
+    assert plan.schedule_sha256 == ir.schedule_sha256(module)
+    assert plan.lhs_local_shape == (128, 128) and plan.rhs_local_shape == (128, 1024)
+    assert plan.partial_local_shape == (128, 1024) and plan.output_local_shape == (128, 128)
+    assert plan.output_sharding == ("", "t") and plan.scatter_dimension == 1
+    assert (plan.tile_m, plan.tile_k, plan.tile_n) == (128, 128, 256)
+    assert plan.collective_implementation is cuda_lowering.MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE
+    assert plan.collective_link_bandwidths == (("t", 900_000_000_000),)
+    along_m = schedule_lowering.lower_distributed_matmul(
+        workloads.distributed_matmul_schedule(mesh_size=8, m=8192, k=16384, n=8192, scatter_dimension="M"),
+        tile=schedule_lowering.MatmulTile(128, 256),
+    )
+    big = cuda_lowering.lower_physical_matmul_to_cuda(along_m, output_dtype="bf16")
+    assert big.output_local_shape == (1024, 8192) and big.scatter_dimension == 0 and big.output_dtype == "bf16"
+
+
+def test_lowering_rejects_other_programs_with_operation_name_in_message():
+    module = workloads.distributed_matmul_schedule(mesh_size=4)
+    module.ops[0].body.ops[1].properties["reducer"] = "max"
+    with pytest.raises((schedule_lowering.UnsupportedLoweringError, ir.VerifyException)):
+        schedule_lowering.lower_distributed_matmul(module)
+    module = workloads.distributed_matmul_schedule(mesh_size=4)
+    del module.ops[0].body.ops[1]
+    with pytest.raises((schedule_lowering.UnsupportedLoweringError, ir.VerifyException)):
+        schedule_lowering.lower_distributed_matmul(module)
+    with pytest.raises(cuda_lowering.UnsupportedLoweringError, match="tiles"):
+        cuda_lowering.lower_physical_matmul_to_cuda(physical(tile=schedule_lowering.MatmulTile(64, 128)))
+
+
+@pytest.mark.parametrize(
+    "mutate, fragment",
+    [
+        (lambda k: k.body.ops[11].properties.__setitem__("tile_k", 64), "tile_k must equal"),
+        (lambda k: k.body.ops[11].properties.__setitem__("tile_m", 96), "tiles must be positive and divide"),
+        (lambda k: k.body.ops[12].properties.__setitem__("group_size", 1), "group_size must exceed 1"),
+        (lambda k: k.body.ops[12].properties.__setitem__("split_dimension", 0), "destination must be"),
+        (lambda k: k.body.ops.pop(14), "every DMA must be waited on"),
+        (lambda k: k.body.ops[8].operands.__setitem__(2, k.body.ops[7].operands[2]), "semaphore reused"),
+        (lambda k: k.properties.__setitem__("vmem_capacity_bytes", 1024), "exceed the capacity"),
+        (lambda k: k.body.ops[11].properties.__setitem__("stage", 4), "not live at stage"),
+    ],
+)
+def test_physical_verifier_fails_closed(mutate, fragment):
+    module = physical()
+    mutate(module.ops[0])
+    with pytest.raises(ir.VerifyException, match=fragment):
+        module.verify()
+
+
+def test_logical_verifier_fails_closed():
+    with pytest.raises(ir.VerifyException, match="not divisible"):
+        workloads.distributed_matmul_schedule(mesh_size=3, m=16, k=32, n=16)
+    module = workloads.distributed_matmul_schedule(mesh_size=4)
+    module.ops[0].body.ops[0].properties["contracting_dimension"] = "M"
+    with pytest.raises(ir.VerifyException, match="contracting dimension"):
+        module.verify()
+
+
+def test_cost_model_known_answers():
+    """The reference's integers for mesh 8, 128 x 1024 x 1024 (its tests/test_cost_model.py:31-34)."""
+    plan = cuda_lowering.lower_physical_matmul_to_cuda(physical())
+    counts = cost_model.matmul_counts(plan)
+    assert counts.operations_per_device == 33_554_432
+    assert counts.hbm_read_bytes_per_device == 819_200
+    assert counts.hbm_write_bytes_per_device == 589_824
+    assert counts.ici_bidirectional_bytes_per_device == 917_504
+    report = cost_model.estimate_distributed_matmul(plan)
+    assert report.limiting_resource == "ici" and report.lower_bound_ns == report.communication_ns
+    big = cuda_lowering.plan_distributed_matmul(
+        mesh_size=8, m=8192, k=16384, n=8192, scatter_dimension=0, output_dtype="bf16",
+        collective_implementation=cuda_lowering.MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE_BF16_TRANSPORT,
+    )
+    big_report = cost_model.estimate_distributed_matmul(big)
+    assert big_report.counts.operations_per_device == 2 * 8192 * 2048 * 8192
+    assert big_report.counts.link_egress_bytes_per_device == 117_440_512
+    assert big_report.limiting_resource == "compute"
+    assert abs(float(big_report.compute_ns) - 168_756.0) < 1_000.0
+
+
+def test_rpa_cost_convention_matches_bench_bytes():
+    lengths, _ = workloads.decode_metadata(workloads.DECODE_64)
+    counts = cost_model.estimate_rpa_decode(lengths, q_heads=32, kv_heads=8, head_dim=128, page_size=16)
+    assert counts.hbm_bytes == workloads.decode_algorithmic_bytes(lengths, 32, 8, 128, 16)
+    assert counts.flops == 4 * 128 * 32 * int(np.asarray(lengths, dtype=np.int64).sum())

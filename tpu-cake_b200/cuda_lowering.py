@@ -357,3 +357,102 @@ class MatmulRsExecutable:
                 f"{role} must be a contiguous bf16 tensor of shape {shape} on {self.mesh.device}, "
                 f"got {tensor.dtype} {tuple(tensor.shape)} on {tensor.device}"
             )
+
+
+_IMPLEMENTATION_TO_STRATEGY = {
+    None: MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER,
+    "nccl": MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER,
+    "p2p_owner_push": MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE,
+    "p2p_owner_push_bf16": MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE_BF16_TRANSPORT,
+}
+_PHYSICAL_MATMUL_OPS = (
+    "tpu_schedule.alloc", "tpu_schedule.alloc", "tpu_schedule.alloc", "tpu_schedule.alloc",
+    "tpu_schedule.semaphore_alloc", "tpu_schedule.semaphore_alloc", "tpu_schedule.semaphore_alloc",
+    "tpu_schedule.dma_start", "tpu_schedule.dma_start", "tpu_schedule.dma_wait", "tpu_schedule.dma_wait",
+    "tpu_schedule.mxu_matmul", "tpu_schedule.collective", "tpu_schedule.dma_start", "tpu_schedule.dma_wait",
+    "tpu_schedule.yield",
+)
+
+
+def _hardware_tile(schedule_tile: int, supported: tuple[int, ...], op, reject) -> int:
+    """The schedule's tile is the block of the output one step produces; the reference's default is
+    the whole local operand (src/tpu_cake/dialects/tpu_schedule.py:982-984). A schedule tile that is
+    a hardware tile is used as is; a larger one is covered by the largest hardware tile (the CTA
+    walks it in sub-tiles); a smaller one that is not a hardware tile cannot be expressed."""
+    if schedule_tile in supported:
+        return schedule_tile
+    if schedule_tile > max(supported):
+        return max(supported)
+    raise reject(f"sm_100a matmul tiles are {supported}, the schedule asks for {schedule_tile}", op)
+
+
+def lower_physical_matmul_to_cuda(module, *, output_dtype: str = "f32") -> CudaMatmulRsPlan:
+    """Physical matmul kernel -> CUDA plan; the counterpart of ``lower_physical_matmul_to_pallas``
+    (src/tpu_cake/pallas_lowering.py:689-847). Accepts exactly the 16-operation kernel that
+    ``lower_distributed_matmul`` emits, checks its dataflow (loads feed the matmul operands, the
+    matmul accumulator feeds the collective, the collective result is stored to the output), bf16
+    inputs with an f32 accumulator, a one-axis mesh, and reads shapes, shardings, tiles, scatter
+    dimension and collective implementation off the operations. ``output_dtype`` selects the dtype
+    the reduced output is stored in (the schedule's result is f32; "bf16" adds the final cast)."""
+    from .ir import schedule_sha256
+
+    module.verify()
+
+    def reject(message: str, op=None) -> UnsupportedLoweringError:
+        where = f": {op.name} at {op.location}" if op is not None else ""
+        return UnsupportedLoweringError(f"{message}{where}")
+
+    if len(module.ops) != 1 or module.ops[0].name != "tpu_schedule.kernel":
+        raise reject("expected one physical kernel")
+    kernel = module.ops[0]
+    ops = kernel.body.ops
+    if tuple(op.name for op in ops) != _PHYSICAL_MATMUL_OPS:
+        unexpected = next((op for op, name in zip(ops, _PHYSICAL_MATMUL_OPS) if op.name != name), kernel)
+        raise reject("kernel is not the physical matmul + reduce-scatter sequence", unexpected)
+    lhs_alloc, rhs_alloc, partial_alloc, reduced_alloc = ops[0:4]
+    load_lhs, load_rhs, wait_lhs, wait_rhs, matmul, collective, store, wait_store = ops[7:15]
+    lhs_arg, rhs_arg, out_arg = kernel.body.args
+    if load_lhs.operands[0] is not lhs_arg or load_lhs.operands[1] is not lhs_alloc.result:
+        raise reject("the first DMA must load the lhs argument into the lhs tile", load_lhs)
+    if load_rhs.operands[0] is not rhs_arg or load_rhs.operands[1] is not rhs_alloc.result:
+        raise reject("the second DMA must load the rhs argument into the rhs tile", load_rhs)
+    if wait_lhs.operands[0] is not load_lhs.result or wait_rhs.operands[0] is not load_rhs.result:
+        raise reject("loads must be waited on in order", wait_lhs)
+    if list(matmul.operands) != [lhs_alloc.result, rhs_alloc.result, partial_alloc.result]:
+        raise reject("the matmul must contract the loaded tiles into the partial accumulator", matmul)
+    if list(collective.operands) != [partial_alloc.result, reduced_alloc.result]:
+        raise reject("the collective must reduce the partial accumulator into the reduced output", collective)
+    if store.operands[0] is not reduced_alloc.result or store.operands[1] is not out_arg or wait_store.operands[0] is not store.result:
+        raise reject("the reduced output must be stored to the output argument", store)
+    lhs_type, rhs_type, partial_type, out_type = lhs_arg.type, rhs_arg.type, partial_alloc.result.type, out_arg.type
+    if lhs_type.element_type != "bf16" or rhs_type.element_type != "bf16" or partial_type.element_type != "f32" or out_type.element_type != "f32":
+        raise reject("the CUDA backend lowers bf16 inputs with f32 accumulation and an f32 schedule result", matmul)
+    axes = kernel.properties["mesh_axis_names"]
+    if len(axes) != 1:
+        raise reject("the CUDA backend lowers a one-axis mesh", kernel)
+    if collective.properties["kind"] != "reduce_scatter" or collective.properties["reducer"] != "sum":
+        raise reject("the collective must be a sum reduce-scatter", collective)
+    implementation = collective.properties.get("implementation")
+    if implementation not in _IMPLEMENTATION_TO_STRATEGY:
+        raise reject(f"unknown collective implementation {implementation}", collective)
+    mesh_size = kernel.properties["mesh_axis_sizes"][0]
+    return CudaMatmulRsPlan(
+        name=kernel.properties["sym_name"],
+        schedule_sha256=schedule_sha256(module),
+        mesh_axis=axes[0],
+        mesh_size=mesh_size,
+        lhs_local_shape=tuple(lhs_type.shape),
+        rhs_local_shape=tuple(rhs_type.shape),
+        partial_local_shape=tuple(partial_type.shape),
+        output_local_shape=tuple(out_type.shape),
+        lhs_sharding=tuple(lhs_type.sharding),
+        rhs_sharding=tuple(rhs_type.sharding),
+        output_sharding=tuple(out_type.sharding),
+        scatter_dimension=collective.properties["split_dimension"],
+        tile_m=_hardware_tile(matmul.properties["tile_m"], SUPPORTED_TILE_M, matmul, reject),
+        tile_k=matmul.properties["tile_k"],
+        tile_n=_hardware_tile(matmul.properties["tile_n"], SUPPORTED_TILE_N, matmul, reject),
+        collective_link_bandwidths=tuple((t.split(":")[0], int(t.split(":")[1])) for t in kernel.properties["topology"]),
+        collective_implementation=_IMPLEMENTATION_TO_STRATEGY[implementation] if mesh_size > 1 else None,
+        output_dtype=output_dtype,
+    )

@@ -106,3 +106,26 @@ def decode_algorithmic_bytes(kv_lens: np.ndarray, q_heads: int, kv_heads: int, h
     q_and_o = lens.size * q_heads * head_dim * elem_bytes * 2
     table = int((-(-lens // page_size)).sum()) * 4 + 8 * lens.size
     return kv + q_and_o + table
+
+
+def distributed_matmul_schedule(*, mesh_size: int = 4, m: int = 16, k: int = 32, n: int = 16, scatter_dimension: str = "N"):
+    """The logical program ``einsum_local(lhs[M, K@t], rhs[K@t, N]) -> f32[M, N]{pending t:sum}``
+    followed by ``reduce_scatter(axes=t, dim=scatter_dimension)``
+    (src/tpu_cake/workloads/distributed_matmul.py:22-46; the reference scatters "N")."""
+    from .dialects import DistributedProgramBuilder, tensor
+    from .ir import SourceLocation
+
+    if scatter_dimension not in ("M", "N"):
+        raise ValueError("scatter_dimension must be 'M' or 'N'")
+    lhs = tensor("bf16", (("M", m), ("K", k)), sharding={"K": ("t",)})
+    rhs = tensor("bf16", (("K", k), ("N", n)), sharding={"K": ("t",)})
+    builder = DistributedProgramBuilder("distributed_matmul", {"t": mesh_size}, (lhs, rhs))
+    partial = builder.einsum_local(
+        builder.inputs[0], builder.inputs[1], tensor("f32", (("M", m), ("N", n)), pending_reductions={"t": "sum"}),
+        contracting_dimension="K", source=SourceLocation("tpu_cake_b200/workloads.py", 1, 1),
+    )
+    result = builder.reduce_scatter(
+        partial, tensor("f32", (("M", m), ("N", n)), sharding={scatter_dimension: ("t",)}), axes=("t",),
+        scatter_dimensions=(scatter_dimension,), source=SourceLocation("tpu_cake_b200/workloads.py", 2, 1),
+    )
+    return builder.module(result)
