@@ -2,7 +2,7 @@
 (src/tpu_cake/cli.py:154-425): ``run-matmul`` (:216-232), ``render-workload`` and
 ``verify-schedule`` for the distributed matmul, and ``estimate`` for its cost model.
 
-    python -m tpu_cake_b200.cli run-matmul OUT --mesh-size 8 --m 128 --k 1024 --n 1024
+    python __graft_entry__.py cli run-matmul OUT --mesh-size 8 --m 128 --k 1024 --n 1024
 """
 
 from __future__ import annotations
