@@ -348,13 +348,25 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
     )
     executable = plan.build(mesh.device)
     out = torch.empty_like(query)
-    gathered = torch.empty((world, config.num_seqs, local_q, config.head_dim), dtype=torch.bfloat16, device=mesh.device) if world > 1 else None
+    gathered = gather_buffer = gather_flags = None
+    if world > 1 and args.rpa_gather == "nccl":
+        gathered = torch.empty((world, config.num_seqs, local_q, config.head_dim), dtype=torch.bfloat16, device=mesh.device)
+    elif world > 1:
+        # Outputs are written straight into every rank's gathered buffer over peer memory.
+        from tpu_cake_b200.mesh import SymmetricBuffer
+
+        gather_buffer = SymmetricBuffer(mesh, world * config.num_seqs * local_q * config.head_dim * 2)
+        gather_flags = SymmetricBuffer(mesh, 64)
     flush_buffer = torch.empty(256 << 20, dtype=torch.uint8, device=mesh.device)
 
     def flush():
         flush_buffer.fill_(1)
 
     def step():
+        if gather_buffer is not None:
+            executable.enqueue_allgather(query, cache, None, lengths_d, table_d, gather_buffer.pointers, gather_flags.pointers,
+                                         world, mesh.rank)
+            return
         plan.invoke(executable, query, cache, None, table_d, lengths_d, out=out)
         if world > 1:
             import torch.distributed as dist
@@ -389,7 +401,7 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
             "workload": config.name, "num_seqs": config.num_seqs, "q_heads": config.q_heads, "kv_heads": config.kv_heads,
             "head_dim": config.head_dim, "page_size": config.page_size, "total_pages": config.total_pages,
             "kv_tokens": int(lengths.astype(np.int64).sum()), "sharding": f"kv_heads/{world}" if world > 1 else "none",
-            "collective": "nccl all_gather of outputs" if world > 1 else "none", "l2": "256 MiB flush between steps",
+            "collective": ("none" if world == 1 else "nccl all_gather of outputs" if gather_buffer is None else "peer-to-peer stores into every rank's gathered buffer + flag barrier"), "l2": "256 MiB flush between steps",
             "launch": launch_mode,
         },
         "roofline": {
@@ -405,7 +417,10 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
     q_host = query.cpu().pin_memory()
     table_host = table_d.cpu().pin_memory()
     lengths_host = lengths_d.cpu().pin_memory()
-    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    result_device = out if gather_buffer is None else gather_buffer.as_tensor(torch.bfloat16, (world, config.num_seqs, local_q, config.head_dim))
+    if gathered is not None:
+        result_device = gathered
+    out_host = torch.empty(result_device.shape, dtype=result_device.dtype).pin_memory()
     e2e_steps = 10
     mesh.barrier()
     torch.cuda.synchronize(mesh.device)
@@ -415,7 +430,7 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
         table_d.copy_(table_host, non_blocking=True)
         lengths_d.copy_(lengths_host, non_blocking=True)
         step()
-        out_host.copy_(out, non_blocking=True)
+        out_host.copy_(result_device, non_blocking=True)
         torch.cuda.synchronize(mesh.device)
     elapsed = reduce_max(mesh, time.perf_counter() - started)
     result["e2e"] = {
@@ -426,6 +441,9 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
     if world == 1 and mesh.rank == 0 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_rpa_sample(lengths, table, config, 32, os.cpu_count() or 1)
     executable.close()
+    for buffer in (gather_buffer, gather_flags):
+        if buffer is not None:
+            buffer.close()
     return result
 
 
@@ -522,6 +540,7 @@ def main() -> None:
     parser.add_argument("--cpu-rows", type=int, default=8192)
     parser.add_argument("--k", type=int, default=K, help="contraction extent (experiments only; the headline uses the default)")
     parser.add_argument("--no-rpa", action="store_true")
+    parser.add_argument("--rpa-gather", choices=("p2p", "nccl"), default="p2p", help="how the sharded decode's outputs are all-gathered")
     parser.add_argument("--no-graph", action="store_true", help="launch the attention step kernel by kernel instead of replaying a CUDA graph")
     parser.add_argument("--only-rpa", action="store_true", help="run only the attention part (profiling aid)")
     parser.add_argument("--rpa-pool-pages", type=int, default=0,

@@ -192,6 +192,24 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
                                 const void* bias0, const void* bias1, void* out, void* workspace,
                                 void* stream);
 
+/* Decode of this rank's KV-head shard with the all-gather of the outputs fused in: every output
+ * row is written straight into the gathered buffer of every rank over peer memory (P2P stores), then
+ * a one-warp kernel publishes an epoch to every rank's flag array and, if `wait` is non-zero, waits
+ * (bounded) until every rank has published. Replaces the "outputs stay sharded" end of the reference's
+ * shard_map (src/tpu_cake/rpa_lowering.py:552-558) plus the all-gather the sharded configuration asks
+ * for. gathered[r]: rank r's [world][num_seqs][q_heads][head_dim] bf16 buffer (q_heads = this shard's
+ * query heads); flags[r]: rank r's CAKE_MAX_WORLD x uint64 array, zero before the first call; entries
+ * [rank] are this rank's own allocations, the others peer mappings. `wait` = 0 lets a host that drives
+ * several ranks from one process enqueue every rank before anybody waits. The first call allocates a
+ * 64-byte device table. */
+int32_t cake_rpa_decode_allgather_enqueue(cake_rpa* plan, const void* q, const void* new_k,
+                                          const void* new_v, void* cache0, void* cache1,
+                                          const int32_t* kv_lens, const int32_t* page_table,
+                                          const int32_t* cu_kv_lens, const void* bias0,
+                                          const void* bias1, void* const* gathered,
+                                          void* const* flags, int32_t world, int32_t rank,
+                                          int32_t wait, void* workspace, void* stream);
+
 /* Decode for hosts that may not allocate device memory. No counterpart in the reference: its
  * kernels get their scratch from the JAX runtime.
  *

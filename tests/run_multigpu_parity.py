@@ -81,12 +81,73 @@ def main() -> int:
                             flush=True,
                         )
                     executable.close()
+    failures += sharded_decode_case(mesh)
     if mesh.world > 1:
         import torch.distributed as dist
 
         dist.barrier()
         dist.destroy_process_group()
     return 1 if failures else 0
+
+
+def sharded_decode_case(mesh) -> int:
+    """Decode with KV heads sharded over the ranks and the outputs all-gathered through peer memory:
+    every rank checks the whole gathered result against the oracle, three calls in a row."""
+    import math
+
+    from oracle import rpa as rpa_oracle
+    from tests.helpers import BF16, to_device, torch_to_bf16
+    from tpu_cake_b200 import rpa_cuda_lowering
+    from tpu_cake_b200.mesh import SymmetricBuffer
+
+    world = mesh.world
+    generator = np.random.default_rng(77)
+    lengths = np.array([33, 900, 1700, 512, 64, 2049], dtype=np.int32)
+    count, kv_heads, group, page_size = len(lengths), 8, 4, 32
+    q_heads = kv_heads * group
+    pages_per = -(-lengths.astype(np.int64) // page_size)
+    pool = int(pages_per.sum()) + 5
+    query = generator.normal(size=(count, q_heads, 128)).astype(np.float32).astype(BF16)
+    keys = generator.normal(size=(pool, page_size, kv_heads, 128)).astype(np.float32).astype(BF16)
+    values = generator.normal(size=(pool, page_size, kv_heads, 128)).astype(np.float32).astype(BF16)
+    table = np.zeros((count, int(pages_per.max())), dtype=np.int32)
+    permutation = generator.permutation(pool)
+    cursor = 0
+    for s in range(count):
+        table[s, : pages_per[s]] = permutation[cursor : cursor + pages_per[s]]
+        cursor += int(pages_per[s])
+    expected = rpa_oracle.rpa_separate(query, keys, values, table, lengths, None, scale=1.0 / math.sqrt(128))
+    local_kv, local_q = kv_heads // world, q_heads // world
+    plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+        name="sharded", schedule_sha256="0" * 64, query_shape=(count, local_q, 128), cache_shape=(pool, page_size, local_kv, 128),
+        page_table_shape=table.shape, bias_shape=None, softmax_scale=1.0 / math.sqrt(128), cache_layout="fused",
+    )
+    executable = plan.build(mesh.device)
+    heads = slice(mesh.rank * local_kv, (mesh.rank + 1) * local_kv)
+    cache = to_device(rpa_oracle.fused_cache_from_separate(keys[:, :, heads], values[:, :, heads]), mesh.device)
+    q_local = to_device(np.ascontiguousarray(query[:, mesh.rank * local_q : (mesh.rank + 1) * local_q]), mesh.device)
+    gathered = SymmetricBuffer(mesh, world * count * local_q * 128 * 2)
+    flags = SymmetricBuffer(mesh, 64)
+    table_d, lengths_d = to_device(table, mesh.device), to_device(lengths, mesh.device)
+    ok = True
+    for _ in range(3):
+        executable.enqueue_allgather(q_local, cache, None, lengths_d, table_d, gathered.pointers, flags.pointers, world, mesh.rank)
+        executable.status()
+        full = torch_to_bf16(gathered.as_tensor(torch.bfloat16, (world, count, local_q, 128))).astype(np.float32)
+        assembled = np.concatenate([full[r] for r in range(world)], axis=1)
+        ok = ok and oracle.max_abs_error(assembled, expected) <= 2e-2 and oracle.relative_l2_error(assembled, expected) <= 1e-2
+        mesh.barrier()
+    flag = torch.tensor([0 if ok else 1], device=mesh.device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(flag, group=mesh.group)
+    if mesh.rank == 0:
+        print(f"{'PASS' if flag.item() == 0 else 'FAIL'} sharded decode W={world} with peer-to-peer all-gather", flush=True)
+    executable.close()
+    gathered.close()
+    flags.close()
+    return int(flag.item())
 
 
 if __name__ == "__main__":

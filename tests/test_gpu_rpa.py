@@ -273,3 +273,48 @@ def test_decode_configuration_full_size(cuda_device):
         )
         assert_close(actual[s : s + 1], expected)
     executable.close()
+
+
+def test_sharded_decode_writes_every_ranks_gathered_buffer(cuda_device):
+    """KV heads sharded over 4 mesh positions, all emulated on this GPU: every position decodes its
+    heads and stores its slice into every position's gathered buffer (no waiting: each call is
+    enqueued with wait=False); afterwards every buffer holds the full [W, S, Hq/W, D] result."""
+    import ctypes
+
+    from tpu_cake_b200 import _native
+
+    world, lengths = 4, [40, 700, 1300, 17, 512]
+    case = random_case(31, num_seqs=len(lengths), q_heads=16, kv_heads=4, page_size=16, lengths=lengths, pool_pages=200, poison=False)
+    query, key_cache, value_cache, table, lens = case
+    expected = expected_for(case)  # [S, 16, 128]
+    count, local_q, local_kv = len(lengths), 4, 1
+    lib = _native.load()
+    gathered = [torch.zeros((world, count, local_q, 128), dtype=torch.bfloat16, device=cuda_device) for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int64, device=cuda_device) for _ in range(world)]
+    table_d, lens_d = to_device(table, cuda_device), to_device(lens, cuda_device)
+    executables, keep = [], []
+    for rank in range(world):
+        plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+            name=f"shard{rank}", schedule_sha256="0" * 64, query_shape=(count, local_q, 128),
+            cache_shape=(key_cache.shape[0], 16, local_kv, 128), page_table_shape=table.shape, bias_shape=None,
+            softmax_scale=1.0 / math.sqrt(128), cache_layout="fused",
+        )
+        executable = plan.build(cuda_device)
+        q_r = to_device(np.ascontiguousarray(query[:, rank * local_q : (rank + 1) * local_q]), cuda_device)
+        fused = oracle.fused_cache_from_separate(key_cache[:, :, rank : rank + 1], value_cache[:, :, rank : rank + 1])
+        cache_r = to_device(fused, cuda_device)
+        keep.append((q_r, cache_r))
+        executable.enqueue_allgather(q_r, cache_r, None, lens_d, table_d, [g.data_ptr() for g in gathered],
+                                     [f.data_ptr() for f in flags], world, rank, wait=False)
+        executables.append(executable)
+    torch.cuda.synchronize(cuda_device)
+    for executable in executables:
+        assert executable.status() == (0, 0, 0, 0)
+        executable.close()
+    for buffer in gathered:
+        full = torch_to_bf16(buffer).astype(np.float32)  # [W, S, Hq/W, D]
+        assembled = np.concatenate([full[r] for r in range(world)], axis=1)
+        assert_close(assembled, expected)
+        np.testing.assert_array_equal(full, torch_to_bf16(gathered[0]).astype(np.float32))
+    for flag in flags:
+        assert flag.cpu().tolist()[:world] == [1] * world

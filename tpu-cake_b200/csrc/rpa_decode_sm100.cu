@@ -60,6 +60,8 @@ constexpr float kNegBig = -1.0e30f;
 struct RpaParams {
   const __nv_bfloat16* q;
   __nv_bfloat16* out;
+  __nv_bfloat16* out_peers[CAKE_MAX_WORLD];  // every destination of an output row (own buffer first)
+  int32_t out_count;
   const int32_t* kv_lens;
   const int32_t* page_table;
   const int32_t* cu_kv_lens;
@@ -358,7 +360,8 @@ __device__ __forceinline__ void rpa_merge(const RpaParams& p, int s, int h, int 
       uint2 packed;
       packed.x = pack_bf16(o.x * inv, o.y * inv);
       packed.y = pack_bf16(o.z * inv, o.w * inv);
-      *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(s) * p.q_heads + h * p.group + r) * p.head_dim + lane * 4) = packed;
+      const size_t at = (static_cast<size_t>(s) * p.q_heads + h * p.group + r) * p.head_dim + lane * 4;
+      for (int o = 0; o < p.out_count; ++o) *reinterpret_cast<uint2*>(p.out_peers[o] + at) = packed;
     }
   }
 }
@@ -674,18 +677,21 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
     }
     if (n_chunks == 1) {
       const float inv0 = 1.f / l_run[0], inv1 = 1.f / l_run[1];
-      __nv_bfloat16* o0 = p.out + (static_cast<size_t>(s) * p.q_heads + h * p.group + qrow) * p.head_dim;
-      __nv_bfloat16* o1 = o0 + p.head_dim;
+      const size_t at0 = (static_cast<size_t>(s) * p.q_heads + h * p.group + qrow) * p.head_dim;
+      for (int o = 0; o < p.out_count; ++o) {
+        __nv_bfloat16* o0 = p.out_peers[o] + at0;
+        __nv_bfloat16* o1 = o0 + p.head_dim;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int d = i * 16 + trow;
-        if (qrow < p.group) {
-          if (d < p.head_dim) o0[d] = __float2bfloat16_rn(oacc[i][0] * inv0);
-          if (d + 8 < p.head_dim) o0[d + 8] = __float2bfloat16_rn(oacc[i][2] * inv0);
-        }
-        if (qrow + 1 < p.group) {
-          if (d < p.head_dim) o1[d] = __float2bfloat16_rn(oacc[i][1] * inv1);
-          if (d + 8 < p.head_dim) o1[d + 8] = __float2bfloat16_rn(oacc[i][3] * inv1);
+        for (int i = 0; i < 8; ++i) {
+          const int d = i * 16 + trow;
+          if (qrow < p.group) {
+            if (d < p.head_dim) o0[d] = __float2bfloat16_rn(oacc[i][0] * inv0);
+            if (d + 8 < p.head_dim) o0[d + 8] = __float2bfloat16_rn(oacc[i][2] * inv0);
+          }
+          if (qrow + 1 < p.group) {
+            if (d < p.head_dim) o1[d] = __float2bfloat16_rn(oacc[i][1] * inv1);
+            if (d + 8 < p.head_dim) o1[d + 8] = __float2bfloat16_rn(oacc[i][3] * inv1);
+          }
         }
       }
     } else {
@@ -734,6 +740,26 @@ __global__ void __launch_bounds__(128) cake_rpa_combine_sm100(const RpaParams p)
   if (n > 1) rpa_merge(p, s, h, r, n, p.item_base[s], p.tail_cs[s], threadIdx.x & 31);
 }
 
+// After the decode and combine kernels have written this rank's output slice into every rank's
+// gathered buffer: tell every rank (release at system scope, after the kernel boundary ordered the
+// slice's stores before this kernel) and wait, bounded, until every rank has told us.
+__global__ void cake_rpa_gather_sync_sm100(unsigned long long* const* flags_of, int world, int rank,
+                                           unsigned long long epoch, int wait, int32_t* status) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flags_of[r] + rank), "l"(epoch) : "memory");
+  if (!wait) return;
+  const unsigned long long start = global_timer_ns();
+  while (ld_acquire_sys_u64(flags_of[rank] + r) < epoch) {
+    if (global_timer_ns() - start > 20000000000ull) {
+      rpa_record(status, 2, rank, r, 0);
+      return;
+    }
+    __nanosleep(100);
+  }
+}
+
 }  // namespace cake
 
 // ====================================================================================== host
@@ -750,6 +776,12 @@ struct cake_rpa {
   const void* last_c1 = nullptr;
   CUtensorMap tmap_k, tmap_v;
   int launches = 0;
+  // all-gather of outputs over peer memory (set for the duration of one gather enqueue)
+  int gather_world = 0;
+  void* gather_out[CAKE_MAX_WORLD] = {};
+  unsigned long long gather_epoch = 0;
+  unsigned long long** gather_flag_table = nullptr;  // device copy of the W flag-array pointers
+  void* gather_flags_seen[CAKE_MAX_WORLD] = {};
 };
 
 namespace {
@@ -870,6 +902,7 @@ int32_t cake_rpa_create(const cake_rpa_desc* desc, cake_rpa** out) {
 
 int32_t cake_rpa_destroy(cake_rpa* plan) {
   if (!plan) return CAKE_OK;
+  if (plan->gather_flag_table) cudaFree(plan->gather_flag_table);
   plan->status.release();
   delete plan;
   return CAKE_OK;
@@ -911,6 +944,13 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_peers[0] = p.out;
+  p.out_count = 1;
+  if (plan->gather_world > 1) {
+    p.out_count = plan->gather_world;
+    for (int o = 0; o < plan->gather_world; ++o) p.out_peers[o] = static_cast<__nv_bfloat16*>(plan->gather_out[o]);
+    p.out = p.out_peers[0];
+  }
   p.kv_lens = kv_lens;
   p.page_table = page_table;
   p.cu_kv_lens = cu_kv_lens;
@@ -976,10 +1016,52 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   return CAKE_OK;
 }
 
+int32_t cake_rpa_decode_allgather_enqueue(cake_rpa* plan, const void* q, const void* new_k,
+                                          const void* new_v, void* cache0, void* cache1,
+                                          const int32_t* kv_lens, const int32_t* page_table,
+                                          const int32_t* cu_kv_lens, const void* bias0,
+                                          const void* bias1, void* const* gathered,
+                                          void* const* flags, int32_t world, int32_t rank,
+                                          int32_t wait, void* workspace, void* stream_v) {
+  if (!plan || !gathered || !flags) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_rpa_decode_allgather_enqueue: null argument");
+  if (world < 1 || world > CAKE_MAX_WORLD || rank < 0 || rank >= world)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa all-gather: bad mesh world=%d rank=%d", world, rank);
+  const cake_rpa_desc& d = plan->d;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const size_t slice_bytes = static_cast<size_t>(d.num_seqs) * d.q_heads * d.head_dim * 2;
+  // Own buffer first, so the local copy does not wait behind link traffic.
+  for (int i = 0; i < world; ++i) {
+    const int r = (rank + i) % world;
+    if (!gathered[r] || !flags[r]) return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa all-gather: missing buffer of rank %d", r);
+    plan->gather_out[i] = static_cast<char*>(gathered[r]) + rank * slice_bytes;
+  }
+  if (!plan->gather_flag_table) {
+    CAKE_CUDA_TRY(cudaMalloc(&plan->gather_flag_table, sizeof(void*) * CAKE_MAX_WORLD));
+  }
+  bool flags_changed = false;
+  for (int r = 0; r < world; ++r) flags_changed |= plan->gather_flags_seen[r] != flags[r];
+  if (flags_changed) {
+    CAKE_CUDA_TRY(cudaMemcpyAsync(plan->gather_flag_table, flags, sizeof(void*) * world, cudaMemcpyHostToDevice, stream));
+    for (int r = 0; r < world; ++r) plan->gather_flags_seen[r] = flags[r];
+  }
+  plan->gather_world = world;
+  int32_t rc = cake_rpa_decode_enqueue(plan, q, new_k, new_v, cache0, cache1, kv_lens, page_table, cu_kv_lens, bias0, bias1,
+                                       plan->gather_out[0], workspace, stream_v);
+  plan->gather_world = 0;
+  if (rc) return rc;
+  plan->gather_epoch += 1;
+  cake::cake_rpa_gather_sync_sm100<<<1, 32, 0, stream>>>(plan->gather_flag_table, world, rank, plan->gather_epoch, wait,
+                                                         plan->status.dev);
+  CAKE_CUDA_TRY(cudaGetLastError());
+  plan->launches += 1;
+  return CAKE_OK;
+}
+
 int32_t cake_rpa_status(cake_rpa* plan, void* stream_v, cake_status* out) {
   if (!plan || !out) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_rpa_status: null argument");
   int32_t rc = plan->status.read_and_clear(static_cast<cudaStream_t>(stream_v), out);
   if (rc) return rc;
+  if (out->code == 2) return fail(CAKE_ERR_TIMEOUT, "rpa all-gather: rank %d never heard from rank %d", out->detail0, out->detail1);
   if (out->code == 1) return fail(CAKE_ERR_TIMEOUT, "rpa: bounded barrier wait ran out (block %d item %d stage %d)", out->detail0, out->detail1, out->detail2);
   if (out->code == 3) return fail(CAKE_ERR_DEVICE_CHECK, "rpa: page index out of range (sequence %d page slot %d value %d)", out->detail0, out->detail1, out->detail2);
   if (out->code == 4) return fail(CAKE_ERR_DEVICE_CHECK, "rpa: sequence metadata out of range (%d, %d, %d)", out->detail0, out->detail1, out->detail2);

@@ -98,6 +98,17 @@ class SymmetricBuffer:
                 self._opened.append(mapped.value)
             mesh.barrier()
 
+    def as_tensor(self, dtype: torch.dtype, shape: tuple[int, ...]) -> torch.Tensor:
+        """A torch view of this rank's own allocation (no copy), through the CUDA array interface."""
+
+        class _Exported:
+            pass
+
+        exported = _Exported()
+        exported.__cuda_array_interface__ = {"shape": (self.nbytes,), "typestr": "|u1", "data": (self.own, False), "version": 2}
+        flat = torch.as_tensor(exported, device=self.mesh.device)
+        return flat.view(dtype).view(shape)
+
     def close(self) -> None:
         for pointer in self._opened:
             self._lib.cake_ipc_close(pointer)

@@ -118,6 +118,20 @@ class RpaDecodeExecutable:
             )
         )
 
+    def enqueue_allgather(self, q, cache0, cache1, kv_lens, page_table, gathered_pointers: list[int], flag_pointers: list[int],
+                          world: int, rank: int, *, wait: bool = True) -> None:
+        """Decode this rank's KV-head shard and write its outputs into every rank's gathered buffer
+        (``gathered_pointers[r]`` / ``flag_pointers[r]``: rank r's buffers as mapped in this process)."""
+        array = ctypes.c_void_p * world
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _native.check(
+            self._lib.cake_rpa_decode_allgather_enqueue(
+                self._handle, q.data_ptr(), None, None, cache0.data_ptr(), None if cache1 is None else cache1.data_ptr(),
+                kv_lens.data_ptr(), page_table.data_ptr(), None, None, None, array(*gathered_pointers), array(*flag_pointers),
+                world, rank, 1 if wait else 0, self.workspace.data_ptr(), stream,
+            )
+        )
+
     def status(self) -> tuple[int, int, int, int]:
         word = _native.CakeStatus()
         stream = torch.cuda.current_stream(self.device).cuda_stream
