@@ -151,7 +151,7 @@ int32_t cake_matmul_rs_launches_per_enqueue(const cake_matmul_rs* plan);
 
 typedef struct cake_rpa_desc {
   int32_t num_seqs;
-  int32_t num_q_tokens;   /* sum of query lengths (== num_seqs for pure decode) */
+  int32_t num_q_tokens;   /* sum of query lengths (== num_seqs for pure decode; larger: cake_rpa_mixed_enqueue) */
   int32_t q_heads;
   int32_t kv_heads;
   int32_t head_dim;       /* 128 */
@@ -191,6 +191,22 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
                                 const int32_t* page_table, const int32_t* cu_kv_lens,
                                 const void* bias0, const void* bias1, void* out, void* workspace,
                                 void* stream);
+
+/* Ragged batch: sequences [0, num_decode_seqs) have one query token each and come first (the
+ * reference's `distribution` order, src/tpu_cake/rpa_owned_kernel.py:58-67); the others are prefill
+ * sequences whose q query tokens are the LAST q of their kv_len positions (causal: query token i
+ * sees positions 0..kv_len-q+i). The reference lowers decode batches only
+ * (src/tpu_cake/rpa_lowering.py:71-95 rejects anything else), so this call has the wrapped kernel's
+ * semantics (causal=1, src/tpu_cake/rpa_lowering.py:232-273) but no reference test behind it.
+ * q, out: bf16 [num_q_tokens, q_heads, 128]; new_k, new_v: bf16 [num_q_tokens, kv_heads, 128] (written
+ * into the cache first when update_cache == 1); cu_q_lens: i32 [num_seqs+1] on the device;
+ * num_decode_seqs: host value. Needs head_dim 128 and bias_mode 0. The decode sequences run through
+ * the decode kernels, the others through the tcgen05 prefill kernel. */
+int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k, const void* new_v,
+                               void* cache0, void* cache1, const int32_t* kv_lens,
+                               const int32_t* page_table, const int32_t* cu_kv_lens,
+                               const int32_t* cu_q_lens, int32_t num_decode_seqs, void* out,
+                               void* workspace, void* stream);
 
 /* Decode of this rank's KV-head shard with the all-gather of the outputs fused in: every output
  * row is written straight into the gathered buffer of every rank over peer memory (P2P stores), then

@@ -1,4 +1,4 @@
-"""Oracle for Inkling ragged paged attention, pure decode (numpy, float32).
+"""Oracle for Inkling ragged paged attention (numpy, float32): pure decode, pinned; mixed batches, unpinned.
 
 Restates the reference's two numpy oracles:
   - ``rpa_separate``: separate K / V caches [pages, page_size, heads, dim], a 2-D page table and a
@@ -168,3 +168,74 @@ def fused_cache_from_separate(key_cache: np.ndarray, value_cache: np.ndarray) ->
     """[P,ps,H,D] x 2 -> fused [P,ps,H,2,D]: head h's K at interleaved index 2h, V at 2h+1
     (pack = 2, inkling_rpa.py:524-534)."""
     return np.ascontiguousarray(np.stack([key_cache, value_cache], axis=3))
+
+
+def rpa_mixed(
+    queries: np.ndarray,
+    new_keys: np.ndarray,
+    new_values: np.ndarray,
+    cache: np.ndarray,
+    kv_lengths: np.ndarray,
+    page_indices: np.ndarray,
+    cu_q_lens: np.ndarray,
+    cu_kv_lens: np.ndarray,
+    *,
+    scale: float | None = None,
+    update_cache: bool = True,
+) -> tuple[np.ndarray, np.ndarray]:
+    """Ragged batch (decode and prefill sequences mixed) on the fused cache, causal, no bias.
+
+    PARITY UNPINNED: the reference has no oracle, test or golden vector for query lengths above one
+    (its oracle rejects them, src/tpu_cake/workloads/inkling_rpa.py:505-509). This function extends
+    ``rpa_fused`` by the semantics of the kernel the reference wraps (causal=1, new tokens appended
+    at the end of each sequence; src/tpu_cake/rpa_lowering.py:232-273): sequence s owns query
+    tokens [cu_q[s], cu_q[s+1]); query token i of a sequence with q query tokens and kv_len cached
+    tokens sits at position kv_len - q + i, its K/V are written there first, and it attends to
+    positions 0..kv_len - q + i. tests/test_oracle_golden.py ties it to the pinned decode oracle:
+    every query token equals a one-token decode at its own length.
+    Returns (output [T,Hq,D] bfloat16, updated cache bfloat16).
+    """
+    q = np.asarray(queries, dtype=np.float32)
+    k_new = np.asarray(new_keys, dtype=np.float32)
+    v_new = np.asarray(new_values, dtype=np.float32)
+    cache = np.array(np.asarray(cache, dtype=np.float32))
+    lengths = np.asarray(kv_lengths, dtype=np.int64)
+    pages_flat = np.asarray(page_indices, dtype=np.int64)
+    cu_q = np.asarray(cu_q_lens, dtype=np.int64)
+    cu_kv = np.asarray(cu_kv_lens, dtype=np.int64)
+    page_size, pack = cache.shape[1], cache.shape[3]
+    dim, kv_heads = q.shape[-1], k_new.shape[1]
+    if scale is None:
+        scale = 1.0 / dim
+    count = lengths.shape[0]
+    if update_cache:
+        for s in range(count):
+            q_len = int(cu_q[s + 1] - cu_q[s])
+            for i in range(q_len):
+                position = int(lengths[s]) - q_len + i
+                page = pages_flat[int(cu_kv[s]) // page_size + position // page_size]
+                for head in range(kv_heads):
+                    for which, source in ((0, k_new), (1, v_new)):
+                        index = 2 * head + which
+                        row = cache[page, position % page_size, index // pack, index % pack]
+                        row[:] = 0.0
+                        row[:dim] = source[cu_q[s] + i, head]
+    flat = cache.reshape(cache.shape[0], page_size, cache.shape[2] * pack, cache.shape[4])
+    out = np.zeros_like(q, dtype=np.float32)
+    group = q.shape[1] // kv_heads
+    for s in range(count):
+        length, q_len = int(lengths[s]), int(cu_q[s + 1] - cu_q[s])
+        if q_len == 0:
+            continue
+        first = int(cu_kv[s]) // page_size
+        pages = pages_flat[first : first + math.ceil(length / page_size)]
+        rows = flat[pages].reshape(-1, flat.shape[2], flat.shape[3])[:length]
+        keys = rows[:, 0::2, :dim][:, :kv_heads]      # [L, Hkv, D]
+        values = rows[:, 1::2, :dim][:, :kv_heads]
+        q_seq = q[cu_q[s] : cu_q[s + 1]].reshape(q_len, kv_heads, group, dim)
+        scores = np.einsum("thgd,lhd->thgl", q_seq, keys, dtype=np.float32) * np.float32(scale)
+        visible = np.arange(length)[None, :] <= (length - q_len + np.arange(q_len))[:, None]
+        scores = np.where(visible[:, None, None, :], scores, -np.inf).astype(np.float32)
+        weights = _softmax_rows(scores)
+        out[cu_q[s] : cu_q[s + 1]] = np.einsum("thgl,lhd->thgd", weights, values, dtype=np.float32).reshape(q_len, -1, dim)
+    return out.astype(BF16), cache.astype(BF16)

@@ -73,7 +73,7 @@ def test_matmul_create_rejects_bad_descriptors(overrides, code, fragment):
 @pytest.mark.parametrize(
     "overrides, code, fragment",
     [
-        ({"num_q_tokens": 9}, _native.CAKE_ERR_UNSUPPORTED, "pure decode"),
+        ({"num_q_tokens": 7}, _native.CAKE_ERR_INVALID_ARGUMENT, "query tokens for"),
         ({"q_heads": 6, "kv_heads": 4}, _native.CAKE_ERR_INVALID_ARGUMENT, "multiple of kv_heads"),
         ({"q_heads": 36, "kv_heads": 2}, _native.CAKE_ERR_UNSUPPORTED, "at most 8"),
         ({"head_dim": 256, "head_dim_padded": 256}, _native.CAKE_ERR_UNSUPPORTED, "head_dim"),

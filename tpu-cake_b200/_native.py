@@ -56,6 +56,7 @@ EXPORTED_SYMBOLS = (
     "cake_rpa_destroy",
     "cake_rpa_workspace_bytes",
     "cake_rpa_decode_enqueue",
+    "cake_rpa_mixed_enqueue",
     "cake_rpa_decode_allgather_enqueue",
     "cake_rpa_decode_static_scratch",
     "cake_rpa_status",
@@ -187,6 +188,8 @@ def load() -> ctypes.CDLL:
     lib.cake_rpa_workspace_bytes.argtypes = [vp]
     lib.cake_rpa_decode_enqueue.restype = i32
     lib.cake_rpa_decode_enqueue.argtypes = [vp] + [vp] * 12 + [vp]
+    lib.cake_rpa_mixed_enqueue.restype = i32
+    lib.cake_rpa_mixed_enqueue.argtypes = [vp] * 10 + [i32, vp, vp, vp]
     lib.cake_rpa_decode_allgather_enqueue.restype = i32
     lib.cake_rpa_decode_allgather_enqueue.argtypes = (
         [vp] * 11 + [ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i32, vp, vp]

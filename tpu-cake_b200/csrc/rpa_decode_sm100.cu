@@ -762,6 +762,8 @@ __global__ void cake_rpa_gather_sync_sm100(unsigned long long* const* flags_of, 
 
 }  // namespace cake
 
+#include "rpa_prefill_sm100.cuh"
+
 // ====================================================================================== host
 
 struct cake_rpa {
@@ -782,6 +784,16 @@ struct cake_rpa {
   unsigned long long gather_epoch = 0;
   unsigned long long** gather_flag_table = nullptr;  // device copy of the W flag-array pointers
   void* gather_flags_seen[CAKE_MAX_WORLD] = {};
+  // mixed batches: the decode kernels run on the first `active_seqs` sequences (0 = all) and leave
+  // the cache update to the ragged update kernel
+  int active_seqs = 0;
+  bool skip_update = false;
+  size_t off_pf_entries = 0;
+  int64_t max_pf_entries = 0;
+  const void* last_q = nullptr;
+  const void* last_pf_c0 = nullptr;
+  const void* last_pf_c1 = nullptr;
+  CUtensorMap tmap_q, tmap_pf_k, tmap_pf_v;
 };
 
 namespace {
@@ -797,7 +809,9 @@ void rpa_layout_workspace(cake_rpa* plan, int group) {
   plan->off_tail = align_up(plan->off_item_desc + 16 * (plan->max_items / d.kv_heads + 1), 256);
   plan->off_part_ml = align_up(plan->off_tail + sizeof(int32_t) * d.num_seqs, 256);
   plan->off_part_o = align_up(plan->off_part_ml + sizeof(float) * 2 * group * plan->max_items, 256);
-  plan->ws_bytes = plan->off_part_o + sizeof(float) * 128 * group * plan->max_items;
+  plan->off_pf_entries = align_up(plan->off_part_o + sizeof(float) * 128 * group * plan->max_items, 256);
+  plan->max_pf_entries = (d.num_q_tokens + 127) / 128 + d.num_seqs;
+  plan->ws_bytes = plan->off_pf_entries + 16 * static_cast<size_t>(plan->max_pf_entries);
 }
 
 int32_t rpa_encode_maps(cake_rpa* plan, const void* c0, const void* c1) {
@@ -831,9 +845,8 @@ int32_t cake_rpa_create(const cake_rpa_desc* desc, cake_rpa** out) {
   const cake_rpa_desc& d = *desc;
   if (d.num_seqs <= 0 || d.q_heads <= 0 || d.kv_heads <= 0 || d.total_pages <= 0)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: num_seqs, q_heads, kv_heads and total_pages must be positive");
-  if (d.num_q_tokens != d.num_seqs)
-    return fail(CAKE_ERR_UNSUPPORTED, "rpa: only pure decode (one query token per sequence) is lowered; got %d tokens for %d sequences",
-                d.num_q_tokens, d.num_seqs);
+  if (d.num_q_tokens < d.num_seqs)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: %d query tokens for %d sequences", d.num_q_tokens, d.num_seqs);
   if (d.q_heads % d.kv_heads != 0)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: q_heads %d must be a multiple of kv_heads %d", d.q_heads, d.kv_heads);
   if (d.q_heads / d.kv_heads > 8)
@@ -920,11 +933,16 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   if (!plan || !q || !cache0 || !kv_lens || !page_table || !out || !workspace)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_rpa_decode_enqueue: null argument");
   const cake_rpa_desc& d = plan->d;
+  if (d.num_q_tokens != d.num_seqs && plan->active_seqs == 0)
+    return fail(CAKE_ERR_UNSUPPORTED, "rpa: the decode call takes one query token per sequence (got %d tokens for %d sequences); "
+                "use cake_rpa_mixed_enqueue", d.num_q_tokens, d.num_seqs);
+  const int num_seqs = plan->active_seqs ? plan->active_seqs : d.num_seqs;
+  const bool update = d.update_cache && !plan->skip_update;
   if (d.cache_layout == CAKE_RPA_CACHE_SEPARATE && !cache1)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: separate cache layout needs a value cache");
   if (d.table_layout == CAKE_RPA_TABLE_FLAT && !cu_kv_lens)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: flat page table needs cu_kv_lens");
-  if (d.update_cache && (!new_k || !new_v))
+  if (update && (!new_k || !new_v))
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: update_cache needs new_k and new_v");
   if (d.bias_mode == 1 && !bias0) return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: bias_mode 1 needs bias0");
   if (d.bias_mode == 2 && (!bias0 || !bias1)) return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: bias_mode 2 needs states and projection");
@@ -954,7 +972,7 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   p.kv_lens = kv_lens;
   p.page_table = page_table;
   p.cu_kv_lens = cu_kv_lens;
-  p.num_seqs = d.num_seqs;
+  p.num_seqs = num_seqs;
   p.q_heads = d.q_heads;
   p.kv_heads = d.kv_heads;
   p.group = d.q_heads / d.kv_heads;
@@ -992,8 +1010,8 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
   cake::cake_rpa_plan_sm100<<<1, 256, 0, stream>>>(p);
   CAKE_CUDA_TRY(cudaGetLastError());
   ++launches;
-  if (d.update_cache) {
-    cake::cake_rpa_cache_update_sm100<<<d.num_seqs, 256, 0, stream>>>(
+  if (update) {
+    cake::cake_rpa_cache_update_sm100<<<num_seqs, 256, 0, stream>>>(
         p, static_cast<const __nv_bfloat16*>(new_k), static_cast<const __nv_bfloat16*>(new_v),
         static_cast<__nv_bfloat16*>(cache0), static_cast<__nv_bfloat16*>(cache1));
     CAKE_CUDA_TRY(cudaGetLastError());
@@ -1009,7 +1027,7 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
       plan->tmap_k, plan->tmap_v, p);
   CAKE_CUDA_TRY(cudaGetLastError());
   ++launches;
-  cake::cake_rpa_combine_sm100<<<(d.num_seqs * d.q_heads + 3) / 4, 128, 0, stream>>>(p);
+  cake::cake_rpa_combine_sm100<<<(num_seqs * d.q_heads + 3) / 4, 128, 0, stream>>>(p);
   CAKE_CUDA_TRY(cudaGetLastError());
   ++launches;
   plan->launches = launches;
@@ -1054,6 +1072,135 @@ int32_t cake_rpa_decode_allgather_enqueue(cake_rpa* plan, const void* q, const v
                                                          plan->status.dev);
   CAKE_CUDA_TRY(cudaGetLastError());
   plan->launches += 1;
+  return CAKE_OK;
+}
+
+int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k, const void* new_v,
+                               void* cache0, void* cache1, const int32_t* kv_lens,
+                               const int32_t* page_table, const int32_t* cu_kv_lens,
+                               const int32_t* cu_q_lens, int32_t num_decode_seqs, void* out,
+                               void* workspace, void* stream_v) {
+  if (!plan || !q || !cache0 || !kv_lens || !page_table || !cu_q_lens || !out || !workspace)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_rpa_mixed_enqueue: null argument");
+  const cake_rpa_desc& d = plan->d;
+  if (num_decode_seqs < 0 || num_decode_seqs > d.num_seqs)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa mixed: num_decode_seqs %d outside [0, %d]", num_decode_seqs, d.num_seqs);
+  if (d.head_dim != 128) return fail(CAKE_ERR_UNSUPPORTED, "rpa mixed: head_dim must be 128, got %d", d.head_dim);
+  if (d.bias_mode != 0) return fail(CAKE_ERR_UNSUPPORTED, "rpa mixed: attention bias is lowered for decode batches only");
+  if (d.cache_layout == CAKE_RPA_CACHE_SEPARATE && !cache1)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: separate cache layout needs a value cache");
+  if (d.table_layout == CAKE_RPA_TABLE_FLAT && !cu_kv_lens)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: flat page table needs cu_kv_lens");
+  if (d.update_cache && (!new_k || !new_v))
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: update_cache needs new_k and new_v");
+  if ((reinterpret_cast<uintptr_t>(cache0) | reinterpret_cast<uintptr_t>(cache1) | reinterpret_cast<uintptr_t>(workspace)) & 255)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: caches and workspace must be 256-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: q and out must be 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int group = d.q_heads / d.kv_heads;
+
+  // Tensor maps: queries [tokens][q_heads*128] in boxes of 64 columns x 128 rows; caches in boxes of
+  // one 64-wide half row x one page (or the part of it a stage takes).
+  if (q != plan->last_q) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(d.q_heads) * 128, static_cast<uint64_t>(d.num_q_tokens)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(d.q_heads) * 256};
+    const uint32_t box[2] = {64, 128};
+    int32_t rc = cake::encode_tensor_map(&plan->tmap_q, q, 2, dims, strides, box, true);
+    if (rc) return rc;
+    plan->last_q = q;
+  }
+  if (cache0 != plan->last_pf_c0 || cache1 != plan->last_pf_c1) {
+    const uint64_t ps = d.page_size;
+    const bool fused = d.cache_layout == CAKE_RPA_CACHE_FUSED;
+    const uint64_t heads = fused ? 2ull * d.kv_heads : static_cast<uint64_t>(d.kv_heads);
+    const uint64_t dims[5] = {64, ps, 2, heads, static_cast<uint64_t>(d.total_pages)};
+    const uint64_t strides[4] = {heads * 256, 128, 256, ps * heads * 256};
+    const uint32_t box[5] = {64, static_cast<uint32_t>(d.page_size), 1, 1, 1};
+    int32_t rc = cake::encode_tensor_map(&plan->tmap_pf_k, cache0, 5, dims, strides, box, true);
+    if (rc) return rc;
+    if (fused) {
+      plan->tmap_pf_v = plan->tmap_pf_k;
+    } else {
+      rc = cake::encode_tensor_map(&plan->tmap_pf_v, cache1, 5, dims, strides, box, true);
+      if (rc) return rc;
+    }
+    plan->last_pf_c0 = cache0;
+    plan->last_pf_c1 = cache1;
+  }
+
+  char* ws = static_cast<char*>(workspace);
+  cake::PrefillParams pp;
+  memset(&pp, 0, sizeof(pp));
+  pp.q = static_cast<const __nv_bfloat16*>(q);
+  pp.out = static_cast<__nv_bfloat16*>(out);
+  pp.kv_lens = kv_lens;
+  pp.cu_q_lens = cu_q_lens;
+  pp.first_seq = num_decode_seqs;
+  pp.sub = group % 2 == 0 ? 2 : 1;
+  pp.heads_items = d.q_heads / pp.sub;
+  pp.work_counter = reinterpret_cast<int32_t*>(ws + 64);
+  pp.entry_count = reinterpret_cast<int32_t*>(ws + 128);
+  pp.entries = reinterpret_cast<int4*>(ws + plan->off_pf_entries);
+  pp.max_entries = static_cast<int32_t>(plan->max_pf_entries);
+  pp.num_q_tokens = d.num_q_tokens;
+  cake::RpaParams& p = pp.r;
+  p.kv_lens = kv_lens;
+  p.page_table = page_table;
+  p.cu_kv_lens = cu_kv_lens;
+  p.num_seqs = d.num_seqs;
+  p.q_heads = d.q_heads;
+  p.kv_heads = d.kv_heads;
+  p.group = group;
+  p.head_dim = d.head_dim;
+  p.page_size = d.page_size;
+  p.log2_ps = plan->log2_ps;
+  p.box_tokens = d.page_size;   // page_size <= 32 < one 64-token stage: one box per page and half row
+  p.log2_box = plan->log2_ps;
+  p.table_layout = d.table_layout;
+  p.max_pages_per_seq = d.max_pages_per_seq;
+  p.table_len = d.max_pages_per_seq;
+  p.total_pages = static_cast<int32_t>(d.total_pages);
+  p.fused = d.cache_layout == CAKE_RPA_CACHE_FUSED;
+  p.scale_log2 = d.sm_scale * 1.4426950408889634f;
+  p.status = plan->status.dev;
+
+  int launches = 0;
+  if (d.update_cache) {
+    cake::cake_rpa_ragged_update_sm100<<<d.num_q_tokens, 256, 0, stream>>>(
+        pp, static_cast<const __nv_bfloat16*>(new_k), static_cast<const __nv_bfloat16*>(new_v),
+        static_cast<__nv_bfloat16*>(cache0), static_cast<__nv_bfloat16*>(cache1));
+    CAKE_CUDA_TRY(cudaGetLastError());
+    ++launches;
+  }
+  cake::cake_rpa_prefill_plan_sm100<<<1, 256, 0, stream>>>(pp);
+  CAKE_CUDA_TRY(cudaGetLastError());
+  ++launches;
+  if (num_decode_seqs > 0) {
+    // Decode sequences come first and own query tokens 0..num_decode_seqs-1 (checked by the plan
+    // kernel above), so the decode kernels index q and out by sequence as in a pure decode batch.
+    plan->active_seqs = num_decode_seqs;
+    plan->skip_update = true;
+    const int32_t rc = cake_rpa_decode_enqueue(plan, q, new_k, new_v, cache0, cache1, kv_lens, page_table, cu_kv_lens,
+                                               nullptr, nullptr, out, workspace, stream_v);
+    plan->active_seqs = 0;
+    plan->skip_update = false;
+    if (rc) return rc;
+    launches += plan->launches;
+  }
+  if (num_decode_seqs < d.num_seqs) {
+    static bool configured = false;
+    if (!configured) {
+      CAKE_CUDA_TRY(cudaFuncSetAttribute(cake::cake_rpa_prefill_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         cake::kPfSmemBytes));
+      configured = true;
+    }
+    cake::cake_rpa_prefill_sm100<<<plan->sm_count, cake::kPfThreads, cake::kPfSmemBytes, stream>>>(
+        plan->tmap_q, plan->tmap_pf_k, plan->tmap_pf_v, pp);
+    CAKE_CUDA_TRY(cudaGetLastError());
+    ++launches;
+  }
+  plan->launches = launches;
   return CAKE_OK;
 }
 

@@ -1,4 +1,4 @@
-"""CUDA backend lowering of Inkling ragged paged attention (pure decode).
+"""CUDA backend lowering of Inkling ragged paged attention (decode, and mixed prefill/decode batches).
 
 Mirror of the reference's RPA backend (src/tpu_cake/rpa_lowering.py):
   - ``CudaFusedRpaPlan`` has the tensor-contract fields of ``FusedRpaPlan`` (:131-170) and its
@@ -6,6 +6,10 @@ Mirror of the reference's RPA backend (src/tpu_cake/rpa_lowering.py):
     sm_100a kernels instead of handing the inputs to a pinned external JAX kernel.
   - ``preflight_decode_metadata`` is the integer validation of ``_preflight_decode_metadata``
     (:71-128), same checks, same messages.
+  - ``CudaMixedRpaPlan`` / ``preflight_mixed_metadata`` extend the same contract to batches whose
+    sequences carry more than one query token, which the reference's adapter rejects (:76-86): decode
+    sequences first, then prefill sequences, as its ``distribution`` triple orders them
+    (src/tpu_cake/rpa_owned_kernel.py:58-67).
   - ``CudaPagedAttentionPlan`` lowers the prototype op ``tpu_schedule.ragged_paged_attention``
     (separate K / V caches, 2-D page table, dense bias;
     src/tpu_cake/dialects/tpu_schedule.py:2003-2103), which has no lowering in the reference.
@@ -88,6 +92,46 @@ def preflight_decode_metadata(inputs: tuple, input_shapes: tuple[tuple[int, ...]
                 raise ValueError("fused RPA active write page is shared across sequences")
 
 
+def preflight_mixed_metadata(inputs: tuple, input_shapes: tuple[tuple[int, ...], ...]) -> int:
+    """Integer validation of a ragged batch, in int64 on the host, in the style of
+    ``preflight_decode_metadata``. Returns the number of leading decode sequences."""
+    lengths = np.asarray(_to_host(inputs[4]), dtype=np.int64)
+    page_indices = np.asarray(_to_host(inputs[5]), dtype=np.int64)
+    cu_q = np.asarray(_to_host(inputs[6]), dtype=np.int64)
+    cu_kv = np.asarray(_to_host(inputs[7]), dtype=np.int64)
+    distribution = np.asarray(_to_host(inputs[8]), dtype=np.int64)
+    tokens = input_shapes[0][0]
+    count = input_shapes[4][0]
+    if distribution.shape != (3,) or not (0 <= distribution[0] <= distribution[1] <= distribution[2] == count):
+        raise ValueError(f"ragged RPA distribution must be (decode end, prefill end, {count}), got {tuple(int(v) for v in distribution)}")
+    if cu_q.shape != (count + 1,) or cu_q[0] != 0 or np.any(np.diff(cu_q) < 1) or cu_q[-1] != tokens:
+        raise ValueError("ragged RPA cumulative query lengths must start at 0, grow by at least one per sequence and end at the token count")
+    q_lens = np.diff(cu_q)
+    decode_end = int(distribution[0])
+    if np.any(q_lens[:decode_end] != 1):
+        raise ValueError("ragged RPA decode sequences must come first with one query token each")
+    if np.any(lengths <= 0) or np.any(lengths < q_lens):
+        raise ValueError("ragged RPA KV lengths must be positive and include the query tokens")
+    total_pages, page_size = input_shapes[3][0], input_shapes[3][1]
+    if np.any(lengths > total_pages * page_size):
+        raise ValueError("fused RPA KV length exceeds total cache capacity")
+    padded = -(-lengths // page_size) * page_size
+    expected_cu_kv = np.zeros(count + 1, dtype=np.int64)
+    np.cumsum(padded, out=expected_cu_kv[1:])
+    if cu_kv.shape != expected_cu_kv.shape or np.any(cu_kv != expected_cu_kv):
+        raise ValueError("fused RPA cumulative KV lengths must be page-aligned")
+    needed = int(expected_cu_kv[-1]) // page_size
+    if needed > page_indices.size:
+        raise ValueError("fused RPA page table cannot cover all KV lengths")
+    used = page_indices[:needed]
+    if np.any(used < 0) or np.any(used >= total_pages):
+        raise ValueError("fused RPA page index is outside the fused cache")
+    # Every sequence writes its new tokens, so no physical page may be shared at all.
+    if np.unique(used).size != used.size:
+        raise ValueError("ragged RPA page table aliases a physical page")
+    return decode_end
+
+
 def _to_host(value):
     if isinstance(value, torch.Tensor):
         return value.detach().cpu().numpy()
@@ -115,6 +159,19 @@ class RpaDecodeExecutable:
             self._lib.cake_rpa_decode_enqueue(
                 self._handle, ptr(q), ptr(new_k), ptr(new_v), ptr(cache0), ptr(cache1), ptr(kv_lens),
                 ptr(page_table), ptr(cu_kv_lens), ptr(bias0), ptr(bias1), ptr(out), self.workspace.data_ptr(), stream,
+            )
+        )
+
+    def enqueue_mixed(self, q, new_k, new_v, cache0, cache1, kv_lens, page_table, cu_kv_lens, cu_q_lens, num_decode_seqs: int, out) -> None:
+        """Ragged batch: ``num_decode_seqs`` one-token sequences first, prefill sequences after."""
+        def ptr(t):
+            return None if t is None else t.data_ptr()
+
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _native.check(
+            self._lib.cake_rpa_mixed_enqueue(
+                self._handle, ptr(q), ptr(new_k), ptr(new_v), ptr(cache0), ptr(cache1), ptr(kv_lens), ptr(page_table),
+                ptr(cu_kv_lens), ptr(cu_q_lens), int(num_decode_seqs), ptr(out), self.workspace.data_ptr(), stream,
             )
         )
 
@@ -278,6 +335,101 @@ class CudaFusedRpaPlan:
     def run_preflighted(self, executable: RpaDecodeExecutable, *inputs) -> tuple[torch.Tensor, torch.Tensor]:
         self.preflight(*inputs)
         return self.invoke(executable, *inputs)
+
+
+@dataclass(frozen=True)
+class CudaMixedRpaPlan:
+    """Ragged batch on the fused cache: ``sequences`` sequences own ``tokens`` query tokens
+    (decode sequences first). Same 11-input signature as ``CudaFusedRpaPlan`` without relative bias."""
+
+    name: str
+    schedule_sha256: str
+    query_shape: tuple[int, ...]          # (tokens, q_heads, 128)
+    key_shape: tuple[int, ...]            # (tokens, kv_heads, 128)
+    fused_cache_shape: tuple[int, ...]
+    sequences: int
+    page_indices_shape: tuple[int, ...]
+    softmax_scale: float
+    causal: int = 1
+    kv_chunk_tokens: int = 0
+    update_cache: bool = True
+
+    def __post_init__(self) -> None:
+        tokens, q_heads, dim = self.query_shape
+        pages, page_size, combined, pack, dim_padded = self.fused_cache_shape
+        if pack != 2 or combined * pack != 2 * self.key_shape[1]:
+            raise ValueError("fused cache must interleave K and V of every KV head with pack = 2")
+        if self.key_shape[0] != tokens or self.key_shape[2] != dim or dim != 128 or dim_padded != 128:
+            raise UnsupportedRaggedBatch("ragged batches are lowered for head_dim 128")
+        if self.causal != 1:
+            raise ValueError("ragged batches are causal")
+        if not 0 < self.sequences <= tokens:
+            raise ValueError("every sequence owns at least one query token")
+
+    @property
+    def input_shapes(self) -> tuple[tuple[int, ...] | None, ...]:
+        return (self.query_shape, self.key_shape, self.key_shape, self.fused_cache_shape, (self.sequences,),
+                self.page_indices_shape, (self.sequences + 1,), (self.sequences + 1,), (3,), None, None)
+
+    def render_executable_source(self) -> str:
+        lines = ["# cake-b200 lowered fused ragged paged attention (mixed prefill / decode)", f"name = {self.name!r}",
+                 f"schedule_sha256 = {self.schedule_sha256!r}",
+                 "kernels = ('cake_rpa_ragged_update_sm100', 'cake_rpa_prefill_plan_sm100', 'cake_rpa_plan_sm100', "
+                 "'cake_rpa_decode_sm100', 'cake_rpa_combine_sm100', 'cake_rpa_prefill_sm100')"]
+        for name, shape in zip(FUSED_INPUT_NAMES, self.input_shapes, strict=True):
+            lines.append(f"{name}_shape = {shape}")
+        lines += [f"softmax_scale = {self.softmax_scale!r}", f"causal = {self.causal}",
+                  f"kv_chunk_tokens = {self.kv_chunk_tokens}", f"update_cache = {self.update_cache}", "abi_version = 1"]
+        return "\n".join(lines) + "\n"
+
+    def source_sha256(self) -> str:
+        return text_sha256(self.render_executable_source())
+
+    def preflight(self, *inputs) -> int:
+        return preflight_mixed_metadata(inputs, self.input_shapes)
+
+    def build(self, device: torch.device | None = None) -> RpaDecodeExecutable:
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        tokens, q_heads, dim = self.query_shape
+        pages, page_size, _, _, dim_padded = self.fused_cache_shape
+        desc = _native.RpaDesc(
+            num_seqs=self.sequences, num_q_tokens=tokens, q_heads=q_heads, kv_heads=self.key_shape[1], head_dim=dim,
+            head_dim_padded=dim_padded, page_size=page_size, cache_layout=_native.CAKE_RPA_CACHE_FUSED,
+            table_layout=_native.CAKE_RPA_TABLE_FLAT, max_pages_per_seq=self.page_indices_shape[0], total_pages=pages,
+            sm_scale=self.softmax_scale, bias_mode=0, bias_extent=0, rel_dim=0, update_cache=1 if self.update_cache else 0,
+            kv_chunk_tokens=self.kv_chunk_tokens, reserved=0,
+        )
+        return RpaDecodeExecutable(desc, device)
+
+    def invoke(self, executable: RpaDecodeExecutable, *inputs, out: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Runs the batch on device tensors; ``distribution`` (input 8) is read on the host. Returns
+        (output, cache); the cache is updated in place."""
+        if len(inputs) != len(FUSED_INPUT_NAMES):
+            raise ValueError(f"fused RPA takes {len(FUSED_INPUT_NAMES)} inputs, got {len(inputs)}")
+        q, k, v, cache, lens, pages, cu_q, cu_kv, distribution, states, projection = inputs
+        if states is not None or projection is not None:
+            raise UnsupportedRaggedBatch("relative bias is lowered for decode batches only")
+        device = executable.device
+        bf16, i32 = torch.bfloat16, torch.int32
+        _require(q, self.query_shape, bf16, "queries", device)
+        _require(cache, self.fused_cache_shape, bf16, "fused_cache", device)
+        _require(lens, (self.sequences,), i32, "kv_lengths", device)
+        _require(pages, self.page_indices_shape, i32, "page_indices", device)
+        _require(cu_q, (self.sequences + 1,), i32, "cumulative_query_lengths", device)
+        _require(cu_kv, (self.sequences + 1,), i32, "cumulative_kv_lengths", device)
+        if self.update_cache:
+            _require(k, self.key_shape, bf16, "keys", device)
+            _require(v, self.key_shape, bf16, "values", device)
+        decode_end = int(np.asarray(_to_host(distribution)).reshape(-1)[0])
+        if out is None:
+            out = torch.empty(self.query_shape, dtype=bf16, device=device)
+        executable.enqueue_mixed(q, k if self.update_cache else None, v if self.update_cache else None, cache, None,
+                                 lens, pages, cu_kv, cu_q, decode_end, out)
+        return out, cache
+
+
+class UnsupportedRaggedBatch(ValueError):
+    """A ragged batch the CUDA backend does not lower."""
 
 
 @dataclass(frozen=True)

@@ -108,6 +108,91 @@ def decode_algorithmic_bytes(kv_lens: np.ndarray, q_heads: int, kv_heads: int, h
     return kv + q_and_o + table
 
 
+@dataclass(frozen=True)
+class MixedConfig:
+    """A ragged batch: decode sequences first (one query token each), then prefill sequences whose
+    query tokens are appended after a prior context, in the order the reference's `distribution`
+    triple expects (src/tpu_cake/rpa_owned_kernel.py:58-67)."""
+
+    name: str
+    decode_seqs: int
+    prefill_seqs: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    page_size: int
+    decode_kv: tuple[int, int]      # inclusive range of decode KV lengths
+    prefill_q: tuple[int, int]      # inclusive range of prefill query lengths
+    prefill_prior: tuple[int, int]  # inclusive range of the context already cached
+
+    @property
+    def softmax_scale(self) -> float:
+        return 1.0 / math.sqrt(self.head_dim)
+
+
+MIXED_8_120 = MixedConfig("rpa-mixed-8prefill-120decode", 120, 8, 32, 8, 128, 16, (256, 32768), (512, 2048), (0, 4096))
+
+
+@dataclass(frozen=True)
+class MixedMetadata:
+    kv_lens: np.ndarray        # int32 [S]
+    cu_q_lens: np.ndarray      # int32 [S+1]
+    cu_kv_lens: np.ndarray     # int32 [S+1], page-aligned cumulative lengths
+    page_indices: np.ndarray   # int32 flat; sequence s starts at cu_kv_lens[s] // page_size
+    distribution: np.ndarray   # int32 [3]: (decode end, prefill end, mixed end)
+    total_pages: int
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.cu_q_lens[-1])
+
+
+def mixed_metadata(config: MixedConfig, *, spare_pages: int = 64) -> MixedMetadata:
+    """Seeded ragged metadata. cu_kv_lens is the cumulative sum of page-aligned lengths, the flat
+    page-index convention of the reference's preflight (src/tpu_cake/rpa_lowering.py:96-101); pages
+    are a seeded permutation of a pool just large enough (plus `spare_pages`)."""
+    generator = np.random.default_rng(semantic_seed(config.name, "inputs"))
+    decode_kv = generator.integers(config.decode_kv[0], config.decode_kv[1] + 1, size=config.decode_seqs)
+    prefill_q = generator.integers(config.prefill_q[0], config.prefill_q[1] + 1, size=config.prefill_seqs)
+    prior = generator.integers(config.prefill_prior[0], config.prefill_prior[1] + 1, size=config.prefill_seqs)
+    kv_lens = np.concatenate([decode_kv, prior + prefill_q]).astype(np.int32)
+    q_lens = np.concatenate([np.ones(config.decode_seqs, dtype=np.int64), prefill_q.astype(np.int64)])
+    return ragged_metadata(kv_lens, q_lens, config.page_size, config.decode_seqs, generator, spare_pages=spare_pages)
+
+
+def ragged_metadata(kv_lens, q_lens, page_size: int, decode_seqs: int, generator, *, spare_pages: int = 8) -> MixedMetadata:
+    kv_lens = np.asarray(kv_lens, dtype=np.int32)
+    q_lens = np.asarray(q_lens, dtype=np.int64)
+    pages_per_seq = -(-kv_lens.astype(np.int64) // page_size)
+    total_pages = int(pages_per_seq.sum()) + spare_pages
+    cu_q = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    cu_kv = np.concatenate([[0], np.cumsum(pages_per_seq * page_size)]).astype(np.int32)
+    page_indices = generator.permutation(total_pages)[: int(pages_per_seq.sum())].astype(np.int32)
+    count = len(kv_lens)
+    distribution = np.array([decode_seqs, count, count], dtype=np.int32)
+    return MixedMetadata(kv_lens, cu_q, cu_kv, page_indices, distribution, total_pages)
+
+
+def mixed_algorithmic_work(meta: MixedMetadata, q_heads: int, kv_heads: int, head_dim: int, *, elem_bytes: int = 2) -> dict:
+    """The two bounds of a mixed batch: HBM bytes (every valid cached token of every KV head read
+    once per sequence, queries read, outputs written, table entries and lengths read) and attention
+    FLOPs 4 * head_dim * q_heads * sum over query rows of the positions the row sees."""
+    kv = meta.kv_lens.astype(np.int64)
+    q_lens = np.diff(meta.cu_q_lens.astype(np.int64))
+    token_bytes = int(kv.sum()) * kv_heads * head_dim * elem_bytes * 2
+    query_bytes = int(q_lens.sum()) * q_heads * head_dim * elem_bytes * 2
+    table_bytes = int(len(meta.page_indices)) * 4 + 8 * len(kv)
+    visible = q_lens * kv - q_lens * (q_lens - 1) // 2  # row i of q rows sees kv - q + i + 1 positions
+    decode = q_lens == 1
+    return {
+        "bytes": token_bytes + query_bytes + table_bytes,
+        "flops": 4 * head_dim * q_heads * int(visible.sum()),
+        "decode_bytes": int(kv[decode].sum()) * kv_heads * head_dim * elem_bytes * 2,
+        "prefill_flops": 4 * head_dim * q_heads * int(visible[~decode].sum()),
+        "query_tokens": int(q_lens.sum()),
+    }
+
+
 def distributed_matmul_schedule(*, mesh_size: int = 4, m: int = 16, k: int = 32, n: int = 16, scatter_dimension: str = "N"):
     """The logical program ``einsum_local(lhs[M, K@t], rhs[K@t, N]) -> f32[M, N]{pending t:sum}``
     followed by ``reduce_scatter(axes=t, dim=scatter_dimension)``
