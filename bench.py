@@ -10,7 +10,8 @@ over the N ranks, result reduce-scattered along M into bf16 [8192/N, 8192] per G
 pass of cake_matmul_rs_sm100 (+ cake_reduce_slots_sm100 when N > 1). The total work is fixed, so
 scaling is "strong". A second object, "rpa_decode", reports the ragged-paged-attention decode
 (HBM-bound): 64 sequences on one GPU, or the 256-sequence configuration with KV heads sharded over
-the ranks and outputs all-gathered.
+the ranks and outputs all-gathered. A third object at N = 1, "rpa_mixed", reports the mixed batch
+(8 prefill + 120 decode sequences): the whole step, and its decode and prefill parts alone.
 
 Timing: CUDA events on the stream the kernels are launched on, one event pair per step, a write of
 a buffer larger than L2 between steps, barrier + synchronize on both sides of the timed region,
@@ -447,6 +448,123 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
     return result
 
 
+def bench_rpa_mixed(mesh, args, peaks, peak_kind) -> dict:
+    """Mixed batch (8 prefill + 120 decode sequences) on one GPU: the whole step, then the decode
+    sequences alone and the prefill sequences alone, so that each part can be held against the
+    bound that governs it (HBM bandwidth for decode, tensor throughput for prefill)."""
+    import torch
+
+    from tpu_cake_b200 import rpa_cuda_lowering, workloads
+
+    config = workloads.MIXED_8_120
+    if args.mixed_prefill_only:
+        import dataclasses
+
+        # Small case for profiler captures: the prefill sequences' distributions without the decode
+        # sequences (about 0.2 GB of KV pages instead of 8 GB).
+        config = dataclasses.replace(config, decode_seqs=0, name=config.name + "-prefill-part")
+    meta = workloads.mixed_metadata(config)
+    device = mesh.device
+    generator = torch.Generator(device=device).manual_seed(2000)
+    tokens = meta.num_tokens
+    cache = torch.empty((meta.total_pages, config.page_size, config.kv_heads, 2, config.head_dim), dtype=torch.bfloat16, device=device)
+    for start in range(0, meta.total_pages, 8192):
+        block = cache[start : start + 8192]
+        block.copy_(torch.randn(block.shape, generator=generator, device=device))
+    q = torch.randn((tokens, config.q_heads, config.head_dim), generator=generator, device=device).to(torch.bfloat16)
+    new_k = torch.randn((tokens, config.kv_heads, config.head_dim), generator=generator, device=device).to(torch.bfloat16)
+    new_v = torch.randn((tokens, config.kv_heads, config.head_dim), generator=generator, device=device).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    flush_buffer = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def flush():
+        flush_buffer.fill_(1)
+
+    def part(first: int, last: int, decode_end: int):
+        """Executable and arguments for sequences [first, last) of the batch."""
+        count = last - first
+        tok0, tok1 = int(meta.cu_q_lens[first]), int(meta.cu_q_lens[last])
+        page0 = int(meta.cu_kv_lens[first]) // config.page_size
+        pages = meta.page_indices[page0:]
+        plan = rpa_cuda_lowering.CudaMixedRpaPlan(
+            name=config.name, schedule_sha256="0" * 64, query_shape=(tok1 - tok0, config.q_heads, config.head_dim),
+            key_shape=(tok1 - tok0, config.kv_heads, config.head_dim), fused_cache_shape=tuple(cache.shape), sequences=count,
+            page_indices_shape=tuple(pages.shape), softmax_scale=config.softmax_scale, kv_chunk_tokens=args.kv_chunk,
+        )
+        executable = plan.build(device)
+        inputs = (
+            q[tok0:tok1], new_k[tok0:tok1], new_v[tok0:tok1], cache, torch.from_numpy(meta.kv_lens[first:last].copy()).to(device),
+            torch.from_numpy(pages.copy()).to(device), torch.from_numpy((meta.cu_q_lens[first : last + 1] - tok0).astype(np.int32)).to(device),
+            torch.from_numpy((meta.cu_kv_lens[first : last + 1] - meta.cu_kv_lens[first]).astype(np.int32)).to(device),
+            np.array([decode_end, count, count], dtype=np.int32), None, None,
+        )
+        result = out[tok0:tok1]
+
+        def call():
+            plan.invoke(executable, *inputs, out=result)
+
+        return executable, call
+
+    decode_count = int(meta.distribution[0])
+    total = len(meta.kv_lens)
+    steps = max(args.steps, 10)
+    timings = {}
+    launches = 0
+    parts = {"whole": (0, total, decode_count), "decode_only": (0, decode_count, decode_count), "prefill_only": (decode_count, total, 0)}
+    if decode_count == 0:
+        parts = {"whole": parts["whole"]}
+    for label, (first, last, decode_end) in parts.items():
+        executable, call = part(first, last, decode_end)
+        step = call
+        if not args.no_graph:
+            call()
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                call()
+            step = graph.replay
+        total_ms, per_step = timed_steps(mesh, step, steps, max(args.warmup, 3), flush)
+        executable.status()
+        timings[label] = total_ms / steps
+        if label == "whole":
+            launches = executable.launches_per_call * steps
+        executable.close()
+    work = workloads.mixed_algorithmic_work(meta, config.q_heads, config.kv_heads, config.head_dim)
+    update_bytes = tokens * config.kv_heads * config.head_dim * 2 * 2 * 2  # new K/V read and written into the cache
+    bytes_total = work["bytes"] + update_bytes
+    hbm_peak, tensor_peak = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops"])
+    bound_hbm_ms = bytes_total / (hbm_peak * 1e9) * 1e3
+    bound_tensor_ms = work["prefill_flops"] / (tensor_peak * 1e12) * 1e3
+    ms = timings["whole"]
+    timings.setdefault("prefill_only", ms)
+    timings.setdefault("decode_only", float("nan"))
+    return {
+        "metric": "rpa_mixed_step_ms", "value": ms, "unit": "ms", "higher_is_better": False, "steps": steps,
+        "config": {
+            "workload": config.name, "decode_seqs": config.decode_seqs, "prefill_seqs": config.prefill_seqs, "query_tokens": tokens,
+            "kv_tokens": int(meta.kv_lens.astype(np.int64).sum()), "q_heads": config.q_heads, "kv_heads": config.kv_heads,
+            "head_dim": config.head_dim, "page_size": config.page_size, "total_pages": meta.total_pages, "causal": True,
+            "cache_update": True, "l2": "256 MiB flush between steps", "launch": "stream" if args.no_graph else "cuda-graph",
+        },
+        "hbm_gbs": bytes_total / (ms * 1e-3) / 1e9,
+        "attention_tflops": work["flops"] / (ms * 1e-3) / 1e12,
+        "roofline": {
+            "bound": "hbm (decode sequences) then tensor (prefill sequences): the kernels run one after the other, so the bounds add",
+            "bound_ms": bound_hbm_ms + bound_tensor_ms, "hbm_bound_ms": bound_hbm_ms, "tensor_bound_ms": bound_tensor_ms,
+            "frac": (bound_hbm_ms + bound_tensor_ms) / ms, "algorithmic_bytes": bytes_total, "prefill_flops": work["prefill_flops"],
+            "peak_source": f"{peak_kind}: device copy bandwidth and cuBLAS bf16 burst",
+        },
+        "parts": {
+            "decode_only_ms": timings["decode_only"], "decode_only_gbs": work["decode_bytes"] / (timings["decode_only"] * 1e-3) / 1e9,
+            "decode_only_frac_of_hbm_peak": work["decode_bytes"] / (timings["decode_only"] * 1e-3) / 1e9 / hbm_peak,
+            "prefill_only_ms": timings["prefill_only"], "prefill_only_tflops": work["prefill_flops"] / (timings["prefill_only"] * 1e-3) / 1e12,
+            "prefill_only_frac_of_bf16_peak": work["prefill_flops"] / (timings["prefill_only"] * 1e-3) / 1e12 / tensor_peak,
+            "kernel": "cake_rpa_prefill_sm100 (tcgen05, TMEM accumulators) for prefill; cake_rpa_decode_sm100 for decode",
+        },
+        "gpu_launches": launches,
+    }
+
+
 def run_ours(args) -> None:
     import torch
 
@@ -457,7 +575,13 @@ def run_ours(args) -> None:
     if mesh.world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {mesh.world}: launch with torch.distributed.run")
     peaks, peak_kind = measured_peaks()
+    if args.only_mixed:
+        # Profiling aid: only the mixed prefill / decode batch runs.
+        if mesh.rank == 0:
+            print(json.dumps(bench_rpa_mixed(mesh, args, peaks, peak_kind)), flush=True)
+        return
     rpa = None if args.no_rpa else bench_rpa(mesh, args, peaks, peak_kind)
+    mixed = None if (args.no_rpa or args.no_mixed or mesh.world != 1) else bench_rpa_mixed(mesh, args, peaks, peak_kind)
     if args.only_rpa:
         # Profiling aid: only the attention kernels run (small enough for an ncu capture).
         if mesh.rank == 0:
@@ -482,6 +606,9 @@ def run_ours(args) -> None:
     if rpa is not None:
         line["rpa_decode"] = rpa
         line["gpu_launches"] += rpa["gpu_launches"]
+    if mixed is not None:
+        line["rpa_mixed"] = mixed
+        line["gpu_launches"] += mixed["gpu_launches"]
     if mesh.rank == 0:
         print(json.dumps(line), flush=True)
     if mesh.world > 1:
@@ -543,6 +670,10 @@ def main() -> None:
     parser.add_argument("--rpa-gather", choices=("p2p", "nccl"), default="p2p", help="how the sharded decode's outputs are all-gathered")
     parser.add_argument("--no-graph", action="store_true", help="launch the attention step kernel by kernel instead of replaying a CUDA graph")
     parser.add_argument("--only-rpa", action="store_true", help="run only the attention part (profiling aid)")
+    parser.add_argument("--only-mixed", action="store_true", help="run only the mixed prefill/decode batch (profiling aid)")
+    parser.add_argument("--no-mixed", action="store_true", help="skip the mixed prefill/decode batch")
+    parser.add_argument("--mixed-prefill-only", action="store_true",
+                        help="with --only-mixed: only prefill sequences, on a small page pool (for profiler captures)")
     parser.add_argument("--rpa-pool-pages", type=int, default=0,
                         help="shrink the KV page pool (same sequences and lengths; for captures that must hold little memory)")
     parser.add_argument("--no-cpu-baseline", action="store_true")

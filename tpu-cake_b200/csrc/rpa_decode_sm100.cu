@@ -1087,6 +1087,7 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa mixed: num_decode_seqs %d outside [0, %d]", num_decode_seqs, d.num_seqs);
   if (d.head_dim != 128) return fail(CAKE_ERR_UNSUPPORTED, "rpa mixed: head_dim must be 128, got %d", d.head_dim);
   if (d.bias_mode != 0) return fail(CAKE_ERR_UNSUPPORTED, "rpa mixed: attention bias is lowered for decode batches only");
+  if (!(d.sm_scale > 0.f)) return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa mixed: sm_scale must be positive");
   if (d.cache_layout == CAKE_RPA_CACHE_SEPARATE && !cache1)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: separate cache layout needs a value cache");
   if (d.table_layout == CAKE_RPA_TABLE_FLAT && !cu_kv_lens)
@@ -1100,8 +1101,7 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const int group = d.q_heads / d.kv_heads;
 
-  // Tensor maps: queries [tokens][q_heads*128] in boxes of 64 columns x 128 rows; caches in boxes of
-  // one 64-wide half row x one page (or the part of it a stage takes).
+  // Tensor maps: queries [tokens][q_heads*128] in boxes of 64 columns x 128 rows; caches below.
   if (q != plan->last_q) {
     const uint64_t dims[2] = {static_cast<uint64_t>(d.q_heads) * 128, static_cast<uint64_t>(d.num_q_tokens)};
     const uint64_t strides[1] = {static_cast<uint64_t>(d.q_heads) * 256};
@@ -1116,7 +1116,10 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
     const uint64_t heads = fused ? 2ull * d.kv_heads : static_cast<uint64_t>(d.kv_heads);
     const uint64_t dims[5] = {64, ps, 2, heads, static_cast<uint64_t>(d.total_pages)};
     const uint64_t strides[4] = {heads * 256, 128, 256, ps * heads * 256};
-    const uint32_t box[5] = {64, static_cast<uint32_t>(d.page_size), 1, 1, 1};
+    // Pages of 8 tokens or more: one box = an 8-token group with both halves of the row (and, in the
+    // fused cache, K and V of the head). Smaller pages: one box = one page of one half row.
+    const bool wide = d.page_size >= 8;
+    const uint32_t box[5] = {64, static_cast<uint32_t>(wide ? 8 : d.page_size), wide ? 2u : 1u, (wide && fused) ? 2u : 1u, 1};
     int32_t rc = cake::encode_tensor_map(&plan->tmap_pf_k, cache0, 5, dims, strides, box, true);
     if (rc) return rc;
     if (fused) {

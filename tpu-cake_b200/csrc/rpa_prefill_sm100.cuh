@@ -16,14 +16,17 @@
 //   cake_rpa_prefill_sm100         persistent, one CTA per SM, warp-specialised:
 //       warpgroup 0 / 1  softmax of query sub-tile 0 / 1 (one thread per query row; two query heads
 //                        of one KV head share every KV tile)
-//       warp 8           TMA producer: query tiles, then 64-token K/V stages gathered page by page
-//                        (four boxes per page: K lo/hi, V lo/hi halves of the 128-wide row, so that a
-//                        stage is laid out [half][token][128 B] as tcgen05 operands need; no multicast)
+//       warp 8           TMA producer: query tiles, then 64-token K/V stages gathered page by page.
+//                        A stage is laid out [8-token group][K lo | K hi | V lo | V hi][8 rows][128 B]
+//                        (lo / hi = the two 64-element halves of a 128-wide row): every 8-token group
+//                        is one 4 KiB box of the fused cache, and the groups are a uniform 4 KiB apart,
+//                        which is what the tcgen05 shared-memory descriptors need; no multicast
 //       warp 9           tcgen05.mma issuer: S = Q K^T (128x64, K-major operands) and PV = P V
 //                        (128x128, V consumed in place as an MN-major operand) into TMEM
 //     S is read from TMEM with tcgen05.ld (a thread owns a row, so the row maximum and sum need no
-//     shuffles), P goes back through shared memory in the 128-byte-swizzled K-major layout, the
-//     running output stays in registers in f32 and is rescaled as the maximum moves.
+//     shuffles), P goes back through shared memory in the 128-byte-swizzled K-major layout, and the
+//     output accumulates in TMEM over all KV steps; it is read, rescaled and written back
+//     (tcgen05.ld / tcgen05.st) only when a row maximum has moved by more than 2^8.
 #pragma once
 
 namespace cake {
@@ -33,11 +36,13 @@ constexpr int kPfTileQ = 128;
 constexpr int kPfTileKv = 64;
 constexpr int kPfStages = 3;
 constexpr int kPfQBytes = kPfTileQ * 256;        // one sub-tile of queries: [2 halves][128 rows][128 B]
-constexpr int kPfStageBytes = kPfTileKv * 512;   // K [2][64][128 B] then V [2][64][128 B]
+constexpr int kPfStageBytes = kPfTileKv * 512;   // [8 groups][K lo | K hi | V lo | V hi][8 rows][128 B]
+constexpr int kPfGroupBytes = 4096;             // one 8-token group of a stage
 constexpr int kPfPBytes = kPfTileQ * 128;        // P sub-tile: [128 rows][64 bf16]
 constexpr int kPfSmemBytes = 2 * kPfQBytes + kPfStages * kPfStageBytes + 2 * kPfPBytes + 1024 + 1024;
 constexpr uint32_t kPfTmemCols = 512;            // S0 @0, S1 @64, PV0 @128, PV1 @256
 constexpr long long kPfBarrierBudget = 2000000000ll;
+constexpr float kPfRescale = 8.f;                // log2 units the row maximum may lag before O is rescaled
 
 struct PrefillParams {
   const __nv_bfloat16* q;
@@ -153,6 +158,18 @@ __global__ void __launch_bounds__(256) cake_rpa_prefill_plan_sm100(PrefillParams
   *pp.entry_count = n;
 }
 
+__device__ __forceinline__ float pf_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float pf_max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ void pf_setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 208;" ::: "memory"); }
 __device__ __forceinline__ void pf_setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 88;" ::: "memory"); }
 
@@ -165,7 +182,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem;                                     // [2 sub-tiles][2 halves][128][128 B]
-  uint8_t* kv_smem = q_smem + 2 * kPfQBytes;                  // [stages][K 16 KiB | V 16 KiB]
+  uint8_t* kv_smem = q_smem + 2 * kPfQBytes;                  // [stages][8 groups][4 atoms][8 rows][128 B]
   uint8_t* p_smem = kv_smem + kPfStages * kPfStageBytes;      // [2 sub-tiles][128][128 B]
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * kPfPBytes);
   uint64_t* q_full = bars;              // [1]
@@ -174,7 +191,8 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   uint64_t* s_full = kv_empty + kPfStages;  // [2]
   uint64_t* p_full = s_full + 2;            // [2]
   uint64_t* pv_full = p_full + 2;           // [2]
-  uint64_t* drain_bar = pv_full + 2;        // [1]
+  uint64_t* s_free = pv_full + 2;           // [2]
+  uint64_t* drain_bar = s_free + 2;         // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   volatile int32_t* item_slot = reinterpret_cast<volatile int32_t*>(tmem_base_slot + 2);  // [2]
@@ -192,6 +210,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       mbar_init(smem_u32(&s_full[g]), 1);
       mbar_init(smem_u32(&p_full[g]), 128);
       mbar_init(smem_u32(&pv_full[g]), 1);
+      mbar_init(smem_u32(&s_free[g]), 128);
     }
     mbar_init(smem_u32(drain_bar), 1);
     *abort_flag = 0;
@@ -256,11 +275,12 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       const uint32_t t_s = t_lane + g * 64;
       const uint32_t t_pv = t_lane + 128 + g * 128;
       uint8_t* p_row = p_smem + g * kPfPBytes + row * 128;
+      const float scale = p.scale_log2;  // positive: checked on the host
       for (uint32_t iter = 0; next_item(iter, it); ++iter) {
         const int limit = min(it.prior + it.q0 + row, it.kv_len - 1);  // last position this row sees
-        float o[128];
-#pragma unroll
-        for (int i = 0; i < 128; ++i) o[i] = 0.f;
+        // Running maximum (log2 domain, scaled) and sum of this thread's row. The output row itself
+        // accumulates in TMEM across all KV steps; it is rescaled only when the maximum moves by more
+        // than kPfRescale, so the exponentials below are bounded by 2^kPfRescale instead of 1.
         float m_run = kNegBig, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < it.n_steps; ++j) {
@@ -271,87 +291,115 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             break;
           }
           tcgen05_fence_after();
-          const int pos0 = j * kPfTileKv;
-          const bool need_mask = pos0 + kPfTileKv - 1 > limit;
-          // ---- pass 1: row maximum of the scaled, masked scores
-          float mx = m_run;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(t_s + half * 32, v);
+          uint32_t v[64];
+          {
+            uint32_t lo[32], hi[32];
+            tmem_ld_32x32b_x32(t_s, lo);
+            tmem_ld_32x32b_x32(t_s + 32, hi);
             tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-              float sv = __uint_as_float(v[c]) * p.scale_log2;
-              if (need_mask && pos0 + half * 32 + c > limit) sv = kNegBig;
-              mx = fmaxf(mx, sv);
+              v[c] = lo[c];
+              v[32 + c] = hi[c];
             }
           }
-          const float alpha = exp2f(m_run - mx);
-          m_run = mx;
-          // ---- pass 2: P = exp2(S - max) as bf16 into shared memory (K-major, 128-byte swizzle)
-          float sum = 0.f;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(t_s + half * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int c = c4 * 8 + e * 2;
-                float a = exp2f(__uint_as_float(v[c]) * p.scale_log2 - mx);
-                float b = exp2f(__uint_as_float(v[c + 1]) * p.scale_log2 - mx);
-                if (need_mask) {
-                  if (pos0 + half * 32 + c > limit) a = 0.f;
-                  if (pos0 + half * 32 + c + 1 > limit) b = 0.f;
-                }
-                // The sum uses the rounded weights, the values the tensor core multiplies with.
-                const __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
-                sum += __low2float(pk) + __high2float(pk);
-                w[e] = *reinterpret_cast<const uint32_t*>(&pk);
-              }
-              const int chunk = half * 4 + c4;
-              *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          tcgen05_fence_before();
+          mbar_arrive(smem_u32(&s_free[g]));  // S is in registers: the next S = Q K^T may overwrite it
+          // Follow every phase of pv_full (the previous step's PV has long been issued), so that the
+          // accumulator may be touched below and the parity of the last phase is unambiguous.
+          if (j > 0) {
+            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[g]), (step_total - 1u) & 1u, abort_flag));
+            if (!ok) {
+              if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 700 + g);
+              *abort_flag = 1;
+              break;
             }
+            tcgen05_fence_after();
           }
-          l_run = l_run * alpha + sum;
+          const int pos0 = j * kPfTileKv;
+          // Only the steps that cross the row's causal limit (or the end of the sequence) mask.
+          if (__any_sync(0xffffffffu, pos0 + kPfTileKv - 1 > limit)) {
+#pragma unroll
+            for (int c = 0; c < 64; ++c)
+              if (pos0 + c > limit) v[c] = 0xff800000u;  // -inf
+          }
+          float mr = __uint_as_float(v[0]);
+#pragma unroll
+          for (int c = 1; c + 1 < 64; c += 2) mr = pf_max3(mr, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+          mr = fmaxf(mr, __uint_as_float(v[63]));
+          const float mx = mr * scale;
+          float alpha = 1.f;
+          if (mx > m_run + kPfRescale) {
+            alpha = pf_exp2(m_run - mx);
+            m_run = mx;
+          }
+          // PV(j-1) is complete (waited above) and PV(j) is issued only after p_full below, so the
+          // accumulator may be read and rewritten here.
+          if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t acc[32];
+              tmem_ld_32x32b_x32(t_pv + c * 32, acc);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+              tmem_st_32x32b_x32(t_pv + c * 32, acc);
+            }
+            tmem_st_wait();
+          }
+          // ---- P = exp2(S * scale - max) as bf16 into shared memory (K-major, 128-byte swizzle)
+          const float neg_m = -m_run;
+          float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+          for (int chunk = 0; chunk < 8; ++chunk) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int c = chunk * 8 + e * 2;
+              const float a = pf_exp2(fmaf(__uint_as_float(v[c]), scale, neg_m));
+              const float b = pf_exp2(fmaf(__uint_as_float(v[c + 1]), scale, neg_m));
+              sum0 += a;
+              sum1 += b;
+              w[e] = pack_bf16(a, b);
+            }
+            *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          l_run = l_run * alpha + (sum0 + sum1);
           fence_proxy_async_smem();   // P written through the generic proxy, read by the tensor core
-          tcgen05_fence_before();     // the S reads above are ordered before the MMA that overwrites S
+          tcgen05_fence_before();     // TMEM reads and writes above are ordered before the next MMAs
           mbar_arrive(smem_u32(&p_full[g]));
-          // ---- O = O * alpha + P V
-          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[g]), step_total & 1u, abort_flag));
+          ++step_total;
+        }
+        if (ok) {
+          // The last PV of the item.
+          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[g]), (step_total - 1u) & 1u, abort_flag));
           if (!ok) {
             if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 600 + g);
             *abort_flag = 1;
-            break;
           }
-          tcgen05_fence_after();
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(t_pv + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) o[c * 32 + e] = o[c * 32 + e] * alpha + __uint_as_float(v[e]);
-          }
-          tcgen05_fence_before();
-          ++step_total;
         }
-        if (ok && row < it.rows) {
+        if (ok) {
+          tcgen05_fence_after();
           const float inv = 1.f / l_run;
           __nv_bfloat16* dst = pp.out + (static_cast<size_t>(it.q_tok0 + row) * p.q_heads + it.head0 + g) * 128;
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            uint4 piece;
-            piece.x = pack_bf16(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv);
-            piece.y = pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-            piece.z = pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
-            piece.w = pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-            *reinterpret_cast<uint4*>(dst + c * 8) = piece;
+          for (int c = 0; c < 4; ++c) {
+            uint32_t acc[32];
+            tmem_ld_32x32b_x32(t_pv + c * 32, acc);
+            tmem_ld_wait();
+            if (row < it.rows) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                uint4 piece;
+                piece.x = pack_bf16(__uint_as_float(acc[e * 8 + 0]) * inv, __uint_as_float(acc[e * 8 + 1]) * inv);
+                piece.y = pack_bf16(__uint_as_float(acc[e * 8 + 2]) * inv, __uint_as_float(acc[e * 8 + 3]) * inv);
+                piece.z = pack_bf16(__uint_as_float(acc[e * 8 + 4]) * inv, __uint_as_float(acc[e * 8 + 5]) * inv);
+                piece.w = pack_bf16(__uint_as_float(acc[e * 8 + 6]) * inv, __uint_as_float(acc[e * 8 + 7]) * inv);
+                *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = piece;
+              }
+            }
           }
+          tcgen05_fence_before();  // the accumulator reads are ordered before the next item's MMAs
         }
       }
     } else {
@@ -363,8 +411,13 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     pf_setmaxnreg_dec();
     if (warp == 8) {
       // ---------------------------------------------------------------- TMA producer
-      const int tb = p.box_tokens;
-      const int boxes = kPfTileKv >> p.log2_box;
+      // Boxes: with pages of 8 tokens or more, one box is an 8-token group (K and V of the KV head,
+      // both halves: 4 KiB of the fused cache, or 2 KiB from each of the separate caches); smaller
+      // pages fill the four atoms of a group row by row, one box per page and atom.
+      const int tb = min(p.page_size, 8);
+      const int log2_tb = min(p.log2_ps, 3);
+      const int boxes = kPfTileKv >> log2_tb;
+      const bool wide = p.page_size >= 8;
       for (uint32_t iter = 0; next_item(iter, it); ++iter) {
         if (lane == 0) {
           mbar_arrive_expect_tx(smem_u32(q_full), static_cast<uint32_t>(sub * kPfQBytes));
@@ -411,11 +464,22 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           for (int rep = 0; rep < 2; ++rep) {
             const int b = lane + rep * 32;
             if (b < boxes) {
-              const uint32_t dst = sbase + static_cast<uint32_t>(b * tb * 128);
-              tma_load_5d(dst, &tmap_k, bar, 0, my_off[rep], 0, hk, my_page[rep]);
-              tma_load_5d(dst + 8192, &tmap_k, bar, 0, my_off[rep], 1, hk, my_page[rep]);
-              tma_load_5d(dst + 16384, &tmap_v, bar, 0, my_off[rep], 0, hv, my_page[rep]);
-              tma_load_5d(dst + 24576, &tmap_v, bar, 0, my_off[rep], 1, hv, my_page[rep]);
+              const int tok_in_stage = b * tb;
+              const uint32_t gbase = sbase + static_cast<uint32_t>((tok_in_stage >> 3) * kPfGroupBytes);
+              if (wide) {
+                if (p.fused) {
+                  tma_load_5d(gbase, &tmap_k, bar, 0, my_off[rep], 0, hk, my_page[rep]);
+                } else {
+                  tma_load_5d(gbase, &tmap_k, bar, 0, my_off[rep], 0, hk, my_page[rep]);
+                  tma_load_5d(gbase + 2048, &tmap_v, bar, 0, my_off[rep], 0, hv, my_page[rep]);
+                }
+              } else {
+                const uint32_t dst = gbase + static_cast<uint32_t>((tok_in_stage & 7) * 128);
+                tma_load_5d(dst, &tmap_k, bar, 0, my_off[rep], 0, hk, my_page[rep]);
+                tma_load_5d(dst + 1024, &tmap_k, bar, 0, my_off[rep], 1, hk, my_page[rep]);
+                tma_load_5d(dst + 2048, &tmap_v, bar, 0, my_off[rep], 0, hv, my_page[rep]);
+                tma_load_5d(dst + 3072, &tmap_v, bar, 0, my_off[rep], 1, hv, my_page[rep]);
+              }
             }
           }
           __syncwarp();
@@ -435,11 +499,12 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             return false;
           const int first_bad = max(it.kv_len - j * kPfTileKv, 0);
           if (first_bad < kPfTileKv) {
-            uint8_t* v_base = kv_smem + (pos % kPfStages) * kPfStageBytes + 16384;
+            uint8_t* v_base = kv_smem + (pos % kPfStages) * kPfStageBytes + 2048;  // V lo of group 0
             for (int e = lane; e < (kPfTileKv - first_bad) * 16; e += 32) {
               const int row = first_bad + (e >> 4);
               const int piece = e & 15;
-              *reinterpret_cast<uint4*>(v_base + (piece >> 3) * 8192 + row * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+              *reinterpret_cast<uint4*>(v_base + (row >> 3) * kPfGroupBytes + (piece >> 3) * 1024 + (row & 7) * 128 +
+                                        (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
             }
             fence_proxy_async_smem();
           }
@@ -452,7 +517,8 @@ __global__ void __launch_bounds__(kPfThreads, 1)
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t a_desc = umma_desc_sw128(qa + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-            const uint64_t b_desc = umma_desc_sw128(kb + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024);
+            // K tile: 8-token groups 4 KiB apart; the second 64 elements of a row are the next atom
+            const uint64_t b_desc = umma_desc_sw128(kb + (ks >> 2) * 1024 + (ks & 3) * 32, 16, kPfGroupBytes);
             tcgen05_mma_bf16(tmem_base + g * 64, a_desc, b_desc, idesc_qk, ks != 0 ? 1u : 0u);
           }
           tcgen05_commit(smem_u32(&s_full[g]));
@@ -470,6 +536,19 @@ __global__ void __launch_bounds__(kPfThreads, 1)
               ok = stage_ready(kv_pos + 1, j + 1);
               if (!ok) break;
             }
+            // Next S first: it only needs the softmax warps to have taken the current S into
+            // registers, so Q K^T of step j+1 runs under the softmax of step j.
+            if (j + 1 < it.n_steps) {
+              for (int g = 0; g < sub; ++g) {
+                where = 350 + g;
+                ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&s_free[g]), step_total & 1u, abort_flag));
+                if (!ok) break;
+                tcgen05_fence_after();
+                if (lane == 0) issue_qk(g, kv_pos + 1);
+                __syncwarp();
+              }
+              if (!ok) break;
+            }
             for (int g = 0; g < sub; ++g) {
               where = 400 + g;
               ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&p_full[g]), step_total & 1u, abort_flag));
@@ -477,15 +556,16 @@ __global__ void __launch_bounds__(kPfThreads, 1)
               tcgen05_fence_after();
               if (lane == 0) {
                 const uint32_t pa = smem_u32(p_smem + g * kPfPBytes);
-                const uint32_t vb = smem_u32(kv_smem + (kv_pos % kPfStages) * kPfStageBytes + 16384);
+                const uint32_t vb = smem_u32(kv_smem + (kv_pos % kPfStages) * kPfStageBytes + 2048);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                   const uint64_t a_desc = umma_desc_sw128(pa + ks * 32, 16, 1024);
-                  const uint64_t b_desc = umma_desc_sw128(vb + ks * 2048, 8192, 1024);
-                  tcgen05_mma_bf16(tmem_base + 128 + g * 128, a_desc, b_desc, idesc_pv, ks != 0 ? 1u : 0u);
+                  // V tile as [token][d] (MN-major): the two 64-wide halves 1 KiB apart (leading
+                  // offset), 8-token groups 4 KiB apart (stride offset); 16 tokens = two groups
+                  const uint64_t b_desc = umma_desc_sw128(vb + ks * 2 * kPfGroupBytes, 1024, kPfGroupBytes);
+                  tcgen05_mma_bf16(tmem_base + 128 + g * 128, a_desc, b_desc, idesc_pv, (j | ks) != 0 ? 1u : 0u);
                 }
                 tcgen05_commit(smem_u32(&pv_full[g]));
-                if (j + 1 < it.n_steps) issue_qk(g, kv_pos + 1);
               }
               __syncwarp();
             }
