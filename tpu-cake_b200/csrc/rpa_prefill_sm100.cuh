@@ -39,7 +39,7 @@ constexpr int kPfQBytes = kPfTileQ * 256;        // one sub-tile of queries: [2 
 constexpr int kPfStageBytes = kPfTileKv * 512;   // [8 groups][K lo | K hi | V lo | V hi][8 rows][128 B]
 constexpr int kPfGroupBytes = 4096;             // one 8-token group of a stage
 constexpr int kPfPBytes = kPfTileQ * 128;        // P sub-tile: [128 rows][64 bf16]
-constexpr int kPfSmemBytes = 2 * kPfQBytes + kPfStages * kPfStageBytes + 2 * kPfPBytes + 1024 + 1024;
+constexpr int kPfSmemBytes = 2 * kPfQBytes + kPfStages * kPfStageBytes + 4 * kPfPBytes + 1024 + 1024;
 constexpr uint32_t kPfTmemCols = 512;            // S0 @0, S1 @64, PV0 @128, PV1 @256
 constexpr long long kPfBarrierBudget = 2000000000ll;
 constexpr float kPfRescale = 8.f;                // log2 units the row maximum may lag before O is rescaled
@@ -59,6 +59,20 @@ struct PrefillParams {
   int32_t num_q_tokens;
   RpaParams r;             // page table, layout, scale, status
 };
+
+#ifdef CAKE_PF_TIMING
+// Development aid (off by default): cycles each role of every CTA spends blocked in its waits.
+// Slots per CTA: 0 softmax wait S, 1 softmax wait PV, 2 softmax total, 3 softmax steps,
+// 4 MMA wait K/V, 5 MMA wait S free, 6 MMA wait P, 7 MMA total, 8 producer wait slot, 9 producer total.
+__device__ unsigned long long g_pf_timing[256 * 16];
+#define PF_T0() const long long pf_t0_ = clock64()
+#define PF_ADD(slot, cond) do { if (cond) g_pf_timing[blockIdx.x * 16 + (slot)] += clock64() - pf_t0_; } while (0)
+#define PF_COUNT(slot, cond) do { if (cond) g_pf_timing[blockIdx.x * 16 + (slot)] += 1; } while (0)
+#else
+#define PF_T0() do {} while (0)
+#define PF_ADD(slot, cond) do {} while (0)
+#define PF_COUNT(slot, cond) do {} while (0)
+#endif
 
 __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -164,6 +178,13 @@ __device__ __forceinline__ float pf_exp2(float x) {
   return y;
 }
 
+// 64-bit shared-memory descriptor from its two words.
+__device__ __forceinline__ uint64_t pf_desc(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 __device__ __forceinline__ float pf_max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -183,15 +204,15 @@ __global__ void __launch_bounds__(kPfThreads, 1)
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem;                                     // [2 sub-tiles][2 halves][128][128 B]
   uint8_t* kv_smem = q_smem + 2 * kPfQBytes;                  // [stages][8 groups][4 atoms][8 rows][128 B]
-  uint8_t* p_smem = kv_smem + kPfStages * kPfStageBytes;      // [2 sub-tiles][128][128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * kPfPBytes);
+  uint8_t* p_smem = kv_smem + kPfStages * kPfStageBytes;      // [2 sub-tiles][2 buffers][128][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 4 * kPfPBytes);
   uint64_t* q_full = bars;              // [1]
   uint64_t* kv_full = bars + 1;         // [stages]
   uint64_t* kv_empty = kv_full + kPfStages;
   uint64_t* s_full = kv_empty + kPfStages;  // [2]
-  uint64_t* p_full = s_full + 2;            // [2]
-  uint64_t* pv_full = p_full + 2;           // [2]
-  uint64_t* s_free = pv_full + 2;           // [2]
+  uint64_t* p_full = s_full + 2;            // [2 sub-tiles][2 P buffers]
+  uint64_t* pv_full = p_full + 4;           // [2 sub-tiles][2 P buffers]
+  uint64_t* s_free = pv_full + 4;           // [2]
   uint64_t* drain_bar = s_free + 2;         // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
@@ -208,8 +229,10 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     }
     for (int g = 0; g < 2; ++g) {
       mbar_init(smem_u32(&s_full[g]), 1);
-      mbar_init(smem_u32(&p_full[g]), 128);
-      mbar_init(smem_u32(&pv_full[g]), 1);
+      mbar_init(smem_u32(&p_full[2 * g]), 128);
+      mbar_init(smem_u32(&p_full[2 * g + 1]), 128);
+      mbar_init(smem_u32(&pv_full[2 * g]), 1);
+      mbar_init(smem_u32(&pv_full[2 * g + 1]), 1);
       mbar_init(smem_u32(&s_free[g]), 128);
     }
     mbar_init(smem_u32(drain_bar), 1);
@@ -274,9 +297,10 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       const uint32_t t_s = t_lane + g * 64;
       const uint32_t t_pv = t_lane + 128 + g * 128;
-      uint8_t* p_row = p_smem + g * kPfPBytes + row * 128;
+      uint8_t* p_rows = p_smem + g * 2 * kPfPBytes + row * 128;  // this thread's row in P buffer 0
       const float scale = p.scale_log2;  // positive: checked on the host
       for (uint32_t iter = 0; next_item(iter, it); ++iter) {
+        PF_T0();
         const int limit = min(it.prior + it.q0 + row, it.kv_len - 1);  // last position this row sees
         // Running maximum (log2 domain, scaled) and sum of this thread's row. The output row itself
         // accumulates in TMEM across all KV steps; it is rescaled only when the maximum moves by more
@@ -284,7 +308,12 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         float m_run = kNegBig, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < it.n_steps; ++j) {
-          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&s_full[g]), step_total & 1u, abort_flag));
+          {
+            PF_T0();
+            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&s_full[g]), step_total & 1u, abort_flag));
+            PF_ADD(0, threadIdx.x == 0);
+            PF_COUNT(3, threadIdx.x == 0);
+          }
           if (!ok) {
             if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 500 + g);
             *abort_flag = 1;
@@ -305,16 +334,19 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           }
           tcgen05_fence_before();
           mbar_arrive(smem_u32(&s_free[g]));  // S is in registers: the next S = Q K^T may overwrite it
-          // Follow every phase of pv_full (the previous step's PV has long been issued), so that the
-          // accumulator may be touched below and the parity of the last phase is unambiguous.
-          if (j > 0) {
-            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[g]), (step_total - 1u) & 1u, abort_flag));
+          // P is double-buffered: this step writes buffer t & 1, which PV(t-2) read. Its barrier
+          // completes every other step, so the wait below names exactly that completion.
+          const uint32_t t = step_total;
+          uint8_t* p_row = p_rows + (t & 1u) * kPfPBytes;
+          if (j >= 2) {
+            PF_T0();
+            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[2 * g + (t & 1u)]), ((t >> 1) & 1u) ^ 1u, abort_flag));
+            PF_ADD(1, threadIdx.x == 0);
             if (!ok) {
               if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 700 + g);
               *abort_flag = 1;
               break;
             }
-            tcgen05_fence_after();
           }
           const int pos0 = j * kPfTileKv;
           // Only the steps that cross the row's causal limit (or the end of the sequence) mask.
@@ -333,9 +365,16 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             alpha = pf_exp2(m_run - mx);
             m_run = mx;
           }
-          // PV(j-1) is complete (waited above) and PV(j) is issued only after p_full below, so the
-          // accumulator may be read and rewritten here.
+          // Rare: the accumulator is read and rewritten once PV(t-1) is complete; PV(t) is issued
+          // only after p_full below.
           if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[2 * g + ((t - 1u) & 1u)]), ((t - 1u) >> 1) & 1u, abort_flag));
+            if (!ok) {
+              if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 800 + g);
+              *abort_flag = 1;
+              break;
+            }
+            tcgen05_fence_after();
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
               uint32_t acc[32];
@@ -367,12 +406,15 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           l_run = l_run * alpha + (sum0 + sum1);
           fence_proxy_async_smem();   // P written through the generic proxy, read by the tensor core
           tcgen05_fence_before();     // TMEM reads and writes above are ordered before the next MMAs
-          mbar_arrive(smem_u32(&p_full[g]));
+          // One barrier per P buffer: the softmax may run up to two steps ahead of the issuer, which a
+          // single barrier's phase parity could not tell apart.
+          mbar_arrive(smem_u32(&p_full[2 * g + (t & 1u)]));
           ++step_total;
         }
         if (ok) {
           // The last PV of the item.
-          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[g]), (step_total - 1u) & 1u, abort_flag));
+          const uint32_t last = step_total - 1u;
+          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[2 * g + (last & 1u)]), (last >> 1) & 1u, abort_flag));
           if (!ok) {
             if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 600 + g);
             *abort_flag = 1;
@@ -401,6 +443,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           }
           tcgen05_fence_before();  // the accumulator reads are ordered before the next item's MMAs
         }
+        PF_ADD(2, threadIdx.x == 0);
       }
     } else {
       // second warpgroup without a role (odd GQA group): only takes part in the item barrier
@@ -419,6 +462,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       const int boxes = kPfTileKv >> log2_tb;
       const bool wide = p.page_size >= 8;
       for (uint32_t iter = 0; next_item(iter, it); ++iter) {
+        PF_T0();
         if (lane == 0) {
           mbar_arrive_expect_tx(smem_u32(q_full), static_cast<uint32_t>(sub * kPfQBytes));
           for (int g = 0; g < sub; ++g)
@@ -428,28 +472,64 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           ++q_issued;
         }
         __syncwarp();
+        // Page ids are read 64 table slots at a time (two per lane) and the next 64 are requested
+        // while the current ones are in use, so no stage waits for a table read of its own.
+        const int pages_needed = (it.kv_needed + p.page_size - 1) >> p.log2_ps;
+        const long long table_base = p.table_layout == CAKE_RPA_TABLE_2D
+                                         ? static_cast<long long>(it.seq) * p.max_pages_per_seq
+                                         : static_cast<long long>(p.cu_kv_lens[it.seq] >> p.log2_ps);
+        const long long table_end = p.table_layout == CAKE_RPA_TABLE_2D ? table_base + p.max_pages_per_seq
+                                                                        : static_cast<long long>(p.table_len);
+        auto load_window = [&](int base_slot, int (&w)[2]) {
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int slot = base_slot + lane + 32 * r;
+            int page = p.total_pages;  // out-of-range coordinate: the TMA unit fills the box with zeros
+            if (slot < pages_needed) {
+              const long long idx = table_base + slot;
+              page = (idx >= 0 && idx < table_end) ? __ldg(p.page_table + idx) : -1;
+              if (page < 0 || page >= p.total_pages) {
+                rpa_record(p.status, 3, it.seq, slot, page);
+                page = p.total_pages;
+              }
+            }
+            w[r] = page;
+          }
+        };
+        int win_base = 0;
+        int win_cur[2], win_nxt[2];
+        load_window(0, win_cur);
+        load_window(64, win_nxt);
         for (int j = 0; j < it.n_steps; ++j) {
           const uint32_t stage = kv_pos % kPfStages;
           const uint32_t parity = (kv_pos / kPfStages) & 1u;
-          // Page ids of this stage's boxes first, so the table read overlaps the wait for the slot.
-          int my_page[2] = {p.total_pages, p.total_pages};  // out-of-range coordinate: zero fill
-          int my_off[2] = {0, 0};
+          const int first_slot = (j * kPfTileKv) >> p.log2_ps;
+          if (first_slot >= win_base + 64) {  // a stage never straddles two windows
+            win_base += 64;
+            win_cur[0] = win_nxt[0];
+            win_cur[1] = win_nxt[1];
+            load_window(win_base + 64, win_nxt);
+          }
+          int my_page[2];
+          int my_off[2];
 #pragma unroll
           for (int rep = 0; rep < 2; ++rep) {
             const int b = lane + rep * 32;
             const int tok = j * kPfTileKv + b * tb;
-            if (b < boxes && tok < it.kv_needed) {
-              const int page_slot = tok >> p.log2_ps;
-              int page = rpa_page_lookup(p, it.seq, page_slot);
-              if (page < 0 || page >= p.total_pages) {
-                rpa_record(p.status, 3, it.seq, page_slot, page);
-                page = p.total_pages;
-              }
-              my_page[rep] = page;
-              my_off[rep] = tok & (p.page_size - 1);
-            }
+            const int rel = (tok >> p.log2_ps) - win_base;  // 0..63 for the boxes of this stage
+            const int from_lo = __shfl_sync(0xffffffffu, win_cur[0], rel & 31);
+            const int from_hi = __shfl_sync(0xffffffffu, win_cur[1], rel & 31);
+            const bool live = b < boxes && tok < it.kv_needed;
+            my_page[rep] = live ? ((rel & 32) ? from_hi : from_lo) : p.total_pages;
+            my_off[rep] = tok & (p.page_size - 1);
           }
-          if (!__all_sync(0xffffffffu, pf_wait(smem_u32(&kv_empty[stage]), parity ^ 1u, abort_flag))) {
+          bool slot_free;
+          {
+            PF_T0();
+            slot_free = __all_sync(0xffffffffu, pf_wait(smem_u32(&kv_empty[stage]), parity ^ 1u, abort_flag));
+            PF_ADD(8, lane == 0);
+          }
+          if (!slot_free) {
             if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 100 + j);
             *abort_flag = 1;
             break;
@@ -485,18 +565,37 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           __syncwarp();
           ++kv_pos;
         }
+        PF_ADD(9, lane == 0);
       }
     } else if (warp == 9) {
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(kPfTileQ, kPfTileKv, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kPfTileQ, 128, 0, 1);
+      // Shared-memory descriptors, split into the low word (address field, which changes per MMA)
+      // and the high word (stride field, version, swizzle mode: constant per operand kind).
+      //   Q and P: K-major, 8-row groups 1 KiB apart.
+      //   K tile:  K-major, 8-token groups 4 KiB apart; the second 64 elements of a row are the next atom.
+      //   V tile:  [token][d] MN-major: the two 64-wide halves 1 KiB apart (leading offset), 8-token
+      //            groups 4 KiB apart (stride offset); a K step of 16 tokens is two groups.
+      const uint32_t desc_hi_1024 = static_cast<uint32_t>(umma_desc_sw128(0, 16, 1024) >> 32);
+      const uint32_t desc_hi_k = static_cast<uint32_t>(umma_desc_sw128(0, 16, kPfGroupBytes) >> 32);
+      const uint32_t desc_hi_v = static_cast<uint32_t>(umma_desc_sw128(0, 1024, kPfGroupBytes) >> 32);
+      const uint32_t desc_q_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(q_smem), 16, 1024));
+      const uint32_t desc_p_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(p_smem), 16, 1024));
+      const uint32_t desc_k_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(kv_smem), 16, kPfGroupBytes));
+      const uint32_t desc_v_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(kv_smem + 2048), 1024, kPfGroupBytes));
       for (uint32_t iter = 0; next_item(iter, it); ++iter) {
+        PF_T0();
         int where = 200;
         // Waits for stage `pos`, then zeroes its V rows at or beyond kv_len (page tails may hold
         // anything; 0 * NaN would poison the product) before the tensor core reads them.
         auto stage_ready = [&](uint32_t pos, int j) -> bool {
-          if (!__all_sync(0xffffffffu, pf_wait(smem_u32(&kv_full[pos % kPfStages]), (pos / kPfStages) & 1u, abort_flag)))
-            return false;
+          {
+            PF_T0();
+            const bool arrived = __all_sync(0xffffffffu, pf_wait(smem_u32(&kv_full[pos % kPfStages]), (pos / kPfStages) & 1u, abort_flag));
+            PF_ADD(4, lane == 0);
+            if (!arrived) return false;
+          }
           const int first_bad = max(it.kv_len - j * kPfTileKv, 0);
           if (first_bad < kPfTileKv) {
             uint8_t* v_base = kv_smem + (pos % kPfStages) * kPfStageBytes + 2048;  // V lo of group 0
@@ -511,15 +610,16 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           __syncwarp();
           return true;
         };
+        // Descriptors are built once (see above the item loop); per MMA only the 14-bit address
+        // field moves, by an addition to the low word. The issuing thread shares its scheduler with
+        // two softmax warps, so every instruction it does not execute is tensor time gained.
         auto issue_qk = [&](int g, uint32_t pos) {
-          const uint32_t qa = smem_u32(q_smem + g * kPfQBytes);
-          const uint32_t kb = smem_u32(kv_smem + (pos % kPfStages) * kPfStageBytes);
+          const uint32_t k_lo = desc_k_lo + (pos % kPfStages) * (kPfStageBytes >> 4);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t a_desc = umma_desc_sw128(qa + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-            // K tile: 8-token groups 4 KiB apart; the second 64 elements of a row are the next atom
-            const uint64_t b_desc = umma_desc_sw128(kb + (ks >> 2) * 1024 + (ks & 3) * 32, 16, kPfGroupBytes);
-            tcgen05_mma_bf16(tmem_base + g * 64, a_desc, b_desc, idesc_qk, ks != 0 ? 1u : 0u);
+            const uint32_t a_lo = desc_q_lo + g * (kPfQBytes >> 4) + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+            const uint32_t b_lo = k_lo + (((ks >> 2) * 1024 + (ks & 3) * 32) >> 4);
+            tcgen05_mma_bf16(tmem_base + g * 64, pf_desc(a_lo, desc_hi_1024), pf_desc(b_lo, desc_hi_k), idesc_qk, ks != 0 ? 1u : 0u);
           }
           tcgen05_commit(smem_u32(&s_full[g]));
         };
@@ -541,7 +641,9 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             if (j + 1 < it.n_steps) {
               for (int g = 0; g < sub; ++g) {
                 where = 350 + g;
+                PF_T0();
                 ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&s_free[g]), step_total & 1u, abort_flag));
+                PF_ADD(5, lane == 0);
                 if (!ok) break;
                 tcgen05_fence_after();
                 if (lane == 0) issue_qk(g, kv_pos + 1);
@@ -551,21 +653,21 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             }
             for (int g = 0; g < sub; ++g) {
               where = 400 + g;
-              ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&p_full[g]), step_total & 1u, abort_flag));
+              PF_T0();
+              ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&p_full[2 * g + (step_total & 1u)]), (step_total >> 1) & 1u, abort_flag));
+              PF_ADD(6, lane == 0);
               if (!ok) break;
               tcgen05_fence_after();
               if (lane == 0) {
-                const uint32_t pa = smem_u32(p_smem + g * kPfPBytes);
-                const uint32_t vb = smem_u32(kv_smem + (kv_pos % kPfStages) * kPfStageBytes + 2048);
+                const uint32_t buf = step_total & 1u;
+                const uint32_t a_lo = desc_p_lo + (g * 2 + buf) * (kPfPBytes >> 4);
+                const uint32_t b_lo = desc_v_lo + (kv_pos % kPfStages) * (kPfStageBytes >> 4);
+                tcgen05_mma_bf16(tmem_base + 128 + g * 128, pf_desc(a_lo, desc_hi_1024), pf_desc(b_lo, desc_hi_v), idesc_pv, j != 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                  const uint64_t a_desc = umma_desc_sw128(pa + ks * 32, 16, 1024);
-                  // V tile as [token][d] (MN-major): the two 64-wide halves 1 KiB apart (leading
-                  // offset), 8-token groups 4 KiB apart (stride offset); 16 tokens = two groups
-                  const uint64_t b_desc = umma_desc_sw128(vb + ks * 2 * kPfGroupBytes, 1024, kPfGroupBytes);
-                  tcgen05_mma_bf16(tmem_base + 128 + g * 128, a_desc, b_desc, idesc_pv, (j | ks) != 0 ? 1u : 0u);
-                }
-                tcgen05_commit(smem_u32(&pv_full[g]));
+                for (int ks = 1; ks < 4; ++ks)
+                  tcgen05_mma_bf16(tmem_base + 128 + g * 128, pf_desc(a_lo + ((ks * 32) >> 4), desc_hi_1024),
+                                   pf_desc(b_lo + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_v), idesc_pv, 1u);
+                tcgen05_commit(smem_u32(&pv_full[2 * g + buf]));
               }
               __syncwarp();
             }
@@ -581,6 +683,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           *abort_flag = 1;
         }
         __syncwarp();
+        PF_ADD(7, lane == 0);
       }
     } else {
       // warps 10 and 11 have no role: they only take part in the item barrier
