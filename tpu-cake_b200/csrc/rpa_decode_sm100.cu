@@ -1116,10 +1116,10 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
     const uint64_t heads = fused ? 2ull * d.kv_heads : static_cast<uint64_t>(d.kv_heads);
     const uint64_t dims[5] = {64, ps, 2, heads, static_cast<uint64_t>(d.total_pages)};
     const uint64_t strides[4] = {heads * 256, 128, 256, ps * heads * 256};
-    // Pages of 8 tokens or more: one box = an 8-token group with both halves of the row (and, in the
-    // fused cache, K and V of the head). Smaller pages: one box = one page of one half row.
+    // Pages of 8 tokens or more: one box = an 8-token group of one head's K (or V) with both halves
+    // of the row. Smaller pages: one box = one page of one half row.
     const bool wide = d.page_size >= 8;
-    const uint32_t box[5] = {64, static_cast<uint32_t>(wide ? 8 : d.page_size), wide ? 2u : 1u, (wide && fused) ? 2u : 1u, 1};
+    const uint32_t box[5] = {64, static_cast<uint32_t>(wide ? 8 : d.page_size), wide ? 2u : 1u, 1, 1};
     int32_t rc = cake::encode_tensor_map(&plan->tmap_pf_k, cache0, 5, dims, strides, box, true);
     if (rc) return rc;
     if (fused) {
@@ -1140,8 +1140,7 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
   pp.kv_lens = kv_lens;
   pp.cu_q_lens = cu_q_lens;
   pp.first_seq = num_decode_seqs;
-  pp.sub = group % 2 == 0 ? 2 : 1;
-  pp.heads_items = d.q_heads / pp.sub;
+  pp.heads_items = d.q_heads;
   pp.work_counter = reinterpret_cast<int32_t*>(ws + 64);
   pp.entry_count = reinterpret_cast<int32_t*>(ws + 128);
   pp.entries = reinterpret_cast<int4*>(ws + plan->off_pf_entries);

@@ -13,34 +13,38 @@
 //   cake_rpa_ragged_update_sm100   writes the new K/V of EVERY query token at its position
 //   cake_rpa_prefill_plan_sm100    cuts every sequence with index >= first_seq into 128-token query
 //                                  tiles, later tiles (more visible KV) first
-//   cake_rpa_prefill_sm100         persistent, one CTA per SM, warp-specialised:
-//       warpgroup 0 / 1  softmax of query sub-tile 0 / 1 (one thread per query row; two query heads
-//                        of one KV head share every KV tile)
-//       warp 8           TMA producer: query tiles, then 64-token K/V stages gathered page by page.
-//                        A stage is laid out [8-token group][K lo | K hi | V lo | V hi][8 rows][128 B]
-//                        (lo / hi = the two 64-element halves of a 128-wide row): every 8-token group
-//                        is one 4 KiB box of the fused cache, and the groups are a uniform 4 KiB apart,
-//                        which is what the tcgen05 shared-memory descriptors need; no multicast
-//       warp 9           tcgen05.mma issuer: S = Q K^T (128x64, K-major operands) and PV = P V
-//                        (128x128, V consumed in place as an MN-major operand) into TMEM
-//     S is read from TMEM with tcgen05.ld (a thread owns a row, so the row maximum and sum need no
-//     shuffles), P goes back through shared memory in the 128-byte-swizzled K-major layout, and the
-//     output accumulates in TMEM over all KV steps; it is read, rescaled and written back
-//     (tcgen05.ld / tcgen05.st) only when a row maximum has moved by more than 2^8.
+//   cake_rpa_prefill_sm100         persistent, one CTA per SM; a work item is 128 query tokens of one
+//                                  query head, walked over the KV range in steps of 128 tokens.
+//       warps 0-3   softmax: one thread per query row (TMEM lane), so the row maximum and sum need
+//                   no shuffles. S comes out of TMEM with tcgen05.ld, P = exp2(S - max) goes back
+//                   through shared memory (bf16, 128-byte-swizzled K-major, double-buffered), and the
+//                   output row accumulates in TMEM over all steps; it is read, rescaled and written
+//                   back (tcgen05.ld / tcgen05.st) only when its maximum has moved by more than 2^8.
+//       warp 4      TMA producer of the query tile and of the K ring (2 slots)
+//       warp 6      TMA producer of the V ring (2 slots). Tiles are gathered page by page in boxes of
+//                   one 8-token group (both 64-element halves of the row: 2 KiB), laid out
+//                   [group][lo | hi][8 rows][128 B]: groups a uniform 2 KiB apart, which is what the
+//                   tcgen05 shared-memory descriptors need. Never multicast.
+//       warp 5      tcgen05.mma issuer: S = Q K^T (128x128x128, K-major operands) as soon as the
+//                   softmax warps have taken the previous S into registers, and O += P V (128x128x128,
+//                   V consumed in place as an MN-major operand) when P is written.
+//     A 128-wide MMA keeps the tensor pipe busy for 64 cycles, about what the issuing thread needs
+//     per instruction when it shares its scheduler with one softmax warp; 64-wide steps were
+//     issue-bound.
 #pragma once
 
 namespace cake {
 
-constexpr int kPfThreads = 384;
-constexpr int kPfTileQ = 128;
-constexpr int kPfTileKv = 64;
-constexpr int kPfStages = 3;
-constexpr int kPfQBytes = kPfTileQ * 256;        // one sub-tile of queries: [2 halves][128 rows][128 B]
-constexpr int kPfStageBytes = kPfTileKv * 512;   // [8 groups][K lo | K hi | V lo | V hi][8 rows][128 B]
-constexpr int kPfGroupBytes = 4096;             // one 8-token group of a stage
-constexpr int kPfPBytes = kPfTileQ * 128;        // P sub-tile: [128 rows][64 bf16]
-constexpr int kPfSmemBytes = 2 * kPfQBytes + kPfStages * kPfStageBytes + 4 * kPfPBytes + 1024 + 1024;
-constexpr uint32_t kPfTmemCols = 512;            // S0 @0, S1 @64, PV0 @128, PV1 @256
+constexpr int kPfThreads = 256;
+constexpr int kPfTileQ = 128;                    // query rows per work item (one query head)
+constexpr int kPfTileKv = 128;                   // KV tokens per step
+constexpr int kPfRing = 2;                       // slots of the K ring and of the V ring
+constexpr int kPfQBytes = kPfTileQ * 256;        // queries: [2 halves][128 rows][128 B]
+constexpr int kPfTileBytes = kPfTileKv * 256;    // a K or V tile: [16 groups][lo | hi][8 rows][128 B]
+constexpr int kPfGroupBytes = 2048;              // one 8-token group of a K or V tile
+constexpr int kPfPBytes = kPfTileQ * 256;        // P: [2 halves of the 128 tokens][128 rows][128 B]
+constexpr int kPfSmemBytes = kPfQBytes + 2 * kPfRing * kPfTileBytes + 2 * kPfPBytes + 1024 + 1024;
+constexpr uint32_t kPfTmemCols = 256;            // S @0 (128 columns), O @128 (128 columns)
 constexpr long long kPfBarrierBudget = 2000000000ll;
 constexpr float kPfRescale = 8.f;                // log2 units the row maximum may lag before O is rescaled
 
@@ -50,8 +54,7 @@ struct PrefillParams {
   const int32_t* kv_lens;
   const int32_t* cu_q_lens;
   int32_t first_seq;       // sequences [first_seq, num_seqs) are handled here
-  int32_t sub;             // query heads per work item: 2 when the GQA group is even, else 1
-  int32_t heads_items;     // q_heads / sub
+  int32_t heads_items;     // work items per (sequence, query tile): one per query head
   int32_t* work_counter;
   int32_t* entry_count;    // number of (sequence, query tile) entries
   int4* entries;           // {sequence, first query row of the tile, q_len, kv_len}
@@ -63,7 +66,8 @@ struct PrefillParams {
 #ifdef CAKE_PF_TIMING
 // Development aid (off by default): cycles each role of every CTA spends blocked in its waits.
 // Slots per CTA: 0 softmax wait S, 1 softmax wait PV, 2 softmax total, 3 softmax steps,
-// 4 MMA wait K/V, 5 MMA wait S free, 6 MMA wait P, 7 MMA total, 8 producer wait slot, 9 producer total.
+// 4 MMA wait K/V, 5 MMA wait S free, 6 MMA wait P, 7 MMA total, 8 K producer wait slot, 9 K producer
+// total, 10 V producer wait slot, 11 V producer total.
 __device__ unsigned long long g_pf_timing[256 * 16];
 #define PF_T0() const long long pf_t0_ = clock64()
 #define PF_ADD(slot, cond) do { if (cond) g_pf_timing[blockIdx.x * 16 + (slot)] += clock64() - pf_t0_; } while (0)
@@ -191,9 +195,6 @@ __device__ __forceinline__ float pf_max3(float a, float b, float c) {
   return r;
 }
 
-__device__ __forceinline__ void pf_setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 208;" ::: "memory"); }
-__device__ __forceinline__ void pf_setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 88;" ::: "memory"); }
-
 __global__ void __launch_bounds__(kPfThreads, 1)
     cake_rpa_prefill_sm100(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
@@ -202,18 +203,21 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   extern __shared__ uint8_t pf_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* q_smem = smem;                                     // [2 sub-tiles][2 halves][128][128 B]
-  uint8_t* kv_smem = q_smem + 2 * kPfQBytes;                  // [stages][8 groups][4 atoms][8 rows][128 B]
-  uint8_t* p_smem = kv_smem + kPfStages * kPfStageBytes;      // [2 sub-tiles][2 buffers][128][128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 4 * kPfPBytes);
-  uint64_t* q_full = bars;              // [1]
-  uint64_t* kv_full = bars + 1;         // [stages]
-  uint64_t* kv_empty = kv_full + kPfStages;
-  uint64_t* s_full = kv_empty + kPfStages;  // [2]
-  uint64_t* p_full = s_full + 2;            // [2 sub-tiles][2 P buffers]
-  uint64_t* pv_full = p_full + 4;           // [2 sub-tiles][2 P buffers]
-  uint64_t* s_free = pv_full + 4;           // [2]
-  uint64_t* drain_bar = s_free + 2;         // [1]
+  uint8_t* q_smem = smem;                                  // [2 halves][128 rows][128 B]
+  uint8_t* k_smem = q_smem + kPfQBytes;                    // [ring][16 groups][lo | hi][8 rows][128 B]
+  uint8_t* v_smem = k_smem + kPfRing * kPfTileBytes;       // same
+  uint8_t* p_smem = v_smem + kPfRing * kPfTileBytes;       // [2 buffers][2 halves][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * kPfPBytes);
+  uint64_t* q_full = bars;                 // [1]
+  uint64_t* k_full = bars + 1;             // [ring]
+  uint64_t* k_empty = k_full + kPfRing;    // [ring]
+  uint64_t* v_full = k_empty + kPfRing;    // [ring]
+  uint64_t* v_empty = v_full + kPfRing;    // [ring]
+  uint64_t* s_full = v_empty + kPfRing;    // [1]
+  uint64_t* s_free = s_full + 1;           // [1]
+  uint64_t* p_full = s_free + 1;           // [2 P buffers]
+  uint64_t* pv_full = p_full + 2;          // [2 P buffers]
+  uint64_t* drain_bar = pv_full + 2;       // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   volatile int32_t* item_slot = reinterpret_cast<volatile int32_t*>(tmem_base_slot + 2);  // [2]
@@ -223,17 +227,17 @@ __global__ void __launch_bounds__(kPfThreads, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
-    for (int s = 0; s < kPfStages; ++s) {
-      mbar_init(smem_u32(&kv_full[s]), 1);
-      mbar_init(smem_u32(&kv_empty[s]), 1);
+    for (int s = 0; s < kPfRing; ++s) {
+      mbar_init(smem_u32(&k_full[s]), 1);
+      mbar_init(smem_u32(&k_empty[s]), 1);
+      mbar_init(smem_u32(&v_full[s]), 1);
+      mbar_init(smem_u32(&v_empty[s]), 1);
     }
-    for (int g = 0; g < 2; ++g) {
-      mbar_init(smem_u32(&s_full[g]), 1);
-      mbar_init(smem_u32(&p_full[2 * g]), 128);
-      mbar_init(smem_u32(&p_full[2 * g + 1]), 128);
-      mbar_init(smem_u32(&pv_full[2 * g]), 1);
-      mbar_init(smem_u32(&pv_full[2 * g + 1]), 1);
-      mbar_init(smem_u32(&s_free[g]), 128);
+    mbar_init(smem_u32(s_full), 1);
+    mbar_init(smem_u32(s_free), 128);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&p_full[b]), 128);
+      mbar_init(smem_u32(&pv_full[b]), 1);
     }
     mbar_init(smem_u32(drain_bar), 1);
     *abort_flag = 0;
@@ -242,7 +246,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     prefetch_tensormap(&tmap_k);
     prefetch_tensormap(&tmap_v);
   }
-  if (warp == 9) {
+  if (warp == 5) {
     tmem_alloc(smem_u32(tmem_base_slot), kPfTmemCols);
     tmem_relinquish();
   }
@@ -251,15 +255,14 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   const int total_items = min(*pp.entry_count, pp.max_entries) * pp.heads_items;
-  const int sub = pp.sub;
 
-  // Running positions that persist across work items (every role that uses one advances it the
-  // same way): K/V stages produced / consumed, KV steps processed (phase of s_full / p_full /
-  // pv_full), query loads issued.
-  uint32_t kv_pos = 0, step_total = 0, q_issued = 0;
+  // Running step count that persists across work items: every role advances it the same way. It
+  // gives the ring slot (t % ring), the P buffer (t & 1) and every barrier phase.
+  uint32_t step_total = 0;
+  uint32_t loads_issued = 0;  // producers: tiles issued, for the orderly exit
 
   struct Item {
-    int id, seq, q0, kv_len, head0, kvh, prior, rows, kv_needed, n_steps, q_tok0;
+    int id, seq, q0, kv_len, head, kvh, prior, rows, kv_needed, n_steps, q_tok0;
   };
   // Claims the next work item for the whole CTA. One thread decides (next item, or -1 after an
   // abort) so that every thread leaves its loop in the same iteration. The barrier also separates
@@ -271,13 +274,12 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     const int id = item_slot[iter & 1];
     if (id < 0 || id >= total_items) return false;
     const int4 entry = __ldg(pp.entries + id / pp.heads_items);
-    const int hi = id % pp.heads_items;
     it.id = id;
     it.seq = entry.x;
     it.q0 = entry.y;
     it.kv_len = entry.w;
-    it.head0 = hi * sub;                        // first query head of the item
-    it.kvh = it.head0 / p.group;                // its KV head
+    it.head = id % pp.heads_items;
+    it.kvh = it.head / p.group;
     it.prior = entry.w - entry.z;               // cached tokens before the first query token
     it.rows = min(kPfTileQ, entry.z - entry.y);
     it.kv_needed = it.prior + it.q0 + it.rows;  // positions any row of the tile can see
@@ -287,423 +289,403 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   };
   Item it;
 
-  if (warp < 8) {
-    pf_setmaxnreg_inc();
-    if (warp < 4 * sub) {
-      // ---------------------------------------------------------------- softmax warpgroups
-      const int g = warp >> 2;
-      const int quarter = warp & 3;
-      const int row = quarter * 32 + lane;
-      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-      const uint32_t t_s = t_lane + g * 64;
-      const uint32_t t_pv = t_lane + 128 + g * 128;
-      uint8_t* p_rows = p_smem + g * 2 * kPfPBytes + row * 128;  // this thread's row in P buffer 0
-      const float scale = p.scale_log2;  // positive: checked on the host
-      for (uint32_t iter = 0; next_item(iter, it); ++iter) {
-        PF_T0();
-        const int limit = min(it.prior + it.q0 + row, it.kv_len - 1);  // last position this row sees
-        // Running maximum (log2 domain, scaled) and sum of this thread's row. The output row itself
-        // accumulates in TMEM across all KV steps; it is rescaled only when the maximum moves by more
-        // than kPfRescale, so the exponentials below are bounded by 2^kPfRescale instead of 1.
-        float m_run = kNegBig, l_run = 0.f;
-        bool ok = true;
-        for (int j = 0; j < it.n_steps; ++j) {
-          {
-            PF_T0();
-            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&s_full[g]), step_total & 1u, abort_flag));
-            PF_ADD(0, threadIdx.x == 0);
-            PF_COUNT(3, threadIdx.x == 0);
+  if (warp < 4) {
+    // ---------------------------------------------------------------- softmax warps
+    const int row = warp * 32 + lane;  // warp w reads TMEM lanes 32w .. 32w+31
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t t_s = t_lane;
+    const uint32_t t_o = t_lane + 128;
+    uint8_t* p_rows = p_smem + row * 128;  // this thread's row in P buffer 0, first half
+    const float scale = p.scale_log2;      // positive: checked on the host
+    for (uint32_t iter = 0; next_item(iter, it); ++iter) {
+      PF_T0();
+      const int limit = min(it.prior + it.q0 + row, it.kv_len - 1);  // last position this row sees
+      // Running maximum (log2 domain, scaled) and sum of this thread's row. The maximum is allowed
+      // to lag by kPfRescale, so the exponentials below are bounded by 2^kPfRescale instead of 1.
+      float m_run = kNegBig, l_run = 0.f;
+      bool ok = true;
+      for (int j = 0; j < it.n_steps; ++j) {
+        const uint32_t t = step_total;
+        {
+          PF_T0();
+          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(s_full), t & 1u, abort_flag));
+          PF_ADD(0, threadIdx.x == 0);
+          PF_COUNT(3, threadIdx.x == 0);
+        }
+        if (!ok) {
+          if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 500);
+          *abort_flag = 1;
+          break;
+        }
+        tcgen05_fence_after();
+        uint32_t v[128];
+        {
+          uint32_t c0[32], c1[32], c2[32], c3[32];
+          tmem_ld_32x32b_x32(t_s, c0);
+          tmem_ld_32x32b_x32(t_s + 32, c1);
+          tmem_ld_32x32b_x32(t_s + 64, c2);
+          tmem_ld_32x32b_x32(t_s + 96, c3);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            v[c] = c0[c];
+            v[32 + c] = c1[c];
+            v[64 + c] = c2[c];
+            v[96 + c] = c3[c];
           }
+        }
+        tcgen05_fence_before();
+        mbar_arrive(smem_u32(s_free));  // S is in registers: the next S = Q K^T may overwrite it
+        // P is double-buffered: this step writes buffer t & 1, which PV(t-2) read. Each buffer has
+        // its own barriers, completing every other step, so a wait names exactly one completion
+        // even though this role may run up to two steps ahead of the issuer.
+        uint8_t* p_row = p_rows + (t & 1u) * kPfPBytes;
+        if (j >= 2) {
+          PF_T0();
+          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[t & 1u]), ((t >> 1) & 1u) ^ 1u, abort_flag));
+          PF_ADD(1, threadIdx.x == 0);
           if (!ok) {
-            if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 500 + g);
+            if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 700);
+            *abort_flag = 1;
+            break;
+          }
+        }
+        const int pos0 = j * kPfTileKv;
+        // Only the steps that cross the row's causal limit (or the end of the sequence) mask.
+        if (__any_sync(0xffffffffu, pos0 + kPfTileKv - 1 > limit)) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c)
+            if (pos0 + c > limit) v[c] = 0xff800000u;  // -inf
+        }
+        float mr0 = __uint_as_float(v[0]), mr1 = __uint_as_float(v[1]);
+#pragma unroll
+        for (int c = 2; c + 3 < 128; c += 4) {
+          mr0 = pf_max3(mr0, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+          mr1 = pf_max3(mr1, __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+        }
+        const float mx = pf_max3(mr0, mr1, fmaxf(__uint_as_float(v[126]), __uint_as_float(v[127]))) * scale;
+        float alpha = 1.f;
+        if (mx > m_run + kPfRescale) {
+          alpha = pf_exp2(m_run - mx);
+          m_run = mx;
+        }
+        // Rare: the accumulator is read and rewritten once PV(t-1) is complete; PV(t) is issued
+        // only after p_full below.
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[(t - 1u) & 1u]), ((t - 1u) >> 1) & 1u, abort_flag));
+          if (!ok) {
+            if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 800);
             *abort_flag = 1;
             break;
           }
           tcgen05_fence_after();
-          uint32_t v[64];
-          {
-            uint32_t lo[32], hi[32];
-            tmem_ld_32x32b_x32(t_s, lo);
-            tmem_ld_32x32b_x32(t_s + 32, hi);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              v[c] = lo[c];
-              v[32 + c] = hi[c];
-            }
-          }
-          tcgen05_fence_before();
-          mbar_arrive(smem_u32(&s_free[g]));  // S is in registers: the next S = Q K^T may overwrite it
-          // P is double-buffered: this step writes buffer t & 1, which PV(t-2) read. Its barrier
-          // completes every other step, so the wait below names exactly that completion.
-          const uint32_t t = step_total;
-          uint8_t* p_row = p_rows + (t & 1u) * kPfPBytes;
-          if (j >= 2) {
-            PF_T0();
-            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[2 * g + (t & 1u)]), ((t >> 1) & 1u) ^ 1u, abort_flag));
-            PF_ADD(1, threadIdx.x == 0);
-            if (!ok) {
-              if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 700 + g);
-              *abort_flag = 1;
-              break;
-            }
-          }
-          const int pos0 = j * kPfTileKv;
-          // Only the steps that cross the row's causal limit (or the end of the sequence) mask.
-          if (__any_sync(0xffffffffu, pos0 + kPfTileKv - 1 > limit)) {
-#pragma unroll
-            for (int c = 0; c < 64; ++c)
-              if (pos0 + c > limit) v[c] = 0xff800000u;  // -inf
-          }
-          float mr = __uint_as_float(v[0]);
-#pragma unroll
-          for (int c = 1; c + 1 < 64; c += 2) mr = pf_max3(mr, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
-          mr = fmaxf(mr, __uint_as_float(v[63]));
-          const float mx = mr * scale;
-          float alpha = 1.f;
-          if (mx > m_run + kPfRescale) {
-            alpha = pf_exp2(m_run - mx);
-            m_run = mx;
-          }
-          // Rare: the accumulator is read and rewritten once PV(t-1) is complete; PV(t) is issued
-          // only after p_full below.
-          if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[2 * g + ((t - 1u) & 1u)]), ((t - 1u) >> 1) & 1u, abort_flag));
-            if (!ok) {
-              if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 800 + g);
-              *abort_flag = 1;
-              break;
-            }
-            tcgen05_fence_after();
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint32_t acc[32];
-              tmem_ld_32x32b_x32(t_pv + c * 32, acc);
-              tmem_ld_wait();
-#pragma unroll
-              for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
-              tmem_st_32x32b_x32(t_pv + c * 32, acc);
-            }
-            tmem_st_wait();
-          }
-          // ---- P = exp2(S * scale - max) as bf16 into shared memory (K-major, 128-byte swizzle)
-          const float neg_m = -m_run;
-          float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-          for (int chunk = 0; chunk < 8; ++chunk) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int c = chunk * 8 + e * 2;
-              const float a = pf_exp2(fmaf(__uint_as_float(v[c]), scale, neg_m));
-              const float b = pf_exp2(fmaf(__uint_as_float(v[c + 1]), scale, neg_m));
-              sum0 += a;
-              sum1 += b;
-              w[e] = pack_bf16(a, b);
-            }
-            *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-          l_run = l_run * alpha + (sum0 + sum1);
-          fence_proxy_async_smem();   // P written through the generic proxy, read by the tensor core
-          tcgen05_fence_before();     // TMEM reads and writes above are ordered before the next MMAs
-          // One barrier per P buffer: the softmax may run up to two steps ahead of the issuer, which a
-          // single barrier's phase parity could not tell apart.
-          mbar_arrive(smem_u32(&p_full[2 * g + (t & 1u)]));
-          ++step_total;
-        }
-        if (ok) {
-          // The last PV of the item.
-          const uint32_t last = step_total - 1u;
-          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[2 * g + (last & 1u)]), (last >> 1) & 1u, abort_flag));
-          if (!ok) {
-            if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 600 + g);
-            *abort_flag = 1;
-          }
-        }
-        if (ok) {
-          tcgen05_fence_after();
-          const float inv = 1.f / l_run;
-          __nv_bfloat16* dst = pp.out + (static_cast<size_t>(it.q_tok0 + row) * p.q_heads + it.head0 + g) * 128;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t acc[32];
-            tmem_ld_32x32b_x32(t_pv + c * 32, acc);
+            tmem_ld_32x32b_x32(t_o + c * 32, acc);
             tmem_ld_wait();
-            if (row < it.rows) {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                uint4 piece;
-                piece.x = pack_bf16(__uint_as_float(acc[e * 8 + 0]) * inv, __uint_as_float(acc[e * 8 + 1]) * inv);
-                piece.y = pack_bf16(__uint_as_float(acc[e * 8 + 2]) * inv, __uint_as_float(acc[e * 8 + 3]) * inv);
-                piece.z = pack_bf16(__uint_as_float(acc[e * 8 + 4]) * inv, __uint_as_float(acc[e * 8 + 5]) * inv);
-                piece.w = pack_bf16(__uint_as_float(acc[e * 8 + 6]) * inv, __uint_as_float(acc[e * 8 + 7]) * inv);
-                *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = piece;
-              }
+            for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+            tmem_st_32x32b_x32(t_o + c * 32, acc);
+          }
+          tmem_st_wait();
+        }
+        // ---- P = exp2(S * scale - max) as bf16 into shared memory (K-major, 128-byte swizzle)
+        const float neg_m = -m_run;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int chunk = 0; chunk < 16; ++chunk) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = chunk * 8 + e * 2;
+            const float a = pf_exp2(fmaf(__uint_as_float(v[c]), scale, neg_m));
+            const float b = pf_exp2(fmaf(__uint_as_float(v[c + 1]), scale, neg_m));
+            sum0 += a;
+            sum1 += b;
+            w[e] = pack_bf16(a, b);
+          }
+          *reinterpret_cast<uint4*>(p_row + (chunk >> 3) * (kPfPBytes / 2) + (((chunk & 7) ^ (row & 7)) << 4)) =
+              make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        l_run = l_run * alpha + (sum0 + sum1);
+        fence_proxy_async_smem();   // P written through the generic proxy, read by the tensor core
+        tcgen05_fence_before();     // TMEM reads and writes above are ordered before the next MMAs
+        mbar_arrive(smem_u32(&p_full[t & 1u]));
+        ++step_total;
+      }
+      if (ok) {
+        // The last PV of the item.
+        const uint32_t last = step_total - 1u;
+        ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[last & 1u]), (last >> 1) & 1u, abort_flag));
+        if (!ok) {
+          if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 600);
+          *abort_flag = 1;
+        }
+      }
+      if (ok) {
+        tcgen05_fence_after();
+        const float inv = 1.f / l_run;
+        __nv_bfloat16* dst = pp.out + (static_cast<size_t>(it.q_tok0 + row) * p.q_heads + it.head) * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t acc[32];
+          tmem_ld_32x32b_x32(t_o + c * 32, acc);
+          tmem_ld_wait();
+          if (row < it.rows) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              uint4 piece;
+              piece.x = pack_bf16(__uint_as_float(acc[e * 8 + 0]) * inv, __uint_as_float(acc[e * 8 + 1]) * inv);
+              piece.y = pack_bf16(__uint_as_float(acc[e * 8 + 2]) * inv, __uint_as_float(acc[e * 8 + 3]) * inv);
+              piece.z = pack_bf16(__uint_as_float(acc[e * 8 + 4]) * inv, __uint_as_float(acc[e * 8 + 5]) * inv);
+              piece.w = pack_bf16(__uint_as_float(acc[e * 8 + 6]) * inv, __uint_as_float(acc[e * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = piece;
             }
           }
-          tcgen05_fence_before();  // the accumulator reads are ordered before the next item's MMAs
         }
-        PF_ADD(2, threadIdx.x == 0);
+        tcgen05_fence_before();  // the accumulator reads are ordered before the next item's MMAs
       }
-    } else {
-      // second warpgroup without a role (odd GQA group): only takes part in the item barrier
-      for (uint32_t iter = 0; next_item(iter, it); ++iter) {
-      }
+      PF_ADD(2, threadIdx.x == 0);
     }
-  } else {
-    pf_setmaxnreg_dec();
-    if (warp == 8) {
-      // ---------------------------------------------------------------- TMA producer
-      // Boxes: with pages of 8 tokens or more, one box is an 8-token group (K and V of the KV head,
-      // both halves: 4 KiB of the fused cache, or 2 KiB from each of the separate caches); smaller
-      // pages fill the four atoms of a group row by row, one box per page and atom.
-      const int tb = min(p.page_size, 8);
-      const int log2_tb = min(p.log2_ps, 3);
-      const int boxes = kPfTileKv >> log2_tb;
-      const bool wide = p.page_size >= 8;
-      for (uint32_t iter = 0; next_item(iter, it); ++iter) {
-        PF_T0();
+  } else if (warp == 4 || warp == 6) {
+    // ---------------------------------------------------------------- TMA producers (K ring, V ring)
+    // Boxes: with pages of 8 tokens or more, one box is an 8-token group with both halves of the
+    // row (2 KiB); smaller pages fill the two atoms of a group row by row, one box per page and atom.
+    const bool is_v = warp == 6;
+    const CUtensorMap* tmap = is_v ? &tmap_v : &tmap_k;
+    uint8_t* ring = is_v ? v_smem : k_smem;
+    uint64_t* full = is_v ? v_full : k_full;
+    uint64_t* empty = is_v ? v_empty : k_empty;
+    const int tb = min(p.page_size, 8);
+    const int log2_tb = min(p.log2_ps, 3);
+    const int boxes = kPfTileKv >> log2_tb;  // 16 .. 128 per tile
+    const int reps = (boxes + 31) >> 5;
+    const bool wide = p.page_size >= 8;
+    for (uint32_t iter = 0; next_item(iter, it); ++iter) {
+      PF_T0();
+      if (!is_v) {
         if (lane == 0) {
-          mbar_arrive_expect_tx(smem_u32(q_full), static_cast<uint32_t>(sub * kPfQBytes));
-          for (int g = 0; g < sub; ++g)
-            for (int half = 0; half < 2; ++half)
-              tma_load_2d(smem_u32(q_smem + g * kPfQBytes + half * (kPfQBytes / 2)), &tmap_q, smem_u32(q_full),
-                          (it.head0 + g) * 128 + half * 64, it.q_tok0);
-          ++q_issued;
+          mbar_arrive_expect_tx(smem_u32(q_full), kPfQBytes);
+          for (int half = 0; half < 2; ++half)
+            tma_load_2d(smem_u32(q_smem + half * (kPfQBytes / 2)), &tmap_q, smem_u32(q_full), it.head * 128 + half * 64,
+                        it.q_tok0);
         }
         __syncwarp();
-        // Page ids are read 64 table slots at a time (two per lane) and the next 64 are requested
-        // while the current ones are in use, so no stage waits for a table read of its own.
-        const int pages_needed = (it.kv_needed + p.page_size - 1) >> p.log2_ps;
-        const long long table_base = p.table_layout == CAKE_RPA_TABLE_2D
-                                         ? static_cast<long long>(it.seq) * p.max_pages_per_seq
-                                         : static_cast<long long>(p.cu_kv_lens[it.seq] >> p.log2_ps);
-        const long long table_end = p.table_layout == CAKE_RPA_TABLE_2D ? table_base + p.max_pages_per_seq
-                                                                        : static_cast<long long>(p.table_len);
-        auto load_window = [&](int base_slot, int (&w)[2]) {
-#pragma unroll
-          for (int r = 0; r < 2; ++r) {
-            const int slot = base_slot + lane + 32 * r;
-            int page = p.total_pages;  // out-of-range coordinate: the TMA unit fills the box with zeros
-            if (slot < pages_needed) {
-              const long long idx = table_base + slot;
-              page = (idx >= 0 && idx < table_end) ? __ldg(p.page_table + idx) : -1;
-              if (page < 0 || page >= p.total_pages) {
-                rpa_record(p.status, 3, it.seq, slot, page);
-                page = p.total_pages;
-              }
-            }
-            w[r] = page;
-          }
-        };
-        int win_base = 0;
-        int win_cur[2], win_nxt[2];
-        load_window(0, win_cur);
-        load_window(64, win_nxt);
-        for (int j = 0; j < it.n_steps; ++j) {
-          const uint32_t stage = kv_pos % kPfStages;
-          const uint32_t parity = (kv_pos / kPfStages) & 1u;
-          const int first_slot = (j * kPfTileKv) >> p.log2_ps;
-          if (first_slot >= win_base + 64) {  // a stage never straddles two windows
-            win_base += 64;
-            win_cur[0] = win_nxt[0];
-            win_cur[1] = win_nxt[1];
-            load_window(win_base + 64, win_nxt);
-          }
-          int my_page[2];
-          int my_off[2];
-#pragma unroll
-          for (int rep = 0; rep < 2; ++rep) {
-            const int b = lane + rep * 32;
-            const int tok = j * kPfTileKv + b * tb;
-            const int rel = (tok >> p.log2_ps) - win_base;  // 0..63 for the boxes of this stage
-            const int from_lo = __shfl_sync(0xffffffffu, win_cur[0], rel & 31);
-            const int from_hi = __shfl_sync(0xffffffffu, win_cur[1], rel & 31);
-            const bool live = b < boxes && tok < it.kv_needed;
-            my_page[rep] = live ? ((rel & 32) ? from_hi : from_lo) : p.total_pages;
-            my_off[rep] = tok & (p.page_size - 1);
-          }
-          bool slot_free;
-          {
-            PF_T0();
-            slot_free = __all_sync(0xffffffffu, pf_wait(smem_u32(&kv_empty[stage]), parity ^ 1u, abort_flag));
-            PF_ADD(8, lane == 0);
-          }
-          if (!slot_free) {
-            if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 100 + j);
-            *abort_flag = 1;
-            break;
-          }
-          const uint32_t bar = smem_u32(&kv_full[stage]);
-          if (lane == 0) mbar_arrive_expect_tx(bar, kPfStageBytes);
-          __syncwarp();
-          const uint32_t sbase = smem_u32(kv_smem + stage * kPfStageBytes);
-          const int hk = p.fused ? 2 * it.kvh : it.kvh;
-          const int hv = p.fused ? 2 * it.kvh + 1 : it.kvh;
-#pragma unroll
-          for (int rep = 0; rep < 2; ++rep) {
-            const int b = lane + rep * 32;
-            if (b < boxes) {
-              const int tok_in_stage = b * tb;
-              const uint32_t gbase = sbase + static_cast<uint32_t>((tok_in_stage >> 3) * kPfGroupBytes);
-              if (wide) {
-                if (p.fused) {
-                  tma_load_5d(gbase, &tmap_k, bar, 0, my_off[rep], 0, hk, my_page[rep]);
-                } else {
-                  tma_load_5d(gbase, &tmap_k, bar, 0, my_off[rep], 0, hk, my_page[rep]);
-                  tma_load_5d(gbase + 2048, &tmap_v, bar, 0, my_off[rep], 0, hv, my_page[rep]);
-                }
-              } else {
-                const uint32_t dst = gbase + static_cast<uint32_t>((tok_in_stage & 7) * 128);
-                tma_load_5d(dst, &tmap_k, bar, 0, my_off[rep], 0, hk, my_page[rep]);
-                tma_load_5d(dst + 1024, &tmap_k, bar, 0, my_off[rep], 1, hk, my_page[rep]);
-                tma_load_5d(dst + 2048, &tmap_v, bar, 0, my_off[rep], 0, hv, my_page[rep]);
-                tma_load_5d(dst + 3072, &tmap_v, bar, 0, my_off[rep], 1, hv, my_page[rep]);
-              }
-            }
-          }
-          __syncwarp();
-          ++kv_pos;
-        }
-        PF_ADD(9, lane == 0);
       }
-    } else if (warp == 9) {
-      // ---------------------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(kPfTileQ, kPfTileKv, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kPfTileQ, 128, 0, 1);
-      // Shared-memory descriptors, split into the low word (address field, which changes per MMA)
-      // and the high word (stride field, version, swizzle mode: constant per operand kind).
-      //   Q and P: K-major, 8-row groups 1 KiB apart.
-      //   K tile:  K-major, 8-token groups 4 KiB apart; the second 64 elements of a row are the next atom.
-      //   V tile:  [token][d] MN-major: the two 64-wide halves 1 KiB apart (leading offset), 8-token
-      //            groups 4 KiB apart (stride offset); a K step of 16 tokens is two groups.
-      const uint32_t desc_hi_1024 = static_cast<uint32_t>(umma_desc_sw128(0, 16, 1024) >> 32);
-      const uint32_t desc_hi_k = static_cast<uint32_t>(umma_desc_sw128(0, 16, kPfGroupBytes) >> 32);
-      const uint32_t desc_hi_v = static_cast<uint32_t>(umma_desc_sw128(0, 1024, kPfGroupBytes) >> 32);
-      const uint32_t desc_q_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(q_smem), 16, 1024));
-      const uint32_t desc_p_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(p_smem), 16, 1024));
-      const uint32_t desc_k_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(kv_smem), 16, kPfGroupBytes));
-      const uint32_t desc_v_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(kv_smem + 2048), 1024, kPfGroupBytes));
-      for (uint32_t iter = 0; next_item(iter, it); ++iter) {
-        PF_T0();
-        int where = 200;
-        // Waits for stage `pos`, then zeroes its V rows at or beyond kv_len (page tails may hold
-        // anything; 0 * NaN would poison the product) before the tensor core reads them.
-        auto stage_ready = [&](uint32_t pos, int j) -> bool {
-          {
-            PF_T0();
-            const bool arrived = __all_sync(0xffffffffu, pf_wait(smem_u32(&kv_full[pos % kPfStages]), (pos / kPfStages) & 1u, abort_flag));
-            PF_ADD(4, lane == 0);
-            if (!arrived) return false;
+      const int head = p.fused ? 2 * it.kvh + (is_v ? 1 : 0) : it.kvh;
+      // Page ids are read 128 table slots at a time (four per lane) and the next 128 are requested
+      // while the current ones are in use, so no tile waits for a table read of its own.
+      const int pages_needed = (it.kv_needed + p.page_size - 1) >> p.log2_ps;
+      const long long table_base = p.table_layout == CAKE_RPA_TABLE_2D
+                                       ? static_cast<long long>(it.seq) * p.max_pages_per_seq
+                                       : static_cast<long long>(p.cu_kv_lens[it.seq] >> p.log2_ps);
+      const long long table_end = p.table_layout == CAKE_RPA_TABLE_2D ? table_base + p.max_pages_per_seq
+                                                                      : static_cast<long long>(p.table_len);
+      auto load_window = [&](int base_slot, int (&w)[4]) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int slot = base_slot + lane + 32 * r;
+          int page = p.total_pages;  // out-of-range coordinate: the TMA unit fills the box with zeros
+          if (slot < pages_needed) {
+            const long long idx = table_base + slot;
+            page = (idx >= 0 && idx < table_end) ? __ldg(p.page_table + idx) : -1;
+            if (page < 0 || page >= p.total_pages) {
+              rpa_record(p.status, 3, it.seq, slot, page);
+              page = p.total_pages;
+            }
           }
+          w[r] = page;
+        }
+      };
+      int win_base = 0;
+      int win_cur[4], win_nxt[4];
+      load_window(0, win_cur);
+      load_window(128, win_nxt);
+      bool alive = true;
+      for (int j = 0; j < it.n_steps && alive; ++j) {
+        const uint32_t t = step_total;
+        const uint32_t slot = t % kPfRing;
+        const uint32_t parity = (t / kPfRing) & 1u;
+        const int first_slot = (j * kPfTileKv) >> p.log2_ps;
+        if (first_slot >= win_base + 128) {  // a tile never straddles two windows
+          win_base += 128;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) win_cur[r] = win_nxt[r];
+          load_window(win_base + 128, win_nxt);
+        }
+        {
+          PF_T0();
+          alive = __all_sync(0xffffffffu, pf_wait(smem_u32(&empty[slot]), parity ^ 1u, abort_flag));
+          PF_ADD(is_v ? 10 : 8, lane == 0);
+        }
+        if (!alive) {
+          if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, (is_v ? 150 : 100) + j);
+          *abort_flag = 1;
+          break;
+        }
+        const uint32_t bar = smem_u32(&full[slot]);
+        if (lane == 0) mbar_arrive_expect_tx(bar, kPfTileBytes);
+        __syncwarp();
+        const uint32_t sbase = smem_u32(ring + slot * kPfTileBytes);
+        for (int rep = 0; rep < reps; ++rep) {
+          const int b = lane + rep * 32;
+          const int tok_in_tile = b * tb;
+          const int tok = j * kPfTileKv + tok_in_tile;
+          const int rel = (tok >> p.log2_ps) - win_base;  // 0..127 for the boxes of this tile
+          const int src = rel & 31;
+          const int w0 = __shfl_sync(0xffffffffu, win_cur[0], src);
+          const int w1 = __shfl_sync(0xffffffffu, win_cur[1], src);
+          const int w2 = __shfl_sync(0xffffffffu, win_cur[2], src);
+          const int w3 = __shfl_sync(0xffffffffu, win_cur[3], src);
+          if (b < boxes) {
+            const int which = (rel >> 5) & 3;
+            const int from = which == 0 ? w0 : which == 1 ? w1 : which == 2 ? w2 : w3;
+            const int page = tok < it.kv_needed ? from : p.total_pages;
+            const int off = tok & (p.page_size - 1);
+            const uint32_t gbase = sbase + static_cast<uint32_t>((tok_in_tile >> 3) * kPfGroupBytes);
+            if (wide) {
+              tma_load_5d(gbase, tmap, bar, 0, off, 0, head, page);
+            } else {
+              const uint32_t dst = gbase + static_cast<uint32_t>((tok_in_tile & 7) * 128);
+              tma_load_5d(dst, tmap, bar, 0, off, 0, head, page);
+              tma_load_5d(dst + 1024, tmap, bar, 0, off, 1, head, page);
+            }
+          }
+        }
+        __syncwarp();
+        ++loads_issued;
+        ++step_total;
+      }
+      PF_ADD(is_v ? 11 : 9, lane == 0);
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc = umma_idesc_bf16_f32(kPfTileQ, 128, 0, 0);     // S = Q K^T, both K-major
+    constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kPfTileQ, 128, 0, 1);  // O += P V, V MN-major
+    // Shared-memory descriptors, split into the low word (address field, which changes per MMA, and
+    // the leading offset) and the high word (stride offset, version, swizzle mode).
+    //   Q and P: K-major, 8-row groups 1 KiB apart; the second 64 elements of a row 16 KiB further.
+    //   K tile:  K-major, 8-token groups 2 KiB apart; the second 64 elements of a row are the next atom.
+    //   V tile:  [token][d] MN-major: the two 64-wide halves 1 KiB apart (leading offset), 8-token
+    //            groups 2 KiB apart (stride offset); a K step of 16 tokens is two groups.
+    const uint32_t desc_hi_1024 = static_cast<uint32_t>(umma_desc_sw128(0, 16, 1024) >> 32);
+    const uint32_t desc_hi_kv = static_cast<uint32_t>(umma_desc_sw128(0, 16, kPfGroupBytes) >> 32);
+    const uint32_t desc_q_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(q_smem), 16, 1024));
+    const uint32_t desc_p_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(p_smem), 16, 1024));
+    const uint32_t desc_k_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(k_smem), 16, kPfGroupBytes));
+    const uint32_t desc_v_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(v_smem), 1024, kPfGroupBytes));
+    for (uint32_t iter = 0; next_item(iter, it); ++iter) {
+      PF_T0();
+      int where = 200;
+      auto issue_qk = [&](uint32_t t) {
+        const uint32_t k_lo = desc_k_lo + (t % kPfRing) * (kPfTileBytes >> 4);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t a_lo = desc_q_lo + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+          const uint32_t b_lo = k_lo + (((ks >> 2) * 1024 + (ks & 3) * 32) >> 4);
+          tcgen05_mma_bf16(tmem_base, pf_desc(a_lo, desc_hi_1024), pf_desc(b_lo, desc_hi_kv), idesc, ks != 0 ? 1u : 0u);
+        }
+        tcgen05_commit(smem_u32(s_full));
+        tcgen05_commit(smem_u32(&k_empty[t % kPfRing]));
+      };
+      auto wait_tile = [&](uint64_t* full, uint32_t t) -> bool {
+        PF_T0();
+        const bool arrived = __all_sync(0xffffffffu, pf_wait(smem_u32(&full[t % kPfRing]), (t / kPfRing) & 1u, abort_flag));
+        PF_ADD(4, lane == 0);
+        return arrived;
+      };
+      bool ok = __all_sync(0xffffffffu, pf_wait(smem_u32(q_full), iter & 1u, abort_flag));
+      if (ok) ok = wait_tile(k_full, step_total);
+      if (ok) {
+        tcgen05_fence_after();
+        if (lane == 0) issue_qk(step_total);
+        __syncwarp();
+        for (int j = 0; j < it.n_steps && ok; ++j) {
+          const uint32_t t = step_total;
+          // Next S first: it only needs the softmax warps to have taken the current S into
+          // registers, so Q K^T of step j+1 runs under the softmax of step j.
+          if (j + 1 < it.n_steps) {
+            where = 300;
+            ok = wait_tile(k_full, t + 1);
+            if (!ok) break;
+            where = 350;
+            {
+              PF_T0();
+              ok = __all_sync(0xffffffffu, pf_wait(smem_u32(s_free), t & 1u, abort_flag));
+              PF_ADD(5, lane == 0);
+            }
+            if (!ok) break;
+            tcgen05_fence_after();
+            if (lane == 0) issue_qk(t + 1);
+            __syncwarp();
+          }
+          where = 380;
+          ok = wait_tile(v_full, t);
+          if (!ok) break;
+          // V rows at or beyond kv_len are zeroed (page tails may hold anything; 0 * NaN would
+          // poison the product) before the tensor core reads them.
           const int first_bad = max(it.kv_len - j * kPfTileKv, 0);
           if (first_bad < kPfTileKv) {
-            uint8_t* v_base = kv_smem + (pos % kPfStages) * kPfStageBytes + 2048;  // V lo of group 0
+            uint8_t* v_base = v_smem + (t % kPfRing) * kPfTileBytes;
             for (int e = lane; e < (kPfTileKv - first_bad) * 16; e += 32) {
-              const int row = first_bad + (e >> 4);
+              const int vrow = first_bad + (e >> 4);
               const int piece = e & 15;
-              *reinterpret_cast<uint4*>(v_base + (row >> 3) * kPfGroupBytes + (piece >> 3) * 1024 + (row & 7) * 128 +
+              *reinterpret_cast<uint4*>(v_base + (vrow >> 3) * kPfGroupBytes + (piece >> 3) * 1024 + (vrow & 7) * 128 +
                                         (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
             }
             fence_proxy_async_smem();
-          }
-          __syncwarp();
-          return true;
-        };
-        // Descriptors are built once (see above the item loop); per MMA only the 14-bit address
-        // field moves, by an addition to the low word. The issuing thread shares its scheduler with
-        // two softmax warps, so every instruction it does not execute is tensor time gained.
-        auto issue_qk = [&](int g, uint32_t pos) {
-          const uint32_t k_lo = desc_k_lo + (pos % kPfStages) * (kPfStageBytes >> 4);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t a_lo = desc_q_lo + g * (kPfQBytes >> 4) + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
-            const uint32_t b_lo = k_lo + (((ks >> 2) * 1024 + (ks & 3) * 32) >> 4);
-            tcgen05_mma_bf16(tmem_base + g * 64, pf_desc(a_lo, desc_hi_1024), pf_desc(b_lo, desc_hi_k), idesc_qk, ks != 0 ? 1u : 0u);
-          }
-          tcgen05_commit(smem_u32(&s_full[g]));
-        };
-        bool ok = __all_sync(0xffffffffu, pf_wait(smem_u32(q_full), iter & 1u, abort_flag));
-        if (ok) ok = stage_ready(kv_pos, 0);
-        if (ok) {
-          tcgen05_fence_after();
-          if (lane == 0)
-            for (int g = 0; g < sub; ++g) issue_qk(g, kv_pos);
-          __syncwarp();
-          for (int j = 0; j < it.n_steps && ok; ++j) {
-            if (j + 1 < it.n_steps) {
-              where = 300;
-              ok = stage_ready(kv_pos + 1, j + 1);
-              if (!ok) break;
-            }
-            // Next S first: it only needs the softmax warps to have taken the current S into
-            // registers, so Q K^T of step j+1 runs under the softmax of step j.
-            if (j + 1 < it.n_steps) {
-              for (int g = 0; g < sub; ++g) {
-                where = 350 + g;
-                PF_T0();
-                ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&s_free[g]), step_total & 1u, abort_flag));
-                PF_ADD(5, lane == 0);
-                if (!ok) break;
-                tcgen05_fence_after();
-                if (lane == 0) issue_qk(g, kv_pos + 1);
-                __syncwarp();
-              }
-              if (!ok) break;
-            }
-            for (int g = 0; g < sub; ++g) {
-              where = 400 + g;
-              PF_T0();
-              ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&p_full[2 * g + (step_total & 1u)]), (step_total >> 1) & 1u, abort_flag));
-              PF_ADD(6, lane == 0);
-              if (!ok) break;
-              tcgen05_fence_after();
-              if (lane == 0) {
-                const uint32_t buf = step_total & 1u;
-                const uint32_t a_lo = desc_p_lo + (g * 2 + buf) * (kPfPBytes >> 4);
-                const uint32_t b_lo = desc_v_lo + (kv_pos % kPfStages) * (kPfStageBytes >> 4);
-                tcgen05_mma_bf16(tmem_base + 128 + g * 128, pf_desc(a_lo, desc_hi_1024), pf_desc(b_lo, desc_hi_v), idesc_pv, j != 0 ? 1u : 0u);
-#pragma unroll
-                for (int ks = 1; ks < 4; ++ks)
-                  tcgen05_mma_bf16(tmem_base + 128 + g * 128, pf_desc(a_lo + ((ks * 32) >> 4), desc_hi_1024),
-                                   pf_desc(b_lo + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_v), idesc_pv, 1u);
-                tcgen05_commit(smem_u32(&pv_full[2 * g + buf]));
-              }
-              __syncwarp();
-            }
-            if (!ok) break;
-            if (lane == 0) tcgen05_commit(smem_u32(&kv_empty[kv_pos % kPfStages]));
             __syncwarp();
-            ++kv_pos;
-            ++step_total;
           }
+          where = 400;
+          {
+            PF_T0();
+            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&p_full[t & 1u]), (t >> 1) & 1u, abort_flag));
+            PF_ADD(6, lane == 0);
+          }
+          if (!ok) break;
+          tcgen05_fence_after();
+          if (lane == 0) {
+            const uint32_t a_base = desc_p_lo + (t & 1u) * (kPfPBytes >> 4);
+            const uint32_t b_base = desc_v_lo + (t % kPfRing) * (kPfTileBytes >> 4);
+            tcgen05_mma_bf16(tmem_base + 128, pf_desc(a_base, desc_hi_1024), pf_desc(b_base, desc_hi_kv), idesc_pv, j != 0 ? 1u : 0u);
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks)
+              tcgen05_mma_bf16(tmem_base + 128, pf_desc(a_base + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), desc_hi_1024),
+                               pf_desc(b_base + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_kv), idesc_pv, 1u);
+            tcgen05_commit(smem_u32(&pv_full[t & 1u]));
+            tcgen05_commit(smem_u32(&v_empty[t % kPfRing]));
+          }
+          __syncwarp();
+          ++step_total;
         }
-        if (!ok) {
-          if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, where);
-          *abort_flag = 1;
-        }
-        __syncwarp();
-        PF_ADD(7, lane == 0);
       }
-    } else {
-      // warps 10 and 11 have no role: they only take part in the item barrier
-      for (uint32_t iter = 0; next_item(iter, it); ++iter) {
+      if (!ok) {
+        if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, where);
+        *abort_flag = 1;
       }
+      __syncwarp();
+      PF_ADD(7, lane == 0);
+    }
+  } else {
+    // warp 7 has no role: it only takes part in the item barrier
+    for (uint32_t iter = 0; next_item(iter, it); ++iter) {
     }
   }
 
   // ---- orderly exit
   __syncthreads();
   if (*abort_flag) {
-    if (warp == 8 && lane == 0) {
+    if ((warp == 4 || warp == 6) && lane == 0) {
       // loads already issued must land before shared memory is released
-      if (q_issued) mbar_wait_bounded(smem_u32(q_full), (q_issued - 1) & 1u, 200000000ll);
-      for (uint32_t back = 0; back < kPfStages && back < kv_pos; ++back) {
-        const uint32_t pos = kv_pos - 1 - back;
-        mbar_wait_bounded(smem_u32(&kv_full[pos % kPfStages]), (pos / kPfStages) & 1u, 200000000ll);
+      uint64_t* full = warp == 6 ? v_full : k_full;
+      for (uint32_t back = 0; back < kPfRing && back < loads_issued; ++back) {
+        const uint32_t t = step_total - 1 - back;
+        mbar_wait_bounded(smem_u32(&full[t % kPfRing]), (t / kPfRing) & 1u, 200000000ll);
       }
+      if (warp == 4) mbar_wait_bounded(smem_u32(q_full), 0, 1000000ll);
     }
-    if (warp == 9 && lane == 0) {
+    if (warp == 5 && lane == 0) {
       tcgen05_commit(smem_u32(drain_bar));
       mbar_wait_bounded(smem_u32(drain_bar), 0, 200000000ll);
     }
@@ -711,7 +693,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 5) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, kPfTmemCols);
   }
