@@ -123,3 +123,78 @@ def test_rpa_cost_convention_matches_bench_bytes():
     counts = cost_model.estimate_rpa_decode(lengths, q_heads=32, kv_heads=8, head_dim=128, page_size=16)
     assert counts.hbm_bytes == workloads.decode_algorithmic_bytes(lengths, 32, 8, 128, 16)
     assert counts.flops == 4 * 128 * 32 * int(np.asarray(lengths, dtype=np.int64).sum())
+
+
+# ------------------------------------------------------------------------------------ RPA op types
+
+
+def test_prototype_attention_op_verifies_and_lowers():
+    from tpu_cake_b200 import rpa_cuda_lowering
+
+    module = workloads.paged_attention_schedule(batch=4, q_heads=8, kv_heads=2, head_dim=128, pages=32, page_size=16, max_pages=8)
+    plan = rpa_cuda_lowering.lower_paged_attention_to_cuda(module)
+    assert plan.query_shape == (4, 8, 128) and plan.cache_shape == (32, 16, 2, 128)
+    assert plan.page_table_shape == (4, 8) and plan.bias_shape == (8, 128) and plan.softmax_scale == 1.0 / 128
+    assert len(plan.schedule_sha256) == 64 and plan.source_sha256() != plan.schedule_sha256
+    toy = workloads.paged_attention_schedule()  # the reference's toy shape: verifies, head_dim 32 is not lowered
+    with pytest.raises(rpa_cuda_lowering.UnsupportedRpaLowering, match="head_dim 128"):
+        rpa_cuda_lowering.lower_paged_attention_to_cuda(toy)
+
+
+@pytest.mark.parametrize(
+    "kwargs, message",
+    [
+        ({"q_heads": 6, "kv_heads": 4}, "divide evenly"),
+        ({"max_pages": 16}, None),  # bias extent follows max_pages: still valid
+    ],
+)
+def test_prototype_attention_op_rules(kwargs, message):
+    if message is None:
+        workloads.paged_attention_schedule(**kwargs)
+        return
+    with pytest.raises(ir.VerifyException, match=message):
+        workloads.paged_attention_schedule(**kwargs)
+
+
+def test_fused_attention_op_strict_and_cuda_authorities():
+    from tpu_cake_b200 import dialects, rpa_cuda_lowering
+
+    shape = dict(q_heads=8, kv_heads=4, head_dim=128, pages=3712, page_size=1, page_indices=8192)
+    strict = workloads.fused_rpa_schedule(tokens=4, **shape)
+    plan = rpa_cuda_lowering.lower_fused_rpa_to_cuda(strict)
+    assert isinstance(plan, rpa_cuda_lowering.CudaFusedRpaPlan) and plan.softmax_scale == 1.0 / 128
+    assert plan.relative_states_shape == (4, 8, 16) and plan.relative_projection_shape == (16, 512)
+    # The reference's authority refuses another scale and ragged query runs ...
+    with pytest.raises(ir.VerifyException, match="must equal 1 / head dimension"):
+        workloads.fused_rpa_schedule(tokens=4, softmax_scale="0.088388", execution_authority=dialects.FUSED_RPA_UPSTREAM_AUTHORITY, **shape)
+    with pytest.raises(ir.VerifyException, match="one query token per sequence"):
+        workloads.fused_rpa_schedule(tokens=40, sequences=4, execution_authority=dialects.FUSED_RPA_UPSTREAM_AUTHORITY, **shape)
+    with pytest.raises(ir.VerifyException, match="delegated execution authority"):
+        workloads.fused_rpa_schedule(tokens=4, execution_authority="someone-else", **shape)
+    # ... this backend's authority takes both.
+    ragged = workloads.fused_rpa_schedule(tokens=40, sequences=4, softmax_scale="0.088388", **shape)
+    mixed = rpa_cuda_lowering.lower_fused_rpa_to_cuda(ragged)
+    assert isinstance(mixed, rpa_cuda_lowering.CudaMixedRpaPlan) and mixed.sequences == 4 and mixed.query_shape == (40, 8, 128)
+    assert abs(mixed.softmax_scale - 0.088388) < 1e-12
+
+
+def test_cuda_decode_resource_contract_op():
+    from tpu_cake_b200 import dialects, rpa_cuda_lowering
+
+    module = workloads.paged_attention_schedule(batch=4, q_heads=8, kv_heads=2, head_dim=128)
+    plan = rpa_cuda_lowering.lower_paged_attention_to_cuda(module)
+    contract = rpa_cuda_lowering.decode_resource_contract(plan)
+    assert contract["shared_memory_bytes"] == 6 * (2 * 32 * 512 + 2048) + 1280 <= dialects.B200_SHARED_MEMORY_PER_CTA
+    kernel = module.ops[0]
+    attention = next(op for op in kernel.body.ops if op.name == "tpu_schedule.ragged_paged_attention")
+    good = ir.Operation("tpu_schedule.cuda_rpa_decode", list(attention.operands), [],
+                        {"stage": 2, "attention": attention.name, "backend": "cake-b200/sm_100a", **contract})
+    dialects.verify_operation(good)
+    bad = ir.Operation("tpu_schedule.cuda_rpa_decode", list(attention.operands), [],
+                       {"stage": 2, "attention": attention.name, "backend": "cake-b200/sm_100a", **{**contract, "kv_chunk_tokens": 48}})
+    with pytest.raises(ir.VerifyException, match="multiple of the stage size"):
+        dialects.verify_operation(bad)
+    wrong_bytes = ir.Operation("tpu_schedule.cuda_rpa_decode", list(attention.operands), [],
+                               {"stage": 2, "attention": attention.name, "backend": "cake-b200/sm_100a", **{**contract, "shared_memory_bytes": 4096}})
+    with pytest.raises(ir.VerifyException, match="shared_memory_bytes must be"):
+        dialects.verify_operation(wrong_bytes)

@@ -16,6 +16,11 @@ from enum import StrEnum
 from .ir import Block, BufferType, DTensorType, Module, OpaqueType, Operation, SourceLocation, Value, VerifyException
 
 
+FUSED_RPA_UPSTREAM_AUTHORITY = "opaque-upstream-wrapper"  # the reference's only authority: decode, scale = 1/head_dim
+FUSED_RPA_CUDA_AUTHORITY = "cake-b200-sm100-kernels"       # this backend: any positive scale, ragged query runs
+B200_SHARED_MEMORY_PER_CTA = 232448
+
+
 class CollectiveImplementation(StrEnum):
     """How a physical collective is carried out. The reference has ``pallas_bidirectional_ring``
     (tpu_schedule.py:89-104) beside the compiler's collective; the B200 backend has the NCCL
@@ -148,6 +153,42 @@ class KernelBuilder:
         if implementation is not None:
             properties["implementation"] = CollectiveImplementation(implementation).value
         return self._append(Operation("tpu_schedule.collective", [source, destination], [], properties))
+
+    def ragged_paged_attention(self, query: Value, key_cache: Value, value_cache: Value, page_table: Value, sequence_lengths: Value,
+                               bias: Value, output: Value, *, stage: int, query_block_size: int, kv_block_size: int) -> Operation:
+        """The prototype decode op (tpu_schedule.py:2003-2103): separate caches, 2-D page table, dense bias."""
+        return self._append(Operation(
+            "tpu_schedule.ragged_paged_attention", [query, key_cache, value_cache, page_table, sequence_lengths, bias, output], [],
+            {"stage": stage, "query_block_size": query_block_size, "kv_block_size": kv_block_size},
+        ))
+
+    def fused_ragged_paged_attention(self, operands: tuple[Value, ...], *, stage: int, softmax_scale: str, causal: int = 1,
+                                     softmax_dtype: str = "float32", sliding_window: int = 0, query_block_size: int = 8,
+                                     kv_block_size: int = 128, query_cluster_size: int = 8, kv_cluster_size: int = 128,
+                                     vmem_limit_bytes: int = 1 << 20, execution_authority: str = FUSED_RPA_UPSTREAM_AUTHORITY,
+                                     donated_operand_indices: tuple[int, ...] = (0, 1, 2, 3)) -> Operation:
+        """The fused-cache op (tpu_schedule.py:2107-2349): 11 inputs + the two aliased outputs."""
+        if len(operands) != 13:
+            raise ValueError("fused RPA takes 11 inputs followed by the output and the updated cache")
+        return self._append(Operation(
+            "tpu_schedule.fused_ragged_paged_attention", list(operands), [],
+            {"stage": stage, "causal": causal, "softmax_scale": softmax_scale, "softmax_dtype": softmax_dtype,
+             "sliding_window": sliding_window, "query_block_size": query_block_size, "kv_block_size": kv_block_size,
+             "query_cluster_size": query_cluster_size, "kv_cluster_size": kv_cluster_size, "vmem_limit_bytes": vmem_limit_bytes,
+             "execution_authority": execution_authority, "donated_operand_indices": tuple(donated_operand_indices)},
+        ))
+
+    def cuda_rpa_decode(self, attention: Operation, *, stage: int, kv_chunk_tokens: int, warps_per_cta: int, ring_stages: int,
+                        stage_tokens: int, shared_memory_bytes: int, workspace_bytes: int) -> Operation:
+        """Static resource contract of the sm_100a decode kernel for one attention op of this kernel:
+        the sibling of the reference's rpa_decode_core (tpu_schedule.py:2357-2885), whose VMEM / DMA
+        semaphore shapes do not transfer to a GPU."""
+        return self._append(Operation(
+            "tpu_schedule.cuda_rpa_decode", list(attention.operands), [],
+            {"stage": stage, "kv_chunk_tokens": kv_chunk_tokens, "warps_per_cta": warps_per_cta, "ring_stages": ring_stages,
+             "stage_tokens": stage_tokens, "shared_memory_bytes": shared_memory_bytes, "workspace_bytes": workspace_bytes,
+             "attention": attention.name, "backend": "cake-b200/sm_100a"},
+        ))
 
     def module(self) -> Module:
         self._append(Operation("tpu_schedule.yield"))
@@ -334,6 +375,164 @@ def _verify_kernel(op: Operation) -> None:
                 raise _fail(op, f"{live} live {space} bytes at stage {stage} exceed the capacity {capacity}")
 
 
+def _verify_paged_attention(op: Operation) -> None:
+    """Rules and messages of RaggedPagedAttentionOp.verify_ (tpu_schedule.py:2039-2103)."""
+    stage = op.properties["stage"]
+    names = ("query", "key_cache", "value_cache", "page_table", "sequence_lengths", "bias", "output")
+    query, key_cache, value_cache, page_table, lengths, bias, output = (_buffer(op, v, n) for v, n in zip(op.operands, names))
+    for name, b in zip(names, (query, key_cache, value_cache, page_table, lengths, bias, output)):
+        if not _live(b, stage):
+            raise _fail(op, f"{name} is not live at stage {stage}")
+    if query.memory != "vmem" or output.memory != "vmem":
+        raise _fail(op, "RPA query and output must be resident in VMEM")
+    if bias.memory != "vmem":
+        raise _fail(op, "RPA relative-position bias must be resident in VMEM")
+    if any(b.memory != "hbm" for b in (key_cache, value_cache, page_table, lengths)):
+        raise _fail(op, "RPA cache and page metadata must reside in HBM")
+    if len(query.shape) != 3 or len(key_cache.shape) != 4 or len(value_cache.shape) != 4 or len(output.shape) != 3:
+        raise _fail(op, "RPA expects query/output [batch, heads, dim] and caches [pages, page, heads, dim]")
+    batch, query_heads, query_dimension = query.shape
+    key_pages, page_size, key_heads, key_dimension = key_cache.shape
+    value_pages, value_page_size, value_heads, value_dimension = value_cache.shape
+    if (key_pages, page_size) != (value_pages, value_page_size):
+        raise _fail(op, "RPA key and value caches must share pages and page size")
+    if query_dimension != key_dimension:
+        raise _fail(op, "RPA query and key head dimensions must match")
+    if key_heads <= 0 or value_heads <= 0:
+        raise _fail(op, "RPA key and value head counts must be positive")
+    if query_heads % key_heads or query_heads % value_heads:
+        raise _fail(op, "RPA query heads must divide evenly across key and value heads")
+    if output.shape != (batch, query_heads, value_dimension):
+        raise _fail(op, "RPA output must use batch/query heads and value dimension")
+    if len(page_table.shape) != 2 or len(bias.shape) != 2:
+        raise _fail(op, "RPA page table and bias must be rank 2")
+    if page_table.shape[0] != batch or lengths.shape != (batch,):
+        raise _fail(op, "RPA page metadata batch dimensions must match query")
+    if bias.shape[0] != query_heads:
+        raise _fail(op, "RPA bias head dimension must match query")
+    if bias.shape[1] < page_table.shape[1] * page_size:
+        raise _fail(op, "RPA bias extent must cover every addressable cache position")
+    if op.properties["kv_block_size"] <= 0 or page_size % op.properties["kv_block_size"]:
+        raise _fail(op, "RPA KV block size must be positive and divide page size")
+    if op.properties["query_block_size"] <= 0:
+        raise _fail(op, "RPA query block size must be positive")
+
+
+def _verify_fused_paged_attention(op: Operation) -> None:
+    """Rules and messages of FusedRaggedPagedAttentionOp.verify_ (tpu_schedule.py:2195-2349). Under the
+    reference's authority the strict decode contract holds (tokens == sequences, scale * dim == 1);
+    under this backend's authority the scale is any positive decimal and sequences may own query runs."""
+    from decimal import Decimal, InvalidOperation
+
+    names = ("queries", "keys", "values", "fused_cache", "kv_lengths", "page_indices", "cumulative_query_lengths",
+             "cumulative_kv_lengths", "distribution", "relative_states", "relative_projection", "output", "updated_cache")
+    buffers = [_buffer(op, v, n) for v, n in zip(op.operands, names)]
+    if any(b.memory != "hbm" for b in buffers):
+        raise _fail(op, "fused RPA wrapper operands must reside in HBM")
+    stage = op.properties["stage"]
+    if any(not _live(b, stage) for b in buffers):
+        raise _fail(op, f"fused RPA operands must be live at stage {stage}")
+    q, k, v, cache, lens, pages, cu_q, cu_kv, dist, states, projection, output, updated = buffers
+    if len(q.shape) != 3 or len(k.shape) != 3 or len(v.shape) != 3:
+        raise _fail(op, "fused RPA Q/K/V must have [tokens, heads, dim] shape")
+    if len(cache.shape) != 5:
+        raise _fail(op, "fused RPA cache must have [pages, page, packed_heads, packing, dim] shape")
+    if any(extent <= 0 for extent in (*q.shape, *k.shape, *v.shape, *cache.shape)):
+        raise _fail(op, "fused RPA Q/K/V/cache dimensions must be positive")
+    if any(b.element_type != "bf16" for b in (q, k, v, cache, states, projection, output, updated)):
+        raise _fail(op, "Inkling fused RPA data buffers must use bf16")
+    if any(b.element_type != "i32" for b in (lens, pages, cu_q, cu_kv, dist)):
+        raise _fail(op, "fused RPA metadata buffers must use i32")
+    tokens, query_heads, dimension = q.shape
+    if (k.shape[0], v.shape[0]) != (tokens, tokens):
+        raise _fail(op, "fused RPA Q/K/V token counts must match")
+    if k.shape[1] != v.shape[1] or query_heads % k.shape[1]:
+        raise _fail(op, "fused RPA requires equal K/V heads dividing query heads")
+    if (k.shape[2], v.shape[2]) != (dimension, dimension):
+        raise _fail(op, "fused RPA Q/K/V head dimensions must match")
+    _, _, packed_heads, packing, cache_dimension = cache.shape
+    if cache_dimension != -(-dimension // 128) * 128:
+        raise _fail(op, "fused RPA cache head dimension must be padded to a multiple of 128")
+    if packing != 2 or packed_heads * packing != 2 * k.shape[1]:
+        raise _fail(op, "fused RPA cache must interleave one K and V per KV head")
+    if output.shape != q.shape:
+        raise _fail(op, "fused RPA output shape must match queries")
+    if updated.shape != cache.shape:
+        raise _fail(op, "fused RPA updated cache shape must match its input cache")
+    if len(lens.shape) != 1 or not lens.shape[0]:
+        raise _fail(op, "fused RPA KV lengths must be nonempty rank 1")
+    if len(pages.shape) != 1:
+        raise _fail(op, "fused RPA page indices must be rank 1")
+    sequences = lens.shape[0]
+    authority = op.properties["execution_authority"]
+    if authority not in (FUSED_RPA_UPSTREAM_AUTHORITY, FUSED_RPA_CUDA_AUTHORITY):
+        raise _fail(op, "fused RPA must declare delegated execution authority")
+    strict = authority == FUSED_RPA_UPSTREAM_AUTHORITY
+    if strict and tokens != sequences:
+        raise _fail(op, "Inkling fused decode RPA requires one query token per sequence")
+    if not strict and tokens < sequences:
+        raise _fail(op, "fused RPA needs at least one query token per sequence")
+    if strict and pages.shape[0] % sequences:
+        raise _fail(op, "fused RPA flat page indices must divide across sequences")
+    if cu_q.shape != (sequences + 1,) or cu_kv.shape != (sequences + 1,):
+        raise _fail(op, "fused RPA cumulative lengths must have sequences + 1 entries")
+    if dist.shape != (3,):
+        raise _fail(op, "fused RPA distribution must contain three boundaries")
+    if len(states.shape) != 3 or len(projection.shape) != 2:
+        raise _fail(op, "fused RPA relative states/projection must be rank 3/rank 2")
+    if states.shape[:2] != (tokens, query_heads):
+        raise _fail(op, "fused RPA relative states must match query tokens and heads")
+    if states.shape[2] != projection.shape[0]:
+        raise _fail(op, "fused RPA relative dimensions must match")
+    if op.properties["causal"] != 1:
+        raise _fail(op, "Inkling fused RPA adapter requires causal attention without a custom mask")
+    try:
+        scale = Decimal(op.properties["softmax_scale"])
+    except (InvalidOperation, TypeError) as error:
+        raise _fail(op, "fused RPA softmax scale must be decimal") from error
+    if not scale.is_finite() or scale <= 0:
+        raise _fail(op, "fused RPA softmax scale must be positive and finite")
+    if strict and scale * dimension != Decimal(1):
+        raise _fail(op, "Inkling fused RPA softmax scale must equal 1 / head dimension")
+    if op.properties["softmax_dtype"] != "float32":
+        raise _fail(op, "Inkling fused RPA softmax must use float32")
+    if op.properties["sliding_window"] < 0:
+        raise _fail(op, "fused RPA sliding window cannot be negative")
+    block_keys = ("query_block_size", "kv_block_size", "query_cluster_size", "kv_cluster_size", "vmem_limit_bytes")
+    if any(op.properties[key] <= 0 for key in block_keys):
+        raise _fail(op, "fused RPA block sizes and VMEM limit must be positive")
+    if tuple(op.properties["donated_operand_indices"]) != (0, 1, 2, 3):
+        raise _fail(op, "fused RPA must donate Q, K, V, and fused cache")
+    if op.operands[11] is not op.operands[0] or op.operands[12] is not op.operands[3]:
+        raise _fail(op, "fused RPA output/cache destinations must alias query/cache inputs")
+    page_size = cache.shape[1]
+    if (op.properties["query_block_size"] % op.properties["query_cluster_size"] or op.properties["kv_block_size"] % op.properties["kv_cluster_size"]
+            or op.properties["kv_block_size"] % page_size):
+        raise _fail(op, "fused RPA blocks must divide into clusters and KV blocks must align to pages")
+
+
+def _verify_cuda_rpa_decode(op: Operation) -> None:
+    """Resource contract of the sm_100a decode kernel: what one CTA holds in shared memory must match
+    what the declared ring needs and fit a B200 CTA; chunks are whole stages."""
+    props = op.properties
+    if props["stage_tokens"] not in (16, 32):
+        raise _fail(op, "a stage is one or two 16-token MMA groups")
+    if props["kv_chunk_tokens"] <= 0 or props["kv_chunk_tokens"] % props["stage_tokens"]:
+        raise _fail(op, "kv_chunk_tokens must be a positive multiple of the stage size")
+    if props["warps_per_cta"] <= 0 or props["ring_stages"] < 2:
+        raise _fail(op, "the kernel needs at least one worker warp and a two-stage ring")
+    row_bytes = 256  # one token of one head: 128 bf16
+    needed = props["warps_per_cta"] * (props["ring_stages"] * props["stage_tokens"] * 2 * row_bytes + 8 * row_bytes) + 1024 + 256
+    if props["shared_memory_bytes"] != needed:
+        raise _fail(op, f"shared_memory_bytes must be {needed} for this ring")
+    if needed > B200_SHARED_MEMORY_PER_CTA:
+        raise _fail(op, f"{needed} bytes of shared memory exceed the {B200_SHARED_MEMORY_PER_CTA} a B200 CTA may use")
+    if props["workspace_bytes"] <= 0:
+        raise _fail(op, "split-KV workspace must be declared")
+    if props["attention"] not in ("tpu_schedule.ragged_paged_attention", "tpu_schedule.fused_ragged_paged_attention"):
+        raise _fail(op, "cuda_rpa_decode refines an attention op of the same kernel")
+
+
 _VERIFIERS = {
     "dtensor.program": _verify_program,
     "dtensor.einsum_local": _verify_einsum_local,
@@ -341,6 +540,9 @@ _VERIFIERS = {
     "tpu_schedule.kernel": _verify_kernel,
     "tpu_schedule.mxu_matmul": _verify_matmul,
     "tpu_schedule.collective": _verify_collective,
+    "tpu_schedule.ragged_paged_attention": _verify_paged_attention,
+    "tpu_schedule.fused_ragged_paged_attention": _verify_fused_paged_attention,
+    "tpu_schedule.cuda_rpa_decode": _verify_cuda_rpa_decode,
 }
 
 

@@ -132,6 +132,84 @@ def preflight_mixed_metadata(inputs: tuple, input_shapes: tuple[tuple[int, ...],
     return decode_end
 
 
+class UnsupportedRpaLowering(ValueError):
+    """A physical RPA kernel the CUDA backend does not lower (mirrors UnsupportedRpaLoweringError,
+    src/tpu_cake/rpa_lowering.py:37-38)."""
+
+
+def _single_op(module, name: str):
+    module.verify()
+    if len(module.ops) != 1 or module.ops[0].name != "tpu_schedule.kernel":
+        raise UnsupportedRpaLowering("expected one physical kernel")
+    kernel = module.ops[0]
+    matches = [op for op in kernel.body.ops if op.name == name]
+    if len(matches) != 1:
+        raise UnsupportedRpaLowering(f"expected exactly one {name} in the kernel, found {len(matches)}")
+    return kernel, matches[0]
+
+
+def lower_paged_attention_to_cuda(module, *, softmax_scale: float | None = None, kv_chunk_tokens: int = 0) -> "CudaPagedAttentionPlan":
+    """``tpu_schedule.ragged_paged_attention`` -> CUDA decode plan. The reference only renders this
+    op's contract (src/tpu_cake/cli.py:667-676); here it gets an executable lowering. The softmax
+    scale is not a property of the op: the reference oracle's 1/head_dim is the default."""
+    from .ir import schedule_sha256
+
+    kernel, op = _single_op(module, "tpu_schedule.ragged_paged_attention")
+    query, key_cache, value_cache, page_table, _lengths, bias, _output = (value.type for value in op.operands)
+    if key_cache.shape != value_cache.shape:
+        raise UnsupportedRpaLowering("key and value caches must have one shape")
+    if key_cache.element_type != "bf16" or query.element_type != "bf16":
+        raise UnsupportedRpaLowering("the CUDA decode kernels take bf16 queries and caches")
+    if query.shape[2] != 128:
+        raise UnsupportedRpaLowering("separate K / V caches are lowered for head_dim 128")
+    return CudaPagedAttentionPlan(
+        name=kernel.properties["sym_name"], schedule_sha256=schedule_sha256(module), query_shape=tuple(query.shape),
+        cache_shape=tuple(key_cache.shape), page_table_shape=tuple(page_table.shape), bias_shape=tuple(bias.shape),
+        softmax_scale=softmax_scale if softmax_scale is not None else 1.0 / query.shape[2], kv_chunk_tokens=kv_chunk_tokens,
+    )
+
+
+def lower_fused_rpa_to_cuda(module, *, with_relative_bias: bool = True, kv_chunk_tokens: int = 0):
+    """``tpu_schedule.fused_ragged_paged_attention`` -> ``CudaFusedRpaPlan`` (one query token per
+    sequence) or ``CudaMixedRpaPlan`` (ragged query runs; relative bias not lowered). Mirrors
+    ``lower_fused_rpa_kernel`` (src/tpu_cake/rpa_lowering.py:291-392)."""
+    from .ir import schedule_sha256
+
+    kernel, op = _single_op(module, "tpu_schedule.fused_ragged_paged_attention")
+    if op.properties["sliding_window"] != 0:
+        raise UnsupportedRpaLowering("sliding-window attention is not lowered by the CUDA backend")
+    types = [value.type for value in op.operands]
+    q, k, _v, cache, lens, pages = types[:6]
+    states, projection = types[9], types[10]
+    scale = float(op.properties["softmax_scale"])
+    if q.shape[0] == lens.shape[0]:
+        return CudaFusedRpaPlan(
+            name=kernel.properties["sym_name"], schedule_sha256=schedule_sha256(module), query_shape=tuple(q.shape),
+            key_shape=tuple(k.shape), value_shape=tuple(k.shape), fused_cache_shape=tuple(cache.shape), kv_lengths_shape=tuple(lens.shape),
+            page_indices_shape=tuple(pages.shape), cumulative_query_lengths_shape=(lens.shape[0] + 1,),
+            cumulative_kv_lengths_shape=(lens.shape[0] + 1,), distribution_shape=(3,),
+            relative_states_shape=tuple(states.shape) if with_relative_bias else None,
+            relative_projection_shape=tuple(projection.shape) if with_relative_bias else None, output_shape=tuple(q.shape),
+            softmax_scale=scale, kv_chunk_tokens=kv_chunk_tokens,
+        )
+    return CudaMixedRpaPlan(
+        name=kernel.properties["sym_name"], schedule_sha256=schedule_sha256(module), query_shape=tuple(q.shape), key_shape=tuple(k.shape),
+        fused_cache_shape=tuple(cache.shape), sequences=lens.shape[0], page_indices_shape=tuple(pages.shape), softmax_scale=scale,
+        kv_chunk_tokens=kv_chunk_tokens,
+    )
+
+
+def decode_resource_contract(plan) -> dict:
+    """Properties of a ``tpu_schedule.cuda_rpa_decode`` op for a decode plan: the static resources of
+    the sm_100a decode kernel as built (6 worker warps, 2-stage rings of 32-token stages)."""
+    warps, stages, stage_tokens, row_bytes = 6, 2, 32, 256
+    batch, q_heads = plan.query_shape[0], plan.query_shape[1]
+    chunk = plan.kv_chunk_tokens or 512
+    shared = warps * (stages * stage_tokens * 2 * row_bytes + 8 * row_bytes) + 1024 + 256
+    return {"kv_chunk_tokens": chunk, "warps_per_cta": warps, "ring_stages": stages, "stage_tokens": stage_tokens,
+            "shared_memory_bytes": shared, "workspace_bytes": max(1, batch * q_heads * 130 * 4)}
+
+
 def _to_host(value):
     if isinstance(value, torch.Tensor):
         return value.detach().cpu().numpy()

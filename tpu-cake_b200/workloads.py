@@ -193,6 +193,82 @@ def mixed_algorithmic_work(meta: MixedMetadata, q_heads: int, kv_heads: int, hea
     }
 
 
+def paged_attention_schedule(*, batch: int = 4, q_heads: int = 4, kv_heads: int = 4, head_dim: int = 32, pages: int = 32,
+                             page_size: int = 16, max_pages: int = 8, target: str = "b200"):
+    """Physical kernel around the prototype decode op: stage the query and the bias on chip, run
+    ``tpu_schedule.ragged_paged_attention``, copy the output back (the shape of
+    src/tpu_cake/workloads/inkling_rpa.py:87-142, whose defaults these are)."""
+    from .dialects import KernelBuilder, buffer
+
+    external = {"memory": "hbm", "ownership": "external", "lifetime": (0, 4)}
+    extent = max_pages * page_size
+    inputs = (
+        buffer((batch, q_heads, head_dim), "B H D".split(), "bf16", **external),
+        buffer((pages, page_size, kv_heads, head_dim), "P S H D".split(), "bf16", **external),
+        buffer((pages, page_size, kv_heads, head_dim), "P S H D".split(), "bf16", **external),
+        buffer((batch, max_pages), "B MP".split(), "i32", **external),
+        buffer((batch,), ("B",), "i32", **external),
+        buffer((q_heads, extent), "H L".split(), "bf16", **external),
+        buffer((batch, q_heads, head_dim), "B H D".split(), "bf16", **external),
+    )
+    builder = KernelBuilder("inkling_rpa_decode", target, inputs, vmem_capacity_bytes=160 << 30, smem_capacity_bytes=227 << 10,
+                            mesh={}, interconnect_bandwidth_bytes_per_second={})
+    query = builder.alloc(buffer((batch, q_heads, head_dim), "B H D".split(), "bf16", memory="vmem", lifetime=(0, 2)), "query_tile")
+    bias = builder.alloc(buffer((q_heads, extent), "H L".split(), "bf16", memory="vmem", lifetime=(0, 2)), "relative_bias")
+    output = builder.alloc(buffer((batch, q_heads, head_dim), "B H D".split(), "bf16", memory="vmem", lifetime=(2, 4)), "attention_output")
+    semaphores = [builder.semaphore() for _ in range(3)]
+    query_dma = builder.dma_start(builder.inputs[0], query, semaphores[0], stage=0)
+    bias_dma = builder.dma_start(builder.inputs[5], bias, semaphores[1], stage=0)
+    builder.dma_wait(query_dma, stage=1)
+    builder.dma_wait(bias_dma, stage=1)
+    builder.ragged_paged_attention(query, builder.inputs[1], builder.inputs[2], builder.inputs[3], builder.inputs[4], bias, output,
+                                   stage=2, query_block_size=1, kv_block_size=min(8, page_size))
+    output_dma = builder.dma_start(output, builder.inputs[6], semaphores[2], stage=3)
+    builder.dma_wait(output_dma, stage=4)
+    return builder.module()
+
+
+def fused_rpa_schedule(*, tokens: int, sequences: int | None = None, q_heads: int, kv_heads: int, head_dim: int, pages: int,
+                       page_size: int, page_indices: int, relative_dim: int = 16, bias_extent: int = 512, softmax_scale: str | None = None,
+                       execution_authority: str | None = None, target: str = "b200"):
+    """Physical kernel holding one ``tpu_schedule.fused_ragged_paged_attention`` over external HBM
+    buffers, output and cache aliased to the query and cache inputs (the contract of
+    src/tpu_cake/dialects/tpu_schedule.py:2107-2349). ``sequences`` below ``tokens`` describes a ragged
+    batch and needs this backend's execution authority."""
+    from .dialects import FUSED_RPA_CUDA_AUTHORITY, FUSED_RPA_UPSTREAM_AUTHORITY, KernelBuilder, buffer
+
+    sequences = tokens if sequences is None else sequences
+    padded = -(-head_dim // 128) * 128
+    external = {"memory": "hbm", "ownership": "external", "lifetime": (0, 0)}
+    inputs = (
+        buffer((tokens, q_heads, head_dim), "T H D".split(), "bf16", **external),
+        buffer((tokens, kv_heads, head_dim), "T KH D".split(), "bf16", **external),
+        buffer((tokens, kv_heads, head_dim), "T KH D".split(), "bf16", **external),
+        buffer((pages, page_size, kv_heads, 2, padded), "P S KH C DP".split(), "bf16", **external),
+        buffer((sequences,), ("N",), "i32", **external),
+        buffer((page_indices,), ("PI",), "i32", **external),
+        buffer((sequences + 1,), ("N1",), "i32", **external),
+        buffer((sequences + 1,), ("N1",), "i32", **external),
+        buffer((3,), ("X",), "i32", **external),
+        buffer((tokens, q_heads, relative_dim), "T H R".split(), "bf16", **external),
+        buffer((relative_dim, bias_extent), "R E".split(), "bf16", **external),
+    )
+    builder = KernelBuilder("inkling_fused_rpa", target, inputs, vmem_capacity_bytes=160 << 30, smem_capacity_bytes=227 << 10,
+                            mesh={}, interconnect_bandwidth_bytes_per_second={})
+    if execution_authority is None:
+        execution_authority = FUSED_RPA_UPSTREAM_AUTHORITY if sequences == tokens and softmax_scale is None else FUSED_RPA_CUDA_AUTHORITY
+    if softmax_scale is None:
+        from decimal import Decimal
+
+        softmax_scale = str(Decimal(1) / Decimal(head_dim))
+    kv_block = max(128, page_size)
+    builder.fused_ragged_paged_attention(
+        (*builder.inputs, builder.inputs[0], builder.inputs[3]), stage=0, softmax_scale=softmax_scale, kv_block_size=kv_block,
+        kv_cluster_size=kv_block, execution_authority=execution_authority,
+    )
+    return builder.module()
+
+
 def distributed_matmul_schedule(*, mesh_size: int = 4, m: int = 16, k: int = 32, n: int = 16, scatter_dimension: str = "N"):
     """The logical program ``einsum_local(lhs[M, K@t], rhs[K@t, N]) -> f32[M, N]{pending t:sum}``
     followed by ``reduce_scatter(axes=t, dim=scatter_dimension)``
