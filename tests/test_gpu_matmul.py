@@ -240,3 +240,21 @@ def test_runner_writes_a_complete_bundle(cuda_device, tmp_path, mesh_size, strat
         assert np.allclose(np.load(out / "output.npy"), np.load(out / "oracle.npy"), atol=1e-3, rtol=1e-3)
     with pytest.raises(FileExistsError):
         runner.run_distributed_matmul(out, mesh_size=mesh_size, m=128, k=1024, n=1024, warmup_iterations=0, measured_iterations=1)
+
+
+def test_tile_search_through_the_runner(cuda_device, tmp_path):
+    """search-matmul on one GPU (the mesh positions emulated): every candidate runs in every round,
+    all pass the oracle on the same inputs, and the result names a baseline and per-candidate medians."""
+    from tpu_cake_b200 import search
+
+    contract = search.MatmulSearchContract(
+        mesh_size=2, m=256, k=1024, n=512, warmup_iterations=1, measured_iterations=3, rounds=5, bootstrap_samples=1000,
+        collective_strategy="p2p_fused_epilogue", scatter_dimension="N", output_dtype="f32",
+        candidates=(search.MatmulSearchCandidate("tile-128x256", 128, 256), search.MatmulSearchCandidate("tile-128x64", 128, 64)),
+    )
+    result = search.run_matmul_search(tmp_path / "search", contract)
+    assert result.baseline == "tile-128x256" and len(result.run_results) == 10
+    assert result.execution_orders[1] == ("tile-128x64", "tile-128x256")
+    assert all(row.sample_count == 15 and row.median_ns > 0 for row in result.candidates)
+    assert result.winner in (None, "tile-128x64")
+    assert (tmp_path / "search" / "round-04" / "tile-128x64" / "result.json").exists()

@@ -41,11 +41,22 @@ def main(argv: list[str] | None = None) -> int:
     render.add_argument("--physical", action="store_true")
     verify = commands.add_parser("verify-schedule", help="build, verify and hash the schedules")
     _add_shape(verify)
+    search = commands.add_parser("search-matmul", help="tile search: run every candidate of a contract in alternating rounds and pick a winner")
+    search.add_argument("contract", type=Path)
+    search.add_argument("output_dir", type=Path)
     estimate = commands.add_parser("estimate", help="cost model of the lowered plan")
     _add_shape(estimate)
     estimate.add_argument("--collective-strategy", choices=[s.value for s in cuda_lowering.MatmulCollectiveStrategy], default="p2p_fused_epilogue_bf16_transport")
     args = parser.parse_args(argv)
 
+    if args.command == "search-matmul":
+        from . import search as search_module
+
+        contract = search_module.MatmulSearchContract.from_json(args.contract.read_text())
+        result = search_module.run_matmul_search(args.output_dir, contract)
+        print(json.dumps({"search_id": result.search_id, "baseline": result.baseline, "winner": result.winner,
+                          "medians_ns": {row.name: row.median_ns for row in result.candidates}}))
+        return 0
     shape = dict(mesh_size=args.mesh_size, m=args.m, k=args.k, n=args.n, scatter_dimension=args.scatter_dimension)
     if args.command == "run-matmul":
         from . import runner
