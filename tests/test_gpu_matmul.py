@@ -258,3 +258,43 @@ def test_tile_search_through_the_runner(cuda_device, tmp_path):
     assert all(row.sample_count == 15 and row.median_ns > 0 for row in result.candidates)
     assert result.winner in (None, "tile-128x64")
     assert (tmp_path / "search" / "round-04" / "tile-128x64" / "result.json").exists()
+
+
+def test_receipt_is_written_validated_and_refuses_tampering(cuda_device, tmp_path):
+    """finalize-matmul-run on a fresh bundle, verify-matmul-bundle on the result, then three kinds of
+    tampering: an artifact byte, a roofline metric, a profile capture with the wrong kernels."""
+    import json
+
+    from tpu_cake_b200 import receipt, runner
+
+    out = tmp_path / "run"
+    runner.run_distributed_matmul(out, mesh_size=2, m=128, k=1024, n=1024, warmup_iterations=1, measured_iterations=3,
+                                  collective_strategy="p2p_fused_epilogue")
+    header = '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"\n'
+
+    def launch(index, kernel):
+        return f'"{index}","1","python","h","{kernel}","1","7","(192, 1, 1)","(148, 1, 1)","0","10.0","s","gpu__time_duration.sum","ns","9000"\n'
+
+    good = tmp_path / "good.csv"
+    good.write_text(header + launch(0, "void cake::cake_matmul_rs_sm100<256, 0>(...)") + launch(1, "void cake::cake_reduce_slots_sm100<float, float>(...)"))
+    wrong = tmp_path / "wrong.csv"
+    wrong.write_text(header + launch(0, "void cake::cake_matmul_rs_sm100<256, 0>(...)") + launch(1, "ncclDevKernel_ReduceScatter_Sum_f32_RING_LL(...)"))
+    with pytest.raises(ValueError, match="PROFILE_CAPTURE_REJECTED"):
+        receipt.finalize_matmul_run(out, profile_csv=wrong)
+    document = receipt.finalize_matmul_run(out, profile_csv=good)
+    assert document["profile"]["attached"] and document["metrics"]["measured_to_two_resource_floor"] > 1.0
+    assert receipt.validate_receipt(out)["receipt_id"] == document["receipt_id"]
+    metrics_path = out / "roofline" / "metrics.json"
+    original = metrics_path.read_text()
+    metrics = json.loads(original)
+    metrics["peak_efficiency"] *= 2
+    metrics_path.write_text(json.dumps(metrics, indent=2) + "\n")
+    with pytest.raises(ValueError, match="ARTIFACT_CHANGED path=roofline/metrics.json"):
+        receipt.validate_receipt(out)
+    metrics_path.write_text(original)
+    receipt.validate_receipt(out)
+    with open(out / "output.npy", "r+b") as handle:
+        handle.seek(200)
+        handle.write(b"\x01")
+    with pytest.raises(ValueError, match="ARTIFACT_CHANGED path=output.npy"):
+        receipt.validate_receipt(out)

@@ -44,11 +44,23 @@ def main(argv: list[str] | None = None) -> int:
     search = commands.add_parser("search-matmul", help="tile search: run every candidate of a contract in alternating rounds and pick a winner")
     search.add_argument("contract", type=Path)
     search.add_argument("output_dir", type=Path)
+    finalize = commands.add_parser("finalize-matmul-run", help="check a finished run bundle and write its receipt and roofline artifacts")
+    finalize.add_argument("root", type=Path)
+    finalize.add_argument("--profile", type=Path, help="ncu --csv launch list of the same run")
+    verify_bundle = commands.add_parser("verify-matmul-bundle", help="re-derive everything a bundle's receipt states")
+    verify_bundle.add_argument("root", type=Path)
     estimate = commands.add_parser("estimate", help="cost model of the lowered plan")
     _add_shape(estimate)
     estimate.add_argument("--collective-strategy", choices=[s.value for s in cuda_lowering.MatmulCollectiveStrategy], default="p2p_fused_epilogue_bf16_transport")
     args = parser.parse_args(argv)
 
+    if args.command in ("finalize-matmul-run", "verify-matmul-bundle"):
+        from . import receipt as receipt_module
+
+        document = (receipt_module.finalize_matmul_run(args.root, profile_csv=args.profile) if args.command == "finalize-matmul-run"
+                    else receipt_module.validate_receipt(args.root))
+        print(json.dumps({"receipt_id": document["receipt_id"], "run_id": document["run_id"], **document["metrics"]}))
+        return 0
     if args.command == "search-matmul":
         from . import search as search_module
 

@@ -595,31 +595,33 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         PF_ADD(4, lane == 0);
         return arrived;
       };
+      // S = Q K^T runs two steps ahead of O += P V: S(t+2) is issued as soon as the softmax warps
+      // have taken S(t+1) into registers, which is right after they finish step t, and before PV(t);
+      // the softmax never waits for a score tile, and PV(t) still finishes well inside step t+1.
+      auto next_scores = [&](uint32_t t_next, uint32_t t_consumed) -> bool {
+        where = 300;
+        if (!wait_tile(k_full, t_next)) return false;
+        where = 350;
+        {
+          PF_T0();
+          const bool taken = __all_sync(0xffffffffu, pf_wait(smem_u32(s_free), t_consumed & 1u, abort_flag));
+          PF_ADD(5, lane == 0);
+          if (!taken) return false;
+        }
+        tcgen05_fence_after();
+        if (lane == 0) issue_qk(t_next);
+        __syncwarp();
+        return true;
+      };
       bool ok = __all_sync(0xffffffffu, pf_wait(smem_u32(q_full), iter & 1u, abort_flag));
       if (ok) ok = wait_tile(k_full, step_total);
       if (ok) {
         tcgen05_fence_after();
         if (lane == 0) issue_qk(step_total);
         __syncwarp();
+        if (it.n_steps > 1) ok = next_scores(step_total + 1, step_total);
         for (int j = 0; j < it.n_steps && ok; ++j) {
           const uint32_t t = step_total;
-          // Next S first: it only needs the softmax warps to have taken the current S into
-          // registers, so Q K^T of step j+1 runs under the softmax of step j.
-          if (j + 1 < it.n_steps) {
-            where = 300;
-            ok = wait_tile(k_full, t + 1);
-            if (!ok) break;
-            where = 350;
-            {
-              PF_T0();
-              ok = __all_sync(0xffffffffu, pf_wait(smem_u32(s_free), t & 1u, abort_flag));
-              PF_ADD(5, lane == 0);
-            }
-            if (!ok) break;
-            tcgen05_fence_after();
-            if (lane == 0) issue_qk(t + 1);
-            __syncwarp();
-          }
           where = 380;
           ok = wait_tile(v_full, t);
           if (!ok) break;
@@ -644,6 +646,10 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             PF_ADD(6, lane == 0);
           }
           if (!ok) break;
+          if (j + 2 < it.n_steps) {
+            ok = next_scores(t + 2, t + 1);
+            if (!ok) break;
+          }
           tcgen05_fence_after();
           if (lane == 0) {
             const uint32_t a_base = desc_p_lo + (t & 1u) * (kPfPBytes >> 4);
