@@ -318,3 +318,18 @@ def test_sharded_decode_writes_every_ranks_gathered_buffer(cuda_device):
         np.testing.assert_array_equal(full, torch_to_bf16(gathered[0]).astype(np.float32))
     for flag in flags:
         assert flag.cpu().tolist()[:world] == [1] * world
+
+
+def test_chunk_search_on_the_decode_kernel(cuda_device, tmp_path):
+    """search-rpa with device timing on a shrunken pool of the 64-sequence configuration: all runs
+    agree with each other within the attention tolerance and the result carries per-candidate medians."""
+    from tpu_cake_b200 import rpa_search
+
+    contract = rpa_search.RpaSearchContract(
+        workload="rpa-decode-64seq", baseline="chunk-512", warmup_iterations=1, measured_iterations=3, rounds=5, bootstrap_samples=1000,
+        pool_pages=20480,
+        candidates=(rpa_search.RpaSearchCandidate("chunk-512", 512), rpa_search.RpaSearchCandidate("chunk-1024", 1024)),
+    )
+    result = rpa_search.run_rpa_search(tmp_path / "search", contract)
+    assert result.baseline == "chunk-512" and all(row.sample_count == 15 for row in result.candidates)
+    assert all(50_000 < row.median_ns < 5_000_000 for row in result.candidates)

@@ -114,3 +114,48 @@ def test_bootstrap_interval_is_seeded_and_brackets_the_median():
     first = search.improvement_interval(paired, samples=2000, seed=7)
     assert first == search.improvement_interval(paired, samples=2000, seed=7)
     assert 0.04 <= first[0] <= 0.052 <= first[1] <= 0.06
+
+
+# ------------------------------------------------------------------------------------ RPA chunk search
+
+
+def rpa_contract(**overrides):
+    from tpu_cake_b200 import rpa_search
+
+    fields = dict(workload="rpa-decode-64seq", baseline="chunk-512", bootstrap_samples=1000, measured_iterations=8,
+                  candidates=(rpa_search.RpaSearchCandidate("chunk-512", 512), rpa_search.RpaSearchCandidate("chunk-256", 256)))
+    fields.update(overrides)
+    return rpa_search.RpaSearchContract(**fields)
+
+
+def test_rpa_search_contract_rules_and_shipped_contract():
+    from tpu_cake_b200 import rpa_search
+
+    with pytest.raises(ValueError, match="multiple of the 32-token stage"):
+        rpa_search.RpaSearchCandidate("c", 48)
+    with pytest.raises(ValueError, match="baseline must be the first candidate"):
+        rpa_contract(baseline="chunk-256")
+    with pytest.raises(ValueError, match="at least 5 rounds"):
+        rpa_contract(rounds=3)
+    text = (ROOT / "tpu-cake_b200" / "contracts" / "rpa-chunk-search-b200.json").read_text()
+    parsed = rpa_search.RpaSearchContract.from_json(text)
+    assert parsed.baseline == "chunk-512" and [c.kv_chunk_tokens for c in parsed.candidates] == [512, 256, 1024]
+    assert rpa_search.RpaSearchContract.from_json(parsed.to_json()) == parsed
+
+
+def test_rpa_search_protocol_with_injected_runs(tmp_path):
+    from tpu_cake_b200 import rpa_search
+
+    generator = np.random.default_rng(1)
+    speed = {"chunk-512": 210_000, "chunk-256": 200_000}
+
+    def run(contract_, candidate):
+        samples = tuple(int(speed[candidate.name] * (1 + 0.003 * generator.standard_normal())) for _ in range(contract_.measured_iterations))
+        return rpa_search.RpaRunEvidence(candidate.name, True, samples, "a" * 64, "b" * 64, candidate.name.ljust(64, "0"), "d" * 64,
+                                         candidate.name.ljust(64, "e"))
+
+    result = rpa_search.run_rpa_search(tmp_path / "r", rpa_contract(), run=run)
+    assert result.baseline == "chunk-512" and result.winner == "chunk-256"
+    assert result.execution_orders[1] == ("chunk-256", "chunk-512")
+    rows = {row.name: row for row in result.candidates}
+    assert rows["chunk-256"].tile_n == 256 and 0.03 < rows["chunk-256"].improvement_over_baseline < 0.06

@@ -44,6 +44,9 @@ def main(argv: list[str] | None = None) -> int:
     search = commands.add_parser("search-matmul", help="tile search: run every candidate of a contract in alternating rounds and pick a winner")
     search.add_argument("contract", type=Path)
     search.add_argument("output_dir", type=Path)
+    rpa_search_cmd = commands.add_parser("search-rpa", help="search over the decode kernel's split-KV chunk size")
+    rpa_search_cmd.add_argument("contract", type=Path)
+    rpa_search_cmd.add_argument("output_dir", type=Path)
     finalize = commands.add_parser("finalize-matmul-run", help="check a finished run bundle and write its receipt and roofline artifacts")
     finalize.add_argument("root", type=Path)
     finalize.add_argument("--profile", type=Path, help="ncu --csv launch list of the same run")
@@ -60,6 +63,14 @@ def main(argv: list[str] | None = None) -> int:
         document = (receipt_module.finalize_matmul_run(args.root, profile_csv=args.profile) if args.command == "finalize-matmul-run"
                     else receipt_module.validate_receipt(args.root))
         print(json.dumps({"receipt_id": document["receipt_id"], "run_id": document["run_id"], **document["metrics"]}))
+        return 0
+    if args.command == "search-rpa":
+        from . import rpa_search
+
+        contract = rpa_search.RpaSearchContract.from_json(args.contract.read_text())
+        result = rpa_search.run_rpa_search(args.output_dir, contract)
+        print(json.dumps({"search_id": result.search_id, "baseline": result.baseline, "winner": result.winner,
+                          "medians_ns": {row.name: row.median_ns for row in result.candidates}}))
         return 0
     if args.command == "search-matmul":
         from . import search as search_module

@@ -30,7 +30,17 @@ constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 constexpr uint32_t kABytes = kTileM * kBlockK * 2;
-constexpr uint32_t kStagingBytesPerWarp = 2 * 32 * 128;  // two 32-row x 128-byte chunks per epilogue warp
+// Chunks (32 rows x 128 bytes) an epilogue warp can have staged for stores still reading shared
+// memory, and the depth of the 256-wide configuration's operand ring: the two compete for the
+// CTA's shared memory (4 stages + 2 chunks, or 3 stages + up to 6 chunks, fit).
+#ifndef CAKE_MM_STAGING_CHUNKS
+#define CAKE_MM_STAGING_CHUNKS 2
+#endif
+#ifndef CAKE_MM_STAGES_256
+#define CAKE_MM_STAGES_256 4
+#endif
+constexpr int kStagingChunks = CAKE_MM_STAGING_CHUNKS;
+constexpr uint32_t kStagingBytesPerWarp = kStagingChunks * 32 * 128;
 constexpr long long kBarrierBudgetCycles = 4000000000ll;  // about two seconds of SM clock
 constexpr unsigned long long kPeerBudgetNs = 20000000000ull;  // 20 s
 
@@ -38,7 +48,7 @@ template <int BN>
 struct GemmCfg {
   static constexpr uint32_t kBBytes = BN * kBlockK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStages = BN == 256 ? CAKE_MM_STAGES_256 : (BN == 128 ? 6 : 8);
   static constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
   static constexpr uint32_t kSmemBytes =
       kStages * kStageBytes + 4 * kStagingBytesPerWarp + 256 /*barriers*/ + 1024 /*alignment*/;
@@ -351,10 +361,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         // Transpose through swizzled smem (the layout of a 128-byte-swizzled TMA box) so that the
         // chunk leaves as 128-byte row segments.
-        uint8_t* my_stage = my_stage_base + (chunk_count & 1) * (32 * 128);
-        if (p.tma_store && chunk_count >= 2) {
-          // The staging half is reused every second chunk: its previous store must have read it.
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        uint8_t* my_stage = my_stage_base + (chunk_count % kStagingChunks) * (32 * 128);
+        if (p.tma_store && chunk_count >= kStagingChunks) {
+          // A staging slot is reused every kStagingChunks chunks: its previous store must have read it.
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStagingChunks - 1) : "memory");
           __syncwarp();
         }
         ++chunk_count;
