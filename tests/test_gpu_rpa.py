@@ -333,3 +333,39 @@ def test_chunk_search_on_the_decode_kernel(cuda_device, tmp_path):
     result = rpa_search.run_rpa_search(tmp_path / "search", contract)
     assert result.baseline == "chunk-512" and all(row.sample_count == 15 for row in result.candidates)
     assert all(50_000 < row.median_ns < 5_000_000 for row in result.candidates)
+
+
+def test_data_tensor_sharded_surface_on_one_gpu(cuda_device):
+    """All eight positions of the 2 x 4 surface run one after the other on one GPU (they exchange
+    nothing): every shard's output and updated cache equal the oracle's for that data block,
+    restricted to the shard's heads."""
+    from tests.sharded_cases import build_sharded_surface
+
+    global_inputs, block_inputs = build_sharded_surface(11)
+    shapes = [tuple(np.asarray(v).shape) for v in global_inputs]
+    local = rpa_cuda_lowering.CudaFusedRpaPlan(
+        name="surface", schedule_sha256="0" * 64, query_shape=(4, 8, 128), key_shape=(4, 4, 128), value_shape=(4, 4, 128),
+        fused_cache_shape=(shapes[3][0] // 2, 1, 4, 2, 128), kv_lengths_shape=(4,), page_indices_shape=(shapes[5][0] // 2,),
+        cumulative_query_lengths_shape=(5,), cumulative_kv_lengths_shape=(5,), distribution_shape=(3,),
+        relative_states_shape=(4, 8, 16), relative_projection_shape=(16, 512), output_shape=(4, 8, 128), softmax_scale=1.0 / 128,
+    )
+    surface = rpa_cuda_lowering.ShardedCudaFusedRpaPlan(local)
+    expected = [oracle.rpa_fused(block) for block in block_inputs]  # per data block, all heads
+    executable = surface.build(cuda_device)
+    try:
+        outputs, caches = {}, {}
+        for rank in range(8):
+            position = surface.mesh_position(rank)
+            shard = surface.shard_inputs(global_inputs, position)
+            device_inputs = tuple(to_device(np.ascontiguousarray(value), cuda_device) for value in shard)
+            output, cache = surface.run_local(executable, *device_inputs)
+            assert executable.status() == (0, 0, 0, 0)
+            outputs[position], caches[position] = torch_to_bf16(output), torch_to_bf16(cache)
+            d, t = position
+            assert_close(outputs[position].astype(np.float32), expected[d][0][:, 8 * t : 8 * t + 8].astype(np.float32))
+        global_cache = surface.assemble(caches, 1)
+        want_cache = np.concatenate([cache for _, cache in expected], axis=0)
+        np.testing.assert_array_equal(global_cache.view(np.uint16), want_cache.view(np.uint16))
+        assert surface.assemble(outputs, 0).shape == (8, 32, 128)
+    finally:
+        executable.close()

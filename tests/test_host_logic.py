@@ -137,3 +137,36 @@ def test_shard_matmul_inputs_partition_k():
     assert pieces[0][0].shape == (16, 8) and pieces[0][1].shape == (8, 16)
     np.testing.assert_array_equal(np.concatenate([p[0] for p in pieces], axis=1), lhs)
     np.testing.assert_array_equal(np.concatenate([p[1] for p in pieces], axis=0), rhs)
+
+
+def test_sharded_surface_partitioning_round_trips():
+    """The 2 x 4 data x tensor surface: global shapes follow the partition specs, every position's
+    shard has the local plan's shapes, and assembling the shards restores the global arrays."""
+    from tests.sharded_cases import build_sharded_surface
+    from tpu_cake_b200 import rpa_cuda_lowering
+
+    global_inputs, _ = build_sharded_surface(3)
+    shapes = [tuple(np.asarray(v).shape) for v in global_inputs]
+    local = rpa_cuda_lowering.CudaFusedRpaPlan(
+        name="surface", schedule_sha256="0" * 64, query_shape=(4, 8, 128), key_shape=(4, 4, 128), value_shape=(4, 4, 128),
+        fused_cache_shape=(shapes[3][0] // 2, 1, 4, 2, 128), kv_lengths_shape=(4,), page_indices_shape=(shapes[5][0] // 2,),
+        cumulative_query_lengths_shape=(5,), cumulative_kv_lengths_shape=(5,), distribution_shape=(3,),
+        relative_states_shape=(4, 8, 16), relative_projection_shape=(16, 512), output_shape=(4, 8, 128), softmax_scale=1.0 / 128,
+    )
+    surface = rpa_cuda_lowering.ShardedCudaFusedRpaPlan(local)
+    assert surface.global_input_shapes[0] == (8, 32, 128) and surface.global_input_shapes[3][2] == 16
+    assert [tuple(s) for s in surface.global_input_shapes] == shapes
+    assert surface.mesh_position(5) == (1, 1) and surface.output_partition_specs == (("data", "tensor", ""), ("data", "", "tensor", "", ""))
+    pieces_q, pieces_cache = {}, {}
+    for rank in range(8):
+        position = surface.mesh_position(rank)
+        shard = surface.shard_inputs(global_inputs, position)
+        for value, shape in zip(shard, local.input_shapes, strict=True):
+            assert tuple(value.shape) == tuple(shape)
+        pieces_q[position], pieces_cache[position] = np.asarray(shard[0]), np.asarray(shard[3])
+    np.testing.assert_array_equal(surface.assemble(pieces_q, 0).view(np.uint16), np.asarray(global_inputs[0]).view(np.uint16))
+    np.testing.assert_array_equal(surface.assemble(pieces_cache, 1).view(np.uint16), np.asarray(global_inputs[3]).view(np.uint16))
+    with pytest.raises(ValueError, match="outside the 2x4 mesh"):
+        surface.mesh_position(8)
+    with pytest.raises(ValueError, match="the surface expects"):
+        surface.shard_inputs((global_inputs[0][:4],) + global_inputs[1:], (0, 0))

@@ -505,6 +505,107 @@ class CudaMixedRpaPlan:
                                  lens, pages, cu_kv, cu_q, decode_end, out)
         return out, cache
 
+SHARDED_INPUT_PARTITION_SPECS = (
+    ("data", "tensor", ""),          # queries  [tokens, q_heads, dim]
+    ("data", "tensor", ""),          # keys     [tokens, kv_heads, dim]
+    ("data", "tensor", ""),          # values
+    ("data", "", "tensor", "", ""),  # fused cache [pages, page, packed heads, 2, dim_padded]
+    ("data",),                       # kv_lengths
+    ("data",),                       # page_indices
+    ("data",),                       # cumulative_query_lengths
+    ("data",),                       # cumulative_kv_lengths
+    ("data",),                       # distribution
+    ("data", "tensor", ""),          # relative_states
+    ("", ""),                        # relative_projection (replicated)
+)
+
+
+@dataclass(frozen=True)
+class ShardedCudaFusedRpaPlan:
+    """The data x tensor surface of the fused decode: the ``data`` axis splits the batch (sequences,
+    their pages, their metadata), the ``tensor`` axis splits heads; every mesh position runs the
+    same local plan on its shard and the outputs keep the query and cache sharding. Mirrors
+    ``ShardedFusedRpaPlan`` (src/tpu_cake/rpa_lowering.py:395-571; partition specs :1124-1136).
+    One process per GPU: rank r sits at (r // tensor, r % tensor). No data-path collective."""
+
+    local_plan: "CudaFusedRpaPlan"
+    mesh_axes: tuple[str, str] = ("data", "tensor")
+    mesh_shape: tuple[int, int] = (2, 4)
+    input_partition_specs: tuple[tuple[str, ...], ...] = SHARDED_INPUT_PARTITION_SPECS
+    execution_scope: str = "one-process-per-gpu-data-tensor-shards"
+
+    def __post_init__(self) -> None:
+        if self.mesh_axes != ("data", "tensor") or min(self.mesh_shape) < 1:
+            raise ValueError("sharded RPA runs on a data x tensor mesh")
+        shapes = self.local_plan.input_shapes
+        if len(self.input_partition_specs) != len(shapes):
+            raise ValueError("sharded RPA needs one partition spec per input")
+        for shape, spec in zip(shapes, self.input_partition_specs, strict=True):
+            if shape is not None and len(shape) != len(spec):
+                raise ValueError("sharded RPA partition specs must match input ranks")
+            if any(axis and axis not in self.mesh_axes for axis in spec):
+                raise ValueError("sharded RPA partition specs use an unknown mesh axis")
+
+    @property
+    def output_partition_specs(self) -> tuple[tuple[str, ...], tuple[str, ...]]:
+        return (self.input_partition_specs[0], self.input_partition_specs[3])
+
+    @property
+    def schedule_sha256(self) -> str:
+        return self.local_plan.schedule_sha256
+
+    @property
+    def global_input_shapes(self) -> tuple[tuple[int, ...] | None, ...]:
+        sizes = dict(zip(self.mesh_axes, self.mesh_shape, strict=True))
+        return tuple(
+            None if shape is None else tuple(extent * sizes.get(axis, 1) for extent, axis in zip(shape, spec, strict=True))
+            for shape, spec in zip(self.local_plan.input_shapes, self.input_partition_specs, strict=True)
+        )
+
+    def mesh_position(self, rank: int) -> tuple[int, int]:
+        data, tensor = self.mesh_shape
+        if not 0 <= rank < data * tensor:
+            raise ValueError(f"rank {rank} outside the {data}x{tensor} mesh")
+        return rank // tensor, rank % tensor
+
+    def shard_inputs(self, global_inputs: tuple, position: tuple[int, int]) -> tuple:
+        """This mesh position's block of every global input (numpy arrays or torch tensors): along
+        each partitioned dimension, the block at the position's index on that axis."""
+        index = dict(zip(self.mesh_axes, position, strict=True))
+        sizes = dict(zip(self.mesh_axes, self.mesh_shape, strict=True))
+        shards = []
+        for value, spec, global_shape in zip(global_inputs, self.input_partition_specs, self.global_input_shapes, strict=True):
+            if value is None:
+                shards.append(None)
+                continue
+            if tuple(value.shape) != tuple(global_shape):
+                raise ValueError(f"global input has shape {tuple(value.shape)}, the surface expects {tuple(global_shape)}")
+            selection = []
+            for extent, axis in zip(value.shape, spec, strict=True):
+                if axis:
+                    step = extent // sizes[axis]
+                    selection.append(slice(index[axis] * step, (index[axis] + 1) * step))
+                else:
+                    selection.append(slice(None))
+            shards.append(value[tuple(selection)])
+        return tuple(shards)
+
+    def assemble(self, per_position: dict[tuple[int, int], object], which: int):
+        """Global output (which = 0) or global cache (which = 1) from the per-position numpy results."""
+        spec = self.output_partition_specs[which]
+        data, tensor = self.mesh_shape
+        tensor_dim = spec.index("tensor")
+        rows = [np.concatenate([per_position[(d, t)] for t in range(tensor)], axis=tensor_dim) for d in range(data)]
+        return np.concatenate(rows, axis=spec.index("data"))
+
+    def build(self, device: torch.device | None = None) -> "RpaDecodeExecutable":
+        return self.local_plan.build(device)
+
+    def run_local(self, executable: "RpaDecodeExecutable", *local_inputs):
+        """Preflight (host integers) and decode of one mesh position's shard."""
+        return self.local_plan.run_preflighted(executable, *local_inputs)
+
+
 
 class UnsupportedRaggedBatch(ValueError):
     """A ragged batch the CUDA backend does not lower."""
