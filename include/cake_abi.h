@@ -48,7 +48,8 @@ const char* cake_last_error(void);
 
 /* Device-written status word of the most recent kernels of a handle family.
  * code: 0 = ok, 1 = bounded wait on a shared-memory barrier ran out, 2 = bounded wait on a
- * peer arrival counter ran out, 3 = page index out of range, 4 = sequence metadata out of range.
+ * peer arrival counter ran out, 3 = page index out of range, 4 = sequence metadata out of range,
+ * 5 = a kernel found its shared memory misaligned and did nothing.
  * detail0..2 carry coordinates (block, tile / sequence, stage / page slot). */
 typedef struct cake_status {
   int32_t code;

@@ -1226,6 +1226,7 @@ int32_t cake_rpa_status(cake_rpa* plan, void* stream_v, cake_status* out) {
   if (out->code == 1) return fail(CAKE_ERR_TIMEOUT, "rpa: bounded barrier wait ran out (block %d item %d stage %d)", out->detail0, out->detail1, out->detail2);
   if (out->code == 3) return fail(CAKE_ERR_DEVICE_CHECK, "rpa: page index out of range (sequence %d page slot %d value %d)", out->detail0, out->detail1, out->detail2);
   if (out->code == 4) return fail(CAKE_ERR_DEVICE_CHECK, "rpa: sequence metadata out of range (%d, %d, %d)", out->detail0, out->detail1, out->detail2);
+  if (out->code == 5) return fail(CAKE_ERR_DEVICE_CHECK, "rpa: dynamic shared memory of block %d is not 1 KiB aligned (offset %d)", out->detail0, out->detail1);
   return CAKE_OK;
 }
 

@@ -15,17 +15,18 @@
 //                                  tiles, later tiles (more visible KV) first
 //   cake_rpa_prefill_sm100         persistent, one CTA per SM; a work item is 128 query tokens of one
 //                                  query head, walked over the KV range in steps of 128 tokens.
-//       warps 0-3   softmax: one thread per query row (TMEM lane), so the row maximum and sum need
-//                   no shuffles. S comes out of TMEM with tcgen05.ld, P = exp2(S - max) goes back
+//       warps 0-7   softmax: two threads per query row (TMEM lane), one per 64-column half of a step,
+//                   so the row maximum needs one exchange through shared memory and no shuffles.
+//                   S comes out of TMEM with tcgen05.ld, P = exp2(S - max) goes back
 //                   through shared memory (bf16, 128-byte-swizzled K-major, double-buffered), and the
 //                   output row accumulates in TMEM over all steps; it is read, rescaled and written
 //                   back (tcgen05.ld / tcgen05.st) only when its maximum has moved by more than 2^8.
-//       warp 4      TMA producer of the query tile and of the K ring (2 slots)
-//       warp 6      TMA producer of the V ring (2 slots). Tiles are gathered page by page in boxes of
+//       warp 8      TMA producer of the query tile and of the K ring (2 slots)
+//       warp 10     TMA producer of the V ring (2 slots). Tiles are gathered page by page in boxes of
 //                   one 8-token group (both 64-element halves of the row: 2 KiB), laid out
 //                   [group][lo | hi][8 rows][128 B]: groups a uniform 2 KiB apart, which is what the
 //                   tcgen05 shared-memory descriptors need. Never multicast.
-//       warp 5      tcgen05.mma issuer: S = Q K^T (128x128x128, K-major operands) as soon as the
+//       warp 9      tcgen05.mma issuer: S = Q K^T (128x128x128, K-major operands) as soon as the
 //                   softmax warps have taken the previous S into registers, and O += P V (128x128x128,
 //                   V consumed in place as an MN-major operand) when P is written.
 //     A 128-wide MMA keeps the tensor pipe busy for 64 cycles, about what the issuing thread needs
@@ -35,7 +36,7 @@
 
 namespace cake {
 
-constexpr int kPfThreads = 256;
+constexpr int kPfThreads = 384;
 constexpr int kPfTileQ = 128;                    // query rows per work item (one query head)
 constexpr int kPfTileKv = 128;                   // KV tokens per step
 constexpr int kPfRing = 2;                       // slots of the K ring and of the V ring
@@ -43,7 +44,8 @@ constexpr int kPfQBytes = kPfTileQ * 256;        // queries: [2 halves][128 rows
 constexpr int kPfTileBytes = kPfTileKv * 256;    // a K or V tile: [16 groups][lo | hi][8 rows][128 B]
 constexpr int kPfGroupBytes = 2048;              // one 8-token group of a K or V tile
 constexpr int kPfPBytes = kPfTileQ * 256;        // P: [2 halves of the 128 tokens][128 rows][128 B]
-constexpr int kPfSmemBytes = kPfQBytes + 2 * kPfRing * kPfTileBytes + 2 * kPfPBytes + 1024 + 1024;
+constexpr int kPfTailBytes = 3072;               // barriers, TMEM slot, item slots, 2 KiB row-maximum exchange
+constexpr int kPfSmemBytes = kPfQBytes + 2 * kPfRing * kPfTileBytes + 2 * kPfPBytes + kPfTailBytes;  // all a CTA may own
 constexpr uint32_t kPfTmemCols = 256;            // S @0 (128 columns), O @128 (128 columns)
 constexpr long long kPfBarrierBudget = 2000000000ll;
 constexpr float kPfRescale = 8.f;                // log2 units the row maximum may lag before O is rescaled
@@ -200,9 +202,14 @@ __global__ void __launch_bounds__(kPfThreads, 1)
                            const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v, const PrefillParams pp) {
   const RpaParams& p = pp.r;
-  extern __shared__ uint8_t pf_smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  // The tiles need 1 KiB alignment (128-byte swizzle atoms) and the CTA uses every byte it may own,
+  // so there is no slack to round the base up: the alignment is requested and checked.
+  extern __shared__ __align__(1024) uint8_t pf_smem_raw[];
+  uint8_t* smem = pf_smem_raw;
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) rpa_record(p.status, 5, blockIdx.x, static_cast<int>(smem_u32(smem) & 1023u), 0);
+    return;
+  }
   uint8_t* q_smem = smem;                                  // [2 halves][128 rows][128 B]
   uint8_t* k_smem = q_smem + kPfQBytes;                    // [ring][16 groups][lo | hi][8 rows][128 B]
   uint8_t* v_smem = k_smem + kPfRing * kPfTileBytes;       // same
@@ -221,6 +228,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   volatile int32_t* item_slot = reinterpret_cast<volatile int32_t*>(tmem_base_slot + 2);  // [2]
+  float* xchg = reinterpret_cast<float*>(tmem_base_slot + 4);  // [2 parities][2 column halves][128 rows]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -234,9 +242,9 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       mbar_init(smem_u32(&v_empty[s]), 1);
     }
     mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(s_free), 128);
+    mbar_init(smem_u32(s_free), 256);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&p_full[b]), 128);
+      mbar_init(smem_u32(&p_full[b]), 256);
       mbar_init(smem_u32(&pv_full[b]), 1);
     }
     mbar_init(smem_u32(drain_bar), 1);
@@ -246,7 +254,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     prefetch_tensormap(&tmap_k);
     prefetch_tensormap(&tmap_v);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(smem_u32(tmem_base_slot), kPfTmemCols);
     tmem_relinquish();
   }
@@ -289,19 +297,26 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   };
   Item it;
 
-  if (warp < 4) {
+  if (warp < 8) {
     // ---------------------------------------------------------------- softmax warps
-    const int row = warp * 32 + lane;  // warp w reads TMEM lanes 32w .. 32w+31
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    const uint32_t t_s = t_lane;
-    const uint32_t t_o = t_lane + 128;
-    uint8_t* p_rows = p_smem + row * 128;  // this thread's row in P buffer 0, first half
-    const float scale = p.scale_log2;      // positive: checked on the host
+    // Two threads per query row: warp w and warp w + 4 read the same TMEM lanes (32 (w & 3) ...) and
+    // take the lower and upper 64 columns of S, P and O. The row maximum is combined through shared
+    // memory once per step (a 64-thread named barrier per warp pair), so both threads derive the
+    // same running maximum and the same rescale decisions; the row sums are combined at the end.
+    const int quarter = warp & 3;
+    const int half = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t t_s = t_lane + half * 64;
+    const uint32_t t_o = t_lane + 128 + half * 64;
+    uint8_t* p_rows = p_smem + half * (kPfPBytes / 2) + row * 128;  // this thread's 128-byte row segment, buffer 0
+    const uint32_t pair_barrier = 2 + quarter;
+    const float scale = p.scale_log2;  // positive: checked on the host
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
       PF_T0();
       const int limit = min(it.prior + it.q0 + row, it.kv_len - 1);  // last position this row sees
-      // Running maximum (log2 domain, scaled) and sum of this thread's row. The maximum is allowed
-      // to lag by kPfRescale, so the exponentials below are bounded by 2^kPfRescale instead of 1.
+      // Running maximum (log2 domain, scaled) of the row and sum of this thread's columns. The
+      // maximum is allowed to lag by kPfRescale, so the exponentials are bounded by 2^kPfRescale.
       float m_run = kNegBig, l_run = 0.f;
       bool ok = true;
       for (int j = 0; j < it.n_steps; ++j) {
@@ -318,24 +333,39 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           break;
         }
         tcgen05_fence_after();
-        uint32_t v[128];
+        uint32_t v[64];
         {
-          uint32_t c0[32], c1[32], c2[32], c3[32];
+          uint32_t c0[32], c1[32];
           tmem_ld_32x32b_x32(t_s, c0);
           tmem_ld_32x32b_x32(t_s + 32, c1);
-          tmem_ld_32x32b_x32(t_s + 64, c2);
-          tmem_ld_32x32b_x32(t_s + 96, c3);
           tmem_ld_wait();
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             v[c] = c0[c];
             v[32 + c] = c1[c];
-            v[64 + c] = c2[c];
-            v[96 + c] = c3[c];
           }
         }
         tcgen05_fence_before();
         mbar_arrive(smem_u32(s_free));  // S is in registers: the next S = Q K^T may overwrite it
+        const int pos0 = j * kPfTileKv + half * 64;
+        // Only the steps that cross the row's causal limit (or the end of the sequence) mask.
+        if (__any_sync(0xffffffffu, pos0 + 63 > limit)) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (pos0 + c > limit) v[c] = 0xff800000u;  // -inf
+        }
+        float mr0 = __uint_as_float(v[0]), mr1 = __uint_as_float(v[1]);
+#pragma unroll
+        for (int c = 2; c + 3 < 64; c += 4) {
+          mr0 = pf_max3(mr0, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+          mr1 = pf_max3(mr1, __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+        }
+        const float mine = pf_max3(mr0, mr1, fmaxf(__uint_as_float(v[62]), __uint_as_float(v[63])));
+        // Combine with the thread that holds the other 64 columns of this row.
+        float* slot = xchg + (t & 1u) * 256;
+        slot[half * 128 + row] = mine;
+        named_bar_sync(pair_barrier, 64);
+        const float mx = fmaxf(mine, slot[(half ^ 1) * 128 + row]) * scale;
         // P is double-buffered: this step writes buffer t & 1, which PV(t-2) read. Each buffer has
         // its own barriers, completing every other step, so a wait names exactly one completion
         // even though this role may run up to two steps ahead of the issuer.
@@ -350,27 +380,13 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             break;
           }
         }
-        const int pos0 = j * kPfTileKv;
-        // Only the steps that cross the row's causal limit (or the end of the sequence) mask.
-        if (__any_sync(0xffffffffu, pos0 + kPfTileKv - 1 > limit)) {
-#pragma unroll
-          for (int c = 0; c < 128; ++c)
-            if (pos0 + c > limit) v[c] = 0xff800000u;  // -inf
-        }
-        float mr0 = __uint_as_float(v[0]), mr1 = __uint_as_float(v[1]);
-#pragma unroll
-        for (int c = 2; c + 3 < 128; c += 4) {
-          mr0 = pf_max3(mr0, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
-          mr1 = pf_max3(mr1, __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
-        }
-        const float mx = pf_max3(mr0, mr1, fmaxf(__uint_as_float(v[126]), __uint_as_float(v[127]))) * scale;
         float alpha = 1.f;
         if (mx > m_run + kPfRescale) {
           alpha = pf_exp2(m_run - mx);
           m_run = mx;
         }
         // Rare: the accumulator is read and rewritten once PV(t-1) is complete; PV(t) is issued
-        // only after p_full below.
+        // only after p_full below. Both threads of a row take the same decision.
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
           ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[(t - 1u) & 1u]), ((t - 1u) >> 1) & 1u, abort_flag));
           if (!ok) {
@@ -380,7 +396,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           }
           tcgen05_fence_after();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t acc[32];
             tmem_ld_32x32b_x32(t_o + c * 32, acc);
             tmem_ld_wait();
@@ -394,7 +410,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         const float neg_m = -m_run;
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-        for (int chunk = 0; chunk < 16; ++chunk) {
+        for (int chunk = 0; chunk < 8; ++chunk) {
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -405,8 +421,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             sum1 += b;
             w[e] = pack_bf16(a, b);
           }
-          *reinterpret_cast<uint4*>(p_row + (chunk >> 3) * (kPfPBytes / 2) + (((chunk & 7) ^ (row & 7)) << 4)) =
-              make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
         l_run = l_run * alpha + (sum0 + sum1);
         fence_proxy_async_smem();   // P written through the generic proxy, read by the tensor core
@@ -423,12 +438,17 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           *abort_flag = 1;
         }
       }
+      // Row sum = the two threads' partial sums, added in a fixed order. The barrier is taken on
+      // every path so that a pair never splits.
+      float* slot = xchg + (step_total & 1u) * 256;
+      slot[half * 128 + row] = l_run;
+      named_bar_sync(pair_barrier, 64);
       if (ok) {
         tcgen05_fence_after();
-        const float inv = 1.f / l_run;
-        __nv_bfloat16* dst = pp.out + (static_cast<size_t>(it.q_tok0 + row) * p.q_heads + it.head) * 128;
+        const float inv = 1.f / (slot[row] + slot[128 + row]);
+        __nv_bfloat16* dst = pp.out + (static_cast<size_t>(it.q_tok0 + row) * p.q_heads + it.head) * 128 + half * 64;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t acc[32];
           tmem_ld_32x32b_x32(t_o + c * 32, acc);
           tmem_ld_wait();
@@ -448,11 +468,11 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       }
       PF_ADD(2, threadIdx.x == 0);
     }
-  } else if (warp == 4 || warp == 6) {
+  } else if (warp == 8 || warp == 10) {
     // ---------------------------------------------------------------- TMA producers (K ring, V ring)
     // Boxes: with pages of 8 tokens or more, one box is an 8-token group with both halves of the
     // row (2 KiB); smaller pages fill the two atoms of a group row by row, one box per page and atom.
-    const bool is_v = warp == 6;
+    const bool is_v = warp == 10;
     const CUtensorMap* tmap = is_v ? &tmap_v : &tmap_k;
     uint8_t* ring = is_v ? v_smem : k_smem;
     uint64_t* full = is_v ? v_full : k_full;
@@ -559,7 +579,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       }
       PF_ADD(is_v ? 11 : 9, lane == 0);
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
     constexpr uint32_t idesc = umma_idesc_bf16_f32(kPfTileQ, 128, 0, 0);     // S = Q K^T, both K-major
     constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kPfTileQ, 128, 0, 1);  // O += P V, V MN-major
@@ -674,7 +694,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       PF_ADD(7, lane == 0);
     }
   } else {
-    // warp 7 has no role: it only takes part in the item barrier
+    // warp 11 has no role: it only takes part in the item barrier
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
     }
   }
@@ -682,16 +702,16 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   // ---- orderly exit
   __syncthreads();
   if (*abort_flag) {
-    if ((warp == 4 || warp == 6) && lane == 0) {
+    if ((warp == 8 || warp == 10) && lane == 0) {
       // loads already issued must land before shared memory is released
-      uint64_t* full = warp == 6 ? v_full : k_full;
+      uint64_t* full = warp == 10 ? v_full : k_full;
       for (uint32_t back = 0; back < kPfRing && back < loads_issued; ++back) {
         const uint32_t t = step_total - 1 - back;
         mbar_wait_bounded(smem_u32(&full[t % kPfRing]), (t / kPfRing) & 1u, 200000000ll);
       }
-      if (warp == 4) mbar_wait_bounded(smem_u32(q_full), 0, 1000000ll);
+      if (warp == 8) mbar_wait_bounded(smem_u32(q_full), 0, 1000000ll);
     }
-    if (warp == 5 && lane == 0) {
+    if (warp == 9 && lane == 0) {
       tcgen05_commit(smem_u32(drain_bar));
       mbar_wait_bounded(smem_u32(drain_bar), 0, 200000000ll);
     }
@@ -699,7 +719,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, kPfTmemCols);
   }
