@@ -17,12 +17,13 @@
 //                                  query head, walked over the KV range in steps of 128 tokens.
 //       warps 0-7   softmax: two threads per query row (TMEM lane), one per 64-column half of a step,
 //                   so the row maximum needs one exchange through shared memory and no shuffles.
-//                   S comes out of TMEM with tcgen05.ld, P = exp2(S - max) goes back
-//                   through shared memory (bf16, 128-byte-swizzled K-major, double-buffered), and the
-//                   output row accumulates in TMEM over all steps; it is read, rescaled and written
-//                   back (tcgen05.ld / tcgen05.st) only when its maximum has moved by more than 2^8.
-//       warp 8      TMA producer of the query tile and of the K ring (2 slots)
-//       warp 10     TMA producer of the V ring (2 slots). Tiles are gathered page by page in boxes of
+//                   S comes out of TMEM with tcgen05.ld, P = exp2(S - max) goes back into TMEM
+//                   (tcgen05.st, bf16 pairs, double-buffered) where the tensor core reads it as the
+//                   A operand, so P never touches shared memory; the output row accumulates in TMEM
+//                   over all steps and is read, rescaled and written back only when its maximum has
+//                   moved by more than 2^8.
+//       warp 8      TMA producer of the query tile and of the K ring (3 slots)
+//       warp 10     TMA producer of the V ring (3 slots). Tiles are gathered page by page in boxes of
 //                   one 8-token group (both 64-element halves of the row: 2 KiB), laid out
 //                   [group][lo | hi][8 rows][128 B]: groups a uniform 2 KiB apart, which is what the
 //                   tcgen05 shared-memory descriptors need. Never multicast.
@@ -39,14 +40,14 @@ namespace cake {
 constexpr int kPfThreads = 384;
 constexpr int kPfTileQ = 128;                    // query rows per work item (one query head)
 constexpr int kPfTileKv = 128;                   // KV tokens per step
-constexpr int kPfRing = 2;                       // slots of the K ring and of the V ring
+constexpr int kPfRing = 3;                       // slots of the K ring and of the V ring
 constexpr int kPfQBytes = kPfTileQ * 256;        // queries: [2 halves][128 rows][128 B]
 constexpr int kPfTileBytes = kPfTileKv * 256;    // a K or V tile: [16 groups][lo | hi][8 rows][128 B]
 constexpr int kPfGroupBytes = 2048;              // one 8-token group of a K or V tile
-constexpr int kPfPBytes = kPfTileQ * 256;        // P: [2 halves of the 128 tokens][128 rows][128 B]
 constexpr int kPfTailBytes = 3072;               // barriers, TMEM slot, item slots, 2 KiB row-maximum exchange
-constexpr int kPfSmemBytes = kPfQBytes + 2 * kPfRing * kPfTileBytes + 2 * kPfPBytes + kPfTailBytes;  // all a CTA may own
-constexpr uint32_t kPfTmemCols = 256;            // S @0 (128 columns), O @128 (128 columns)
+constexpr int kPfSmemBytes = kPfQBytes + 2 * kPfRing * kPfTileBytes + kPfTailBytes;  // all a CTA may own
+constexpr uint32_t kPfTmemCols = 512;            // S @0 (128 columns), O @128 (128), P buffers @256 and @320 (64 each)
+constexpr uint32_t kPfTmemP = 256;
 constexpr long long kPfBarrierBudget = 2000000000ll;
 constexpr float kPfRescale = 8.f;                // log2 units the row maximum may lag before O is rescaled
 
@@ -213,8 +214,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   uint8_t* q_smem = smem;                                  // [2 halves][128 rows][128 B]
   uint8_t* k_smem = q_smem + kPfQBytes;                    // [ring][16 groups][lo | hi][8 rows][128 B]
   uint8_t* v_smem = k_smem + kPfRing * kPfTileBytes;       // same
-  uint8_t* p_smem = v_smem + kPfRing * kPfTileBytes;       // [2 buffers][2 halves][128 rows][128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * kPfPBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + kPfRing * kPfTileBytes);
   uint64_t* q_full = bars;                 // [1]
   uint64_t* k_full = bars + 1;             // [ring]
   uint64_t* k_empty = k_full + kPfRing;    // [ring]
@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t t_s = t_lane + half * 64;
     const uint32_t t_o = t_lane + 128 + half * 64;
-    uint8_t* p_rows = p_smem + half * (kPfPBytes / 2) + row * 128;  // this thread's 128-byte row segment, buffer 0
+    const uint32_t t_p = t_lane + kPfTmemP + half * 32;  // this thread's 32 packed columns of P buffer 0
     const uint32_t pair_barrier = 2 + quarter;
     const float scale = p.scale_log2;  // positive: checked on the host
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
@@ -369,7 +369,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         // P is double-buffered: this step writes buffer t & 1, which PV(t-2) read. Each buffer has
         // its own barriers, completing every other step, so a wait names exactly one completion
         // even though this role may run up to two steps ahead of the issuer.
-        uint8_t* p_row = p_rows + (t & 1u) * kPfPBytes;
         if (j >= 2) {
           PF_T0();
           ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[t & 1u]), ((t >> 1) & 1u) ^ 1u, abort_flag));
@@ -406,25 +405,22 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           }
           tmem_st_wait();
         }
-        // ---- P = exp2(S * scale - max) as bf16 into shared memory (K-major, 128-byte swizzle)
+        // ---- P = exp2(S * scale - max) as bf16 into tensor memory: row = lane, two values per
+        //      32-bit column, which is the form tcgen05.mma reads an A operand from TMEM in
         const float neg_m = -m_run;
         float sum0 = 0.f, sum1 = 0.f;
+        uint32_t w[32];
 #pragma unroll
-        for (int chunk = 0; chunk < 8; ++chunk) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = chunk * 8 + e * 2;
-            const float a = pf_exp2(fmaf(__uint_as_float(v[c]), scale, neg_m));
-            const float b = pf_exp2(fmaf(__uint_as_float(v[c + 1]), scale, neg_m));
-            sum0 += a;
-            sum1 += b;
-            w[e] = pack_bf16(a, b);
-          }
-          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int c = 0; c < 32; ++c) {
+          const float a = pf_exp2(fmaf(__uint_as_float(v[2 * c]), scale, neg_m));
+          const float b = pf_exp2(fmaf(__uint_as_float(v[2 * c + 1]), scale, neg_m));
+          sum0 += a;
+          sum1 += b;
+          w[c] = pack_bf16(a, b);
         }
+        tmem_st_32x32b_x32(t_p + (t & 1u) * 64, w);
         l_run = l_run * alpha + (sum0 + sum1);
-        fence_proxy_async_smem();   // P written through the generic proxy, read by the tensor core
+        tmem_st_wait();
         tcgen05_fence_before();     // TMEM reads and writes above are ordered before the next MMAs
         mbar_arrive(smem_u32(&p_full[t & 1u]));
         ++step_total;
@@ -585,14 +581,13 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kPfTileQ, 128, 0, 1);  // O += P V, V MN-major
     // Shared-memory descriptors, split into the low word (address field, which changes per MMA, and
     // the leading offset) and the high word (stride offset, version, swizzle mode).
-    //   Q and P: K-major, 8-row groups 1 KiB apart; the second 64 elements of a row 16 KiB further.
+    //   Q:       K-major, 8-row groups 1 KiB apart; the second 64 elements of a row 16 KiB further.
     //   K tile:  K-major, 8-token groups 2 KiB apart; the second 64 elements of a row are the next atom.
     //   V tile:  [token][d] MN-major: the two 64-wide halves 1 KiB apart (leading offset), 8-token
     //            groups 2 KiB apart (stride offset); a K step of 16 tokens is two groups.
     const uint32_t desc_hi_1024 = static_cast<uint32_t>(umma_desc_sw128(0, 16, 1024) >> 32);
     const uint32_t desc_hi_kv = static_cast<uint32_t>(umma_desc_sw128(0, 16, kPfGroupBytes) >> 32);
     const uint32_t desc_q_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(q_smem), 16, 1024));
-    const uint32_t desc_p_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(p_smem), 16, 1024));
     const uint32_t desc_k_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(k_smem), 16, kPfGroupBytes));
     const uint32_t desc_v_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(v_smem), 1024, kPfGroupBytes));
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
@@ -672,13 +667,13 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           }
           tcgen05_fence_after();
           if (lane == 0) {
-            const uint32_t a_base = desc_p_lo + (t & 1u) * (kPfPBytes >> 4);
+            const uint32_t a_base = tmem_base + kPfTmemP + (t & 1u) * 64;  // 8 columns per 16-token K step
             const uint32_t b_base = desc_v_lo + (t % kPfRing) * (kPfTileBytes >> 4);
-            tcgen05_mma_bf16(tmem_base + 128, pf_desc(a_base, desc_hi_1024), pf_desc(b_base, desc_hi_kv), idesc_pv, j != 0 ? 1u : 0u);
+            tcgen05_mma_bf16_ts(tmem_base + 128, a_base, pf_desc(b_base, desc_hi_kv), idesc_pv, j != 0 ? 1u : 0u);
 #pragma unroll
             for (int ks = 1; ks < 8; ++ks)
-              tcgen05_mma_bf16(tmem_base + 128, pf_desc(a_base + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), desc_hi_1024),
-                               pf_desc(b_base + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_kv), idesc_pv, 1u);
+              tcgen05_mma_bf16_ts(tmem_base + 128, a_base + ks * 8, pf_desc(b_base + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_kv),
+                                  idesc_pv, 1u);
             tcgen05_commit(smem_u32(&pv_full[t & 1u]));
             tcgen05_commit(smem_u32(&v_empty[t % kPfRing]));
           }
