@@ -1122,12 +1122,10 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
     const uint32_t box[5] = {64, static_cast<uint32_t>(wide ? 8 : d.page_size), wide ? 2u : 1u, 1, 1};
     int32_t rc = cake::encode_tensor_map(&plan->tmap_pf_k, cache0, 5, dims, strides, box, true);
     if (rc) return rc;
-    if (fused) {
-      plan->tmap_pf_v = plan->tmap_pf_k;
-    } else {
-      rc = cake::encode_tensor_map(&plan->tmap_pf_v, cache1, 5, dims, strides, box, true);
-      if (rc) return rc;
-    }
+    // V tiles are consumed 16 tokens per MMA: with pages of 16 tokens or more a V box is 16 tokens.
+    const uint32_t box_v[5] = {64, static_cast<uint32_t>(d.page_size >= 16 ? 16 : box[1]), box[2], 1, 1};
+    rc = cake::encode_tensor_map(&plan->tmap_pf_v, fused ? cache0 : cache1, 5, dims, strides, box_v, true);
+    if (rc) return rc;
     plan->last_pf_c0 = cache0;
     plan->last_pf_c1 = cache1;
   }

@@ -23,10 +23,12 @@
 //                   over all steps and is read, rescaled and written back only when its maximum has
 //                   moved by more than 2^8.
 //       warp 8      TMA producer of the query tile and of the K ring (3 slots)
-//       warp 10     TMA producer of the V ring (3 slots). Tiles are gathered page by page in boxes of
+//       warp 10     TMA producer of the V ring (3 slots). K tiles are gathered page by page in boxes of
 //                   one 8-token group (both 64-element halves of the row: 2 KiB), laid out
 //                   [group][lo | hi][8 rows][128 B]: groups a uniform 2 KiB apart, which is what the
-//                   tcgen05 shared-memory descriptors need. Never multicast.
+//                   tcgen05 shared-memory descriptor of a 128-token operand needs. V tiles are read
+//                   16 tokens per MMA, so their boxes are 16 tokens (4 KiB) when pages allow: half
+//                   as many copy instructions, which is what bounds the loop. Never multicast.
 //       warp 9      tcgen05.mma issuer: S = Q K^T (128x128x128, K-major operands) as soon as the
 //                   softmax warps have taken the previous S into registers, and O += P V (128x128x128,
 //                   V consumed in place as an MN-major operand) when P is written.
@@ -70,15 +72,19 @@ struct PrefillParams {
 // Development aid (off by default): cycles each role of every CTA spends blocked in its waits.
 // Slots per CTA: 0 softmax wait S, 1 softmax wait PV, 2 softmax total, 3 softmax steps,
 // 4 MMA wait K/V, 5 MMA wait S free, 6 MMA wait P, 7 MMA total, 8 K producer wait slot, 9 K producer
-// total, 10 V producer wait slot, 11 V producer total.
+// total, 10 V producer wait slot, 11 V producer total, 12 MMA issue of S = Q K^T, 13 MMA issue of O += P V.
 __device__ unsigned long long g_pf_timing[256 * 16];
+#define PF_DECLARE() long long pf_acc_[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
 #define PF_T0() const long long pf_t0_ = clock64()
-#define PF_ADD(slot, cond) do { if (cond) g_pf_timing[blockIdx.x * 16 + (slot)] += clock64() - pf_t0_; } while (0)
-#define PF_COUNT(slot, cond) do { if (cond) g_pf_timing[blockIdx.x * 16 + (slot)] += 1; } while (0)
+#define PF_ADD(slot, cond) do { if (cond) pf_acc_[slot] += clock64() - pf_t0_; } while (0)
+#define PF_COUNT(slot, cond) do { if (cond) pf_acc_[slot] += 1; } while (0)
+#define PF_FLUSH() do { for (int i_ = 0; i_ < 16; ++i_) if (pf_acc_[i_]) atomicAdd(&g_pf_timing[blockIdx.x * 16 + i_], static_cast<unsigned long long>(pf_acc_[i_])); } while (0)
 #else
+#define PF_DECLARE() do {} while (0)
 #define PF_T0() do {} while (0)
 #define PF_ADD(slot, cond) do {} while (0)
 #define PF_COUNT(slot, cond) do {} while (0)
+#define PF_FLUSH() do {} while (0)
 #endif
 
 __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
@@ -232,6 +238,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  PF_DECLARE();
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
@@ -473,9 +480,14 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     uint8_t* ring = is_v ? v_smem : k_smem;
     uint64_t* full = is_v ? v_full : k_full;
     uint64_t* empty = is_v ? v_empty : k_empty;
-    const int tb = min(p.page_size, 8);
-    const int log2_tb = min(p.log2_ps, 3);
-    const int boxes = kPfTileKv >> log2_tb;  // 16 .. 128 per tile
+    // The tensor-memory engine takes of the order of a hundred cycles per copy instruction, so the
+    // number of boxes per tile matters. K tiles need a uniform 8-token group stride (the 128 tokens
+    // are the N extent of one MMA), which caps a box at one group. A V tile is consumed 16 tokens per
+    // MMA, so with pages of 16 tokens or more one box is 16 tokens: [lo g0 | lo g1 | hi g0 | hi g1].
+    const bool v_pages = is_v && p.page_size >= 16;
+    const int tb = v_pages ? 16 : min(p.page_size, 8);
+    const int log2_tb = v_pages ? 4 : min(p.log2_ps, 3);
+    const int boxes = kPfTileKv >> log2_tb;  // 8 .. 128 per tile
     const int reps = (boxes + 31) >> 5;
     const bool wide = p.page_size >= 8;
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
@@ -559,7 +571,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             const int from = which == 0 ? w0 : which == 1 ? w1 : which == 2 ? w2 : w3;
             const int page = tok < it.kv_needed ? from : p.total_pages;
             const int off = tok & (p.page_size - 1);
-            const uint32_t gbase = sbase + static_cast<uint32_t>((tok_in_tile >> 3) * kPfGroupBytes);
+            const uint32_t gbase = sbase + static_cast<uint32_t>((tok_in_tile >> 3) * kPfGroupBytes);  // 16 tokens = 4 KiB too
             if (wide) {
               tma_load_5d(gbase, tmap, bar, 0, off, 0, head, page);
             } else {
@@ -589,7 +601,10 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     const uint32_t desc_hi_kv = static_cast<uint32_t>(umma_desc_sw128(0, 16, kPfGroupBytes) >> 32);
     const uint32_t desc_q_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(q_smem), 16, 1024));
     const uint32_t desc_k_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(k_smem), 16, kPfGroupBytes));
-    const uint32_t desc_v_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(v_smem), 1024, kPfGroupBytes));
+    // V with 16-token boxes: halves 2 KiB apart, the two 8-token groups of a box 1 KiB apart.
+    const bool v_pages = p.page_size >= 16;
+    const uint32_t desc_v_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(v_smem), v_pages ? 2048 : 1024, kPfGroupBytes));
+    const uint32_t desc_hi_v = v_pages ? desc_hi_1024 : desc_hi_kv;
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
       PF_T0();
       int where = 200;
@@ -624,7 +639,11 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           if (!taken) return false;
         }
         tcgen05_fence_after();
-        if (lane == 0) issue_qk(t_next);
+        {
+          PF_T0();
+          if (lane == 0) issue_qk(t_next);
+          PF_ADD(12, lane == 0);
+        }
         __syncwarp();
         return true;
       };
@@ -648,8 +667,9 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             for (int e = lane; e < (kPfTileKv - first_bad) * 16; e += 32) {
               const int vrow = first_bad + (e >> 4);
               const int piece = e & 15;
-              *reinterpret_cast<uint4*>(v_base + (vrow >> 3) * kPfGroupBytes + (piece >> 3) * 1024 + (vrow & 7) * 128 +
-                                        (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+              const int at = v_pages ? (vrow >> 4) * 4096 + (piece >> 3) * 2048 + ((vrow >> 3) & 1) * 1024
+                                     : (vrow >> 3) * kPfGroupBytes + (piece >> 3) * 1024;
+              *reinterpret_cast<uint4*>(v_base + at + (vrow & 7) * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
             }
             fence_proxy_async_smem();
             __syncwarp();
@@ -666,17 +686,19 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             if (!ok) break;
           }
           tcgen05_fence_after();
+          PF_T0();
           if (lane == 0) {
             const uint32_t a_base = tmem_base + kPfTmemP + (t & 1u) * 64;  // 8 columns per 16-token K step
             const uint32_t b_base = desc_v_lo + (t % kPfRing) * (kPfTileBytes >> 4);
-            tcgen05_mma_bf16_ts(tmem_base + 128, a_base, pf_desc(b_base, desc_hi_kv), idesc_pv, j != 0 ? 1u : 0u);
+            tcgen05_mma_bf16_ts(tmem_base + 128, a_base, pf_desc(b_base, desc_hi_v), idesc_pv, j != 0 ? 1u : 0u);
 #pragma unroll
             for (int ks = 1; ks < 8; ++ks)
-              tcgen05_mma_bf16_ts(tmem_base + 128, a_base + ks * 8, pf_desc(b_base + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_kv),
+              tcgen05_mma_bf16_ts(tmem_base + 128, a_base + ks * 8, pf_desc(b_base + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_v),
                                   idesc_pv, 1u);
             tcgen05_commit(smem_u32(&pv_full[t & 1u]));
             tcgen05_commit(smem_u32(&v_empty[t % kPfRing]));
           }
+          PF_ADD(13, lane == 0);
           __syncwarp();
           ++step_total;
         }
@@ -695,6 +717,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   }
 
   // ---- orderly exit
+  PF_FLUSH();
   __syncthreads();
   if (*abort_flag) {
     if ((warp == 8 || warp == 10) && lane == 0) {
