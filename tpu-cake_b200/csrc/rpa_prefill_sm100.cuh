@@ -22,7 +22,7 @@
 //                   A operand, so P never touches shared memory; the output row accumulates in TMEM
 //                   over all steps and is read, rescaled and written back only when its maximum has
 //                   moved by more than 2^8.
-//       warp 8      TMA producer of the query tile and of the K ring (3 slots)
+//       warps 8, 11 TMA producers of the query tile and of the K ring (3 slots), half a tile each
 //       warp 10     TMA producer of the V ring (3 slots). K tiles are gathered page by page in boxes of
 //                   one 8-token group (both 64-element halves of the row: 2 KiB), laid out
 //                   [group][lo | hi][8 rows][128 B]: groups a uniform 2 KiB apart, which is what the
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
     for (int s = 0; s < kPfRing; ++s) {
-      mbar_init(smem_u32(&k_full[s]), 1);
+      mbar_init(smem_u32(&k_full[s]), 2);  // two producer warps, half a tile each
       mbar_init(smem_u32(&k_empty[s]), 1);
       mbar_init(smem_u32(&v_full[s]), 1);
       mbar_init(smem_u32(&v_empty[s]), 1);
@@ -471,7 +471,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       }
       PF_ADD(2, threadIdx.x == 0);
     }
-  } else if (warp == 8 || warp == 10) {
+  } else if (warp == 8 || warp == 10 || warp == 11) {
     // ---------------------------------------------------------------- TMA producers (K ring, V ring)
     // Boxes: with pages of 8 tokens or more, one box is an 8-token group with both halves of the
     // row (2 KiB); smaller pages fill the two atoms of a group row by row, one box per page and atom.
@@ -487,12 +487,17 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     const bool v_pages = is_v && p.page_size >= 16;
     const int tb = v_pages ? 16 : min(p.page_size, 8);
     const int log2_tb = v_pages ? 4 : min(p.log2_ps, 3);
-    const int boxes = kPfTileKv >> log2_tb;  // 8 .. 128 per tile
+    // Issuing a copy costs the issuing warp about 70 cycles per box, so the 16 boxes of a K tile are
+    // split between warps 8 and 11 (each arrives with half the tile's bytes).
+    const int parts = is_v ? 1 : 2;
+    const int part = warp == 11 ? 1 : 0;
+    const int boxes = (kPfTileKv >> log2_tb) / parts;  // boxes this warp issues per tile
+    const int first_box = part * boxes;
     const int reps = (boxes + 31) >> 5;
     const bool wide = p.page_size >= 8;
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
       PF_T0();
-      if (!is_v) {
+      if (warp == 8) {
         if (lane == 0) {
           mbar_arrive_expect_tx(smem_u32(q_full), kPfQBytes);
           for (int half = 0; half < 2; ++half)
@@ -545,7 +550,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         {
           PF_T0();
           alive = __all_sync(0xffffffffu, pf_wait(smem_u32(&empty[slot]), parity ^ 1u, abort_flag));
-          PF_ADD(is_v ? 10 : 8, lane == 0);
+          PF_ADD(is_v ? 10 : 8, lane == 0 && warp != 11);
         }
         if (!alive) {
           if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, (is_v ? 150 : 100) + j);
@@ -553,12 +558,12 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           break;
         }
         const uint32_t bar = smem_u32(&full[slot]);
-        if (lane == 0) mbar_arrive_expect_tx(bar, kPfTileBytes);
+        if (lane == 0) mbar_arrive_expect_tx(bar, kPfTileBytes / parts);
         __syncwarp();
         const uint32_t sbase = smem_u32(ring + slot * kPfTileBytes);
         for (int rep = 0; rep < reps; ++rep) {
           const int b = lane + rep * 32;
-          const int tok_in_tile = b * tb;
+          const int tok_in_tile = (first_box + b) * tb;
           const int tok = j * kPfTileKv + tok_in_tile;
           const int rel = (tok >> p.log2_ps) - win_base;  // 0..127 for the boxes of this tile
           const int src = rel & 31;
@@ -585,7 +590,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         ++loads_issued;
         ++step_total;
       }
-      PF_ADD(is_v ? 11 : 9, lane == 0);
+      PF_ADD(is_v ? 11 : 9, lane == 0 && warp != 11);
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
@@ -711,7 +716,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       PF_ADD(7, lane == 0);
     }
   } else {
-    // warp 11 has no role: it only takes part in the item barrier
+    // (every warp has a role)
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
     }
   }
@@ -720,7 +725,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   PF_FLUSH();
   __syncthreads();
   if (*abort_flag) {
-    if ((warp == 8 || warp == 10) && lane == 0) {
+    if ((warp == 8 || warp == 10 || warp == 11) && lane == 0) {
       // loads already issued must land before shared memory is released
       uint64_t* full = warp == 10 ? v_full : k_full;
       for (uint32_t back = 0; back < kPfRing && back < loads_issued; ++back) {
