@@ -811,7 +811,7 @@ void rpa_layout_workspace(cake_rpa* plan, int group) {
   plan->off_part_o = align_up(plan->off_part_ml + sizeof(float) * 2 * group * plan->max_items, 256);
   plan->off_pf_entries = align_up(plan->off_part_o + sizeof(float) * 128 * group * plan->max_items, 256);
   plan->max_pf_entries = (d.num_q_tokens + 127) / 128 + d.num_seqs;
-  plan->ws_bytes = plan->off_pf_entries + 16 * static_cast<size_t>(plan->max_pf_entries);
+  plan->ws_bytes = plan->off_pf_entries + 32 * static_cast<size_t>(plan->max_pf_entries);
 }
 
 int32_t rpa_encode_maps(cake_rpa* plan, const void* c0, const void* c1) {

@@ -62,7 +62,7 @@ struct PrefillParams {
   int32_t heads_items;     // work items per (sequence, query tile): one per query head
   int32_t* work_counter;
   int32_t* entry_count;    // number of (sequence, query tile) entries
-  int4* entries;           // {sequence, first query row of the tile, q_len, kv_len}
+  int4* entries;           // two per tile: {sequence, first query row, q_len, kv_len}, {first query token, first page-table slot, 0, 0}
   int32_t max_entries;
   int32_t num_q_tokens;
   RpaParams r;             // page table, layout, scale, status
@@ -174,7 +174,12 @@ __global__ void __launch_bounds__(256) cake_rpa_prefill_plan_sm100(PrefillParams
       if (q_len <= 0 || len < q_len) continue;
       const int tiles = (q_len + kPfTileQ - 1) / kPfTileQ;
       if (tiles <= r) continue;
-      if (n < pp.max_entries) pp.entries[n] = make_int4(s, (tiles - 1 - r) * kPfTileQ, q_len, len);
+      if (n < pp.max_entries) {
+        const int q0 = (tiles - 1 - r) * kPfTileQ;
+        const int table_base = p.table_layout == CAKE_RPA_TABLE_2D ? s * p.max_pages_per_seq : (p.cu_kv_lens[s] >> p.log2_ps);
+        pp.entries[2 * n] = make_int4(s, q0, q_len, len);
+        pp.entries[2 * n + 1] = make_int4(pp.cu_q_lens[s] + q0, table_base, 0, 0);  // saves two dependent loads per item
+      }
       ++n;
     }
   }
@@ -256,6 +261,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     }
     mbar_init(smem_u32(drain_bar), 1);
     *abort_flag = 0;
+    item_slot[0] = atomicAdd(pp.work_counter, 1);
     fence_mbar_init();
     prefetch_tensormap(&tmap_q);
     prefetch_tensormap(&tmap_k);
@@ -277,18 +283,21 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   uint32_t loads_issued = 0;  // producers: tiles issued, for the orderly exit
 
   struct Item {
-    int id, seq, q0, kv_len, head, kvh, prior, rows, kv_needed, n_steps, q_tok0;
+    int id, seq, q0, kv_len, head, kvh, prior, rows, kv_needed, n_steps, q_tok0, table_base;
   };
-  // Claims the next work item for the whole CTA. One thread decides (next item, or -1 after an
-  // abort) so that every thread leaves its loop in the same iteration. The barrier also separates
-  // items: when it opens, every role has finished the previous one, so the query and P buffers and
-  // all TMEM columns are free.
+  // Hands the next work item to the whole CTA. One thread claims (an item, or -1 after an abort),
+  // one item ahead, so that every thread leaves its loop in the same iteration. The barrier also
+  // separates items: when it opens, every role has finished the previous one, so the query buffer
+  // and all TMEM columns are free.
   auto next_item = [&](uint32_t iter, Item& it) -> bool {
-    if (threadIdx.x == 0) item_slot[iter & 1] = *abort_flag ? -1 : atomicAdd(pp.work_counter, 1);
     named_bar_sync(1, kPfThreads);
     const int id = item_slot[iter & 1];
+    // The claim for the item after this one is issued now, so its latency hides under this item.
+    if (threadIdx.x == 0) item_slot[(iter + 1) & 1] = *abort_flag ? -1 : atomicAdd(pp.work_counter, 1);
     if (id < 0 || id >= total_items) return false;
-    const int4 entry = __ldg(pp.entries + id / pp.heads_items);
+    const int4* entry_pair = pp.entries + 2 * (id / pp.heads_items);
+    const int4 entry = __ldg(entry_pair);
+    const int4 where = __ldg(entry_pair + 1);
     it.id = id;
     it.seq = entry.x;
     it.q0 = entry.y;
@@ -299,7 +308,8 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     it.rows = min(kPfTileQ, entry.z - entry.y);
     it.kv_needed = it.prior + it.q0 + it.rows;  // positions any row of the tile can see
     it.n_steps = (it.kv_needed + kPfTileKv - 1) / kPfTileKv;
-    it.q_tok0 = __ldg(pp.cu_q_lens + it.seq) + it.q0;
+    it.q_tok0 = where.x;
+    it.table_base = where.y;
     return true;
   };
   Item it;
@@ -510,9 +520,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       // Page ids are read 128 table slots at a time (four per lane) and the next 128 are requested
       // while the current ones are in use, so no tile waits for a table read of its own.
       const int pages_needed = (it.kv_needed + p.page_size - 1) >> p.log2_ps;
-      const long long table_base = p.table_layout == CAKE_RPA_TABLE_2D
-                                       ? static_cast<long long>(it.seq) * p.max_pages_per_seq
-                                       : static_cast<long long>(p.cu_kv_lens[it.seq] >> p.log2_ps);
+      const long long table_base = it.table_base;
       const long long table_end = p.table_layout == CAKE_RPA_TABLE_2D ? table_base + p.max_pages_per_seq
                                                                       : static_cast<long long>(p.table_len);
       auto load_window = [&](int base_slot, int (&w)[4]) {
