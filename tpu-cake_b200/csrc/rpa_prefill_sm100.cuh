@@ -28,13 +28,14 @@
 //                   [group][lo | hi][8 rows][128 B]: groups a uniform 2 KiB apart, which is what the
 //                   tcgen05 shared-memory descriptor of a 128-token operand needs. V tiles are read
 //                   16 tokens per MMA, so their boxes are 16 tokens (4 KiB) when pages allow: half
-//                   as many copy instructions, which is what bounds the loop. Never multicast.
-//       warp 9      tcgen05.mma issuer: S = Q K^T (128x128x128, K-major operands) as soon as the
-//                   softmax warps have taken the previous S into registers, and O += P V (128x128x128,
-//                   V consumed in place as an MN-major operand) when P is written.
-//     A 128-wide MMA keeps the tensor pipe busy for 64 cycles, about what the issuing thread needs
-//     per instruction when it shares its scheduler with one softmax warp; 64-wide steps were
-//     issue-bound.
+//                   as many copy instructions (each costs its issuing warp about 70 cycles).
+//                   Never multicast.
+//       warp 9      tcgen05.mma issuer: S = Q K^T (128x128x128, both operands K-major in shared
+//                   memory) two steps ahead of the softmax, as soon as the softmax warps have taken
+//                   the previous S into registers, and O += P V (128x128x128, P from TMEM, V consumed
+//                   in place from shared memory as an MN-major operand) when P is written.
+//     A 128-wide MMA keeps the tensor pipe busy for about 64 cycles, which is also what the issuing
+//     thread needs per instruction; 64-wide steps were issue-bound.
 #pragma once
 
 namespace cake {
@@ -722,10 +723,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       }
       __syncwarp();
       PF_ADD(7, lane == 0);
-    }
-  } else {
-    // (every warp has a role)
-    for (uint32_t iter = 0; next_item(iter, it); ++iter) {
     }
   }
 
