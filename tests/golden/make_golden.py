@@ -186,7 +186,9 @@ def make_rpa_fixtures() -> None:
 
 
 def main() -> None:
-    reference_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference").resolve()
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py PATH_TO_TPU_CAKE_CHECKOUT")
+    reference_root = Path(sys.argv[1]).resolve()
     _install_reference(reference_root)
     identity = make_identity_fixture()
     identity["confirmation_contract_input_hashes"] = make_confirmation_input_hashes(reference_root)
