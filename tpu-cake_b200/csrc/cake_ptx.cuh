@@ -254,6 +254,17 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while the kernel before it on the stream still runs; it must wait here before it touches
+// anything that kernel writes. The earlier kernel lets its dependents start early with the trigger.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dependency_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -102,6 +102,7 @@ __device__ __forceinline__ void rpa_record(int32_t* status, int code, int d0, in
 // of small items. item_base[s] = index of the sequence's first full chunk, tail_cs[s] = index of its
 // remainder chunk (-1 if none), item_base[num_seqs] = total number of (sequence, chunk) pairs.
 __global__ void __launch_bounds__(256) cake_rpa_plan_sm100(RpaParams p) {
+  grid_dependency_trigger();  // the decode kernel may set itself up while this one runs
   __shared__ int s_full[256];
   __shared__ int s_tail[256];
   __shared__ int s_carry_full, s_carry_tail, s_total_full;
@@ -342,15 +343,22 @@ __device__ __forceinline__ void rpa_merge(const RpaParams& p, int s, int h, int 
         l += ml.y * w;
       }
       const int cnt = min(32, n - c0);
-#pragma unroll 4
-      for (int jj = 0; jj < cnt; ++jj) {  // fixed chunk order; the loads are independent and pipeline
-        const float wj = __shfl_sync(0xffffffffu, w, jj);
-        const size_t row = row_of(c0 + jj, r);
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + row * 128) + lane);
-        o.x += v.x * wj;
-        o.y += v.y * wj;
-        o.z += v.z * wj;
-        o.w += v.w * wj;
+      // Fixed chunk order; eight partial rows are requested together so their latencies overlap.
+      for (int j0 = 0; j0 < cnt; j0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int jj = min(j0 + u, cnt - 1);
+          v[u] = __ldcg(reinterpret_cast<const float4*>(p.part_o + row_of(c0 + jj, r) * 128) + lane);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float wj = (j0 + u < cnt) ? __shfl_sync(0xffffffffu, w, (j0 + u) & 31) : 0.f;
+          o.x += v[u].x * wj;
+          o.y += v[u].y * wj;
+          o.z += v[u].z * wj;
+          o.w += v[u].w * wj;
+        }
       }
     }
 #pragma unroll
@@ -392,6 +400,10 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
     *reinterpret_cast<uint4*>(qbuf + i * 16) = make_uint4(0u, 0u, 0u, 0u);
   __syncwarp();
 
+  // Everything above touched only this CTA's shared memory: it overlapped the kernels before this
+  // one (launched with programmatic serialization). From here on their results are read.
+  grid_dependency_wait();
+  grid_dependency_trigger();
   const int total_items = p.item_base[p.num_seqs] * p.kv_heads;
   const int trow = lane >> 2;        // token (QK^T) or head-dim row (PV) this thread holds, +8 for c2/c3
   const int qrow = (lane & 3) * 2;   // query rows qrow, qrow + 1 of the accumulator fragments
@@ -729,6 +741,7 @@ __global__ void __launch_bounds__(kRpaThreads, 1)
 
 // One warp per (sequence, KV head, query row): merges its split-KV partials in chunk order.
 __global__ void __launch_bounds__(128) cake_rpa_combine_sm100(const RpaParams p) {
+  grid_dependency_wait();  // launched early; the partials are complete only when the decode kernel is
   const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (unit >= p.num_seqs * p.kv_heads * p.group) return;
   const int pair = unit / p.group;
@@ -1023,12 +1036,26 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, cake::kRpaSmemBytes));
     configured = true;
   }
-  cake::cake_rpa_decode_sm100<<<plan->sm_count, cake::kRpaThreads, cake::kRpaSmemBytes, stream>>>(
-      plan->tmap_k, plan->tmap_v, p);
-  CAKE_CUDA_TRY(cudaGetLastError());
+  // Decode and combine are launched with programmatic stream serialization: each may be scheduled
+  // while its predecessor still runs and waits on the device (griddepcontrol.wait) before reading
+  // what the predecessor wrote, so launch latency and set-up overlap the predecessor's tail.
+  cudaLaunchAttribute overlap_attr;
+  overlap_attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  overlap_attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config;
+  memset(&config, 0, sizeof(config));
+  config.stream = stream;
+  config.attrs = &overlap_attr;
+  config.numAttrs = 1;
+  config.gridDim = dim3(plan->sm_count);
+  config.blockDim = dim3(cake::kRpaThreads);
+  config.dynamicSmemBytes = cake::kRpaSmemBytes;
+  CAKE_CUDA_TRY(cudaLaunchKernelEx(&config, cake::cake_rpa_decode_sm100, plan->tmap_k, plan->tmap_v, p));
   ++launches;
-  cake::cake_rpa_combine_sm100<<<(num_seqs * d.q_heads + 3) / 4, 128, 0, stream>>>(p);
-  CAKE_CUDA_TRY(cudaGetLastError());
+  config.gridDim = dim3((num_seqs * d.q_heads + 3) / 4);
+  config.blockDim = dim3(128);
+  config.dynamicSmemBytes = 0;
+  CAKE_CUDA_TRY(cudaLaunchKernelEx(&config, cake::cake_rpa_combine_sm100, p));
   ++launches;
   plan->launches = launches;
   return CAKE_OK;
