@@ -70,3 +70,53 @@ def test_two_cpu_ranks_reduce_scatter_and_handle_exchange(scatter_dimension):
     results = manager.dict()
     mp.spawn(_rank_main, args=(world, _free_port(), scatter_dimension, results), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True}
+
+
+def _decode_rank_main(rank: int, world: int, port: int, results) -> None:
+    """KV-head sharding of the decode and the layout of the gathered outputs: rank r holds KV heads
+    [r*Hkv/W, (r+1)*Hkv/W) of every page and the matching query heads, computes its heads (the oracle
+    stands in for the kernel) and the outputs are all-gathered as [W][S][Hq/W][D]."""
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__
+
+    __graft_entry__.load_package()
+    from oracle import rpa as rpa_oracle
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+    try:
+        generator = np.random.default_rng(5)  # same seed on every rank: replicated metadata and inputs
+        lengths = np.array([9, 40, 17], dtype=np.int32)
+        count, kv_heads, group, page_size, dim = 3, 4, 2, 8, 16
+        q_heads = kv_heads * group
+        pages_per = -(-lengths // page_size)
+        pool = int(pages_per.sum()) + 2
+        query = generator.normal(size=(count, q_heads, dim)).astype(np.float32)
+        keys = generator.normal(size=(pool, page_size, kv_heads, dim)).astype(np.float32)
+        values = generator.normal(size=(pool, page_size, kv_heads, dim)).astype(np.float32)
+        table = np.zeros((count, int(pages_per.max())), dtype=np.int32)
+        order = generator.permutation(pool)
+        cursor = 0
+        for s in range(count):
+            table[s, : pages_per[s]] = order[cursor : cursor + pages_per[s]]
+            cursor += int(pages_per[s])
+        local_kv, local_q = kv_heads // world, q_heads // world
+        heads = slice(rank * local_kv, (rank + 1) * local_kv)
+        mine = rpa_oracle.rpa_separate(query[:, rank * local_q : (rank + 1) * local_q], keys[:, :, heads], values[:, :, heads],
+                                       table, lengths)
+        gathered = [torch.zeros((count, local_q, dim), dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(np.ascontiguousarray(mine)))
+        assembled = np.concatenate([piece.numpy() for piece in gathered], axis=1)  # [W][S][Hq/W][D] -> [S][Hq][D]
+        expected = rpa_oracle.rpa_separate(query, keys, values, table, lengths)
+        results[rank] = bool(np.allclose(assembled, expected, atol=1e-6, rtol=1e-6)) and assembled.shape == expected.shape
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_cpu_ranks_shard_decode_by_kv_head_and_gather():
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_decode_rank_main, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True}
