@@ -369,3 +369,33 @@ def test_data_tensor_sharded_surface_on_one_gpu(cuda_device):
         assert surface.assemble(outputs, 0).shape == (8, 32, 128)
     finally:
         executable.close()
+
+
+def test_sharded_surface_chained_timing_rounds(cuda_device):
+    """The surface's timing protocol on one mesh position: rounds restart from the placed inputs,
+    calls inside a round feed output and cache forward; every round yields its samples."""
+    from tests.sharded_cases import build_sharded_surface
+
+    global_inputs, _ = build_sharded_surface(13)
+    shapes = [tuple(np.asarray(v).shape) for v in global_inputs]
+    local = rpa_cuda_lowering.CudaFusedRpaPlan(
+        name="surface", schedule_sha256="0" * 64, query_shape=(4, 8, 128), key_shape=(4, 4, 128), value_shape=(4, 4, 128),
+        fused_cache_shape=(shapes[3][0] // 2, 1, 4, 2, 128), kv_lengths_shape=(4,), page_indices_shape=(shapes[5][0] // 2,),
+        cumulative_query_lengths_shape=(5,), cumulative_kv_lengths_shape=(5,), distribution_shape=(3,),
+        relative_states_shape=(4, 8, 16), relative_projection_shape=(16, 512), output_shape=(4, 8, 128), softmax_scale=1.0 / 128,
+    )
+    surface = rpa_cuda_lowering.ShardedCudaFusedRpaPlan(local)
+    shard = tuple(np.ascontiguousarray(v) for v in surface.shard_inputs(global_inputs, surface.mesh_position(6)))
+    executable = surface.build(cuda_device)
+    try:
+        rounds = surface.timing_rounds(executable, shard, warmup_iterations=2, timing_rounds=3, samples_per_round=5)
+        assert [r["round_index"] for r in rounds] == [0, 1, 2]
+        assert all(len(r["samples_ns"]) == 5 and r["median_ns"] > 0 for r in rounds)
+        # A chained call is still a valid decode: run one more from placed inputs and compare with the oracle.
+        device_inputs = tuple(to_device(v, cuda_device) for v in shard)
+        output, _ = surface.run_local(executable, *device_inputs)
+        expected, _ = oracle.rpa_fused(shard)
+        maximum, relative = rpa_cuda_lowering.surface_errors(torch_to_bf16(output).astype(np.float32), expected.astype(np.float32))
+        assert maximum <= MAX_ABS and relative <= REL_L2
+    finally:
+        executable.close()

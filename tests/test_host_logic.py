@@ -170,3 +170,17 @@ def test_sharded_surface_partitioning_round_trips():
         surface.mesh_position(8)
     with pytest.raises(ValueError, match="the surface expects"):
         surface.shard_inputs((global_inputs[0][:4],) + global_inputs[1:], (0, 0))
+
+
+def test_surface_error_metrics():
+    from tpu_cake_b200 import rpa_cuda_lowering
+
+    expected = np.array([[1.0, -2.0], [0.5, 4.0]], dtype=np.float32)
+    actual = expected + np.array([[0.0, 0.01], [-0.02, 0.0]], dtype=np.float32)
+    maximum, relative = rpa_cuda_lowering.surface_errors(actual, expected)
+    assert abs(maximum - 0.02) < 1e-6
+    assert abs(relative - np.sqrt((0.01**2 + 0.02**2) / (1 + 4 + 0.25 + 16))) < 1e-6
+    with pytest.raises(ValueError, match="ABI_MISMATCH"):
+        rpa_cuda_lowering.surface_errors(actual.astype(np.float64), expected)
+    with pytest.raises(ValueError, match="NONFINITE"):
+        rpa_cuda_lowering.surface_errors(np.full_like(expected, np.nan), expected)

@@ -210,6 +210,32 @@ def decode_resource_contract(plan) -> dict:
             "shared_memory_bytes": shared, "workspace_bytes": max(1, batch * q_heads * 130 * 4)}
 
 
+def _to_device_tensor(value, device: torch.device) -> torch.Tensor:
+    """numpy (bfloat16 via ml_dtypes included) or torch value -> contiguous tensor on ``device``, bits unchanged."""
+    if isinstance(value, torch.Tensor):
+        return value.to(device).contiguous()
+    array = np.ascontiguousarray(value)
+    if array.dtype.name == "bfloat16":
+        return torch.from_numpy(array.view(np.uint16).copy()).view(torch.bfloat16).to(device)
+    return torch.from_numpy(array.copy()).to(device)
+
+
+def surface_errors(actual: np.ndarray, expected: np.ndarray) -> tuple[float, float]:
+    """(max-abs, relative-L2) in float64, the error metrics of the reference's surface runner
+    (src/tpu_cake/rpa_surface_runner.py:394-411); shape / dtype mismatches and non-finite values are errors."""
+    import math
+
+    if actual.shape != expected.shape or actual.dtype != expected.dtype:
+        raise ValueError(f"SHARDED_RPA_OUTPUT_ABI_MISMATCH actual={actual.shape}/{actual.dtype} expected={expected.shape}/{expected.dtype}")
+    a, e = actual.astype(np.float64), expected.astype(np.float64)
+    if not np.all(np.isfinite(a)) or not np.all(np.isfinite(e)):
+        raise ValueError("SHARDED_RPA_OUTPUT_NONFINITE")
+    difference = a - e
+    maximum = float(np.abs(difference).max()) if difference.size else 0.0
+    relative = math.sqrt(math.fsum((difference.ravel() ** 2).tolist()) / max(math.fsum((e.ravel() ** 2).tolist()), 1e-60))
+    return maximum, round(relative, 15)
+
+
 def _to_host(value):
     if isinstance(value, torch.Tensor):
         return value.detach().cpu().numpy()
@@ -604,6 +630,47 @@ class ShardedCudaFusedRpaPlan:
     def run_local(self, executable: "RpaDecodeExecutable", *local_inputs):
         """Preflight (host integers) and decode of one mesh position's shard."""
         return self.local_plan.run_preflighted(executable, *local_inputs)
+
+    def timing_rounds(self, executable: "RpaDecodeExecutable", host_inputs: tuple, *, warmup_iterations: int, timing_rounds: int,
+                      samples_per_round: int) -> tuple[dict, ...]:
+        """The chained-state timing protocol of the reference surface runner
+        (src/tpu_cake/rpa_surface_runner.py:490-517): every round starts from freshly placed inputs;
+        inside a round each call's output becomes the next call's queries and its updated cache the
+        next call's cache; one synchronized wall-clock sample per call."""
+        import statistics
+        import time
+
+        device = executable.device
+
+        def place():
+            return tuple(None if value is None else _to_device_tensor(value, device) for value in host_inputs)
+
+        def chain(inputs, outputs):
+            output, cache = outputs
+            return (output, *inputs[1:3], cache, *inputs[4:])
+
+        def execute(inputs):
+            outputs = self.local_plan.invoke(executable, *inputs)
+            torch.cuda.synchronize(device)
+            return outputs
+
+        inputs = place()
+        self.local_plan.preflight(*host_inputs)
+        for _ in range(warmup_iterations):
+            inputs = chain(inputs, execute(inputs))
+        rounds = []
+        for round_index in range(timing_rounds):
+            inputs = place()
+            torch.cuda.synchronize(device)
+            samples = []
+            for _ in range(samples_per_round):
+                started = time.perf_counter_ns()
+                outputs = execute(inputs)
+                samples.append(time.perf_counter_ns() - started)
+                inputs = chain(inputs, outputs)
+            rounds.append({"round_index": round_index, "samples_ns": tuple(samples), "median_ns": float(statistics.median(samples))})
+        executable.status()
+        return tuple(rounds)
 
 
 
