@@ -201,7 +201,7 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
  * semantics (causal=1, src/tpu_cake/rpa_lowering.py:232-273) but no reference test behind it.
  * q, out: bf16 [num_q_tokens, q_heads, 128]; new_k, new_v: bf16 [num_q_tokens, kv_heads, 128] (written
  * into the cache first when update_cache == 1); cu_q_lens: i32 [num_seqs+1] on the device;
- * num_decode_seqs: host value. Needs head_dim 128 and bias_mode 0. The decode sequences run through
+ * num_decode_seqs: host value. Needs head_dim 128, bias_mode 0 and the fused cache layout. The decode sequences run through
  * the decode kernels, the others through the tcgen05 prefill kernel. */
 int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k, const void* new_v,
                                void* cache0, void* cache1, const int32_t* kv_lens,

@@ -1115,6 +1115,8 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
   if (d.head_dim != 128) return fail(CAKE_ERR_UNSUPPORTED, "rpa mixed: head_dim must be 128, got %d", d.head_dim);
   if (d.bias_mode != 0) return fail(CAKE_ERR_UNSUPPORTED, "rpa mixed: attention bias is lowered for decode batches only");
   if (!(d.sm_scale > 0.f)) return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa mixed: sm_scale must be positive");
+  if (d.cache_layout != CAKE_RPA_CACHE_FUSED)
+    return fail(CAKE_ERR_UNSUPPORTED, "rpa mixed: ragged batches are lowered for the fused cache layout");
   if (d.cache_layout == CAKE_RPA_CACHE_SEPARATE && !cache1)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa: separate cache layout needs a value cache");
   if (d.table_layout == CAKE_RPA_TABLE_FLAT && !cu_kv_lens)
