@@ -48,7 +48,7 @@ const char* cake_last_error(void);
 
 /* Device-written status word of the most recent kernels of a handle family.
  * code: 0 = ok, 1 = bounded wait on a shared-memory barrier ran out, 2 = bounded wait on a
- * peer arrival counter ran out, 3 = page index out of range, 4 = sequence metadata out of range,
+ * peer's data or flag ran out, 3 = page index out of range, 4 = sequence metadata out of range,
  * 5 = a kernel found its shared memory misaligned and did nothing.
  * detail0..2 carry coordinates (block, tile / sequence, stage / page slot). */
 typedef struct cake_status {
@@ -76,8 +76,8 @@ int32_t cake_ipc_close(void* ptr);
 
 #define CAKE_RS_LOCAL_PARTIAL 0 /* write the partial, laid out owner-major; the host runs the
                                    library collective (NCCL reduce-scatter) on it */
-#define CAKE_RS_P2P_OWNER_PUSH 1 /* epilogue pushes each partial tile to its owner GPU; a second
-                                    kernel sums the W slots in rank order */
+#define CAKE_RS_P2P_OWNER_PUSH 1 /* epilogue pushes each partial tile to its owner GPU; four more
+                                    warps of the same kernel sum the W slots in rank order */
 
 typedef struct cake_matmul_rs_desc {
   int64_t m;            /* rows of lhs and of the partial */
@@ -93,7 +93,8 @@ typedef struct cake_matmul_rs_desc {
   int32_t tile_n;       /* 64, 128 or 256 */
   int32_t rhs_layout;   /* 0 = rhs is [k_local, n] row-major (the reference layout),
                            1 = rhs is [n, k_local] row-major (pre-transposed) */
-  int32_t reserved;
+  int32_t wait_budget_ms; /* how long the slot reduction waits for a peer's data before it gives up
+                             with CAKE_ERR_TIMEOUT; 0 = the default of 20 s */
 } cake_matmul_rs_desc;
 
 typedef struct cake_matmul_rs cake_matmul_rs;
@@ -104,13 +105,25 @@ int32_t cake_matmul_rs_destroy(cake_matmul_rs* plan);
 /* Bytes of the partial buffer for CAKE_RS_LOCAL_PARTIAL (m * n * transport size). */
 size_t cake_matmul_rs_partial_bytes(const cake_matmul_rs* plan);
 
-/* CAKE_RS_P2P_OWNER_PUSH: bytes of this rank's receive slots / arrival counters. */
+/* CAKE_RS_P2P_OWNER_PUSH: bytes of this rank's receive slots (two parities x W sources x one local
+ * output in the transport dtype, each padded to 128 bytes). */
 size_t cake_matmul_rs_slot_bytes(const cake_matmul_rs* plan);
-size_t cake_matmul_rs_flag_bytes(const cake_matmul_rs* plan);
 
-/* CAKE_RS_P2P_OWNER_PUSH: slot and counter buffers of every rank (entry [rank] is this rank's own
- * allocation, the others are IPC mappings). Must be called once before the first enqueue. */
-int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void* const* flags);
+/* CAKE_RS_P2P_OWNER_PUSH: the slot buffer of every rank (entry [rank] is this rank's own allocation
+ * of cake_matmul_rs_slot_bytes, 128-byte aligned; the others are IPC mappings). Called once before
+ * the first enqueue. It fills this rank's own slots with the "nothing has arrived" pattern (all
+ * ones) and synchronises the device, so the host must pass a barrier over all ranks between this
+ * call and the first enqueue: a peer that started earlier would have its data overwritten.
+ *
+ * Protocol. Arrival is detected in the data: the reduction polls each 16-byte piece of a slot until
+ * none of its elements is the pattern (0xFFFF per bf16, 0xFFFFFFFF per f32 -- NaNs the pushing side
+ * replaces by the default NaN before it sends), and writes the pattern back when it has consumed the
+ * piece. Call e uses the slots of parity e & 1, so a rank may run one call ahead of a slower peer.
+ * If a reduction runs out of its wait budget (CAKE_ERR_TIMEOUT from cake_matmul_rs_status, code 2,
+ * detail1 = the source rank that was missing), pieces consumed before that are gone: destroy and
+ * re-create the plans of every rank. The one exception is a peer that had not pushed anything yet:
+ * nothing was consumed, and cake_matmul_rs_enqueue_reduce may be called again once it has. */
+int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots);
 
 /* lhs: bf16 [m, k_local]; rhs: bf16 per rhs_layout; out: world == 1 or P2P: the reduced local
  * output [m/W, n] or [m, n/W] in out_dtype; LOCAL_PARTIAL with world > 1: the owner-major partial
@@ -118,10 +131,11 @@ int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void
 int32_t cake_matmul_rs_enqueue(cake_matmul_rs* plan, const void* lhs, const void* rhs, void* out,
                                void* stream);
 
-/* CAKE_RS_P2P_OWNER_PUSH only: the two halves of cake_matmul_rs_enqueue as separate calls, so a
- * host that drives several mesh positions in one process (a test that emulates W ranks on one GPU,
- * a single-process multi-GPU driver) can enqueue every position's push before any reduction and
- * never has one launch wait on a later one. */
+/* CAKE_RS_P2P_OWNER_PUSH only: the two halves of cake_matmul_rs_enqueue as separate kernels (the
+ * contraction without its reduction warps, and cake_reduce_slots_sm100), so a host that drives
+ * several mesh positions in one process (a test that emulates W ranks on one GPU, a single-process
+ * multi-GPU driver) can enqueue every position's push before any reduction and never has one launch
+ * wait on a later one. */
 int32_t cake_matmul_rs_enqueue_push(cake_matmul_rs* plan, const void* lhs, const void* rhs,
                                     void* stream);
 int32_t cake_matmul_rs_enqueue_reduce(cake_matmul_rs* plan, void* out, void* stream);

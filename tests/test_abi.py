@@ -59,7 +59,7 @@ def test_struct_layouts_match_header():
 def test_matmul_create_rejects_bad_descriptors(overrides, code, fragment):
     lib = _native.load()
     fields = dict(m=128, n=256, k_local=64, world=1, rank=0, scatter_dim=1, out_dtype=0, transport_dtype=0,
-                  strategy=0, tile_m=128, tile_n=128, rhs_layout=0, reserved=0)
+                  strategy=0, tile_m=128, tile_n=128, rhs_layout=0, wait_budget_ms=0)
     fields.update(overrides)
     desc = _native.MatmulRsDesc(**fields)
     handle = ctypes.c_void_p()

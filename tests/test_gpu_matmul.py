@@ -96,7 +96,7 @@ def _emulated_ranks(lhs, rhs, world, device, *, scatter_dimension, transport, ou
             m=m, n=n, k_local=k // world, world=world, rank=rank, scatter_dim=scatter_dimension,
             out_dtype=_native.CAKE_DTYPE_F32 if output_dtype == "f32" else _native.CAKE_DTYPE_BF16,
             transport_dtype=_native.CAKE_DTYPE_F32 if transport == "f32" else _native.CAKE_DTYPE_BF16,
-            strategy=strategy, tile_m=128, tile_n=tile_n, rhs_layout=0, reserved=0,
+            strategy=strategy, tile_m=128, tile_n=tile_n, rhs_layout=0, wait_budget_ms=0,
         )
         handle = ctypes.c_void_p()
         _native.check(lib.cake_matmul_rs_create(ctypes.byref(desc), ctypes.byref(handle)))
@@ -109,29 +109,35 @@ def _emulated_ranks(lhs, rhs, world, device, *, scatter_dimension, transport, ou
     results = []
     try:
         if strategy == _native.CAKE_RS_P2P_OWNER_PUSH:
-            slots, flags = [], []
+            slots = []
             for handle in handles:
-                slot, flag = ctypes.c_void_p(), ctypes.c_void_p()
+                slot = ctypes.c_void_p()
                 _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_slot_bytes(handle), ctypes.byref(slot)))
-                _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_flag_bytes(handle), ctypes.byref(flag)))
                 slots.append(slot.value)
-                flags.append(flag.value)
             array = ctypes.c_void_p * world
             for handle in handles:
-                _native.check(lib.cake_matmul_rs_bind_peers(handle, array(*slots), array(*flags)))
-            for repeat in range(3):  # exercises both slot parities and the monotonic counters
+                _native.check(lib.cake_matmul_rs_bind_peers(handle, array(*slots)))
+            for repeat in range(4):  # exercises both slot parities and the restored "not arrived" pattern
                 outs = [torch.full((out_rows, out_cols), float("nan"), dtype=torch_out, device=device) for _ in range(world)]
-                for handle, (lhs_d, rhs_d) in zip(handles, operands):
-                    _native.check(lib.cake_matmul_rs_enqueue_push(handle, lhs_d.data_ptr(), rhs_d.data_ptr(), stream))
-                for handle, out in zip(handles, outs):
-                    _native.check(lib.cake_matmul_rs_enqueue_reduce(handle, out.data_ptr(), stream))
+                # On odd repeats the last position runs the one-kernel form (its reduction warps
+                # work while its own contraction still pushes): by then every other position has
+                # pushed, so that launch too waits on nothing that is enqueued after it.
+                fused_last = repeat % 2 == 1
+                for rank, (handle, (lhs_d, rhs_d)) in enumerate(zip(handles, operands)):
+                    if fused_last and rank == world - 1:
+                        _native.check(lib.cake_matmul_rs_enqueue(handle, lhs_d.data_ptr(), rhs_d.data_ptr(), outs[rank].data_ptr(), stream))
+                    else:
+                        _native.check(lib.cake_matmul_rs_enqueue_push(handle, lhs_d.data_ptr(), rhs_d.data_ptr(), stream))
+                for rank, (handle, out) in enumerate(zip(handles, outs)):
+                    if not (fused_last and rank == world - 1):
+                        _native.check(lib.cake_matmul_rs_enqueue_reduce(handle, out.data_ptr(), stream))
                 torch.cuda.synchronize(device)
                 results.append([out.float().cpu().numpy() for out in outs])
             for handle in handles:
                 word = _native.CakeStatus()
                 _native.check(lib.cake_matmul_rs_status(handle, stream, ctypes.byref(word)))
                 assert word.code == 0
-            for pointer in slots + flags:
+            for pointer in slots:
                 lib.cake_symm_free(pointer)
         else:
             tdtype = torch.float32 if transport == "f32" else torch.bfloat16
@@ -179,6 +185,97 @@ def test_p2p_owner_push_all_ranks_on_one_gpu(cuda_device, scatter_dimension, tra
     for later in runs[1:]:
         for rank in range(world):
             np.testing.assert_array_equal(later[rank], runs[0][rank])
+
+
+@pytest.mark.parametrize("shape, world, scatter_dimension, transport", [
+    ((3, 16, 8), 2, 1, "bf16"),     # local output 3 x 4 bf16: 24 bytes per source, nothing 16-byte aligned
+    ((5, 16, 24), 2, 1, "f32"),     # 5 x 12 f32: whole pieces but rows not in groups of 8
+    ((96, 96, 40), 3, 0, "bf16"),   # a mesh size the vector reduction does not cover
+    ((256, 192, 520), 4, 0, "f32"), # rows aligned, 520 columns: vector pieces, ragged last chunk
+    ((384, 128, 768), 2, 1, "bf16"),
+])
+def test_p2p_owner_push_odd_shapes(cuda_device, shape, world, scatter_dimension, transport):
+    """Shapes whose local output is not a whole number of 16-byte pieces, 128-byte chunks or
+    128-row tiles go through the element-wise push and reduction; all must match the oracle."""
+    m, k, n = shape
+    generator = np.random.default_rng(m * 131 + n)
+    lhs = generator.normal(size=(m, k)).astype(np.float32).astype(BF16)
+    rhs = generator.normal(size=(k, n)).astype(np.float32).astype(BF16)
+    expected = oracle.matmul_reduce_scatter(lhs.astype(np.float32), rhs.astype(np.float32), world=world,
+                                            scatter_dimension=scatter_dimension, transport_dtype=transport, out_dtype="f32")
+    runs = _emulated_ranks(lhs, rhs, world, cuda_device, scatter_dimension=scatter_dimension, transport=transport,
+                           output_dtype="f32", strategy=_native.CAKE_RS_P2P_OWNER_PUSH, tile_n=128)
+    for outputs in runs:
+        for rank in range(world):
+            if transport == "f32":
+                assert np.allclose(outputs[rank], expected[rank], atol=1e-3, rtol=1e-3)
+            else:
+                assert oracle.relative_l2_error(outputs[rank], expected[rank]) < 4e-3
+    for later in runs[1:]:
+        for rank in range(world):
+            np.testing.assert_array_equal(later[rank], runs[0][rank])
+
+
+def test_reduction_gives_up_when_a_peer_never_pushes(cuda_device):
+    """Two mesh positions on one GPU, a wait budget of 5 ms, and position 1 does not push: position
+    0's reduction must give up (CAKE_ERR_TIMEOUT, code 2, missing source 1) without touching its
+    output -- the wait runs out and the kernel returns, nothing faults or hangs. Position 1 then
+    pushes late; since nothing had been consumed, enqueueing the reduction again completes the step."""
+    lib = _native.load()
+    world, m, k, n = 2, 256, 512, 512
+    lhs, rhs = workloads.distributed_matmul_inputs(world, m, k, n)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    handles, operands, slots = [], [], []
+    for rank in range(world):
+        desc = _native.MatmulRsDesc(m=m, n=n, k_local=k // world, world=world, rank=rank, scatter_dim=0, out_dtype=_native.CAKE_DTYPE_F32,
+                                    transport_dtype=_native.CAKE_DTYPE_F32, strategy=_native.CAKE_RS_P2P_OWNER_PUSH, tile_m=128, tile_n=256,
+                                    rhs_layout=0, wait_budget_ms=5)
+        handle = ctypes.c_void_p()
+        _native.check(lib.cake_matmul_rs_create(ctypes.byref(desc), ctypes.byref(handle)))
+        handles.append(handle)
+        lhs_r, rhs_r = workloads.shard_matmul_inputs(lhs, rhs, world, rank)
+        operands.append((bf16_to_torch(lhs_r, cuda_device), bf16_to_torch(rhs_r, cuda_device)))
+        slot = ctypes.c_void_p()
+        _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_slot_bytes(handle), ctypes.byref(slot)))
+        slots.append(slot.value)
+    try:
+        array = ctypes.c_void_p * world
+        for handle in handles:
+            _native.check(lib.cake_matmul_rs_bind_peers(handle, array(*slots)))
+        outs = [torch.full((m // world, n), float("nan"), dtype=torch.float32, device=cuda_device) for _ in range(world)]
+        _native.check(lib.cake_matmul_rs_enqueue_push(handles[0], operands[0][0].data_ptr(), operands[0][1].data_ptr(), stream))
+        _native.check(lib.cake_matmul_rs_enqueue_reduce(handles[0], outs[0].data_ptr(), stream))
+        word = _native.CakeStatus()
+        code = lib.cake_matmul_rs_status(handles[0], stream, ctypes.byref(word))
+        assert code == _native.CAKE_ERR_TIMEOUT
+        assert word.code == 2 and word.detail1 == 1
+        assert bool(torch.isnan(outs[0]).all())
+        # The late peer arrives; both reductions now complete.
+        _native.check(lib.cake_matmul_rs_enqueue_push(handles[1], operands[1][0].data_ptr(), operands[1][1].data_ptr(), stream))
+        for handle, out in zip(handles, outs):
+            _native.check(lib.cake_matmul_rs_enqueue_reduce(handle, out.data_ptr(), stream))
+        for handle in handles:
+            _native.check(lib.cake_matmul_rs_status(handle, stream, ctypes.byref(word)))
+            assert word.code == 0
+        expected = oracle.matmul_reduce_scatter(lhs.astype(np.float32), rhs.astype(np.float32), world=world, scatter_dimension=0)
+        for rank in range(world):
+            assert np.allclose(outs[rank].cpu().numpy(), expected[rank], atol=1e-3, rtol=1e-3)
+        # And the next call, on the other slot parity, is an ordinary one.
+        for handle, (lhs_d, rhs_d) in zip(handles, operands):
+            _native.check(lib.cake_matmul_rs_enqueue_push(handle, lhs_d.data_ptr(), rhs_d.data_ptr(), stream))
+        for handle, out in zip(handles, outs):
+            out.fill_(float("nan"))
+            _native.check(lib.cake_matmul_rs_enqueue_reduce(handle, out.data_ptr(), stream))
+        for handle in handles:
+            _native.check(lib.cake_matmul_rs_status(handle, stream, ctypes.byref(word)))
+            assert word.code == 0
+        for rank in range(world):
+            assert np.allclose(outs[rank].cpu().numpy(), expected[rank], atol=1e-3, rtol=1e-3)
+    finally:
+        for handle in handles:
+            lib.cake_matmul_rs_destroy(handle)
+        for pointer in slots:
+            lib.cake_symm_free(pointer)
 
 
 @pytest.mark.parametrize("world, scatter_dimension, tile_n", [(2, 0, 256), (4, 1, 64), (8, 1, 128)])

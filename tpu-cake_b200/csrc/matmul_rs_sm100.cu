@@ -4,16 +4,25 @@
 // launched :429-444) and the collective that follows it (lax.psum_scatter :459-464, or the
 // bidirectional Pallas ring :117-326). The reference materialises the f32 partial [M,N] in HBM
 // between the two; here the epilogue of the contraction writes every partial tile straight to the
-// GPU that owns it, and a second small kernel sums the W received copies in rank order.
+// GPU that owns it, and four more warps of the same kernel sum the W received copies in rank order
+// while the contraction is still running.
 //
 // cake_matmul_rs_sm100<BN, B_KMAJOR>: persistent, warp-specialised.
 //   warp 0    TMA producer: A tile 128x64 and B tile 64xBN (bf16) per stage into 128B-swizzled smem
 //   warp 1    owns TMEM; one lane issues tcgen05.mma (M=128, N=BN, K=16), f32 accumulators in TMEM,
 //             two accumulator buffers so the epilogue of tile i overlaps the main loop of tile i+1
 //   warps 2-5 epilogue: tcgen05.ld -> convert -> swizzled smem staging -> 128-byte row segments to
-//             the owner's memory (local or peer), then a release-add on the owner's arrival counter
-// cake_reduce_slots_sm100: waits (bounded) for the W arrival counters, then out = sum over source
-//   ranks in fixed order (deterministic), cast to the output dtype.
+//             the owner's receive slot (local or peer memory)
+//   warps 6-9 slot reduction (peer-to-peer strategy): walk this rank's receive slots in the order
+//             the peers fill them, out = sum over source ranks in fixed order (deterministic)
+//
+// Arrival is detected in the data itself. A receive slot holds an all-ones pattern (a NaN that the
+// epilogue never sends: 0xFFFF per bf16, 0xFFFFFFFF per f32) wherever nothing has arrived; the
+// reduction polls each 16-byte piece until no element of it is the pattern, and writes the pattern
+// back once it has consumed the piece. The pushing side therefore needs no fence, counter or flag:
+// a tile's stores are fire-and-forget, and the link never drains for a publication.
+// cake_reduce_slots_sm100 is the same reduction as a kernel of its own, for hosts that enqueue
+// the pushes of several mesh positions on one GPU before any reduction.
 #include <cuda_bf16.h>
 #include <stdlib.h>
 #include <string.h>
@@ -28,7 +37,8 @@ namespace cake {
 constexpr int kTileM = 128;
 constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // producer, issuer, 4 epilogue warps, 4 reduction warps
+constexpr int kReduceWarps = 4;
 constexpr uint32_t kABytes = kTileM * kBlockK * 2;
 // Chunks (32 rows x 128 bytes) an epilogue warp can have staged for stores still reading shared
 // memory, and the depth of the 256-wide configuration's operand ring: the two compete for the
@@ -42,7 +52,8 @@ constexpr uint32_t kABytes = kTileM * kBlockK * 2;
 constexpr int kStagingChunks = CAKE_MM_STAGING_CHUNKS;
 constexpr uint32_t kStagingBytesPerWarp = kStagingChunks * 32 * 128;
 constexpr long long kBarrierBudgetCycles = 4000000000ll;  // about two seconds of SM clock
-constexpr unsigned long long kPeerBudgetNs = 20000000000ull;  // 20 s
+constexpr unsigned long long kDefaultPeerBudgetMs = 20000ull;  // 20 s unless the descriptor says otherwise
+constexpr uint32_t kNotArrived = 0xFFFFFFFFu;  // 32 bits of the receive slots' "nothing here yet" pattern
 
 template <int BN>
 struct GemmCfg {
@@ -54,6 +65,20 @@ struct GemmCfg {
       kStages * kStageBytes + 4 * kStagingBytesPerWarp + 256 /*barriers*/ + 1024 /*alignment*/;
 };
 
+// What the slot reduction needs: this rank's receive slots of the current parity (source s at
+// slots + s * slot_stride, each a [out_rows, out_cols] array in the transport dtype) and the output.
+struct ReduceParams {
+  const char* slots;
+  void* out;
+  unsigned long long slot_stride;  // bytes, a multiple of 128
+  unsigned long long budget_ns;    // how long a piece may stay "not arrived" before the reduction gives up
+  int32_t out_rows, out_cols, world;
+  int32_t in_f32, out_f32;  // transport / output element type: 1 = f32, 0 = bf16
+  int32_t vec_ok;           // rows are whole 16-byte pieces in both the transport and the output dtype
+  int32_t tile_n;           // the pushing side's tile width (sets the order the slots fill in)
+  int32_t* status;
+};
+
 struct MatmulParams {
   int32_t m, n, k_local;
   int32_t m_tiles, n_tiles, k_blocks;
@@ -61,11 +86,13 @@ struct MatmulParams {
   int32_t out_rows, out_cols;  // shape of one owner's local output
   int32_t store_f32;           // destination element type: 1 = f32, 0 = bf16
   int32_t vec_ok;              // 16-byte pieces never straddle owners or bounds
-  int32_t count_arrivals;      // peer-to-peer strategy: signal the owner's counter per tile
+  int32_t to_slots;            // destinations are receive slots: never send the "not arrived" pattern
   int32_t tma_store;           // epilogue chunks leave shared memory as TMA tensor stores
   int32_t region_order;        // consecutive tiles go to consecutive owners, starting at rank+1
+  int32_t owner_rotation;      // tile groups after which the owner sequence shifts by one
+  int32_t reduce_in_kernel;    // warps 6-9 run the slot reduction
   void* dest[CAKE_MAX_WORLD];  // per-owner base of the [out_rows, out_cols] destination
-  unsigned long long* arrive[CAKE_MAX_WORLD];  // per-owner counter written by this rank
+  ReduceParams red;
   int32_t* status;
 };
 
@@ -103,23 +130,27 @@ __device__ __forceinline__ void raster(int t, int mt_count, int nt_count, int& m
   ni = r / gm;
 }
 
+// Tile t of this rank's walk. With region_order, W consecutive tiles are the same tile of the W
+// owners' regions, so every owner's region fills front to back at the pace of the whole kernel and
+// link traffic is spread over all destination ports. Which owner comes first shifts by one every
+// `owner_rotation` groups: a CTA's stride through the tile list (the grid size) would otherwise
+// give it the same one or two owners for the whole kernel, and the CTAs that never meet their own
+// (link-free) tiles would finish last.
 template <int BN>
 __device__ __forceinline__ void tile_coords(const MatmulParams& p, int t, int& mt, int& nt) {
   if (p.region_order) {
+    const int group = t / p.world;
+    const int j = (t - group * p.world + group / p.owner_rotation) % p.world;
+    const int owner = (p.rank + 1 + j) % p.world;
+    int mi, ni;
     if (p.scatter_dim == 0) {
       const int m_tiles_r = p.out_rows / kTileM;
-      const int j = t % p.world;
-      const int owner = (p.rank + 1 + j) % p.world;
-      int mi, ni;
-      raster(t / p.world, m_tiles_r, p.n_tiles, mi, ni);
+      raster(group, m_tiles_r, p.n_tiles, mi, ni);
       mt = owner * m_tiles_r + mi;
       nt = ni;
     } else {
       const int n_tiles_r = p.out_cols / BN;
-      const int j = t % p.world;
-      const int owner = (p.rank + 1 + j) % p.world;
-      int mi, ni;
-      raster(t / p.world, p.m_tiles, n_tiles_r, mi, ni);
+      raster(group, p.m_tiles, n_tiles_r, mi, ni);
       mt = mi;
       nt = owner * n_tiles_r + ni;
     }
@@ -144,6 +175,210 @@ __device__ __forceinline__ char* dest_addr(const MatmulParams& p, int r, int c, 
          (static_cast<size_t>(lr) * p.out_cols + lc) * static_cast<size_t>(elem_bytes);
 }
 
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// ------------------------------------------------------------------------------ slot reduction
+//
+// A receive slot is filled by remote (or local) stores that no flag announces: a piece is there
+// when none of its elements is the all-ones pattern any more. Loads go to L2 (volatile), where
+// peer writes land.
+
+// Both are volatile asm without a memory clobber: they keep their order among themselves (a piece
+// is overwritten only after it has been read) and leave the compiler free to keep everything else
+// in registers.
+__device__ __forceinline__ uint4 ld_slot_v4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr));
+  return v;
+}
+
+__device__ __forceinline__ void st_slot_not_arrived_v4(void* ptr) {
+  asm volatile("st.global.v4.u32 [%0], {%1, %1, %1, %1};" ::"l"(ptr), "r"(kNotArrived));
+}
+
+// Non-zero when at least one element of the piece is still the "not arrived" pattern.
+template <bool IN_F32>
+__device__ __forceinline__ uint32_t piece_missing(const uint4& v) {
+  if (IN_F32) return max(max(v.x, v.y), max(v.z, v.w)) == kNotArrived ? 1u : 0u;
+  return __vcmpeq2(v.x, kNotArrived) | __vcmpeq2(v.y, kNotArrived) | __vcmpeq2(v.z, kNotArrived) |
+         __vcmpeq2(v.w, kNotArrived);
+}
+
+// One chunk = 32 rows x 128 bytes of the transport dtype (what one epilogue tensor store carries).
+// Lane l owns the 16-byte piece (l & 7) of rows (l >> 3) + 4 i. Two rows are in flight at a time:
+// the loads of every source are issued before any is looked at, the sum runs in rank order, and a
+// consumed piece is overwritten with the pattern so that the slot is ready for its next use.
+// The caller guarantees out_rows % 8 == 0, so the two rows of a step are inside the output together.
+// Returns false when a piece stayed "not arrived" for longer than the budget.
+template <bool IN_F32, int W>
+__device__ __forceinline__ bool reduce_chunk_vec(const ReduceParams& r, int row0, int col0, int lane,
+                                                 unsigned long long start, int item) {
+  constexpr int EPP = IN_F32 ? 4 : 8;  // elements per 16-byte piece
+  constexpr int TS = IN_F32 ? 4 : 2;
+  const int col = col0 + (lane & 7) * EPP;
+  if (col >= r.out_cols) return true;
+#pragma unroll 1
+  for (int i = 0; i < 8; i += 2) {
+    const int row_a = row0 + i * 4 + (lane >> 3);
+    if (row_a >= r.out_rows) break;
+    const size_t offset[2] = {static_cast<size_t>(row_a) * r.out_cols + col,
+                              static_cast<size_t>(row_a + 4) * r.out_cols + col};
+    uint4 raw[2][W];
+    while (true) {
+      uint32_t missing_any = 0;
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int src = 0; src < W; ++src) raw[u][src] = ld_slot_v4(r.slots + src * r.slot_stride + offset[u] * TS);
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int src = 0; src < W; ++src) missing_any |= piece_missing<IN_F32>(raw[u][src]);
+      if (missing_any == 0) break;
+      if (global_timer_ns() - start > r.budget_ns) {
+        // Name the first source whose piece is missing.
+        int missing = 0;
+#pragma unroll
+        for (int u = 1; u >= 0; --u)
+#pragma unroll
+          for (int src = W - 1; src >= 0; --src)
+            if (piece_missing<IN_F32>(raw[u][src]) != 0) missing = src;
+        record_status(r.status, 2, blockIdx.x, missing, item);
+        return false;
+      }
+      __nanosleep(100);
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      float acc[EPP];
+#pragma unroll
+      for (int e = 0; e < EPP; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (int src = 0; src < W; ++src) {
+        const uint4 v = raw[u][src];
+        if (IN_F32) {
+          acc[0] += __uint_as_float(v.x);
+          acc[1] += __uint_as_float(v.y);
+          acc[2] += __uint_as_float(v.z);
+          acc[3] += __uint_as_float(v.w);
+        } else {
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] += __uint_as_float(w[e] << 16);
+            acc[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+          }
+        }
+      }
+      if (r.out_f32) {
+        float* dst = static_cast<float*>(r.out) + offset[u];
+#pragma unroll
+        for (int e = 0; e < EPP; e += 4)
+          *reinterpret_cast<float4*>(dst + e) = make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
+      } else if (EPP == 8) {
+        uint4 packed;
+        packed.x = pack2_bf16(acc[0], acc[1]);
+        packed.y = pack2_bf16(acc[2], acc[3]);
+        packed.z = pack2_bf16(acc[4], acc[5]);
+        packed.w = pack2_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(r.out) + offset[u]) = packed;
+      } else {
+        uint2 packed;
+        packed.x = pack2_bf16(acc[0], acc[1]);
+        packed.y = pack2_bf16(acc[2], acc[3]);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(r.out) + offset[u]) = packed;
+      }
+#pragma unroll
+      for (int src = 0; src < W; ++src)
+        st_slot_not_arrived_v4(const_cast<char*>(r.slots) + src * r.slot_stride + offset[u] * TS);
+    }
+  }
+  return true;
+}
+
+template <bool IN_F32>
+__device__ __forceinline__ bool reduce_chunk_vec_world(const ReduceParams& r, int row0, int col0, int lane,
+                                                       unsigned long long start, int item) {
+  if (r.world == 8) return reduce_chunk_vec<IN_F32, 8>(r, row0, col0, lane, start, item);
+  if (r.world == 4) return reduce_chunk_vec<IN_F32, 4>(r, row0, col0, lane, start, item);
+  return reduce_chunk_vec<IN_F32, 2>(r, row0, col0, lane, start, item);
+}
+
+// The same chunk element by element, for shapes whose rows are not whole 16-byte pieces.
+__device__ __forceinline__ bool reduce_chunk_scalar(const ReduceParams& r, int row0, int col0, int lane,
+                                                    unsigned long long start, int item) {
+  const int ts = r.in_f32 ? 4 : 2;
+  const int cols_per_chunk = 128 / ts;
+  for (int idx = lane; idx < 32 * cols_per_chunk; idx += 32) {
+    const int row = row0 + idx / cols_per_chunk;
+    const int col = col0 + idx % cols_per_chunk;
+    if (row >= r.out_rows || col >= r.out_cols) continue;
+    const size_t offset = static_cast<size_t>(row) * r.out_cols + col;
+    float acc = 0.f;
+    for (int src = 0; src < r.world; ++src) {
+      const char* piece = r.slots + src * r.slot_stride + offset * ts;
+      uint32_t v;
+      while (true) {
+        v = r.in_f32 ? *reinterpret_cast<const volatile uint32_t*>(piece)
+                     : static_cast<uint32_t>(*reinterpret_cast<const volatile uint16_t*>(piece));
+        if (v != (r.in_f32 ? kNotArrived : 0xFFFFu)) break;
+        if (global_timer_ns() - start > r.budget_ns) {
+          record_status(r.status, 2, blockIdx.x, src, item);
+          return false;
+        }
+        __nanosleep(64);
+      }
+      acc += __uint_as_float(r.in_f32 ? v : v << 16);
+    }
+    for (int src = 0; src < r.world; ++src) {
+      char* piece = const_cast<char*>(r.slots) + src * r.slot_stride + offset * ts;
+      if (r.in_f32) *reinterpret_cast<volatile uint32_t*>(piece) = kNotArrived;
+      else *reinterpret_cast<volatile uint16_t*>(piece) = 0xFFFFu;
+    }
+    if (r.out_f32) static_cast<float*>(r.out)[offset] = acc;
+    else static_cast<__nv_bfloat16*>(r.out)[offset] = __float2bfloat16_rn(acc);
+  }
+  return true;
+}
+
+// One reduction worker (a warp) of `workers`: chunks are numbered in the order the pushing side
+// produces them -- tiles of 128 x tile_n in the raster order of tile_coords, then the four 32-row
+// quarters, then the 128-byte column chunks -- and dealt round-robin, so every worker has work
+// from the first tile to the last and the chunks still missing when the peers finish are spread
+// over all workers.
+__device__ __forceinline__ void reduce_worker(const ReduceParams& r, int worker, int workers, int lane) {
+  const int cols_per_chunk = r.in_f32 ? 32 : 64;
+  const int chunks_per_quarter = r.tile_n / cols_per_chunk;
+  const int m_tiles = (r.out_rows + kTileM - 1) / kTileM;
+  const int n_tiles = (r.out_cols + r.tile_n - 1) / r.tile_n;
+  const int items = m_tiles * n_tiles * 4 * chunks_per_quarter;
+  const unsigned long long start = global_timer_ns();
+  for (int item = worker; item < items; item += workers) {
+    const int tile = item / (4 * chunks_per_quarter);
+    const int rest = item - tile * 4 * chunks_per_quarter;
+    int mi, ni;
+    raster(tile, m_tiles, n_tiles, mi, ni);
+    const int row0 = mi * kTileM + (rest / chunks_per_quarter) * 32;
+    const int col0 = ni * r.tile_n + (rest % chunks_per_quarter) * cols_per_chunk;
+    if (row0 >= r.out_rows || col0 >= r.out_cols) continue;
+    bool ok;
+    if (!r.vec_ok) ok = reduce_chunk_scalar(r, row0, col0, lane, start, item);
+    else if (r.in_f32) ok = reduce_chunk_vec_world<true>(r, row0, col0, lane, start, item);
+    else ok = reduce_chunk_vec_world<false>(r, row0, col0, lane, start, item);
+    if (!ok) return;
+  }
+}
+
+// The slot reduction as a kernel of its own (8 workers per block).
+__global__ void __launch_bounds__(256) cake_reduce_slots_sm100(const __grid_constant__ ReduceParams r) {
+  reduce_worker(r, blockIdx.x * 8 + (threadIdx.x >> 5), gridDim.x * 8, threadIdx.x & 31);
+}
+
 // One tensor map per owner: its [out_rows, out_cols] destination (own output, owner-major partial or
 // a peer's receive slot), boxes of 32 rows x 128 bytes, 128-byte swizzle.
 struct OwnerMaps {
@@ -154,7 +389,8 @@ template <int BN, bool B_KMAJOR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     cake_matmul_rs_sm100(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ OwnerMaps owner_maps, const MatmulParams p) {
+                         const __grid_constant__ OwnerMaps owner_maps,
+                         const __grid_constant__ MatmulParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
 
@@ -296,14 +532,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tcgen05_commit(smem_u32(drain_bar));
       mbar_wait_bounded(smem_u32(drain_bar), 0, kBarrierBudgetCycles);
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue warps 2..5
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint8_t* my_stage_base = staging + (warp - 2) * kStagingBytesPerWarp;
     int chunk_count = 0;  // chunks this warp has staged so far (selects the staging half)
-    unsigned long long sent[CAKE_MAX_WORLD];  // lane 0: elements pushed to each owner so far
-#pragma unroll
-    for (int o = 0; o < CAKE_MAX_WORLD; ++o) sent[o] = 0;
     const int elem_bytes = p.store_f32 ? 4 : 2;
     const int cols_per_chunk = p.store_f32 ? 32 : 64;  // 128 bytes per row per chunk
     const int epp = 16 / elem_bytes;                   // elements per 16-byte piece
@@ -331,6 +564,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_row + ch * 32, v);
           tmem_ld_wait();
+          if (p.to_slots) {
+            // A receive slot reads all-ones as "not arrived": send the default NaN instead.
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = v[j] == kNotArrived ? 0x7FFFFFFFu : v[j];
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             pieces[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -348,6 +586,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]),
                                                                 __uint_as_float(v[8 * j + 2 * e + 1]));
                 w[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                // Same rule per bf16 half: 0xFFFF (a NaN) goes out as 0x7FFF.
+                if (p.to_slots) w[e] &= ~(__vcmpeq2(w[e], kNotArrived) & 0x80008000u);
               }
               pieces[h * 4 + j] = make_uint4(w[0], w[1], w[2], w[3]);
             }
@@ -423,143 +663,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         __syncwarp();
       }
-      if (p.count_arrivals && lane == 0) {
-        // Tally what this warp has sent to each owner; the owners are told once, after the last
-        // tile (a system-scope fence per tile would stall the pushes behind a link round trip).
-        const int r_lo = row0, r_hi = min(row0 + 32, p.m);
-        const int c_lo = nt * BN, c_hi = min(c_lo + BN, p.n);
-        if (r_hi > r_lo && c_hi > c_lo) {
-          if (p.scatter_dim == 0) {
-            for (int o = r_lo / p.out_rows; o <= (r_hi - 1) / p.out_rows; ++o) {
-              const int rows = min(r_hi, (o + 1) * p.out_rows) - max(r_lo, o * p.out_rows);
-              sent[o] += static_cast<unsigned long long>(rows) * (c_hi - c_lo);
-            }
-          } else {
-            for (int o = c_lo / p.out_cols; o <= (c_hi - 1) / p.out_cols; ++o) {
-              const int cols = min(c_hi, (o + 1) * p.out_cols) - max(c_lo, o * p.out_cols);
-              sent[o] += static_cast<unsigned long long>(cols) * (r_hi - r_lo);
-            }
-          }
-        }
-      }
     }
-    if (p.count_arrivals) {
-      // Publish: every store of this warp has been performed (tensor stores: group complete; plain
-      // stores: ordered by the warp sync), one system-scope fence, then one release-add per owner.
-      // Each epilogue warp publishes for itself: no CTA-wide barrier, so a warp that has given up
-      // on a wait can never leave the others stuck at one.
-      __syncwarp();
-      if (lane == 0) {
-        if (p.tma_store) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-        __threadfence_system();
-        for (int o = 0; o < p.world; ++o)
-          if (sent[o] != 0) red_release_sys_add_u64(p.arrive[o], sent[o]);
-      }
-    }
+  } else if (p.reduce_in_kernel) {
+    // ------------------------------------------------------------------ slot reduction warps 6..9
+    reduce_worker(p.red, blockIdx.x * kReduceWarps + (warp - 6), gridDim.x * kReduceWarps, lane);
   }
 
   // Shared memory must outlive every tensor store that still reads it.
-  if (p.tma_store && warp >= 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (p.tma_store && warp >= 2 && warp < 6 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
-}
-
-__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-// out[i] = sum over source ranks (fixed order) of slot[src][i]; waits for every source's arrival
-// counter to reach `expected` first. The wait is bounded; on expiry nothing is written and the
-// status word records which source was late.
-template <typename TIn, typename TOut>
-__global__ void __launch_bounds__(256)
-    cake_reduce_slots_sm100(const TIn* __restrict__ slots, TOut* __restrict__ out, size_t elems,
-                            int world, const unsigned long long* arrive,
-                            unsigned long long expected, int32_t* status) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) {
-    int ok = 1;
-    const unsigned long long start = global_timer_ns();
-    for (int src = 0; src < world && ok; ++src) {
-      while (ld_acquire_sys_u64(arrive + src) < expected) {
-        if (global_timer_ns() - start > kPeerBudgetNs) {
-          record_status(status, 2, blockIdx.x, src, 0);
-          ok = 0;
-          break;
-        }
-        __nanosleep(200);
-      }
-    }
-    s_ok = ok;
-  }
-  __syncthreads();
-  if (!s_ok) return;
-  constexpr int V = 16 / sizeof(TIn);  // elements per 16-byte load
-  const size_t groups = elems / V;
-  for (size_t g = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; g < groups;
-       g += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float acc[V];
-#pragma unroll
-    for (int e = 0; e < V; ++e) acc[e] = 0.f;
-    // All sources' loads are issued before any is used (independent, so they overlap); the sum
-    // itself runs in rank order.
-    uint4 raw_all[CAKE_MAX_WORLD];
-#pragma unroll
-    for (int src = 0; src < CAKE_MAX_WORLD; ++src)
-      if (src < world) raw_all[src] = __ldcg(reinterpret_cast<const uint4*>(slots + src * elems) + g);
-#pragma unroll
-    for (int src = 0; src < CAKE_MAX_WORLD; ++src) {
-      if (src >= world) break;
-      const uint4 raw = raw_all[src];
-      if (sizeof(TIn) == 4) {
-        acc[0] += __uint_as_float(raw.x);
-        acc[1] += __uint_as_float(raw.y);
-        acc[2] += __uint_as_float(raw.z);
-        acc[3] += __uint_as_float(raw.w);
-      } else {
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc[2 * e] += __uint_as_float(w[e] << 16);
-          acc[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
-        }
-      }
-    }
-    if (sizeof(TOut) == 4) {
-#pragma unroll
-      for (int e = 0; e < V; e += 4)
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + g * V + e) =
-            make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
-    } else if (V == 8) {
-      uint4 packed;
-      packed.x = pack2_bf16(acc[0], acc[1]);
-      packed.y = pack2_bf16(acc[2], acc[3]);
-      packed.z = pack2_bf16(acc[4], acc[5]);
-      packed.w = pack2_bf16(acc[6], acc[7]);
-      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + g * V) = packed;
-    } else {
-      uint2 packed;
-      packed.x = pack2_bf16(acc[0], acc[1]);
-      packed.y = pack2_bf16(acc[2], acc[3]);
-      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + g * V) = packed;
-    }
-  }
-  // Tail (elems not a multiple of V).
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    for (size_t i = groups * V; i < elems; ++i) {
-      float a = 0.f;
-      for (int src = 0; src < world; ++src) {
-        const TIn v = slots[src * elems + i];
-        a += sizeof(TIn) == 4 ? *reinterpret_cast<const float*>(&v)
-                              : __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&v)) << 16);
-      }
-      if (sizeof(TOut) == 4) reinterpret_cast<float*>(out)[i] = a;
-      else reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(a);
-    }
-  }
 }
 
 // bf16 [rows, cols] -> [cols, rows]; used only when the caller asks the library to consume the
@@ -593,7 +708,7 @@ struct cake_matmul_rs {
   bool rhs_via_transpose = false;
   void* rhs_t = nullptr;  // [n, k_local] scratch when rhs_via_transpose
   void* slots[CAKE_MAX_WORLD] = {};
-  void* flags[CAKE_MAX_WORLD] = {};
+  size_t slot_stride = 0;  // bytes between two sources' slots: one local output, padded to 128 bytes
   bool bound = false;
   unsigned long long epoch = 0;
   cake::StatusWord status;
@@ -618,11 +733,13 @@ template <int BN, bool KM>
 int32_t launch_gemm(const cake_matmul_rs* plan, const cake::MatmulParams& p, int grid,
                     cudaStream_t stream, int maps_index) {
   auto kernel = cake::cake_matmul_rs_sm100<BN, KM>;
-  static bool configured = false;
-  if (!configured) {
+  // The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute.
+  static bool configured[64] = {};
+  const int slot = plan->device >= 0 && plan->device < 64 ? plan->device : 0;
+  if (!configured[slot]) {
     CAKE_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        cake::GemmCfg<BN>::kSmemBytes));
-    configured = true;
+    configured[slot] = plan->device >= 0 && plan->device < 64;
   }
   kernel<<<grid, cake::kGemmThreads, cake::GemmCfg<BN>::kSmemBytes, stream>>>(
       plan->tmap_a, plan->tmap_b, plan->owner_maps[maps_index], p);
@@ -687,6 +804,8 @@ int32_t cake_matmul_rs_create(const cake_matmul_rs_desc* desc, cake_matmul_rs** 
                 (long long)scattered, d.world);
   if (d.world > 1 && d.strategy != CAKE_RS_LOCAL_PARTIAL && d.strategy != CAKE_RS_P2P_OWNER_PUSH)
     return fail(CAKE_ERR_INVALID_ARGUMENT, "unknown reduce-scatter strategy %d", d.strategy);
+  if (d.wait_budget_ms < 0)
+    return fail(CAKE_ERR_INVALID_ARGUMENT, "wait_budget_ms must be >= 0 (0 = default), got %d", d.wait_budget_ms);
 
   cake_matmul_rs* plan = new (std::nothrow) cake_matmul_rs();
   if (!plan) return fail(CAKE_ERR_CUDA, "out of host memory");
@@ -707,6 +826,7 @@ int32_t cake_matmul_rs_create(const cake_matmul_rs_desc* desc, cake_matmul_rs** 
   plan->out_cols = d.scatter_dim == 1 ? d.n / d.world : d.n;
   plan->osize = d.out_dtype == CAKE_DTYPE_F32 ? 4 : 2;
   plan->tsize = d.world == 1 ? plan->osize : (d.transport_dtype == CAKE_DTYPE_F32 ? 4 : 2);
+  plan->slot_stride = (static_cast<size_t>(plan->out_rows) * plan->out_cols * plan->tsize + 127) / 128 * 128;
   const char* env = getenv("CAKE_MATMUL_TRANSPOSE_RHS");
   plan->rhs_via_transpose = d.rhs_layout == 0 && env && env[0] == '1';
   int32_t rc = plan->status.ensure();
@@ -739,22 +859,21 @@ size_t cake_matmul_rs_partial_bytes(const cake_matmul_rs* plan) {
 
 size_t cake_matmul_rs_slot_bytes(const cake_matmul_rs* plan) {
   if (!plan || plan->d.world == 1) return 0;
-  // two parities x W sources x one local output in the transport dtype
-  return 2ull * plan->d.world * plan->out_rows * plan->out_cols * plan->tsize;
+  // two parities x W sources x one local output in the transport dtype (padded to 128 bytes)
+  return 2ull * plan->d.world * plan->slot_stride;
 }
 
-size_t cake_matmul_rs_flag_bytes(const cake_matmul_rs* plan) {
-  if (!plan || plan->d.world == 1) return 0;
-  return sizeof(unsigned long long) * CAKE_MAX_WORLD;
-}
-
-int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void* const* flags) {
-  if (!plan || !slots || !flags) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_bind_peers: null argument");
+int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots) {
+  if (!plan || !slots) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_bind_peers: null argument");
   for (int r = 0; r < plan->d.world; ++r) {
-    if (!slots[r] || !flags[r]) return fail(CAKE_ERR_INVALID_ARGUMENT, "missing slot/flag pointer for rank %d", r);
+    if (!slots[r]) return fail(CAKE_ERR_INVALID_ARGUMENT, "missing slot pointer for rank %d", r);
+    if (reinterpret_cast<uintptr_t>(slots[r]) & 127)
+      return fail(CAKE_ERR_INVALID_ARGUMENT, "slot pointer of rank %d is not 128-byte aligned", r);
     plan->slots[r] = slots[r];
-    plan->flags[r] = flags[r];
   }
+  // Nothing has arrived yet: this rank's own slots start as the all-ones pattern.
+  CAKE_CUDA_TRY(cudaMemset(plan->slots[plan->d.rank], 0xFF, cake_matmul_rs_slot_bytes(plan)));
+  CAKE_CUDA_TRY(cudaDeviceSynchronize());
   plan->bound = true;
   return CAKE_OK;
 }
@@ -766,6 +885,31 @@ int32_t cake_matmul_rs_launches_per_enqueue(const cake_matmul_rs* plan) { return
 namespace {
 constexpr int kPhasePush = 1;    // contraction + epilogue stores / pushes
 constexpr int kPhaseReduce = 2;  // slot reduction (peer-to-peer strategy only)
+
+// Fills the reduction's parameters for the slots of `parity`.
+void fill_reduce_params(const cake_matmul_rs* plan, unsigned long long parity, void* out,
+                        cake::ReduceParams* r) {
+  const cake_matmul_rs_desc& d = plan->d;
+  r->slots = static_cast<const char*>(plan->slots[d.rank]) + parity * d.world * plan->slot_stride;
+  r->out = out;
+  r->slot_stride = plan->slot_stride;
+  const unsigned long long ms = d.wait_budget_ms > 0 ? static_cast<unsigned long long>(d.wait_budget_ms)
+                                                     : cake::kDefaultPeerBudgetMs;
+  r->budget_ns = ms * 1000000ull;
+  r->out_rows = (int)plan->out_rows;
+  r->out_cols = (int)plan->out_cols;
+  r->world = d.world;
+  r->in_f32 = plan->tsize == 4;
+  r->out_f32 = plan->osize == 4;
+  // The vector path wants whole 16-byte pieces per row in the transport dtype (the output row then
+  // is a whole number of 8-byte (bf16 out of f32) to 32-byte (f32 out of bf16) pieces of a 16-byte
+  // aligned base), rows in whole groups of 8, and a mesh of 2, 4 or 8; anything else goes element
+  // by element.
+  r->vec_ok = plan->out_cols % (16 / (int)plan->tsize) == 0 && plan->out_rows % 8 == 0 &&
+              (d.world == 2 || d.world == 4 || d.world == 8);
+  r->tile_n = d.tile_n;
+  r->status = plan->status.dev;
+}
 
 int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, void* out,
                      void* stream_v, int phases) {
@@ -784,105 +928,101 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
     return fail(CAKE_ERR_STATE, "reduce phase enqueued before any push phase");
   int launches = 0;
   const size_t chunk_elems = static_cast<size_t>(plan->out_rows) * plan->out_cols;
-  unsigned long long parity = plan->epoch & 1ull;
   if (phases & kPhasePush) {
+    const void* rhs_used = rhs;
+    if (plan->rhs_via_transpose) {
+      dim3 grid((d.n + 31) / 32, (d.k_local + 31) / 32), block(32, 8);
+      cake::cake_transpose_bf16<<<grid, block, 0, stream>>>(static_cast<const uint16_t*>(rhs),
+                                                            static_cast<uint16_t*>(plan->rhs_t),
+                                                            (int)d.k_local, (int)d.n);
+      CAKE_CUDA_TRY(cudaGetLastError());
+      rhs_used = plan->rhs_t;
+      ++launches;
+    }
+    if (lhs != plan->last_lhs || rhs_used != plan->last_rhs) {
+      int32_t rc = encode_maps(plan, lhs, rhs_used);
+      if (rc) return rc;
+      plan->last_lhs = lhs;
+      plan->last_rhs = rhs_used;
+    }
 
-  const void* rhs_used = rhs;
-  if (plan->rhs_via_transpose) {
-    dim3 grid((d.n + 31) / 32, (d.k_local + 31) / 32), block(32, 8);
-    cake::cake_transpose_bf16<<<grid, block, 0, stream>>>(static_cast<const uint16_t*>(rhs),
-                                                          static_cast<uint16_t*>(plan->rhs_t),
-                                                          (int)d.k_local, (int)d.n);
-    CAKE_CUDA_TRY(cudaGetLastError());
-    rhs_used = plan->rhs_t;
-    ++launches;
-  }
-  if (lhs != plan->last_lhs || rhs_used != plan->last_rhs) {
-    int32_t rc = encode_maps(plan, lhs, rhs_used);
+    cake::MatmulParams p;
+    memset(&p, 0, sizeof(p));
+    p.m = (int)d.m;
+    p.n = (int)d.n;
+    p.k_local = (int)d.k_local;
+    p.m_tiles = (int)((d.m + cake::kTileM - 1) / cake::kTileM);
+    p.n_tiles = (int)((d.n + d.tile_n - 1) / d.tile_n);
+    p.k_blocks = (int)((d.k_local + cake::kBlockK - 1) / cake::kBlockK);
+    p.world = d.world;
+    p.rank = d.rank;
+    p.scatter_dim = d.scatter_dim;
+    p.out_rows = (int)plan->out_rows;
+    p.out_cols = (int)plan->out_cols;
+    p.store_f32 = plan->tsize == 4;
+    const int epp = 16 / (int)plan->tsize;
+    p.vec_ok = (plan->out_cols % epp == 0) && (d.n % epp == 0);
+    p.to_slots = p2p;
+    p.status = plan->status.dev;
+    unsigned long long parity = 0;
+    if (d.world == 1) {
+      p.dest[0] = out;
+    } else if (!p2p) {
+      for (int o = 0; o < d.world; ++o) p.dest[o] = static_cast<char*>(out) + o * chunk_elems * plan->tsize;
+    } else {
+      plan->epoch += 1;
+      parity = plan->epoch & 1ull;
+      for (int o = 0; o < d.world; ++o)
+        p.dest[o] = static_cast<char*>(plan->slots[o]) + (parity * d.world + d.rank) * plan->slot_stride;
+      if (phases & kPhaseReduce) {
+        p.reduce_in_kernel = 1;
+        fill_reduce_params(plan, parity, out, &p.red);
+      }
+    }
+    // Tensor stores need 16-byte row pitch, and chunks (32 rows x 128 bytes) that never straddle owners.
+    const int chunk_cols = 128 / (int)plan->tsize;
+    const bool tma_ok = (plan->out_cols * plan->tsize) % 16 == 0 &&
+                        (d.world == 1 || (d.scatter_dim == 0 ? plan->out_rows % 32 == 0 : plan->out_cols % chunk_cols == 0));
+    const int maps_index = p2p ? (int)parity : 0;
+    p.tma_store = tma_ok ? 1 : 0;
+    if (tma_ok && plan->owner_maps_base[maps_index] != p.dest[0]) {
+      for (int o = 0; o < d.world; ++o) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(plan->out_cols), static_cast<uint64_t>(plan->out_rows)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(plan->out_cols) * plan->tsize};
+        const uint32_t box[2] = {static_cast<uint32_t>(chunk_cols), 32};
+        int32_t mrc = cake::encode_tensor_map_typed(&plan->owner_maps[maps_index].m[o], p.dest[o], 2, dims, strides, box, true,
+                                                    plan->tsize == 4 ? 4 : 2);
+        if (mrc) return mrc;
+      }
+      plan->owner_maps_base[maps_index] = p.dest[0];
+    }
+    const int num_tiles = p.m_tiles * p.n_tiles;
+    const int grid = num_tiles < plan->sm_count ? num_tiles : plan->sm_count;
+    p.owner_rotation = 1;
+    if (d.world > 1) {
+      const bool aligned = d.scatter_dim == 0 ? (plan->out_rows % cake::kTileM == 0)
+                                              : (plan->out_cols % d.tile_n == 0);
+      p.region_order = aligned ? 1 : 0;
+      // One wave of the grid covers grid / W tile groups: shift the owner sequence once per wave.
+      p.owner_rotation = grid / d.world > 0 ? grid / d.world : 1;
+    }
+    const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
+    int32_t rc;
+    if (d.tile_n == 256) rc = kmajor ? launch_gemm<256, true>(plan, p, grid, stream, maps_index) : launch_gemm<256, false>(plan, p, grid, stream, maps_index);
+    else if (d.tile_n == 128) rc = kmajor ? launch_gemm<128, true>(plan, p, grid, stream, maps_index) : launch_gemm<128, false>(plan, p, grid, stream, maps_index);
+    else rc = kmajor ? launch_gemm<64, true>(plan, p, grid, stream, maps_index) : launch_gemm<64, false>(plan, p, grid, stream, maps_index);
     if (rc) return rc;
-    plan->last_lhs = lhs;
-    plan->last_rhs = rhs_used;
-  }
-
-  cake::MatmulParams p;
-  memset(&p, 0, sizeof(p));
-  p.m = (int)d.m;
-  p.n = (int)d.n;
-  p.k_local = (int)d.k_local;
-  p.m_tiles = (int)((d.m + cake::kTileM - 1) / cake::kTileM);
-  p.n_tiles = (int)((d.n + d.tile_n - 1) / d.tile_n);
-  p.k_blocks = (int)((d.k_local + cake::kBlockK - 1) / cake::kBlockK);
-  p.world = d.world;
-  p.rank = d.rank;
-  p.scatter_dim = d.scatter_dim;
-  p.out_rows = (int)plan->out_rows;
-  p.out_cols = (int)plan->out_cols;
-  p.store_f32 = plan->tsize == 4;
-  const int epp = 16 / (int)plan->tsize;
-  p.vec_ok = (plan->out_cols % epp == 0) && (d.n % epp == 0);
-  p.count_arrivals = p2p;
-  p.status = plan->status.dev;
-  if (d.world == 1) {
-    p.dest[0] = out;
-  } else if (!p2p) {
-    for (int o = 0; o < d.world; ++o) p.dest[o] = static_cast<char*>(out) + o * chunk_elems * plan->tsize;
-  } else {
-    plan->epoch += 1;
-    parity = plan->epoch & 1ull;
-    for (int o = 0; o < d.world; ++o) {
-      p.dest[o] = static_cast<char*>(plan->slots[o]) + (parity * d.world + d.rank) * chunk_elems * plan->tsize;
-      p.arrive[o] = static_cast<unsigned long long*>(plan->flags[o]) + d.rank;
-    }
-  }
-  // Tensor stores need 16-byte row pitch, and chunks (32 rows x 128 bytes) that never straddle owners.
-  const int chunk_cols = 128 / (int)plan->tsize;
-  const bool tma_ok = (plan->out_cols * plan->tsize) % 16 == 0 &&
-                      (d.world == 1 || (d.scatter_dim == 0 ? plan->out_rows % 32 == 0 : plan->out_cols % chunk_cols == 0));
-  const int maps_index = p2p ? (int)parity : 0;
-  p.tma_store = tma_ok ? 1 : 0;
-  if (tma_ok && plan->owner_maps_base[maps_index] != p.dest[0]) {
-    for (int o = 0; o < d.world; ++o) {
-      const uint64_t dims[2] = {static_cast<uint64_t>(plan->out_cols), static_cast<uint64_t>(plan->out_rows)};
-      const uint64_t strides[1] = {static_cast<uint64_t>(plan->out_cols) * plan->tsize};
-      const uint32_t box[2] = {static_cast<uint32_t>(chunk_cols), 32};
-      int32_t mrc = cake::encode_tensor_map_typed(&plan->owner_maps[maps_index].m[o], p.dest[o], 2, dims, strides, box, true,
-                                                  plan->tsize == 4 ? 4 : 2);
-      if (mrc) return mrc;
-    }
-    plan->owner_maps_base[maps_index] = p.dest[0];
-  }
-  if (d.world > 1) {
-    const bool aligned = d.scatter_dim == 0 ? (plan->out_rows % cake::kTileM == 0)
-                                            : (plan->out_cols % d.tile_n == 0);
-    p.region_order = aligned ? 1 : 0;
-  }
-  const int num_tiles = p.m_tiles * p.n_tiles;
-  const int grid = num_tiles < plan->sm_count ? num_tiles : plan->sm_count;
-  const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
-  int32_t rc;
-  if (d.tile_n == 256) rc = kmajor ? launch_gemm<256, true>(plan, p, grid, stream, maps_index) : launch_gemm<256, false>(plan, p, grid, stream, maps_index);
-  else if (d.tile_n == 128) rc = kmajor ? launch_gemm<128, true>(plan, p, grid, stream, maps_index) : launch_gemm<128, false>(plan, p, grid, stream, maps_index);
-  else rc = kmajor ? launch_gemm<64, true>(plan, p, grid, stream, maps_index) : launch_gemm<64, false>(plan, p, grid, stream, maps_index);
-  if (rc) return rc;
-  ++launches;
-  }  // push phase
-
-  if (p2p && (phases & kPhaseReduce)) {
-    const unsigned long long expected = plan->epoch * chunk_elems;
-    const char* my_slots = static_cast<const char*>(plan->slots[d.rank]) + parity * d.world * chunk_elems * plan->tsize;
-    const unsigned long long* my_flags = static_cast<const unsigned long long*>(plan->flags[d.rank]);
-    const size_t groups = chunk_elems / (16 / plan->tsize);
-    int rgrid = (int)((groups + 255) / 256);
-    if (rgrid > plan->sm_count * 8) rgrid = plan->sm_count * 8;
+    ++launches;
+  } else if (p2p) {
+    // The reduction of the most recent push, as a kernel of its own.
+    cake::ReduceParams r;
+    memset(&r, 0, sizeof(r));
+    fill_reduce_params(plan, plan->epoch & 1ull, out, &r);
+    const size_t chunks = (chunk_elems * plan->tsize + 4095) / 4096;
+    int rgrid = (int)((chunks + 7) / 8);
+    if (rgrid > plan->sm_count * 4) rgrid = plan->sm_count * 4;
     if (rgrid < 1) rgrid = 1;
-    if (plan->tsize == 4 && plan->osize == 4)
-      cake::cake_reduce_slots_sm100<float, float><<<rgrid, 256, 0, stream>>>((const float*)my_slots, (float*)out, chunk_elems, d.world, my_flags, expected, plan->status.dev);
-    else if (plan->tsize == 4)
-      cake::cake_reduce_slots_sm100<float, __nv_bfloat16><<<rgrid, 256, 0, stream>>>((const float*)my_slots, (__nv_bfloat16*)out, chunk_elems, d.world, my_flags, expected, plan->status.dev);
-    else if (plan->osize == 4)
-      cake::cake_reduce_slots_sm100<__nv_bfloat16, float><<<rgrid, 256, 0, stream>>>((const __nv_bfloat16*)my_slots, (float*)out, chunk_elems, d.world, my_flags, expected, plan->status.dev);
-    else
-      cake::cake_reduce_slots_sm100<__nv_bfloat16, __nv_bfloat16><<<rgrid, 256, 0, stream>>>((const __nv_bfloat16*)my_slots, (__nv_bfloat16*)out, chunk_elems, d.world, my_flags, expected, plan->status.dev);
+    cake::cake_reduce_slots_sm100<<<rgrid, 256, 0, stream>>>(r);
     CAKE_CUDA_TRY(cudaGetLastError());
     ++launches;
   }

@@ -48,10 +48,10 @@ class P2pCollectiveResources:
     """Static resources of the owner-push reduce-scatter, the counterpart of
     ``pallas_bidirectional_ring_resources`` (src/tpu_cake/dialects/tpu_schedule.py:89-104)."""
 
-    receive_slot_bytes: int  # 2 parities x W sources x local output, in the transport dtype
-    arrival_counter_bytes: int
+    receive_slot_bytes: int  # 2 parities x W sources x local output (padded to 128 B), in the transport dtype
     remote_payload_bytes: int  # bytes this rank sends to other ranks per call
     reduce_read_bytes: int  # bytes the slot reduction reads per call
+    reduce_restore_bytes: int  # bytes of "not arrived" pattern it writes back over consumed pieces
 
 
 @dataclass(frozen=True)
@@ -134,10 +134,10 @@ class CudaMatmulRsPlan:
         size = 2 if self.transport_dtype == "bf16" else 4
         local = self.output_local_shape[0] * self.output_local_shape[1] * size
         return P2pCollectiveResources(
-            receive_slot_bytes=2 * self.mesh_size * local,
-            arrival_counter_bytes=8 * _native.CAKE_MAX_WORLD,
+            receive_slot_bytes=2 * self.mesh_size * (-(-local // 128) * 128),
             remote_payload_bytes=(self.mesh_size - 1) * local,
             reduce_read_bytes=self.mesh_size * local,
+            reduce_restore_bytes=self.mesh_size * local,
         )
 
     # ------------------------------------------------------------------ identity
@@ -232,10 +232,11 @@ class MatmulRsExecutable:
     stream. Fails loudly if libcake_b200.so is not built or the GPU is not sm_100.
     """
 
-    def __init__(self, plan: CudaMatmulRsPlan, mesh: ProcessMesh, *, contraction_only: bool = False):
+    def __init__(self, plan: CudaMatmulRsPlan, mesh: ProcessMesh, *, contraction_only: bool = False, wait_budget_ms: int = 0):
         """``contraction_only`` builds the same contraction with the same tiles and transport dtype
         but leaves the partial in local memory (owner-major) and runs no collective: the
-        "pushes disabled" twin used to measure how much communication time is exposed."""
+        "pushes disabled" twin used to measure how much communication time is exposed.
+        ``wait_budget_ms`` bounds how long the slot reduction waits for a peer (0 = 20 s)."""
         self.plan = plan
         self.mesh = mesh
         self._lib = _native.load()
@@ -255,25 +256,21 @@ class MatmulRsExecutable:
             tile_m=plan.tile_m,
             tile_n=plan.tile_n,
             rhs_layout=0,
-            reserved=0,
+            wait_budget_ms=wait_budget_ms,
         )
         handle = ctypes.c_void_p()
         with torch.cuda.device(mesh.device):
             _native.check(self._lib.cake_matmul_rs_create(ctypes.byref(desc), ctypes.byref(handle)))
         self._handle = handle
         self._slots: SymmetricBuffer | None = None
-        self._flags: SymmetricBuffer | None = None
         self._partial: torch.Tensor | None = None
         if self._p2p:
             with torch.cuda.device(mesh.device):
                 self._slots = SymmetricBuffer(mesh, self._lib.cake_matmul_rs_slot_bytes(handle))
-                self._flags = SymmetricBuffer(mesh, self._lib.cake_matmul_rs_flag_bytes(handle))
-            pointer_array = ctypes.c_void_p * mesh.world
-            _native.check(
-                self._lib.cake_matmul_rs_bind_peers(
-                    handle, pointer_array(*self._slots.pointers), pointer_array(*self._flags.pointers)
-                )
-            )
+                pointer_array = ctypes.c_void_p * mesh.world
+                _native.check(self._lib.cake_matmul_rs_bind_peers(handle, pointer_array(*self._slots.pointers)))
+            # bind_peers marks this rank's slots "nothing arrived": nobody may push before everybody has.
+            mesh.barrier()
         elif mesh.world > 1:
             self._partial = torch.empty(
                 (mesh.world,) + plan.output_local_shape, dtype=_TORCH_DTYPE[plan.transport_dtype], device=mesh.device
@@ -346,10 +343,9 @@ class MatmulRsExecutable:
             torch.cuda.synchronize(self.mesh.device)
             self._lib.cake_matmul_rs_destroy(self._handle)
             self._handle = None
-        for buffer in (self._slots, self._flags):
-            if buffer is not None:
-                buffer.close()
-        self._slots = self._flags = None
+        if self._slots is not None:
+            self._slots.close()
+        self._slots = None
 
     def _check_operand(self, tensor: torch.Tensor, shape: tuple[int, int], role: str) -> None:
         if tensor.dtype != torch.bfloat16 or tuple(tensor.shape) != shape or not tensor.is_contiguous() or tensor.device != self.mesh.device:

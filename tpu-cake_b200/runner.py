@@ -121,28 +121,26 @@ class _EmulatedMesh:
         world = plan.mesh_size
         peer = plan.collective_implementation is not cuda_lowering.MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER
         self.peer = peer
-        self.handles, self.slots, self.flags = [], [], []
+        self.handles, self.slots = [], []
         for rank in range(world):
             desc = _native.MatmulRsDesc(
                 m=plan.partial_local_shape[0], n=plan.partial_local_shape[1], k_local=plan.lhs_local_shape[1], world=world, rank=rank,
                 scatter_dim=plan.scatter_dimension, out_dtype=cuda_lowering._CAKE_DTYPE[plan.output_dtype],
                 transport_dtype=cuda_lowering._CAKE_DTYPE[plan.transport_dtype],
                 strategy=_native.CAKE_RS_P2P_OWNER_PUSH if peer else _native.CAKE_RS_LOCAL_PARTIAL, tile_m=plan.tile_m, tile_n=plan.tile_n,
-                rhs_layout=0, reserved=0,
+                rhs_layout=0, wait_budget_ms=0,
             )
             handle = ctypes.c_void_p()
             _native.check(self.lib.cake_matmul_rs_create(ctypes.byref(desc), ctypes.byref(handle)))
             self.handles.append(handle)
         if peer:
             for handle in self.handles:
-                slot, flag = ctypes.c_void_p(), ctypes.c_void_p()
+                slot = ctypes.c_void_p()
                 _native.check(self.lib.cake_symm_alloc(self.lib.cake_matmul_rs_slot_bytes(handle), ctypes.byref(slot)))
-                _native.check(self.lib.cake_symm_alloc(self.lib.cake_matmul_rs_flag_bytes(handle), ctypes.byref(flag)))
                 self.slots.append(slot.value)
-                self.flags.append(flag.value)
             array = ctypes.c_void_p * world
             for handle in self.handles:
-                _native.check(self.lib.cake_matmul_rs_bind_peers(handle, array(*self.slots), array(*self.flags)))
+                _native.check(self.lib.cake_matmul_rs_bind_peers(handle, array(*self.slots)))
 
     def __call__(self, lhs_shards, rhs_shards) -> list[torch.Tensor]:
         plan, world = self.plan, self.plan.mesh_size
@@ -174,9 +172,9 @@ class _EmulatedMesh:
         torch.cuda.synchronize(self.device)
         for handle in self.handles:
             self.lib.cake_matmul_rs_destroy(handle)
-        for pointer in self.slots + self.flags:
+        for pointer in self.slots:
             self.lib.cake_symm_free(pointer)
-        self.handles, self.slots, self.flags = [], [], []
+        self.handles, self.slots = [], []
 
 
 def run_distributed_matmul(
