@@ -76,7 +76,7 @@ int32_t cake_ipc_close(void* ptr);
 
 #define CAKE_RS_LOCAL_PARTIAL 0 /* write the partial, laid out owner-major; the host runs the
                                    library collective (NCCL reduce-scatter) on it */
-#define CAKE_RS_P2P_OWNER_PUSH 1 /* epilogue pushes each partial tile to its owner GPU; four more
+#define CAKE_RS_P2P_OWNER_PUSH 1 /* epilogue pushes each partial tile to its owner GPU; six more
                                     warps of the same kernel sum the W slots in rank order */
 
 typedef struct cake_matmul_rs_desc {
@@ -106,24 +106,24 @@ int32_t cake_matmul_rs_destroy(cake_matmul_rs* plan);
 size_t cake_matmul_rs_partial_bytes(const cake_matmul_rs* plan);
 
 /* CAKE_RS_P2P_OWNER_PUSH: bytes of this rank's receive slots (two parities x W sources x one local
- * output in the transport dtype, each padded to 128 bytes). */
+ * output in the transport dtype, each padded to 128 bytes) and of its arrival flags (one 32-bit word
+ * per source rank and quarter tile). */
 size_t cake_matmul_rs_slot_bytes(const cake_matmul_rs* plan);
+size_t cake_matmul_rs_flag_bytes(const cake_matmul_rs* plan);
 
-/* CAKE_RS_P2P_OWNER_PUSH: the slot buffer of every rank (entry [rank] is this rank's own allocation
- * of cake_matmul_rs_slot_bytes, 128-byte aligned; the others are IPC mappings). Called once before
- * the first enqueue. It fills this rank's own slots with the "nothing has arrived" pattern (all
- * ones) and synchronises the device, so the host must pass a barrier over all ranks between this
- * call and the first enqueue: a peer that started earlier would have its data overwritten.
+/* CAKE_RS_P2P_OWNER_PUSH: the slot and flag buffers of every rank (entry [rank] is this rank's own
+ * allocation -- slots 128-byte aligned, flags ZERO before the first enqueue, as cake_symm_alloc
+ * returns them -- the others are IPC mappings). Called once before the first enqueue.
  *
- * Protocol. Arrival is detected in the data: the reduction polls each 16-byte piece of a slot until
- * none of its elements is the pattern (0xFFFF per bf16, 0xFFFFFFFF per f32 -- NaNs the pushing side
- * replaces by the default NaN before it sends), and writes the pattern back when it has consumed the
- * piece. Call e uses the slots of parity e & 1, so a rank may run one call ahead of a slower peer.
- * If a reduction runs out of its wait budget (CAKE_ERR_TIMEOUT from cake_matmul_rs_status, code 2,
- * detail1 = the source rank that was missing), pieces consumed before that are gone: destroy and
- * re-create the plans of every rank. The one exception is a peer that had not pushed anything yet:
- * nothing was consumed, and cake_matmul_rs_enqueue_reduce may be called again once it has. */
-int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots);
+ * Protocol. Call number e (1, 2, ...) writes its partial tiles into the slots of parity e & 1 and then
+ * stores e into the owner's flag of each quarter tile (32 rows x tile_n columns) it has sent; the
+ * reduction waits until all W flags of a quarter have reached e before it reads the quarter. Flags
+ * only grow and a reduction consumes nothing, so a rank may run one call ahead of a slower peer, and
+ * a reduction that ran out of its wait budget (CAKE_ERR_TIMEOUT from cake_matmul_rs_status, code 2,
+ * detail1 = the source rank that was missing) can be enqueued again with
+ * cake_matmul_rs_enqueue_reduce once the peer has caught up. Every rank must make the same sequence
+ * of calls. */
+int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void* const* flags);
 
 /* lhs: bf16 [m, k_local]; rhs: bf16 per rhs_layout; out: world == 1 or P2P: the reduced local
  * output [m/W, n] or [m, n/W] in out_dtype; LOCAL_PARTIAL with world > 1: the owner-major partial

@@ -109,15 +109,17 @@ def _emulated_ranks(lhs, rhs, world, device, *, scatter_dimension, transport, ou
     results = []
     try:
         if strategy == _native.CAKE_RS_P2P_OWNER_PUSH:
-            slots = []
+            slots, flags = [], []
             for handle in handles:
-                slot = ctypes.c_void_p()
+                slot, flag = ctypes.c_void_p(), ctypes.c_void_p()
                 _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_slot_bytes(handle), ctypes.byref(slot)))
+                _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_flag_bytes(handle), ctypes.byref(flag)))
                 slots.append(slot.value)
+                flags.append(flag.value)
             array = ctypes.c_void_p * world
             for handle in handles:
-                _native.check(lib.cake_matmul_rs_bind_peers(handle, array(*slots)))
-            for repeat in range(4):  # exercises both slot parities and the restored "not arrived" pattern
+                _native.check(lib.cake_matmul_rs_bind_peers(handle, array(*slots), array(*flags)))
+            for repeat in range(4):  # exercises both slot parities and the growing call numbers in the flags
                 outs = [torch.full((out_rows, out_cols), float("nan"), dtype=torch_out, device=device) for _ in range(world)]
                 # On odd repeats the last position runs the one-kernel form (its reduction warps
                 # work while its own contraction still pushes): by then every other position has
@@ -137,7 +139,7 @@ def _emulated_ranks(lhs, rhs, world, device, *, scatter_dimension, transport, ou
                 word = _native.CakeStatus()
                 _native.check(lib.cake_matmul_rs_status(handle, stream, ctypes.byref(word)))
                 assert word.code == 0
-            for pointer in slots:
+            for pointer in slots + flags:
                 lib.cake_symm_free(pointer)
         else:
             tdtype = torch.float32 if transport == "f32" else torch.bfloat16
@@ -220,12 +222,12 @@ def test_reduction_gives_up_when_a_peer_never_pushes(cuda_device):
     """Two mesh positions on one GPU, a wait budget of 5 ms, and position 1 does not push: position
     0's reduction must give up (CAKE_ERR_TIMEOUT, code 2, missing source 1) without touching its
     output -- the wait runs out and the kernel returns, nothing faults or hangs. Position 1 then
-    pushes late; since nothing had been consumed, enqueueing the reduction again completes the step."""
+    pushes late; a reduction consumes nothing, so enqueueing it again completes the step."""
     lib = _native.load()
     world, m, k, n = 2, 256, 512, 512
     lhs, rhs = workloads.distributed_matmul_inputs(world, m, k, n)
     stream = torch.cuda.current_stream(cuda_device).cuda_stream
-    handles, operands, slots = [], [], []
+    handles, operands, slots, flags = [], [], [], []
     for rank in range(world):
         desc = _native.MatmulRsDesc(m=m, n=n, k_local=k // world, world=world, rank=rank, scatter_dim=0, out_dtype=_native.CAKE_DTYPE_F32,
                                     transport_dtype=_native.CAKE_DTYPE_F32, strategy=_native.CAKE_RS_P2P_OWNER_PUSH, tile_m=128, tile_n=256,
@@ -235,13 +237,15 @@ def test_reduction_gives_up_when_a_peer_never_pushes(cuda_device):
         handles.append(handle)
         lhs_r, rhs_r = workloads.shard_matmul_inputs(lhs, rhs, world, rank)
         operands.append((bf16_to_torch(lhs_r, cuda_device), bf16_to_torch(rhs_r, cuda_device)))
-        slot = ctypes.c_void_p()
+        slot, flag = ctypes.c_void_p(), ctypes.c_void_p()
         _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_slot_bytes(handle), ctypes.byref(slot)))
+        _native.check(lib.cake_symm_alloc(lib.cake_matmul_rs_flag_bytes(handle), ctypes.byref(flag)))
         slots.append(slot.value)
+        flags.append(flag.value)
     try:
         array = ctypes.c_void_p * world
         for handle in handles:
-            _native.check(lib.cake_matmul_rs_bind_peers(handle, array(*slots)))
+            _native.check(lib.cake_matmul_rs_bind_peers(handle, array(*slots), array(*flags)))
         outs = [torch.full((m // world, n), float("nan"), dtype=torch.float32, device=cuda_device) for _ in range(world)]
         _native.check(lib.cake_matmul_rs_enqueue_push(handles[0], operands[0][0].data_ptr(), operands[0][1].data_ptr(), stream))
         _native.check(lib.cake_matmul_rs_enqueue_reduce(handles[0], outs[0].data_ptr(), stream))
@@ -274,7 +278,7 @@ def test_reduction_gives_up_when_a_peer_never_pushes(cuda_device):
     finally:
         for handle in handles:
             lib.cake_matmul_rs_destroy(handle)
-        for pointer in slots:
+        for pointer in slots + flags:
             lib.cake_symm_free(pointer)
 
 

@@ -44,6 +44,7 @@ EXPORTED_SYMBOLS = (
     "cake_matmul_rs_destroy",
     "cake_matmul_rs_partial_bytes",
     "cake_matmul_rs_slot_bytes",
+    "cake_matmul_rs_flag_bytes",
     "cake_matmul_rs_bind_peers",
     "cake_matmul_rs_enqueue",
     "cake_matmul_rs_enqueue_push",
@@ -161,11 +162,11 @@ def load() -> ctypes.CDLL:
     lib.cake_matmul_rs_create.argtypes = [ctypes.POINTER(MatmulRsDesc), ctypes.POINTER(vp)]
     lib.cake_matmul_rs_destroy.restype = i32
     lib.cake_matmul_rs_destroy.argtypes = [vp]
-    for name in ("cake_matmul_rs_partial_bytes", "cake_matmul_rs_slot_bytes"):
+    for name in ("cake_matmul_rs_partial_bytes", "cake_matmul_rs_slot_bytes", "cake_matmul_rs_flag_bytes"):
         getattr(lib, name).restype = sz
         getattr(lib, name).argtypes = [vp]
     lib.cake_matmul_rs_bind_peers.restype = i32
-    lib.cake_matmul_rs_bind_peers.argtypes = [vp, ctypes.POINTER(vp)]
+    lib.cake_matmul_rs_bind_peers.argtypes = [vp, ctypes.POINTER(vp), ctypes.POINTER(vp)]
     lib.cake_matmul_rs_enqueue.restype = i32
     lib.cake_matmul_rs_enqueue.argtypes = [vp, vp, vp, vp, vp]
     lib.cake_matmul_rs_enqueue_push.restype = i32

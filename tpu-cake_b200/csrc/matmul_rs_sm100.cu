@@ -4,7 +4,7 @@
 // launched :429-444) and the collective that follows it (lax.psum_scatter :459-464, or the
 // bidirectional Pallas ring :117-326). The reference materialises the f32 partial [M,N] in HBM
 // between the two; here the epilogue of the contraction writes every partial tile straight to the
-// GPU that owns it, and four more warps of the same kernel sum the W received copies in rank order
+// GPU that owns it, and six more warps of the same kernel sum the W received copies in rank order
 // while the contraction is still running.
 //
 // cake_matmul_rs_sm100<BN, B_KMAJOR>: persistent, warp-specialised.
@@ -13,14 +13,15 @@
 //             two accumulator buffers so the epilogue of tile i overlaps the main loop of tile i+1
 //   warps 2-5 epilogue: tcgen05.ld -> convert -> swizzled smem staging -> 128-byte row segments to
 //             the owner's receive slot (local or peer memory)
-//   warps 6-9 slot reduction (peer-to-peer strategy): walk this rank's receive slots in the order
+//   warps 6-11 slot reduction (peer-to-peer strategy): walk this rank's receive slots in the order
 //             the peers fill them, out = sum over source ranks in fixed order (deterministic)
 //
-// Arrival is detected in the data itself. A receive slot holds an all-ones pattern (a NaN that the
-// epilogue never sends: 0xFFFF per bf16, 0xFFFFFFFF per f32) wherever nothing has arrived; the
-// reduction polls each 16-byte piece until no element of it is the pattern, and writes the pattern
-// back once it has consumed the piece. The pushing side therefore needs no fence, counter or flag:
-// a tile's stores are fire-and-forget, and the link never drains for a publication.
+// Arrival is announced by flags, one 32-bit word per source rank and per quarter tile (32 rows x BN
+// columns: what one epilogue warp sends of a tile), holding the number of the call whose data is in
+// the slot. An epilogue warp publishes a quarter one tile late: by then the tensor stores that
+// carried it have completed, so the warp never waits for the link, and the release store costs a
+// fence but no drain. Flags only grow, slots alternate between two parities, and nothing is
+// consumed destructively: a reduction that gave up can simply be enqueued again.
 // cake_reduce_slots_sm100 is the same reduction as a kernel of its own, for hosts that enqueue
 // the pushes of several mesh positions on one GPU before any reduction.
 #include <cuda_bf16.h>
@@ -37,8 +38,9 @@ namespace cake {
 constexpr int kTileM = 128;
 constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kGemmThreads = 320;  // producer, issuer, 4 epilogue warps, 4 reduction warps
-constexpr int kReduceWarps = 4;
+// Producer, issuer, 4 epilogue warps, 6 reduction warps. Twelve warps are three per scheduler, whose
+// register file (16 K) then allows 168 registers per thread -- the same as ten warps would get.
+constexpr int kGemmThreads = 384;
 constexpr uint32_t kABytes = kTileM * kBlockK * 2;
 // Chunks (32 rows x 128 bytes) an epilogue warp can have staged for stores still reading shared
 // memory, and the depth of the 256-wide configuration's operand ring: the two compete for the
@@ -53,7 +55,6 @@ constexpr int kStagingChunks = CAKE_MM_STAGING_CHUNKS;
 constexpr uint32_t kStagingBytesPerWarp = kStagingChunks * 32 * 128;
 constexpr long long kBarrierBudgetCycles = 4000000000ll;  // about two seconds of SM clock
 constexpr unsigned long long kDefaultPeerBudgetMs = 20000ull;  // 20 s unless the descriptor says otherwise
-constexpr uint32_t kNotArrived = 0xFFFFFFFFu;  // 32 bits of the receive slots' "nothing here yet" pattern
 
 template <int BN>
 struct GemmCfg {
@@ -66,18 +67,28 @@ struct GemmCfg {
 };
 
 // What the slot reduction needs: this rank's receive slots of the current parity (source s at
-// slots + s * slot_stride, each a [out_rows, out_cols] array in the transport dtype) and the output.
+// slots + s * slot_stride, each a [out_rows, out_cols] array in the transport dtype), its arrival
+// flags ([W sources][quarters], quarter ((mi * n_tiles + ni) * 4 + q) of the region's tile grid) and
+// the output.
 struct ReduceParams {
   const char* slots;
   void* out;
+  const uint32_t* flags;
   unsigned long long slot_stride;  // bytes, a multiple of 128
-  unsigned long long budget_ns;    // how long a piece may stay "not arrived" before the reduction gives up
+  unsigned long long budget_ns;    // how long a quarter may stay unannounced before the reduction gives up
+  uint32_t epoch;                  // the call number a flag must have reached
+  int32_t quarters;                // flags per source
   int32_t out_rows, out_cols, world;
   int32_t in_f32, out_f32;  // transport / output element type: 1 = f32, 0 = bf16
-  int32_t vec_ok;           // rows are whole 16-byte pieces in both the transport and the output dtype
+  int32_t vec_ok;           // rows are whole 16-byte pieces, in groups of 8 rows, mesh of 2, 4 or 8
   int32_t tile_n;           // the pushing side's tile width (sets the order the slots fill in)
+  int32_t* tickets;         // [0] next chunk to hand out, [1] blocks that have finished; both 0 between launches
   int32_t* status;
 };
+
+// MatmulParams::publish: 0 = destinations are not receive slots, nothing to announce.
+constexpr int kPublishPerTile = 1;  // every epilogue warp announces its quarter, one tile late
+constexpr int kPublishAtEnd = 2;    // the last block to finish announces everything (tiles may straddle owners)
 
 struct MatmulParams {
   int32_t m, n, k_local;
@@ -86,12 +97,17 @@ struct MatmulParams {
   int32_t out_rows, out_cols;  // shape of one owner's local output
   int32_t store_f32;           // destination element type: 1 = f32, 0 = bf16
   int32_t vec_ok;              // 16-byte pieces never straddle owners or bounds
-  int32_t to_slots;            // destinations are receive slots: never send the "not arrived" pattern
   int32_t tma_store;           // epilogue chunks leave shared memory as TMA tensor stores
   int32_t region_order;        // consecutive tiles go to consecutive owners, starting at rank+1
   int32_t owner_rotation;      // tile groups after which the owner sequence shifts by one
-  int32_t reduce_in_kernel;    // warps 6-9 run the slot reduction
+  int32_t publish;             // kPublish*
+  int32_t reduce_in_kernel;    // the slot reduction runs in this kernel
+  uint32_t epoch;              // value written to the flags
+  int32_t region_n_tiles;      // tile columns of one owner's region (flag indexing)
+  int32_t quarters;            // flags per source rank: region tiles x 4
   void* dest[CAKE_MAX_WORLD];  // per-owner base of the [out_rows, out_cols] destination
+  uint32_t* flags_at[CAKE_MAX_WORLD];  // per owner: its flags for this source rank, [quarters]
+  int32_t* push_done;          // kPublishAtEnd: blocks whose stores have completed; 0 between launches
   ReduceParams red;
   int32_t* status;
 };
@@ -137,11 +153,14 @@ __device__ __forceinline__ void raster(int t, int mt_count, int nt_count, int& m
 // give it the same one or two owners for the whole kernel, and the CTAs that never meet their own
 // (link-free) tiles would finish last.
 template <int BN>
-__device__ __forceinline__ void tile_coords(const MatmulParams& p, int t, int& mt, int& nt) {
+__device__ __forceinline__ void tile_coords(const MatmulParams& p, int t, int& mt, int& nt, int& owner,
+                                            int& region_tile) {
+  owner = 0;
+  region_tile = 0;
   if (p.region_order) {
     const int group = t / p.world;
     const int j = (t - group * p.world + group / p.owner_rotation) % p.world;
-    const int owner = (p.rank + 1 + j) % p.world;
+    owner = (p.rank + 1 + j) % p.world;
     int mi, ni;
     if (p.scatter_dim == 0) {
       const int m_tiles_r = p.out_rows / kTileM;
@@ -154,6 +173,7 @@ __device__ __forceinline__ void tile_coords(const MatmulParams& p, int t, int& m
       mt = mi;
       nt = owner * n_tiles_r + ni;
     }
+    region_tile = mi * p.region_n_tiles + ni;
   } else {
     raster(t, p.m_tiles, p.n_tiles, mt, nt);
   }
@@ -181,80 +201,74 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
 }
 
 // ------------------------------------------------------------------------------ slot reduction
-//
-// A receive slot is filled by remote (or local) stores that no flag announces: a piece is there
-// when none of its elements is the all-ones pattern any more. Loads go to L2 (volatile), where
-// peer writes land.
 
-// Both are volatile asm without a memory clobber: they keep their order among themselves (a piece
-// is overwritten only after it has been read) and leave the compiler free to keep everything else
-// in registers.
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+
+// Slot data is read once, after its flag has been seen: straight from L2, no L1 allocation.
 __device__ __forceinline__ uint4 ld_slot_v4(const void* ptr) {
   uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(ptr));
   return v;
 }
 
-__device__ __forceinline__ void st_slot_not_arrived_v4(void* ptr) {
-  asm volatile("st.global.v4.u32 [%0], {%1, %1, %1, %1};" ::"l"(ptr), "r"(kNotArrived));
+// Waits until every source rank has announced `quarter` for this call: lane s watches source s.
+// Warp-uniform result; false when the budget ran out (the status word names the first missing source).
+__device__ __forceinline__ bool wait_quarter(const ReduceParams& r, int quarter, int lane,
+                                             unsigned long long start, int item) {
+  const uint32_t* flag = r.flags + static_cast<size_t>(lane < r.world ? lane : 0) * r.quarters + quarter;
+  while (true) {
+    const uint32_t seen = ld_acquire_sys_u32(flag);
+    const uint32_t missing =
+        __ballot_sync(0xffffffffu, lane < r.world && static_cast<int32_t>(seen - r.epoch) < 0);
+    if (missing == 0) return true;
+    if (__any_sync(0xffffffffu, global_timer_ns() - start > r.budget_ns)) {
+      if (lane == 0) record_status(r.status, 2, blockIdx.x, __ffs(missing) - 1, item);
+      return false;
+    }
+    __nanosleep(250);
+  }
 }
 
-// Non-zero when at least one element of the piece is still the "not arrived" pattern.
-template <bool IN_F32>
-__device__ __forceinline__ uint32_t piece_missing(const uint4& v) {
-  if (IN_F32) return max(max(v.x, v.y), max(v.z, v.w)) == kNotArrived ? 1u : 0u;
-  return __vcmpeq2(v.x, kNotArrived) | __vcmpeq2(v.y, kNotArrived) | __vcmpeq2(v.z, kNotArrived) |
-         __vcmpeq2(v.w, kNotArrived);
-}
-
-// One chunk = 32 rows x 128 bytes of the transport dtype (what one epilogue tensor store carries).
-// Lane l owns the 16-byte piece (l & 7) of rows (l >> 3) + 4 i. Two rows are in flight at a time:
-// the loads of every source are issued before any is looked at, the sum runs in rank order, and a
-// consumed piece is overwritten with the pattern so that the slot is ready for its next use.
-// The caller guarantees out_rows % 8 == 0, so the two rows of a step are inside the output together.
-// Returns false when a piece stayed "not arrived" for longer than the budget.
+// One chunk = 32 rows x 128 bytes of the transport dtype (what one epilogue tensor store carries),
+// reduced by one warp once its quarter has arrived. Lane l owns the 16-byte piece (l & 7) of rows
+// (l >> 3) + 4 j, j = 0..7; 16 / W rows are in flight per lane at a time (16 loads of 16 bytes
+// whatever the mesh size), all issued before any is used; the sum runs in rank order.
+// The caller guarantees out_rows % 8 == 0, so rows j and j + 1 (j even) are inside the output together.
 template <bool IN_F32, int W>
-__device__ __forceinline__ bool reduce_chunk_vec(const ReduceParams& r, int row0, int col0, int lane,
-                                                 unsigned long long start, int item) {
+__device__ __forceinline__ void reduce_chunk_vec(const ReduceParams& r, int row0, int col0, int lane) {
   constexpr int EPP = IN_F32 ? 4 : 8;  // elements per 16-byte piece
   constexpr int TS = IN_F32 ? 4 : 2;
+  constexpr int ROWS = 16 / W;
   const int col = col0 + (lane & 7) * EPP;
-  if (col >= r.out_cols) return true;
+  if (col >= r.out_cols) return;  // the last chunk of a row may be ragged
+  const size_t first = static_cast<size_t>(row0 + (lane >> 3)) * r.out_cols + col;
 #pragma unroll 1
-  for (int i = 0; i < 8; i += 2) {
-    const int row_a = row0 + i * 4 + (lane >> 3);
-    if (row_a >= r.out_rows) break;
-    const size_t offset[2] = {static_cast<size_t>(row_a) * r.out_cols + col,
-                              static_cast<size_t>(row_a + 4) * r.out_cols + col};
-    uint4 raw[2][W];
-    while (true) {
-      uint32_t missing_any = 0;
+  for (int i = 0; i < 8; i += ROWS) {
+    if (row0 + 4 * i >= r.out_rows) break;
+    size_t offset[ROWS];
+    bool active[ROWS];
+    uint4 raw[ROWS][W];
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
+    for (int u = 0; u < ROWS; ++u) {
+      active[u] = row0 + 4 * ((i + u) & ~1) < r.out_rows;
+      // A row outside the output re-reads the chunk's first row (in bounds, no predicate needed).
+      offset[u] = active[u] ? first + static_cast<size_t>(4 * (i + u)) * r.out_cols : first;
 #pragma unroll
-        for (int src = 0; src < W; ++src) raw[u][src] = ld_slot_v4(r.slots + src * r.slot_stride + offset[u] * TS);
-#pragma unroll
-      for (int u = 0; u < 2; ++u)
-#pragma unroll
-        for (int src = 0; src < W; ++src) missing_any |= piece_missing<IN_F32>(raw[u][src]);
-      if (missing_any == 0) break;
-      if (global_timer_ns() - start > r.budget_ns) {
-        // Name the first source whose piece is missing.
-        int missing = 0;
-#pragma unroll
-        for (int u = 1; u >= 0; --u)
-#pragma unroll
-          for (int src = W - 1; src >= 0; --src)
-            if (piece_missing<IN_F32>(raw[u][src]) != 0) missing = src;
-        record_status(r.status, 2, blockIdx.x, missing, item);
-        return false;
-      }
-      __nanosleep(100);
+      for (int src = 0; src < W; ++src) raw[u][src] = ld_slot_v4(r.slots + src * r.slot_stride + offset[u] * TS);
     }
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < ROWS; ++u) {
+      if (!active[u]) continue;
       float acc[EPP];
 #pragma unroll
       for (int e = 0; e < EPP; ++e) acc[e] = 0.f;
@@ -293,25 +307,19 @@ __device__ __forceinline__ bool reduce_chunk_vec(const ReduceParams& r, int row0
         packed.y = pack2_bf16(acc[2], acc[3]);
         *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(r.out) + offset[u]) = packed;
       }
-#pragma unroll
-      for (int src = 0; src < W; ++src)
-        st_slot_not_arrived_v4(const_cast<char*>(r.slots) + src * r.slot_stride + offset[u] * TS);
     }
   }
-  return true;
 }
 
 template <bool IN_F32>
-__device__ __forceinline__ bool reduce_chunk_vec_world(const ReduceParams& r, int row0, int col0, int lane,
-                                                       unsigned long long start, int item) {
-  if (r.world == 8) return reduce_chunk_vec<IN_F32, 8>(r, row0, col0, lane, start, item);
-  if (r.world == 4) return reduce_chunk_vec<IN_F32, 4>(r, row0, col0, lane, start, item);
-  return reduce_chunk_vec<IN_F32, 2>(r, row0, col0, lane, start, item);
+__device__ __forceinline__ void reduce_chunk_vec_world(const ReduceParams& r, int row0, int col0, int lane) {
+  if (r.world == 8) reduce_chunk_vec<IN_F32, 8>(r, row0, col0, lane);
+  else if (r.world == 4) reduce_chunk_vec<IN_F32, 4>(r, row0, col0, lane);
+  else reduce_chunk_vec<IN_F32, 2>(r, row0, col0, lane);
 }
 
-// The same chunk element by element, for shapes whose rows are not whole 16-byte pieces.
-__device__ __forceinline__ bool reduce_chunk_scalar(const ReduceParams& r, int row0, int col0, int lane,
-                                                    unsigned long long start, int item) {
+// The same chunk element by element, for shapes the vector path does not cover.
+__device__ __forceinline__ void reduce_chunk_scalar(const ReduceParams& r, int row0, int col0, int lane) {
   const int ts = r.in_f32 ? 4 : 2;
   const int cols_per_chunk = 128 / ts;
   for (int idx = lane; idx < 32 * cols_per_chunk; idx += 32) {
@@ -322,61 +330,76 @@ __device__ __forceinline__ bool reduce_chunk_scalar(const ReduceParams& r, int r
     float acc = 0.f;
     for (int src = 0; src < r.world; ++src) {
       const char* piece = r.slots + src * r.slot_stride + offset * ts;
-      uint32_t v;
-      while (true) {
-        v = r.in_f32 ? *reinterpret_cast<const volatile uint32_t*>(piece)
-                     : static_cast<uint32_t>(*reinterpret_cast<const volatile uint16_t*>(piece));
-        if (v != (r.in_f32 ? kNotArrived : 0xFFFFu)) break;
-        if (global_timer_ns() - start > r.budget_ns) {
-          record_status(r.status, 2, blockIdx.x, src, item);
-          return false;
-        }
-        __nanosleep(64);
-      }
-      acc += __uint_as_float(r.in_f32 ? v : v << 16);
-    }
-    for (int src = 0; src < r.world; ++src) {
-      char* piece = const_cast<char*>(r.slots) + src * r.slot_stride + offset * ts;
-      if (r.in_f32) *reinterpret_cast<volatile uint32_t*>(piece) = kNotArrived;
-      else *reinterpret_cast<volatile uint16_t*>(piece) = 0xFFFFu;
+      const uint32_t v = r.in_f32 ? __ldcg(reinterpret_cast<const uint32_t*>(piece))
+                                  : static_cast<uint32_t>(__ldcg(reinterpret_cast<const uint16_t*>(piece))) << 16;
+      acc += __uint_as_float(v);
     }
     if (r.out_f32) static_cast<float*>(r.out)[offset] = acc;
     else static_cast<__nv_bfloat16*>(r.out)[offset] = __float2bfloat16_rn(acc);
   }
-  return true;
 }
 
-// One reduction worker (a warp) of `workers`: chunks are numbered in the order the pushing side
-// produces them -- tiles of 128 x tile_n in the raster order of tile_coords, then the four 32-row
-// quarters, then the 128-byte column chunks -- and dealt round-robin, so every worker has work
-// from the first tile to the last and the chunks still missing when the peers finish are spread
-// over all workers.
-__device__ __forceinline__ void reduce_worker(const ReduceParams& r, int worker, int workers, int lane) {
+// One reduction worker (a whole warp). Chunks are numbered in the order the pushing side produces
+// them -- tiles of 128 x tile_n in the raster order of tile_coords, then the four 32-row quarters,
+// then the 128-byte column chunks -- and handed out through a ticket counter, so whichever warps
+// are free take the next chunk to arrive: the dedicated reduction warps during the contraction,
+// and every warp of the kernel once its own role is done, which keeps the tail after the last
+// tile short. The next ticket is drawn before the current chunk is worked on.
+__device__ __forceinline__ void reduce_worker(const ReduceParams& r, int lane) {
   const int cols_per_chunk = r.in_f32 ? 32 : 64;
   const int chunks_per_quarter = r.tile_n / cols_per_chunk;
   const int m_tiles = (r.out_rows + kTileM - 1) / kTileM;
   const int n_tiles = (r.out_cols + r.tile_n - 1) / r.tile_n;
   const int items = m_tiles * n_tiles * 4 * chunks_per_quarter;
   const unsigned long long start = global_timer_ns();
-  for (int item = worker; item < items; item += workers) {
+  int next = 0;
+  if (lane == 0) next = atomicAdd(r.tickets, 1);
+  while (true) {
+    const int item = __shfl_sync(0xffffffffu, next, 0);
+    if (item >= items) break;
+    if (lane == 0) next = atomicAdd(r.tickets, 1);
     const int tile = item / (4 * chunks_per_quarter);
     const int rest = item - tile * 4 * chunks_per_quarter;
+    const int q = rest / chunks_per_quarter;
     int mi, ni;
     raster(tile, m_tiles, n_tiles, mi, ni);
-    const int row0 = mi * kTileM + (rest / chunks_per_quarter) * 32;
-    const int col0 = ni * r.tile_n + (rest % chunks_per_quarter) * cols_per_chunk;
+    const int row0 = mi * kTileM + q * 32;
+    const int col0 = ni * r.tile_n + (rest - q * chunks_per_quarter) * cols_per_chunk;
     if (row0 >= r.out_rows || col0 >= r.out_cols) continue;
-    bool ok;
-    if (!r.vec_ok) ok = reduce_chunk_scalar(r, row0, col0, lane, start, item);
-    else if (r.in_f32) ok = reduce_chunk_vec_world<true>(r, row0, col0, lane, start, item);
-    else ok = reduce_chunk_vec_world<false>(r, row0, col0, lane, start, item);
-    if (!ok) return;
+    if (!wait_quarter(r, (mi * n_tiles + ni) * 4 + q, lane, start, item)) break;
+    if (!r.vec_ok) reduce_chunk_scalar(r, row0, col0, lane);
+    else if (r.in_f32) reduce_chunk_vec_world<true>(r, row0, col0, lane);
+    else reduce_chunk_vec_world<false>(r, row0, col0, lane);
   }
 }
 
-// The slot reduction as a kernel of its own (8 workers per block).
+// Called by one thread of every block after the block's last worker has left reduce_worker: the
+// last block to get here puts the ticket counter back to zero for the next launch.
+__device__ __forceinline__ void reduce_block_done(const ReduceParams& r) {
+  __threadfence();
+  if (atomicAdd(r.tickets + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+    r.tickets[0] = 0;
+    r.tickets[1] = 0;
+    __threadfence();
+  }
+}
+
+// The slot reduction as a kernel of its own.
 __global__ void __launch_bounds__(256) cake_reduce_slots_sm100(const __grid_constant__ ReduceParams r) {
-  reduce_worker(r, blockIdx.x * 8 + (threadIdx.x >> 5), gridDim.x * 8, threadIdx.x & 31);
+  reduce_worker(r, threadIdx.x & 31);
+  __syncthreads();
+  if (threadIdx.x == 0) reduce_block_done(r);
+}
+
+// cp.async.bulk.wait_group takes its count as an immediate.
+__device__ __forceinline__ void bulk_wait_group_at_most(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
+    default: asm volatile("cp.async.bulk.wait_group 8;" ::: "memory"); break;
+  }
 }
 
 // One tensor map per owner: its [out_rows, out_cols] destination (own output, owner-major partial or
@@ -406,6 +429,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* drain_bar = tmem_empty + 2;      // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
+  volatile uint32_t* epilogue_done = tmem_base_slot + 2;  // epilogue warps whose stores have completed
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -422,6 +446,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     mbar_init(smem_u32(drain_bar), 1);
     *abort_flag = 0;
+    *epilogue_done = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
@@ -442,8 +467,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int mt, nt;
-        tile_coords<BN>(p, t, mt, nt);
+        int mt, nt, owner_unused, region_unused;
+        tile_coords<BN>(p, t, mt, nt, owner_unused, region_unused);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!wait_or_abort(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
             if (!*abort_flag) record_status(p.status, 1, blockIdx.x, t, 100 + stage);
@@ -537,14 +562,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint8_t* my_stage_base = staging + (warp - 2) * kStagingBytesPerWarp;
     int chunk_count = 0;  // chunks this warp has staged so far (selects the staging half)
+    uint32_t* pending_flag = nullptr;  // lane 0: the flag of the quarter sent last, not yet announced
     const int elem_bytes = p.store_f32 ? 4 : 2;
     const int cols_per_chunk = p.store_f32 ? 32 : 64;  // 128 bytes per row per chunk
     const int epp = 16 / elem_bytes;                   // elements per 16-byte piece
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
-      int mt, nt;
-      tile_coords<BN>(p, t, mt, nt);
+      int mt, nt, owner, region_tile;
+      tile_coords<BN>(p, t, mt, nt, owner, region_tile);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // The decision is made warp-uniform: tcgen05.ld below is a warp-collective instruction.
@@ -564,11 +590,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_row + ch * 32, v);
           tmem_ld_wait();
-          if (p.to_slots) {
-            // A receive slot reads all-ones as "not arrived": send the default NaN instead.
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = v[j] == kNotArrived ? 0x7FFFFFFFu : v[j];
-          }
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             pieces[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -586,8 +607,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]),
                                                                 __uint_as_float(v[8 * j + 2 * e + 1]));
                 w[e] = *reinterpret_cast<const uint32_t*>(&b2);
-                // Same rule per bf16 half: 0xFFFF (a NaN) goes out as 0x7FFF.
-                if (p.to_slots) w[e] &= ~(__vcmpeq2(w[e], kNotArrived) & 0x80008000u);
               }
               pieces[h * 4 + j] = make_uint4(w[0], w[1], w[2], w[3]);
             }
@@ -663,17 +682,61 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         __syncwarp();
       }
+      if (p.publish == kPublishPerTile && lane == 0) {
+        // Announce the quarter sent one tile ago: its stores were issued a whole main loop ago, so
+        // waiting for all but this tile's groups costs nothing. Completion of a bulk group makes
+        // its writes visible to this thread; the proxy fence orders them before the release store.
+        if (pending_flag != nullptr) {
+          bulk_wait_group_at_most(num_chunks);
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          st_release_sys_u32(pending_flag, p.epoch);
+        }
+        pending_flag = p.flags_at[owner] + region_tile * 4 + (warp - 2);
+      }
     }
-  } else if (p.reduce_in_kernel) {
-    // ------------------------------------------------------------------ slot reduction warps 6..9
-    reduce_worker(p.red, blockIdx.x * kReduceWarps + (warp - 6), gridDim.x * kReduceWarps, lane);
+    if (p.publish == kPublishPerTile && lane == 0 && pending_flag != nullptr && ok) {
+      bulk_wait_group_at_most(0);
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      st_release_sys_u32(pending_flag, p.epoch);
+    }
+    if (p.publish == kPublishAtEnd && ok) {
+      // Tiles may straddle owners here, so nothing is announced per tile: every epilogue warp
+      // makes its own stores visible, the block's last warp counts the block as done, and the
+      // last block of the grid announces every quarter to every owner.
+      __syncwarp();
+      int last_block = 0;
+      if (lane == 0) {
+        if (p.tma_store) {
+          bulk_wait_group_at_most(0);
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+        __threadfence_system();
+        if (atomicAdd(const_cast<uint32_t*>(epilogue_done), 1u) == 3u) {
+          __threadfence_system();
+          last_block = atomicAdd(p.push_done, 1) == static_cast<int>(gridDim.x) - 1;
+        }
+      }
+      last_block = __shfl_sync(0xffffffffu, last_block, 0);
+      if (last_block) {
+        __threadfence_system();
+        for (int o = 0; o < p.world; ++o)
+          for (int idx = lane; idx < p.quarters; idx += 32) st_release_sys_u32(p.flags_at[o] + idx, p.epoch);
+        if (lane == 0) *p.push_done = 0;
+      }
+    }
   }
+  // ------------------------------------------------------------------ slot reduction
+  // Warps 6..11 do nothing else; the others join when their own role is done (unless the block has
+  // given up on one of its barriers), so the chunks that arrive last find every warp free.
+  __syncwarp();
+  if (p.reduce_in_kernel && !*abort_flag) reduce_worker(p.red, lane);
 
   // Shared memory must outlive every tensor store that still reads it.
   if (p.tma_store && warp >= 2 && warp < 6 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
+  if (p.reduce_in_kernel && threadIdx.x == 0) reduce_block_done(p.red);
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
@@ -708,7 +771,11 @@ struct cake_matmul_rs {
   bool rhs_via_transpose = false;
   void* rhs_t = nullptr;  // [n, k_local] scratch when rhs_via_transpose
   void* slots[CAKE_MAX_WORLD] = {};
+  void* flags[CAKE_MAX_WORLD] = {};
   size_t slot_stride = 0;  // bytes between two sources' slots: one local output, padded to 128 bytes
+  int region_m_tiles = 0, region_n_tiles = 0;  // tile grid of one owner's region
+  int quarters = 0;                            // arrival flags per source rank
+  int32_t* tickets = nullptr;  // 3 x int32 on the device: chunk ticket, reduction blocks done, push blocks done
   bool bound = false;
   unsigned long long epoch = 0;
   cake::StatusWord status;
@@ -827,9 +894,17 @@ int32_t cake_matmul_rs_create(const cake_matmul_rs_desc* desc, cake_matmul_rs** 
   plan->osize = d.out_dtype == CAKE_DTYPE_F32 ? 4 : 2;
   plan->tsize = d.world == 1 ? plan->osize : (d.transport_dtype == CAKE_DTYPE_F32 ? 4 : 2);
   plan->slot_stride = (static_cast<size_t>(plan->out_rows) * plan->out_cols * plan->tsize + 127) / 128 * 128;
+  plan->region_m_tiles = (int)((plan->out_rows + cake::kTileM - 1) / cake::kTileM);
+  plan->region_n_tiles = (int)((plan->out_cols + d.tile_n - 1) / d.tile_n);
+  plan->quarters = plan->region_m_tiles * plan->region_n_tiles * 4;
   const char* env = getenv("CAKE_MATMUL_TRANSPOSE_RHS");
   plan->rhs_via_transpose = d.rhs_layout == 0 && env && env[0] == '1';
   int32_t rc = plan->status.ensure();
+  if (rc == CAKE_OK && d.world > 1 && d.strategy == CAKE_RS_P2P_OWNER_PUSH) {
+    e = cudaMalloc(&plan->tickets, 3 * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemset(plan->tickets, 0, 3 * sizeof(int32_t));
+    if (e != cudaSuccess) rc = fail(CAKE_ERR_CUDA, "cudaMalloc(tickets) failed: %s", cudaGetErrorString(e));
+  }
   if (rc == CAKE_OK && plan->rhs_via_transpose) {
     e = cudaMalloc(&plan->rhs_t, static_cast<size_t>(d.n) * d.k_local * 2);
     if (e != cudaSuccess) rc = fail(CAKE_ERR_CUDA, "cudaMalloc(rhs_t) failed: %s", cudaGetErrorString(e));
@@ -845,6 +920,7 @@ int32_t cake_matmul_rs_create(const cake_matmul_rs_desc* desc, cake_matmul_rs** 
 int32_t cake_matmul_rs_destroy(cake_matmul_rs* plan) {
   if (!plan) return CAKE_OK;
   plan->status.release();
+  if (plan->tickets) cudaFree(plan->tickets);
   if (plan->rhs_t) cudaFree(plan->rhs_t);
   if (plan->h_lhs) cudaFree(plan->h_lhs);
   if (plan->h_rhs) cudaFree(plan->h_rhs);
@@ -863,17 +939,21 @@ size_t cake_matmul_rs_slot_bytes(const cake_matmul_rs* plan) {
   return 2ull * plan->d.world * plan->slot_stride;
 }
 
-int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots) {
-  if (!plan || !slots) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_bind_peers: null argument");
+size_t cake_matmul_rs_flag_bytes(const cake_matmul_rs* plan) {
+  if (!plan || plan->d.world == 1) return 0;
+  // one 32-bit call number per source rank and quarter tile
+  return (static_cast<size_t>(plan->d.world) * plan->quarters * sizeof(uint32_t) + 127) / 128 * 128;
+}
+
+int32_t cake_matmul_rs_bind_peers(cake_matmul_rs* plan, void* const* slots, void* const* flags) {
+  if (!plan || !slots || !flags) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_bind_peers: null argument");
   for (int r = 0; r < plan->d.world; ++r) {
-    if (!slots[r]) return fail(CAKE_ERR_INVALID_ARGUMENT, "missing slot pointer for rank %d", r);
-    if (reinterpret_cast<uintptr_t>(slots[r]) & 127)
-      return fail(CAKE_ERR_INVALID_ARGUMENT, "slot pointer of rank %d is not 128-byte aligned", r);
+    if (!slots[r] || !flags[r]) return fail(CAKE_ERR_INVALID_ARGUMENT, "missing slot/flag pointer for rank %d", r);
+    if ((reinterpret_cast<uintptr_t>(slots[r]) & 127) || (reinterpret_cast<uintptr_t>(flags[r]) & 3))
+      return fail(CAKE_ERR_INVALID_ARGUMENT, "slot pointer of rank %d must be 128-byte aligned, flags 4-byte aligned", r);
     plan->slots[r] = slots[r];
+    plan->flags[r] = flags[r];
   }
-  // Nothing has arrived yet: this rank's own slots start as the all-ones pattern.
-  CAKE_CUDA_TRY(cudaMemset(plan->slots[plan->d.rank], 0xFF, cake_matmul_rs_slot_bytes(plan)));
-  CAKE_CUDA_TRY(cudaDeviceSynchronize());
   plan->bound = true;
   return CAKE_OK;
 }
@@ -891,6 +971,9 @@ void fill_reduce_params(const cake_matmul_rs* plan, unsigned long long parity, v
                         cake::ReduceParams* r) {
   const cake_matmul_rs_desc& d = plan->d;
   r->slots = static_cast<const char*>(plan->slots[d.rank]) + parity * d.world * plan->slot_stride;
+  r->flags = static_cast<const uint32_t*>(plan->flags[d.rank]);
+  r->epoch = static_cast<uint32_t>(plan->epoch);
+  r->quarters = plan->quarters;
   r->out = out;
   r->slot_stride = plan->slot_stride;
   const unsigned long long ms = d.wait_budget_ms > 0 ? static_cast<unsigned long long>(d.wait_budget_ms)
@@ -908,6 +991,7 @@ void fill_reduce_params(const cake_matmul_rs* plan, unsigned long long parity, v
   r->vec_ok = plan->out_cols % (16 / (int)plan->tsize) == 0 && plan->out_rows % 8 == 0 &&
               (d.world == 2 || d.world == 4 || d.world == 8);
   r->tile_n = d.tile_n;
+  r->tickets = plan->tickets;
   r->status = plan->status.dev;
 }
 
@@ -962,7 +1046,6 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
     p.store_f32 = plan->tsize == 4;
     const int epp = 16 / (int)plan->tsize;
     p.vec_ok = (plan->out_cols % epp == 0) && (d.n % epp == 0);
-    p.to_slots = p2p;
     p.status = plan->status.dev;
     unsigned long long parity = 0;
     if (d.world == 1) {
@@ -972,8 +1055,14 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
     } else {
       plan->epoch += 1;
       parity = plan->epoch & 1ull;
-      for (int o = 0; o < d.world; ++o)
+      for (int o = 0; o < d.world; ++o) {
         p.dest[o] = static_cast<char*>(plan->slots[o]) + (parity * d.world + d.rank) * plan->slot_stride;
+        p.flags_at[o] = static_cast<uint32_t*>(plan->flags[o]) + static_cast<size_t>(d.rank) * plan->quarters;
+      }
+      p.epoch = static_cast<uint32_t>(plan->epoch);
+      p.quarters = plan->quarters;
+      p.region_n_tiles = plan->region_n_tiles;
+      p.push_done = plan->tickets + 2;
       if (phases & kPhaseReduce) {
         p.reduce_in_kernel = 1;
         fill_reduce_params(plan, parity, out, &p.red);
@@ -1005,6 +1094,7 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
       p.region_order = aligned ? 1 : 0;
       // One wave of the grid covers grid / W tile groups: shift the owner sequence once per wave.
       p.owner_rotation = grid / d.world > 0 ? grid / d.world : 1;
+      if (p2p) p.publish = (p.region_order && p.tma_store) ? cake::kPublishPerTile : cake::kPublishAtEnd;
     }
     const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
     int32_t rc;
@@ -1020,7 +1110,7 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
     fill_reduce_params(plan, plan->epoch & 1ull, out, &r);
     const size_t chunks = (chunk_elems * plan->tsize + 4095) / 4096;
     int rgrid = (int)((chunks + 7) / 8);
-    if (rgrid > plan->sm_count * 4) rgrid = plan->sm_count * 4;
+    if (rgrid > plan->sm_count * 2) rgrid = plan->sm_count * 2;
     if (rgrid < 1) rgrid = 1;
     cake::cake_reduce_slots_sm100<<<rgrid, 256, 0, stream>>>(r);
     CAKE_CUDA_TRY(cudaGetLastError());

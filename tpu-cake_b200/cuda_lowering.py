@@ -49,9 +49,9 @@ class P2pCollectiveResources:
     ``pallas_bidirectional_ring_resources`` (src/tpu_cake/dialects/tpu_schedule.py:89-104)."""
 
     receive_slot_bytes: int  # 2 parities x W sources x local output (padded to 128 B), in the transport dtype
+    arrival_flag_bytes: int  # one 32-bit call number per source rank and quarter tile (32 rows x tile_n)
     remote_payload_bytes: int  # bytes this rank sends to other ranks per call
     reduce_read_bytes: int  # bytes the slot reduction reads per call
-    reduce_restore_bytes: int  # bytes of "not arrived" pattern it writes back over consumed pieces
 
 
 @dataclass(frozen=True)
@@ -133,11 +133,12 @@ class CudaMatmulRsPlan:
             return P2pCollectiveResources(0, 0, 0, 0)
         size = 2 if self.transport_dtype == "bf16" else 4
         local = self.output_local_shape[0] * self.output_local_shape[1] * size
+        quarters = -(-self.output_local_shape[0] // 128) * -(-self.output_local_shape[1] // self.tile_n) * 4
         return P2pCollectiveResources(
             receive_slot_bytes=2 * self.mesh_size * (-(-local // 128) * 128),
+            arrival_flag_bytes=-(-self.mesh_size * quarters * 4 // 128) * 128,
             remote_payload_bytes=(self.mesh_size - 1) * local,
             reduce_read_bytes=self.mesh_size * local,
-            reduce_restore_bytes=self.mesh_size * local,
         )
 
     # ------------------------------------------------------------------ identity
@@ -263,14 +264,18 @@ class MatmulRsExecutable:
             _native.check(self._lib.cake_matmul_rs_create(ctypes.byref(desc), ctypes.byref(handle)))
         self._handle = handle
         self._slots: SymmetricBuffer | None = None
+        self._flags: SymmetricBuffer | None = None
         self._partial: torch.Tensor | None = None
         if self._p2p:
             with torch.cuda.device(mesh.device):
                 self._slots = SymmetricBuffer(mesh, self._lib.cake_matmul_rs_slot_bytes(handle))
-                pointer_array = ctypes.c_void_p * mesh.world
-                _native.check(self._lib.cake_matmul_rs_bind_peers(handle, pointer_array(*self._slots.pointers)))
-            # bind_peers marks this rank's slots "nothing arrived": nobody may push before everybody has.
-            mesh.barrier()
+                self._flags = SymmetricBuffer(mesh, self._lib.cake_matmul_rs_flag_bytes(handle))
+            pointer_array = ctypes.c_void_p * mesh.world
+            _native.check(
+                self._lib.cake_matmul_rs_bind_peers(
+                    handle, pointer_array(*self._slots.pointers), pointer_array(*self._flags.pointers)
+                )
+            )
         elif mesh.world > 1:
             self._partial = torch.empty(
                 (mesh.world,) + plan.output_local_shape, dtype=_TORCH_DTYPE[plan.transport_dtype], device=mesh.device
@@ -343,9 +348,10 @@ class MatmulRsExecutable:
             torch.cuda.synchronize(self.mesh.device)
             self._lib.cake_matmul_rs_destroy(self._handle)
             self._handle = None
-        if self._slots is not None:
-            self._slots.close()
-        self._slots = None
+        for buffer in (self._slots, self._flags):
+            if buffer is not None:
+                buffer.close()
+        self._slots = self._flags = None
 
     def _check_operand(self, tensor: torch.Tensor, shape: tuple[int, int], role: str) -> None:
         if tensor.dtype != torch.bfloat16 or tuple(tensor.shape) != shape or not tensor.is_contiguous() or tensor.device != self.mesh.device:

@@ -121,7 +121,7 @@ class _EmulatedMesh:
         world = plan.mesh_size
         peer = plan.collective_implementation is not cuda_lowering.MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER
         self.peer = peer
-        self.handles, self.slots = [], []
+        self.handles, self.slots, self.flags = [], [], []
         for rank in range(world):
             desc = _native.MatmulRsDesc(
                 m=plan.partial_local_shape[0], n=plan.partial_local_shape[1], k_local=plan.lhs_local_shape[1], world=world, rank=rank,
@@ -135,12 +135,14 @@ class _EmulatedMesh:
             self.handles.append(handle)
         if peer:
             for handle in self.handles:
-                slot = ctypes.c_void_p()
+                slot, flag = ctypes.c_void_p(), ctypes.c_void_p()
                 _native.check(self.lib.cake_symm_alloc(self.lib.cake_matmul_rs_slot_bytes(handle), ctypes.byref(slot)))
+                _native.check(self.lib.cake_symm_alloc(self.lib.cake_matmul_rs_flag_bytes(handle), ctypes.byref(flag)))
                 self.slots.append(slot.value)
+                self.flags.append(flag.value)
             array = ctypes.c_void_p * world
             for handle in self.handles:
-                _native.check(self.lib.cake_matmul_rs_bind_peers(handle, array(*self.slots)))
+                _native.check(self.lib.cake_matmul_rs_bind_peers(handle, array(*self.slots), array(*self.flags)))
 
     def __call__(self, lhs_shards, rhs_shards) -> list[torch.Tensor]:
         plan, world = self.plan, self.plan.mesh_size
@@ -172,9 +174,9 @@ class _EmulatedMesh:
         torch.cuda.synchronize(self.device)
         for handle in self.handles:
             self.lib.cake_matmul_rs_destroy(handle)
-        for pointer in self.slots:
+        for pointer in self.slots + self.flags:
             self.lib.cake_symm_free(pointer)
-        self.handles, self.slots = [], []
+        self.handles, self.slots, self.flags = [], [], []
 
 
 def run_distributed_matmul(
