@@ -184,7 +184,8 @@ typedef struct cake_rpa_desc {
   int32_t rel_dim;        /* R for bias_mode 2 */
   int32_t update_cache;   /* 1 = first write new_k/new_v of each sequence at position kv_len-1 */
   int32_t kv_chunk_tokens;/* split-KV chunk; 0 = library default */
-  int32_t reserved;
+  int32_t wait_budget_ms; /* cake_rpa_decode_allgather_enqueue: how long the flag barrier waits for a
+                             peer before it gives up with CAKE_ERR_TIMEOUT; 0 = the default of 20 s */
 } cake_rpa_desc;
 
 typedef struct cake_rpa cake_rpa;
@@ -228,11 +229,15 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
  * a one-warp kernel publishes an epoch to every rank's flag array and, if `wait` is non-zero, waits
  * (bounded) until every rank has published. Replaces the "outputs stay sharded" end of the reference's
  * shard_map (src/tpu_cake/rpa_lowering.py:552-558) plus the all-gather the sharded configuration asks
- * for. gathered[r]: rank r's [world][num_seqs][q_heads][head_dim] bf16 buffer (q_heads = this shard's
- * query heads); flags[r]: rank r's CAKE_MAX_WORLD x uint64 array, zero before the first call; entries
- * [rank] are this rank's own allocations, the others peer mappings. `wait` = 0 lets a host that drives
- * several ranks from one process enqueue every rank before anybody waits. The first call allocates a
- * 64-byte device table. */
+ * for. gathered[r]: rank r's [2][world][num_seqs][q_heads][head_dim] bf16 buffer (q_heads = this
+ * shard's query heads): the n-th call on a plan (n = 1, 2, ...) fills half n & 1 on every rank, so a
+ * rank that runs one call ahead of a peer never overwrites what the peer's consumer of the previous
+ * call -- ordered on the peer's stream after that call -- is still reading. Every rank must make the
+ * same sequence of calls. flags[r]: rank r's CAKE_MAX_WORLD x uint64 array, zero before the first
+ * call; entries [rank] are this rank's own allocations, the others peer mappings. `wait` = 0 lets a
+ * host that drives several ranks from one process enqueue every rank before anybody waits. If a peer
+ * never publishes, the wait gives up after wait_budget_ms (cake_rpa_status: CAKE_ERR_TIMEOUT, code 2,
+ * detail1 = the missing rank). The first call allocates a 64-byte device table. */
 int32_t cake_rpa_decode_allgather_enqueue(cake_rpa* plan, const void* q, const void* new_k,
                                           const void* new_v, void* cache0, void* cache1,
                                           const int32_t* kv_lens, const int32_t* page_table,

@@ -87,7 +87,7 @@ def test_rpa_create_rejects_bad_descriptors(overrides, code, fragment):
     lib = _native.load()
     fields = dict(num_seqs=8, num_q_tokens=8, q_heads=8, kv_heads=2, head_dim=128, head_dim_padded=128, page_size=16,
                   cache_layout=1, table_layout=0, max_pages_per_seq=4, total_pages=64, sm_scale=0.1, bias_mode=0,
-                  bias_extent=0, rel_dim=0, update_cache=0, kv_chunk_tokens=0, reserved=0)
+                  bias_extent=0, rel_dim=0, update_cache=0, kv_chunk_tokens=0, wait_budget_ms=0)
     fields.update(overrides)
     desc = _native.RpaDesc(**fields)
     handle = ctypes.c_void_p()

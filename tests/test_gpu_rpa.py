@@ -240,6 +240,75 @@ def test_out_of_range_page_is_reported_not_faulted(cuda_device):
     executable.close()
 
 
+def test_length_beyond_the_page_table_row_is_reported_and_skipped(cuda_device):
+    """A sequence whose length needs more pages than its page-table row holds (the reference rejects
+    it on the host, src/tpu_cake/rpa_lowering.py:94-104): the device reports code 4 for that
+    sequence, leaves its output rows untouched and never reads the next sequence's row; the other
+    sequences are computed as usual. The check skips the access, so nothing faults."""
+    from tpu_cake_b200 import _native
+
+    case = random_case(9, num_seqs=3, q_heads=8, kv_heads=2, page_size=16, lengths=[40, 50, 33], pool_pages=16, poison=False)
+    query, key_cache, value_cache, table, lengths = case
+    bad = lengths.copy()
+    bad[1] = table.shape[1] * 16 + 1  # one token more than the row can address
+    for cache_layout in ("separate", "fused"):
+        plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+            name="long", schedule_sha256="0" * 64, query_shape=query.shape, cache_shape=key_cache.shape,
+            page_table_shape=table.shape, bias_shape=None, softmax_scale=1.0 / math.sqrt(128), cache_layout=cache_layout,
+        )
+        executable = plan.build(cuda_device)
+        if cache_layout == "fused":
+            caches = (to_device(oracle.fused_cache_from_separate(key_cache, value_cache), cuda_device), None)
+        else:
+            caches = (to_device(key_cache, cuda_device), to_device(value_cache, cuda_device))
+        out = torch.full(query.shape, 7.0, dtype=torch.bfloat16, device=cuda_device)
+        plan.invoke(executable, to_device(query, cuda_device), caches[0], caches[1], to_device(table, cuda_device),
+                    to_device(bad, cuda_device), out=out)
+        with pytest.raises(_native.CakeError) as raised:
+            executable.status()
+        assert raised.value.code == _native.CAKE_ERR_DEVICE_CHECK
+        actual = torch_to_bf16(out).astype(np.float32)
+        assert np.all(actual[1] == 7.0)
+        expected = expected_for(case)
+        assert_close(actual[[0, 2]], expected[[0, 2]])
+        executable.close()
+
+
+def test_gather_barrier_gives_up_when_a_peer_never_publishes(cuda_device):
+    """Two mesh positions, only position 0 runs, with a wait budget of 5 ms: its flag barrier gives
+    up (CAKE_ERR_TIMEOUT, code 2, missing rank 1) and the kernel returns -- nothing hangs -- its own
+    slice is in both gathered buffers, and the plan works again afterwards."""
+    from tpu_cake_b200 import _native
+
+    world, lengths = 2, [40, 700, 17]
+    case = random_case(32, num_seqs=len(lengths), q_heads=8, kv_heads=2, page_size=16, lengths=lengths, pool_pages=64, poison=False)
+    query, key_cache, value_cache, table, lens = case
+    expected = expected_for(case)
+    count, local_q = len(lengths), 4
+    gathered = [torch.zeros((2, world, count, local_q, 128), dtype=torch.bfloat16, device=cuda_device) for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int64, device=cuda_device) for _ in range(world)]
+    plan = rpa_cuda_lowering.CudaPagedAttentionPlan(
+        name="shard0", schedule_sha256="0" * 64, query_shape=(count, local_q, 128), cache_shape=(key_cache.shape[0], 16, 1, 128),
+        page_table_shape=table.shape, bias_shape=None, softmax_scale=1.0 / math.sqrt(128), cache_layout="fused", wait_budget_ms=5,
+    )
+    executable = plan.build(cuda_device)
+    q0 = to_device(np.ascontiguousarray(query[:, :local_q]), cuda_device)
+    cache0 = to_device(oracle.fused_cache_from_separate(key_cache[:, :, :1], value_cache[:, :, :1]), cuda_device)
+    table_d, lens_d = to_device(table, cuda_device), to_device(lens, cuda_device)
+    half = executable.enqueue_allgather(q0, cache0, None, lens_d, table_d, [g.data_ptr() for g in gathered], [f.data_ptr() for f in flags], world, 0)
+    with pytest.raises(_native.CakeError) as raised:
+        executable.status()
+    assert raised.value.code == _native.CAKE_ERR_TIMEOUT and "never heard from rank 1" in str(raised.value)
+    for buffer in gathered:
+        assert_close(torch_to_bf16(buffer[half, 0]).astype(np.float32), expected[:, :local_q])
+    # The peer "arrives": with its flag published the next call's barrier passes.
+    flags[0][1] = 2
+    half = executable.enqueue_allgather(q0, cache0, None, lens_d, table_d, [g.data_ptr() for g in gathered], [f.data_ptr() for f in flags], world, 0)
+    assert executable.status() == (0, 0, 0, 0)
+    assert_close(torch_to_bf16(gathered[1][half, 0]).astype(np.float32), expected[:, :local_q])
+    executable.close()
+
+
 def test_decode_configuration_full_size(cuda_device):
     """64 sequences, KV lengths uniform in [128, 8192], 32 / 8 heads, page 16, pool of 65536 pages:
     a sample of sequences (shortest, longest, and a few between) against the oracle."""
@@ -289,7 +358,7 @@ def test_sharded_decode_writes_every_ranks_gathered_buffer(cuda_device):
     expected = expected_for(case)  # [S, 16, 128]
     count, local_q, local_kv = len(lengths), 4, 1
     lib = _native.load()
-    gathered = [torch.zeros((world, count, local_q, 128), dtype=torch.bfloat16, device=cuda_device) for _ in range(world)]
+    gathered = [torch.zeros((2, world, count, local_q, 128), dtype=torch.bfloat16, device=cuda_device) for _ in range(world)]
     flags = [torch.zeros(8, dtype=torch.int64, device=cuda_device) for _ in range(world)]
     table_d, lens_d = to_device(table, cuda_device), to_device(lens, cuda_device)
     executables, keep = [], []
@@ -304,20 +373,32 @@ def test_sharded_decode_writes_every_ranks_gathered_buffer(cuda_device):
         fused = oracle.fused_cache_from_separate(key_cache[:, :, rank : rank + 1], value_cache[:, :, rank : rank + 1])
         cache_r = to_device(fused, cuda_device)
         keep.append((q_r, cache_r))
-        executable.enqueue_allgather(q_r, cache_r, None, lens_d, table_d, [g.data_ptr() for g in gathered],
-                                     [f.data_ptr() for f in flags], world, rank, wait=False)
+        half = executable.enqueue_allgather(q_r, cache_r, None, lens_d, table_d, [g.data_ptr() for g in gathered],
+                                            [f.data_ptr() for f in flags], world, rank, wait=False)
+        assert half == 1  # the first call fills half 1, the second half 0
         executables.append(executable)
+    torch.cuda.synchronize(cuda_device)
+    first = [torch_to_bf16(buffer[1]).astype(np.float32) for buffer in gathered]
+    # Second call with negated queries: it must land in the other half and leave the first alone.
+    for rank, (executable, (q_r, cache_r)) in enumerate(zip(executables, keep)):
+        half = executable.enqueue_allgather(-q_r, cache_r, None, lens_d, table_d, [g.data_ptr() for g in gathered],
+                                            [f.data_ptr() for f in flags], world, rank, wait=False)
+        assert half == 0
     torch.cuda.synchronize(cuda_device)
     for executable in executables:
         assert executable.status() == (0, 0, 0, 0)
         executable.close()
-    for buffer in gathered:
-        full = torch_to_bf16(buffer).astype(np.float32)  # [W, S, Hq/W, D]
+    for index, buffer in enumerate(gathered):
+        full = torch_to_bf16(buffer[1]).astype(np.float32)  # [W, S, Hq/W, D]
         assembled = np.concatenate([full[r] for r in range(world)], axis=1)
         assert_close(assembled, expected)
-        np.testing.assert_array_equal(full, torch_to_bf16(gathered[0]).astype(np.float32))
+        np.testing.assert_array_equal(full, first[index])
+        np.testing.assert_array_equal(full, torch_to_bf16(gathered[0][1]).astype(np.float32))
+        other = torch_to_bf16(buffer[0]).astype(np.float32)
+        assert np.isfinite(other).all() and not np.array_equal(other, full)
+        np.testing.assert_array_equal(other, torch_to_bf16(gathered[0][0]).astype(np.float32))
     for flag in flags:
-        assert flag.cpu().tolist()[:world] == [1] * world
+        assert flag.cpu().tolist()[:world] == [2] * world
 
 
 def test_chunk_search_on_the_decode_kernel(cuda_device, tmp_path):

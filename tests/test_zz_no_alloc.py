@@ -52,7 +52,7 @@ def descriptor(case, chunk: int) -> _native.RpaDesc:
         num_seqs=query.shape[0], num_q_tokens=query.shape[0], q_heads=query.shape[1], kv_heads=keys.shape[2], head_dim=128,
         head_dim_padded=128, page_size=keys.shape[1], cache_layout=_native.CAKE_RPA_CACHE_SEPARATE,
         table_layout=_native.CAKE_RPA_TABLE_2D, max_pages_per_seq=table.shape[1], total_pages=keys.shape[0],
-        sm_scale=1.0 / math.sqrt(128), bias_mode=0, bias_extent=0, rel_dim=0, update_cache=0, kv_chunk_tokens=chunk, reserved=0,
+        sm_scale=1.0 / math.sqrt(128), bias_mode=0, bias_extent=0, rel_dim=0, update_cache=0, kv_chunk_tokens=chunk, wait_budget_ms=0,
     )
 
 
@@ -96,7 +96,7 @@ def test_static_scratch_rejects_shapes_beyond_its_array(cuda_device):
     desc = _native.RpaDesc(
         num_seqs=256, num_q_tokens=256, q_heads=64, kv_heads=8, head_dim=128, head_dim_padded=128, page_size=32,
         cache_layout=_native.CAKE_RPA_CACHE_FUSED, table_layout=_native.CAKE_RPA_TABLE_2D, max_pages_per_seq=1024,
-        total_pages=262144, sm_scale=0.1, bias_mode=0, bias_extent=0, rel_dim=0, update_cache=0, kv_chunk_tokens=0, reserved=0,
+        total_pages=262144, sm_scale=0.1, bias_mode=0, bias_extent=0, rel_dim=0, update_cache=0, kv_chunk_tokens=0, wait_budget_ms=0,
     )
     code = lib.cake_rpa_decode_static_scratch(ctypes.byref(desc), *([None] * 13))
     assert code == _native.CAKE_ERR_UNSUPPORTED

@@ -118,7 +118,7 @@ class RpaDesc(ctypes.Structure):
         ("rel_dim", ctypes.c_int32),
         ("update_cache", ctypes.c_int32),
         ("kv_chunk_tokens", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("wait_budget_ms", ctypes.c_int32),
     ]
 
 

@@ -97,6 +97,21 @@ __device__ __forceinline__ void rpa_record(int32_t* status, int code, int d0, in
   }
 }
 
+// kv_lens[s] if the page table can hold that many tokens, else 0: a length that is negative or
+// larger than the table's room for the sequence (the 2-D table's row, or the rest of the flat index
+// array) would walk into another sequence's pages, so every kernel treats such a sequence as empty
+// and its output rows are left untouched. The planning kernels report it through the status word
+// (code 4); the reference rejects the same inputs on the host
+// (src/tpu_cake/rpa_lowering.py:94-104).
+__device__ __forceinline__ int rpa_checked_len(const RpaParams& p, int s) {
+  const int len = p.kv_lens[s];
+  if (len <= 0) return 0;
+  const long long pages = (static_cast<long long>(len) + p.page_size - 1) >> p.log2_ps;
+  if (p.table_layout == CAKE_RPA_TABLE_2D) return pages <= p.max_pages_per_seq ? len : 0;
+  const int start = p.cu_kv_lens[s];
+  return (start >= 0 && (start >> p.log2_ps) + pages <= p.table_len) ? len : 0;
+}
+
 // Builds the work-item table. Every sequence is cut into chunks of chunk_tokens; the full chunks of
 // all sequences come first in the queue and the shorter remainders last, so the kernel's tail is made
 // of small items. item_base[s] = index of the sequence's first full chunk, tail_cs[s] = index of its
@@ -109,9 +124,9 @@ __global__ void __launch_bounds__(256) cake_rpa_plan_sm100(RpaParams p) {
   const int tid = threadIdx.x;
   int local_full = 0;
   for (int s = tid; s < p.num_seqs; s += 256) {
-    const int len = p.kv_lens[s];
+    const int len = rpa_checked_len(p, s);
     if (len > 0) local_full += len / p.chunk_tokens;
-    if (len < 0) rpa_record(p.status, 4, s, len, 0);
+    if (len != p.kv_lens[s]) rpa_record(p.status, 4, s, p.kv_lens[s], 0);
   }
   s_full[tid] = local_full;
   if (tid == 0) {
@@ -131,7 +146,7 @@ __global__ void __launch_bounds__(256) cake_rpa_plan_sm100(RpaParams p) {
     const int s = base + tid;
     int nf = 0, ht = 0, len = 0;
     if (s < p.num_seqs) {
-      len = p.kv_lens[s];
+      len = rpa_checked_len(p, s);
       if (len > 0) {
         nf = len / p.chunk_tokens;
         ht = (len - nf * p.chunk_tokens) > 0 ? 1 : 0;
@@ -175,6 +190,7 @@ __global__ void __launch_bounds__(256) cake_rpa_plan_sm100(RpaParams p) {
 // Logical page slot -> physical page for token `tok` of sequence `s`.
 __device__ __forceinline__ int rpa_page_lookup(const RpaParams& p, int s, int page_slot) {
   if (p.table_layout == CAKE_RPA_TABLE_2D) {
+    if (page_slot < 0 || page_slot >= p.max_pages_per_seq) return -1;
     return p.page_table[static_cast<size_t>(s) * p.max_pages_per_seq + page_slot];
   }
   const int idx = (p.cu_kv_lens[s] >> p.log2_ps) + page_slot;
@@ -189,7 +205,7 @@ __global__ void cake_rpa_cache_update_sm100(RpaParams p, const __nv_bfloat16* ne
                                             const __nv_bfloat16* new_v, __nv_bfloat16* cache0,
                                             __nv_bfloat16* cache1) {
   const int s = blockIdx.x;
-  const int len = p.kv_lens[s];
+  const int len = rpa_checked_len(p, s);
   if (len <= 0) return;
   const int pos = len - 1;
   const int page = rpa_page_lookup(p, s, pos >> p.log2_ps);
@@ -748,16 +764,20 @@ __global__ void __launch_bounds__(128) cake_rpa_combine_sm100(const RpaParams p)
   const int r = unit - pair * p.group;
   const int s = pair / p.kv_heads;
   const int h = pair - s * p.kv_heads;
-  const int len = p.kv_lens[s];
+  const int len = rpa_checked_len(p, s);
   const int n = len > 0 ? (len + p.chunk_tokens - 1) / p.chunk_tokens : 0;
   if (n > 1) rpa_merge(p, s, h, r, n, p.item_base[s], p.tail_cs[s], threadIdx.x & 31);
 }
 
 // After the decode and combine kernels have written this rank's output slice into every rank's
-// gathered buffer: tell every rank (release at system scope, after the kernel boundary ordered the
-// slice's stores before this kernel) and wait, bounded, until every rank has told us.
+// gathered buffer: tell every rank (release at system scope, after the wait on the kernels before
+// ordered the slice's stores before this kernel) and wait, bounded, until every rank has told us.
+// Launched with programmatic stream serialization, so its launch latency hides behind the combine
+// kernel; the wait below is where it meets it.
 __global__ void cake_rpa_gather_sync_sm100(unsigned long long* const* flags_of, int world, int rank,
-                                           unsigned long long epoch, int wait, int32_t* status) {
+                                           unsigned long long epoch, int wait,
+                                           unsigned long long budget_ns, int32_t* status) {
+  grid_dependency_wait();
   const int r = threadIdx.x;
   if (r >= world) return;
   __threadfence_system();
@@ -765,7 +785,7 @@ __global__ void cake_rpa_gather_sync_sm100(unsigned long long* const* flags_of, 
   if (!wait) return;
   const unsigned long long start = global_timer_ns();
   while (ld_acquire_sys_u64(flags_of[rank] + r) < epoch) {
-    if (global_timer_ns() - start > 20000000000ull) {
+    if (global_timer_ns() - start > budget_ns) {
       rpa_record(status, 2, rank, r, 0);
       return;
     }
@@ -811,6 +831,19 @@ struct cake_rpa {
 
 namespace {
 using cake::fail;
+
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of the (function, device)
+// pair: remember per device ordinal whether it has been set.
+template <typename Kernel>
+int32_t opt_in_shared_memory(Kernel kernel, int bytes, bool (&configured)[64]) {
+  int device = 0;
+  CAKE_CUDA_TRY(cudaGetDevice(&device));
+  const bool tracked = device >= 0 && device < 64;
+  if (tracked && configured[device]) return CAKE_OK;
+  CAKE_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (tracked) configured[device] = true;
+  return CAKE_OK;
+}
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -1030,11 +1063,10 @@ int32_t cake_rpa_decode_enqueue(cake_rpa* plan, const void* q, const void* new_k
     CAKE_CUDA_TRY(cudaGetLastError());
     ++launches;
   }
-  static bool configured = false;
-  if (!configured) {
-    CAKE_CUDA_TRY(cudaFuncSetAttribute(cake::cake_rpa_decode_sm100,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, cake::kRpaSmemBytes));
-    configured = true;
+  {
+    static bool configured[64] = {};
+    int32_t arc = opt_in_shared_memory(cake::cake_rpa_decode_sm100, cake::kRpaSmemBytes, configured);
+    if (arc) return arc;
   }
   // Decode and combine are launched with programmatic stream serialization: each may be scheduled
   // while its predecessor still runs and waits on the device (griddepcontrol.wait) before reading
@@ -1074,11 +1106,14 @@ int32_t cake_rpa_decode_allgather_enqueue(cake_rpa* plan, const void* q, const v
   const cake_rpa_desc& d = plan->d;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const size_t slice_bytes = static_cast<size_t>(d.num_seqs) * d.q_heads * d.head_dim * 2;
+  // Call n writes half n & 1 of every rank's buffer: a rank that is one call ahead of a peer
+  // cannot overwrite what the peer's consumer of the previous call is still reading.
+  const size_t half_offset = ((plan->gather_epoch + 1) & 1ull) * world * slice_bytes;
   // Own buffer first, so the local copy does not wait behind link traffic.
   for (int i = 0; i < world; ++i) {
     const int r = (rank + i) % world;
     if (!gathered[r] || !flags[r]) return fail(CAKE_ERR_INVALID_ARGUMENT, "rpa all-gather: missing buffer of rank %d", r);
-    plan->gather_out[i] = static_cast<char*>(gathered[r]) + rank * slice_bytes;
+    plan->gather_out[i] = static_cast<char*>(gathered[r]) + half_offset + rank * slice_bytes;
   }
   if (!plan->gather_flag_table) {
     CAKE_CUDA_TRY(cudaMalloc(&plan->gather_flag_table, sizeof(void*) * CAKE_MAX_WORLD));
@@ -1095,9 +1130,21 @@ int32_t cake_rpa_decode_allgather_enqueue(cake_rpa* plan, const void* q, const v
   plan->gather_world = 0;
   if (rc) return rc;
   plan->gather_epoch += 1;
-  cake::cake_rpa_gather_sync_sm100<<<1, 32, 0, stream>>>(plan->gather_flag_table, world, rank, plan->gather_epoch, wait,
-                                                         plan->status.dev);
-  CAKE_CUDA_TRY(cudaGetLastError());
+  const unsigned long long budget_ns =
+      (d.wait_budget_ms > 0 ? static_cast<unsigned long long>(d.wait_budget_ms) : 20000ull) * 1000000ull;
+  cudaLaunchAttribute overlap_attr;
+  overlap_attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  overlap_attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config;
+  memset(&config, 0, sizeof(config));
+  config.stream = stream;
+  config.attrs = &overlap_attr;
+  config.numAttrs = 1;
+  config.gridDim = dim3(1);
+  config.blockDim = dim3(32);
+  CAKE_CUDA_TRY(cudaLaunchKernelEx(&config, cake::cake_rpa_gather_sync_sm100,
+                                   static_cast<unsigned long long* const*>(plan->gather_flag_table), world, rank,
+                                   plan->gather_epoch, wait, budget_ns, plan->status.dev));
   plan->launches += 1;
   return CAKE_OK;
 }
@@ -1218,12 +1265,9 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
     launches += plan->launches;
   }
   if (num_decode_seqs < d.num_seqs) {
-    static bool configured = false;
-    if (!configured) {
-      CAKE_CUDA_TRY(cudaFuncSetAttribute(cake::cake_rpa_prefill_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         cake::kPfSmemBytes));
-      configured = true;
-    }
+    static bool configured[64] = {};
+    int32_t arc = opt_in_shared_memory(cake::cake_rpa_prefill_sm100, cake::kPfSmemBytes, configured);
+    if (arc) return arc;
     cake::cake_rpa_prefill_sm100<<<plan->sm_count, cake::kPfThreads, cake::kPfSmemBytes, stream>>>(
         plan->tmap_q, plan->tmap_pf_k, plan->tmap_pf_v, pp);
     CAKE_CUDA_TRY(cudaGetLastError());

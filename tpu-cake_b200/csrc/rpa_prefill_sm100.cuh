@@ -115,9 +115,9 @@ __global__ void cake_rpa_ragged_update_sm100(PrefillParams pp, const __nv_bfloat
   const int s = lo;
   const int q_len = pp.cu_q_lens[s + 1] - pp.cu_q_lens[s];
   const int i = t - pp.cu_q_lens[s];
-  const int pos = p.kv_lens[s] - q_len + i;
+  const int pos = rpa_checked_len(p, s) - q_len + i;
   if (i >= q_len) return;  // tokens past the last sequence
-  if (pos < 0) {
+  if (pos < 0) {  // also: a length the page table cannot hold (checked length 0)
     if (threadIdx.x == 0) rpa_record(p.status, 4, s, p.kv_lens[s], q_len);
     return;
   }
@@ -158,8 +158,8 @@ __global__ void __launch_bounds__(256) cake_rpa_prefill_plan_sm100(PrefillParams
   int local_max = 0;
   for (int s = threadIdx.x; s < p.num_seqs; s += blockDim.x) {
     const int q_len = pp.cu_q_lens[s + 1] - pp.cu_q_lens[s];
-    const int len = p.kv_lens[s];
-    if (q_len < 0 || len < q_len || (s < pp.first_seq && q_len != 1) || pp.cu_q_lens[s + 1] > pp.num_q_tokens)
+    const int len = rpa_checked_len(p, s);
+    if (len != p.kv_lens[s] || q_len < 0 || len < q_len || (s < pp.first_seq && q_len != 1) || pp.cu_q_lens[s + 1] > pp.num_q_tokens)
       rpa_record(p.status, 4, s, len, q_len);
     else if (s >= pp.first_seq)
       local_max = max(local_max, (q_len + kPfTileQ - 1) / kPfTileQ);
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(256) cake_rpa_prefill_plan_sm100(PrefillParams
   for (int r = 0; r < s_max_tiles; ++r) {
     for (int s = pp.first_seq; s < p.num_seqs; ++s) {
       const int q_len = pp.cu_q_lens[s + 1] - pp.cu_q_lens[s];
-      const int len = p.kv_lens[s];
+      const int len = rpa_checked_len(p, s);
       if (q_len <= 0 || len < q_len) continue;
       const int tiles = (q_len + kPfTileQ - 1) / kPfTileQ;
       if (tiles <= r) continue;

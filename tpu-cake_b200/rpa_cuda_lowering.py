@@ -253,18 +253,20 @@ class RpaDecodeExecutable:
             _native.check(self._lib.cake_rpa_create(ctypes.byref(desc), ctypes.byref(handle)))
         self._handle = handle
         self.workspace = torch.empty(self._lib.cake_rpa_workspace_bytes(handle), dtype=torch.uint8, device=device)
+        self.gather_calls = 0  # all-gather calls made so far: call n fills half n & 1 of the gathered buffers
 
     def enqueue(self, q, new_k, new_v, cache0, cache1, kv_lens, page_table, cu_kv_lens, bias0, bias1, out) -> None:
         def ptr(t):
             return None if t is None else t.data_ptr()
 
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        _native.check(
-            self._lib.cake_rpa_decode_enqueue(
-                self._handle, ptr(q), ptr(new_k), ptr(new_v), ptr(cache0), ptr(cache1), ptr(kv_lens),
-                ptr(page_table), ptr(cu_kv_lens), ptr(bias0), ptr(bias1), ptr(out), self.workspace.data_ptr(), stream,
+        with torch.cuda.device(self.device):  # the library launches on the current device
+            _native.check(
+                self._lib.cake_rpa_decode_enqueue(
+                    self._handle, ptr(q), ptr(new_k), ptr(new_v), ptr(cache0), ptr(cache1), ptr(kv_lens),
+                    ptr(page_table), ptr(cu_kv_lens), ptr(bias0), ptr(bias1), ptr(out), self.workspace.data_ptr(), stream,
+                )
             )
-        )
 
     def enqueue_mixed(self, q, new_k, new_v, cache0, cache1, kv_lens, page_table, cu_kv_lens, cu_q_lens, num_decode_seqs: int, out) -> None:
         """Ragged batch: ``num_decode_seqs`` one-token sequences first, prefill sequences after."""
@@ -272,26 +274,32 @@ class RpaDecodeExecutable:
             return None if t is None else t.data_ptr()
 
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        _native.check(
-            self._lib.cake_rpa_mixed_enqueue(
-                self._handle, ptr(q), ptr(new_k), ptr(new_v), ptr(cache0), ptr(cache1), ptr(kv_lens), ptr(page_table),
-                ptr(cu_kv_lens), ptr(cu_q_lens), int(num_decode_seqs), ptr(out), self.workspace.data_ptr(), stream,
+        with torch.cuda.device(self.device):
+            _native.check(
+                self._lib.cake_rpa_mixed_enqueue(
+                    self._handle, ptr(q), ptr(new_k), ptr(new_v), ptr(cache0), ptr(cache1), ptr(kv_lens), ptr(page_table),
+                    ptr(cu_kv_lens), ptr(cu_q_lens), int(num_decode_seqs), ptr(out), self.workspace.data_ptr(), stream,
+                )
             )
-        )
 
     def enqueue_allgather(self, q, cache0, cache1, kv_lens, page_table, gathered_pointers: list[int], flag_pointers: list[int],
-                          world: int, rank: int, *, wait: bool = True) -> None:
+                          world: int, rank: int, *, wait: bool = True) -> int:
         """Decode this rank's KV-head shard and write its outputs into every rank's gathered buffer
-        (``gathered_pointers[r]`` / ``flag_pointers[r]``: rank r's buffers as mapped in this process)."""
+        (``gathered_pointers[r]`` / ``flag_pointers[r]``: rank r's buffers as mapped in this process).
+        The buffers hold two halves of [world, num_seqs, q_heads, head_dim]; returns the half this
+        call fills (calls alternate, so a consumer of one call can still read while the next runs)."""
         array = ctypes.c_void_p * world
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        _native.check(
-            self._lib.cake_rpa_decode_allgather_enqueue(
-                self._handle, q.data_ptr(), None, None, cache0.data_ptr(), None if cache1 is None else cache1.data_ptr(),
-                kv_lens.data_ptr(), page_table.data_ptr(), None, None, None, array(*gathered_pointers), array(*flag_pointers),
-                world, rank, 1 if wait else 0, self.workspace.data_ptr(), stream,
+        with torch.cuda.device(self.device):
+            _native.check(
+                self._lib.cake_rpa_decode_allgather_enqueue(
+                    self._handle, q.data_ptr(), None, None, cache0.data_ptr(), None if cache1 is None else cache1.data_ptr(),
+                    kv_lens.data_ptr(), page_table.data_ptr(), None, None, None, array(*gathered_pointers), array(*flag_pointers),
+                    world, rank, 1 if wait else 0, self.workspace.data_ptr(), stream,
+                )
             )
-        )
+        self.gather_calls += 1
+        return self.gather_calls & 1
 
     def status(self) -> tuple[int, int, int, int]:
         word = _native.CakeStatus()
@@ -339,6 +347,7 @@ class CudaFusedRpaPlan:
     softmax_dtype: str = "float32"
     sliding_window: int = 0
     kv_chunk_tokens: int = 0
+    wait_budget_ms: int = 0  # bound on the all-gather flag barrier (0 = 20 s)
     update_cache: bool = True
     execution_scope: str = "local-shard-caller-owned-sharding"
 
@@ -409,7 +418,7 @@ class CudaFusedRpaPlan:
             sm_scale=self.softmax_scale, bias_mode=2 if with_bias else 0,
             bias_extent=self.relative_projection_shape[1] if with_bias else 0,
             rel_dim=self.relative_states_shape[2] if with_bias else 0, update_cache=1 if self.update_cache else 0,
-            kv_chunk_tokens=self.kv_chunk_tokens, reserved=0,
+            kv_chunk_tokens=self.kv_chunk_tokens, wait_budget_ms=self.wait_budget_ms,
         )
         return RpaDecodeExecutable(desc, device)
 
@@ -456,6 +465,7 @@ class CudaMixedRpaPlan:
     softmax_scale: float
     causal: int = 1
     kv_chunk_tokens: int = 0
+    wait_budget_ms: int = 0  # bound on the all-gather flag barrier (0 = 20 s)
     update_cache: bool = True
 
     def __post_init__(self) -> None:
@@ -501,7 +511,7 @@ class CudaMixedRpaPlan:
             head_dim_padded=dim_padded, page_size=page_size, cache_layout=_native.CAKE_RPA_CACHE_FUSED,
             table_layout=_native.CAKE_RPA_TABLE_FLAT, max_pages_per_seq=self.page_indices_shape[0], total_pages=pages,
             sm_scale=self.softmax_scale, bias_mode=0, bias_extent=0, rel_dim=0, update_cache=1 if self.update_cache else 0,
-            kv_chunk_tokens=self.kv_chunk_tokens, reserved=0,
+            kv_chunk_tokens=self.kv_chunk_tokens, wait_budget_ms=self.wait_budget_ms,
         )
         return RpaDecodeExecutable(desc, device)
 
@@ -691,6 +701,7 @@ class CudaPagedAttentionPlan:
     bias_shape: tuple[int, int] | None
     softmax_scale: float
     kv_chunk_tokens: int = 0
+    wait_budget_ms: int = 0  # bound on the all-gather flag barrier (0 = 20 s)
     cache_layout: str = "separate"  # or "fused": one [pages, page_size, kv_heads, 2, head_dim] tensor
 
     def __post_init__(self) -> None:
@@ -726,7 +737,7 @@ class CudaPagedAttentionPlan:
             table_layout=_native.CAKE_RPA_TABLE_2D, max_pages_per_seq=self.page_table_shape[1], total_pages=pages,
             sm_scale=self.softmax_scale, bias_mode=1 if self.bias_shape is not None else 0,
             bias_extent=self.bias_shape[1] if self.bias_shape is not None else 0, rel_dim=0, update_cache=0,
-            kv_chunk_tokens=self.kv_chunk_tokens, reserved=0,
+            kv_chunk_tokens=self.kv_chunk_tokens, wait_budget_ms=self.wait_budget_ms,
         )
         return RpaDecodeExecutable(desc, device)
 
