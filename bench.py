@@ -10,8 +10,15 @@ over the N ranks, result reduce-scattered along M into bf16 [8192/N, 8192] per G
 pass of cake_matmul_rs_sm100 (+ cake_reduce_slots_sm100 when N > 1). The total work is fixed, so
 scaling is "strong". A second object, "rpa_decode", reports the ragged-paged-attention decode
 (HBM-bound): 64 sequences on one GPU, or the 256-sequence configuration with KV heads sharded over
-the ranks and outputs all-gathered. A third object at N = 1, "rpa_mixed", reports the mixed batch
-(8 prefill + 120 decode sequences): the whole step, and its decode and prefill parts alone.
+the ranks and outputs all-gathered ("rpa_decode_sharded", at every N including 1, so its curve has
+its own anchor). A third object at N = 1, "rpa_mixed", reports the mixed batch (8 prefill + 120
+decode sequences): the whole step, and its decode and prefill parts alone.
+
+Parity: outside the timed regions every rank compares sampled rows of its local matmul output with
+the oracle's split-K reduce-scatter (plus the row-sum identity over the whole local output), and
+sampled sequences of the attention result -- the gathered buffer when sharded -- with the oracle,
+three different steps in a row; the line carries "parity" objects and the exit code is non-zero if
+any rank disagrees.
 
 Timing: CUDA events on the stream the kernels are launched on, one event pair per step, a write of
 a buffer larger than L2 between steps, barrier + synchronize on both sides of the timed region,
@@ -118,6 +125,49 @@ def reduce_max(mesh, value: float) -> float:
     return float(t.item())
 
 
+def all_ranks_ok(mesh, ok: bool) -> bool:
+    return reduce_max(mesh, 0.0 if ok else 1.0) == 0.0
+
+
+def matmul_config(world: int, collective: str) -> dict:
+    """The workload description both arms print (the reference arm names the same configuration)."""
+    return {
+        "workload": f"K-sharded bf16 matmul {M}x{K}x{N} + reduce-scatter along M to bf16 [{M // world},{N}] per GPU",
+        "m": M, "k": K, "n": N, "mesh": world, "accumulate": "f32", "collective": collective,
+        "l2": "256 MiB flush between steps",
+    }
+
+
+def host_threads() -> int:
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+class blas_threads:
+    """Runs the numpy oracle on every host core this process may use, whatever OMP_NUM_THREADS the
+    launcher exported (torch.distributed.run sets it to 1), and reports the count actually in use."""
+
+    def __init__(self):
+        self.used = 1
+        self._limit = None
+
+    def __enter__(self):
+        try:
+            import threadpoolctl
+
+            self._limit = threadpoolctl.threadpool_limits(limits=host_threads())
+            self._limit.__enter__()
+            pools = [pool for pool in threadpoolctl.threadpool_info() if pool.get("user_api") == "blas"]
+            self.used = max([int(pool.get("num_threads", 1)) for pool in pools] or [1])
+        except Exception:  # noqa: BLE001 - threadpoolctl absent or no BLAS pool: single-threaded numpy
+            self.used = 1
+        return self
+
+    def __exit__(self, *exc):
+        if self._limit is not None:
+            self._limit.__exit__(*exc)
+        return False
+
+
 def timed_steps(mesh, step, steps: int, warmup: int, flush) -> tuple[float, list[float]]:
     """Runs ``warmup`` untimed and ``steps`` timed calls of ``step``; returns (total ms = max over
     ranks of the sum of per-step device times, this rank's per-step ms)."""
@@ -142,40 +192,42 @@ def timed_steps(mesh, step, steps: int, warmup: int, flush) -> tuple[float, list
     return reduce_max(mesh, sum(per_step)), per_step
 
 
-def cpu_matmul_sample(rows: int, threads: int) -> dict:
+def cpu_matmul_sample(rows: int) -> dict:
     """Times the oracle (numpy float32 matmul on bf16-valued inputs) on ``rows`` lhs rows of the
-    headline shape; all host threads numpy's BLAS uses."""
+    headline shape, on every host core this process may use."""
     from oracle import matmul_rs
 
     generator = np.random.default_rng(0)
     lhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(rows, K)).astype(np.float32))
     rhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(K, N)).astype(np.float32))
-    matmul_rs.matmul_reference(lhs[:64], rhs)
-    best = float("inf")
-    repeats = 0
-    budget_started = time.perf_counter()
-    while repeats < 3 or (time.perf_counter() - budget_started < 10.0 and repeats < 20):
-        started = time.perf_counter()
-        matmul_rs.matmul_reference(lhs, rhs)
-        best = min(best, time.perf_counter() - started)
-        repeats += 1
+    with blas_threads() as pool:
+        matmul_rs.matmul_reference(lhs[:64], rhs)
+        best = float("inf")
+        repeats = 0
+        budget_started = time.perf_counter()
+        while repeats < 3 or (time.perf_counter() - budget_started < 10.0 and repeats < 20):
+            started = time.perf_counter()
+            matmul_rs.matmul_reference(lhs, rhs)
+            best = min(best, time.perf_counter() - started)
+            repeats += 1
     return {
         "value": 2.0 * rows * K * N / best / 1e12,
         "unit": "TFLOP/s",
-        "cores": threads,
+        "cores": pool.used,
         "kind": "port",
         "sample": f"{rows} of {M} lhs rows of the {M}x{K}x{N} product, numpy float32 matmul, best of {repeats}",
         "seconds": best,
     }
 
 
-def cpu_rpa_sample(lengths: np.ndarray, table: np.ndarray, config, sequences: int, threads: int) -> dict:
+def cpu_rpa_sample(lengths: np.ndarray, table: np.ndarray, config, sequences: int) -> dict:
     from oracle import rpa
     from tpu_cake_b200 import workloads
 
     generator = np.random.default_rng(1)
     order = np.argsort(lengths)[:: max(1, len(lengths) // sequences)][:sequences]
     total_bytes, seconds = 0, 0.0
+    pool = blas_threads().__enter__()
     for s in order:
         count = -(-int(lengths[s]) // config.page_size)
         keys = generator.standard_normal((count, config.page_size, config.kv_heads, config.head_dim), dtype=np.float32)
@@ -185,10 +237,11 @@ def cpu_rpa_sample(lengths: np.ndarray, table: np.ndarray, config, sequences: in
         rpa.rpa_separate(query, keys, values, np.arange(count, dtype=np.int32)[None, :], lengths[s : s + 1], None, scale=config.softmax_scale)
         seconds += time.perf_counter() - started
         total_bytes += workloads.decode_algorithmic_bytes(lengths[s : s + 1], config.q_heads, config.kv_heads, config.head_dim, config.page_size)
+    pool.__exit__(None, None, None)
     return {
         "value": total_bytes / seconds / 1e9,
         "unit": "GB/s",
-        "cores": threads,
+        "cores": pool.used,
         "kind": "port",
         "sample": f"{len(order)} of {len(lengths)} sequences of {config.name}, numpy oracle, algorithmic bf16 bytes / wall time",
         "seconds": seconds,
@@ -215,13 +268,25 @@ def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
     )
     executable, _ = plan.build(mesh=mesh)
     k_local = K // world
+    # Every rank draws the whole operands from the same seed and keeps its K slice; what the parity
+    # check needs of the whole (sampled lhs rows, rhs, the row-sum identity) is taken before the rest
+    # is freed.
     generator = torch.Generator(device=mesh.device).manual_seed(20261125)
     lhs_full = (torch.randn((M, K), generator=generator, device=mesh.device) * K**-0.5).to(torch.bfloat16)
     lhs = lhs_full[:, mesh.rank * k_local : (mesh.rank + 1) * k_local].contiguous()
-    del lhs_full
     rhs_full = (torch.randn((K, N), generator=generator, device=mesh.device) * K**-0.5).to(torch.bfloat16)
     rhs = rhs_full[mesh.rank * k_local : (mesh.rank + 1) * k_local].contiguous()
-    del rhs_full
+    local_rows = M // world
+    sampled = sorted({0, 1, 127, 128, local_rows // 2, local_rows - 129, local_rows - 2, local_rows - 1})
+    sampled_rows = torch.tensor(sampled, device=mesh.device)
+    parity_inputs = {
+        "rows": sampled,
+        "lhs_rows": lhs_full[mesh.rank * local_rows + sampled_rows].float().cpu().numpy(),
+        "rhs": rhs_full.float().cpu().numpy(),
+        # C 1 = A (B 1): the row sums this rank's local output must have, in float64.
+        "row_sums": lhs_full[mesh.rank * local_rows : (mesh.rank + 1) * local_rows].double() @ rhs_full.double().sum(dim=1),
+    }
+    del lhs_full, rhs_full
     out = torch.empty(plan.output_local_shape, dtype=torch.bfloat16, device=mesh.device)
     flush_buffer = torch.empty(256 << 20, dtype=torch.uint8, device=mesh.device)
 
@@ -236,6 +301,8 @@ def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
     total_ms, per_step = timed_steps(mesh, step, args.steps, args.warmup, flush)
     clocks = sampler.stop()
     executable.status()
+    parity = matmul_parity(mesh, plan, out, parity_inputs)
+    del parity_inputs
     launches = executable.launches_per_call * args.steps
     flops_total = 2.0 * M * N * K
     ms_per_step = total_ms / args.steps
@@ -315,16 +382,45 @@ def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
     return {
         "value": value, "ms_per_step": ms_per_step, "roofline": roofline, "e2e": e2e, "clocks": clocks,
         "gpu_launches": launches, "strategy": args.strategy if world > 1 else "single", "phases": phases,
+        "parity": parity,
     }
 
 
-def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
+def matmul_parity(mesh, plan, out, inputs) -> dict:
+    """This rank's local output of the last timed step against the oracle: the sampled rows must
+    equal the rank-ordered sum of the W split-K partials (rounded to the transport and output dtypes
+    as the device does) within max-abs 2e-2 and relative-L2 1e-2, and every row's sum must satisfy
+    C 1 = A (B 1) within 2e-2 (the accumulated bf16 rounding of 8192 outputs of magnitude ~1/128).
+    All ranks check; the verdict is the logical AND, the errors the maxima over ranks."""
+    import torch
+
+    from oracle import matmul_rs
+
+    expected = matmul_rs.reduced_rows(inputs["lhs_rows"], inputs["rhs"], world=mesh.world,
+                                      transport_dtype=plan.transport_dtype if mesh.world > 1 else "f32", out_dtype=plan.output_dtype)
+    rows = torch.tensor(inputs["rows"], device=out.device)
+    actual = out[rows].float().cpu().numpy()
+    max_abs = matmul_rs.max_abs_error(actual, expected)
+    rel_l2 = matmul_rs.relative_l2_error(actual, expected)
+    row_sum_error = float((out.double().sum(dim=1) - inputs["row_sums"]).abs().max().item())
+    finite = bool(torch.isfinite(out.float()).all().item())
+    ok = finite and max_abs <= 2e-2 and rel_l2 <= 1e-2 and row_sum_error <= 2e-2
+    return {
+        "checked": f"{len(inputs['rows'])} rows x {out.shape[1]} columns per rank against the oracle's split-K reduce-scatter, "
+                   f"and the row-sum identity over all {out.shape[0]} local rows, on every rank",
+        "max_abs": reduce_max(mesh, max_abs), "rel_l2": reduce_max(mesh, rel_l2), "row_sum_max_abs": reduce_max(mesh, row_sum_error),
+        "tolerance": {"max_abs": 2e-2, "rel_l2": 1e-2, "row_sum_max_abs": 2e-2}, "ok": all_ranks_ok(mesh, ok),
+    }
+
+
+def bench_rpa(mesh, args, peaks, peak_kind, config) -> dict:
+    """Decode step of ``config`` with its KV heads sharded over the mesh (world 1: all heads here, no
+    collective)."""
     import torch
 
     from tpu_cake_b200 import rpa_cuda_lowering, workloads
 
     world = mesh.world
-    config = workloads.DECODE_64 if world == 1 else workloads.DECODE_SHARDED_256
     if args.rpa_pool_pages:
         import dataclasses
 
@@ -356,23 +452,35 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
         # Outputs are written straight into every rank's gathered buffer over peer memory.
         from tpu_cake_b200.mesh import SymmetricBuffer
 
-        gather_buffer = SymmetricBuffer(mesh, world * config.num_seqs * local_q * config.head_dim * 2)
+        # two halves: call n fills half n & 1, so a rank one call ahead never disturbs a peer's reader
+        gather_buffer = SymmetricBuffer(mesh, 2 * world * config.num_seqs * local_q * config.head_dim * 2)
         gather_flags = SymmetricBuffer(mesh, 64)
+        gather_view = gather_buffer.as_tensor(torch.bfloat16, (2, world, config.num_seqs, local_q, config.head_dim))
     flush_buffer = torch.empty(256 << 20, dtype=torch.uint8, device=mesh.device)
 
     def flush():
         flush_buffer.fill_(1)
 
+    last_half = [0]
+
     def step():
         if gather_buffer is not None:
-            executable.enqueue_allgather(query, cache, None, lengths_d, table_d, gather_buffer.pointers, gather_flags.pointers,
-                                         world, mesh.rank)
+            last_half[0] = executable.enqueue_allgather(query, cache, None, lengths_d, table_d, gather_buffer.pointers,
+                                                        gather_flags.pointers, world, mesh.rank)
             return
         plan.invoke(executable, query, cache, None, table_d, lengths_d, out=out)
         if world > 1:
             import torch.distributed as dist
 
             dist.all_gather_into_tensor(gathered, out, group=mesh.group)
+
+    def result_rows(sample):
+        """[n, all query heads, head_dim] of the sequences in ``sample`` from the step just enqueued."""
+        if gather_buffer is not None:
+            return gather_view[last_half[0]][:, sample].permute(1, 0, 2, 3).reshape(len(sample), config.q_heads, config.head_dim)
+        if gathered is not None:
+            return gathered[:, sample].permute(1, 0, 2, 3).reshape(len(sample), config.q_heads, config.head_dim)
+        return out[sample]
 
     steps = max(args.steps, 10)
     launch_mode = "stream"
@@ -390,6 +498,8 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
 
         launch_mode = "cuda-graph"
     total_ms, per_step = timed_steps(mesh, step, steps, max(args.warmup, 3), flush)
+    executable.status()
+    parity = rpa_parity(mesh, config, lengths, table, cache, query, step, result_rows)
     executable.status()
     bytes_total = workloads.decode_algorithmic_bytes(lengths, config.q_heads, config.kv_heads, config.head_dim, config.page_size)
     ms_per_step = total_ms / steps
@@ -412,13 +522,14 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
             "algorithmic_bytes": bytes_total // world,
         },
         "gpu_launches": executable.launches_per_call * steps,
+        "parity": parity,
     }
     # End to end: per-step inputs (queries, lengths, page table) come from pinned host memory and the
     # outputs go back; the KV pool is resident state, as in serving.
     q_host = query.cpu().pin_memory()
     table_host = table_d.cpu().pin_memory()
     lengths_host = lengths_d.cpu().pin_memory()
-    result_device = out if gather_buffer is None else gather_buffer.as_tensor(torch.bfloat16, (world, config.num_seqs, local_q, config.head_dim))
+    result_device = out if gather_buffer is None else gather_view[0]
     if gathered is not None:
         result_device = gathered
     out_host = torch.empty(result_device.shape, dtype=result_device.dtype).pin_memory()
@@ -431,7 +542,7 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
         table_d.copy_(table_host, non_blocking=True)
         lengths_d.copy_(lengths_host, non_blocking=True)
         step()
-        out_host.copy_(result_device, non_blocking=True)
+        out_host.copy_(result_device if gather_buffer is None else gather_view[last_half[0]], non_blocking=True)
         torch.cuda.synchronize(mesh.device)
     elapsed = reduce_max(mesh, time.perf_counter() - started)
     result["e2e"] = {
@@ -440,12 +551,71 @@ def bench_rpa(mesh, args, peaks, peak_kind) -> dict:
         "ms_per_step": elapsed / e2e_steps * 1e3,
     }
     if world == 1 and mesh.rank == 0 and not args.no_cpu_baseline:
-        result["cpu_baseline"] = cpu_rpa_sample(lengths, table, config, 32, os.cpu_count() or 1)
+        result["cpu_baseline"] = cpu_rpa_sample(lengths, table, config, 32 if config.num_seqs <= 64 else 8)
     executable.close()
     for buffer in (gather_buffer, gather_flags):
         if buffer is not None:
             buffer.close()
     return result
+
+
+def rpa_parity(mesh, config, lengths, table, cache, query, step, result_rows) -> dict:
+    """Three steps in a row with three different query tensors (the timed one, its negative, its
+    half) and no host synchronisation between them; after each, the rows of four sampled sequences
+    (shortest, longest, two between) are copied from where the step left its result -- the gathered
+    buffer of all ranks' heads when the decode is sharded. Every rank compares all query heads of
+    those rows with the oracle: each rank runs the oracle on the KV heads it holds and the expected
+    rows are exchanged over torch.distributed. Tolerance: max-abs 2e-2, relative-L2 1e-2."""
+    import torch
+
+    from oracle import matmul_rs, rpa
+
+    order = np.argsort(lengths)
+    count = len(order)
+    sample = sorted({int(order[0]), int(order[count // 3]), int(order[2 * count // 3]), int(order[-1])})
+    sample_device = torch.tensor(sample, device=mesh.device)
+    base = query.clone()
+    factors = (1.0, -1.0, 0.5)
+    snapshots = []
+    for factor in factors:
+        query.copy_((base.float() * factor).to(torch.bfloat16))
+        step()
+        snapshots.append(result_rows(sample_device).clone())
+    query.copy_(base)
+    torch.cuda.synchronize(mesh.device)
+    pages_of = {}
+    for s in sample:
+        pages = -(-int(lengths[s]) // config.page_size)
+        index = torch.from_numpy(table[s, :pages].astype(np.int64)).to(mesh.device)
+        pages_of[s] = cache[index].float().cpu().numpy()  # [pages, page_size, local KV heads, 2, head_dim]
+    max_abs, rel_l2, finite = 0.0, 0.0, True
+    for factor, snapshot in zip(factors, snapshots):
+        expected_local = np.zeros((len(sample), query.shape[1], config.head_dim), dtype=np.float32)
+        for i, s in enumerate(sample):
+            rows = pages_of[s]
+            q = (base[s : s + 1].float() * factor).to(torch.bfloat16).float().cpu().numpy()
+            expected_local[i] = rpa.rpa_separate(q, rows[:, :, :, 0, :], rows[:, :, :, 1, :], np.arange(rows.shape[0], dtype=np.int32)[None, :],
+                                                 lengths[s : s + 1], None, scale=config.softmax_scale)[0]
+        if mesh.world > 1:
+            import torch.distributed as dist
+
+            mine = torch.from_numpy(expected_local).to(mesh.device)
+            everyone = torch.empty((mesh.world,) + tuple(mine.shape), dtype=mine.dtype, device=mesh.device)
+            dist.all_gather_into_tensor(everyone, mine, group=mesh.group)
+            expected = everyone.permute(1, 0, 2, 3).reshape(len(sample), config.q_heads, config.head_dim).cpu().numpy()
+        else:
+            expected = expected_local
+        actual = snapshot.float().cpu().numpy()
+        finite = finite and bool(np.isfinite(actual).all())
+        max_abs = max(max_abs, matmul_rs.max_abs_error(actual, expected))
+        rel_l2 = max(rel_l2, matmul_rs.relative_l2_error(actual, expected))
+    ok = finite and max_abs <= 2e-2 and rel_l2 <= 1e-2
+    return {
+        "checked": f"{len(sample)} sequences x {config.q_heads} query heads, 3 steps in a row, "
+                   f"{'the gathered buffer on every rank' if mesh.world > 1 else 'the output buffer'} against the oracle",
+        "max_abs": reduce_max(mesh, max_abs), "rel_l2": reduce_max(mesh, rel_l2),
+        "tolerance": {"max_abs": 2e-2, "rel_l2": 1e-2}, "ok": all_ranks_ok(mesh, ok),
+    }
 
 
 def bench_rpa_mixed(mesh, args, peaks, peak_kind) -> dict:
@@ -457,7 +627,7 @@ def bench_rpa_mixed(mesh, args, peaks, peak_kind) -> dict:
     from tpu_cake_b200 import rpa_cuda_lowering, workloads
 
     config = workloads.MIXED_8_120
-    if args.mixed_prefill_only:
+    if args.case == "rpa-prefill":
         import dataclasses
 
         # Small case for profiler captures: the prefill sequences' distributions without the decode
@@ -569,46 +739,53 @@ def run_ours(args) -> None:
     import torch
 
     __graft_entry__.load_package()
+    from tpu_cake_b200 import workloads
     from tpu_cake_b200.mesh import ProcessMesh
 
     mesh = ProcessMesh.from_environment()
     if mesh.world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {mesh.world}: launch with torch.distributed.run")
     peaks, peak_kind = measured_peaks()
-    if args.only_mixed:
-        # Profiling aid: only the mixed prefill / decode batch runs.
+    if args.case == "rpa-mixed" or args.case == "rpa-prefill":
+        # Small cases for profiler captures (the commands recorded under profiles/).
         if mesh.rank == 0:
             print(json.dumps(bench_rpa_mixed(mesh, args, peaks, peak_kind)), flush=True)
         return
-    rpa = None if args.no_rpa else bench_rpa(mesh, args, peaks, peak_kind)
-    mixed = None if (args.no_rpa or args.no_mixed or mesh.world != 1) else bench_rpa_mixed(mesh, args, peaks, peak_kind)
-    if args.only_rpa:
-        # Profiling aid: only the attention kernels run (small enough for an ncu capture).
+    if args.case == "rpa-decode":
+        result = bench_rpa(mesh, args, peaks, peak_kind, workloads.DECODE_64)
         if mesh.rank == 0:
-            print(json.dumps(rpa), flush=True)
+            print(json.dumps(result), flush=True)
         return
+    rpa = sharded = mixed = None
+    if not args.no_rpa:
+        if mesh.world == 1:
+            rpa = bench_rpa(mesh, args, peaks, peak_kind, workloads.DECODE_64)
+            mixed = None if args.no_mixed else bench_rpa_mixed(mesh, args, peaks, peak_kind)
+        sharded = bench_rpa(mesh, args, peaks, peak_kind, workloads.DECODE_SHARDED_256)
+        sharded["metric"] = "rpa_decode_sharded_hbm_gbs"
     matmul = bench_matmul(mesh, args, peaks, peak_kind)
     line = {
         "metric": "matmul_reduce_scatter_tflops", "value": matmul["value"], "unit": "TFLOP/s", "n_gpus": mesh.world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": matmul["ms_per_step"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {
-            "workload": f"K-sharded bf16 matmul {M}x{K}x{N} + reduce-scatter along M to bf16 [{M // mesh.world},{N}] per GPU",
-            "m": M, "k": K, "n": N, "mesh": mesh.world, "accumulate": "f32", "collective": matmul["strategy"],
-            "l2": "256 MiB flush between steps",
-        },
+        "config": matmul_config(mesh.world, matmul["strategy"]),
         "roofline": matmul["roofline"], "e2e": matmul["e2e"], "gpu_launches": matmul["gpu_launches"], "clocks": matmul["clocks"],
+        "parity": matmul["parity"],
     }
     if matmul["phases"] is not None:
         line["communication"] = matmul["phases"]
     if mesh.rank == 0 and mesh.world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_matmul_sample(args.cpu_rows, os.cpu_count() or 1)
-    if rpa is not None:
-        line["rpa_decode"] = rpa
-        line["gpu_launches"] += rpa["gpu_launches"]
+        line["cpu_baseline"] = cpu_matmul_sample(args.cpu_rows)
+    # "rpa_decode": the 64-sequence decode on one GPU; at N > 1 the sharded 256-sequence decode (the
+    # key earlier runs used for it). "rpa_decode_sharded": the 256-sequence decode at every N.
+    if sharded is not None:
+        line["rpa_decode_sharded"] = sharded
+        line["rpa_decode"] = rpa if rpa is not None else sharded
+        line["gpu_launches"] += sharded["gpu_launches"] + (rpa["gpu_launches"] if rpa is not None else 0)
     if mixed is not None:
         line["rpa_mixed"] = mixed
         line["gpu_launches"] += mixed["gpu_launches"]
+    ok = line["parity"]["ok"] and all(part is None or part["parity"]["ok"] for part in (rpa, sharded))
     if mesh.rank == 0:
         print(json.dumps(line), flush=True)
     if mesh.world > 1:
@@ -616,6 +793,8 @@ def run_ours(args) -> None:
 
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("PARITY_FAILED: a rank's result disagrees with the oracle (see the parity objects of the line)")
 
 
 # ------------------------------------------------------------------------------------ reference
@@ -624,35 +803,54 @@ def run_ours(args) -> None:
 def run_reference(args) -> None:
     """The reference's CPU path for the same metric and config. The reference's own JAX program
     cannot run on this machine (jax and xDSL are not installed and cannot be), so this arm times the
-    oracle port, which restates the numpy oracle the reference itself checks against; each step is a
-    bounded sample of the workload."""
+    oracle port, which restates the numpy oracle the reference itself checks against, in the form
+    the reference's device program has: ``mesh`` split-K partial products summed in rank order and
+    sliced along M (src/tpu_cake/pallas_lowering.py:446-464). Each step is a bounded sample of the
+    workload (``--cpu-rows`` of the 8192 lhs rows); rank 0 alone runs it, on every host core it may use."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    threads = os.cpu_count() or 1
-    rows = args.cpu_rows
+    world = args.gpus
+    rows = max(world, args.cpu_rows // world * world)
     from oracle import matmul_rs
 
     generator = np.random.default_rng(0)
     lhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(rows, K)).astype(np.float32))
     rhs = matmul_rs.quantize_bf16(generator.normal(scale=K**-0.5, size=(K, N)).astype(np.float32))
-    for _ in range(min(args.warmup, 3)):
-        matmul_rs.matmul_reference(lhs, rhs)
-    steps = min(args.steps, 10)
-    started = time.perf_counter()
-    for _ in range(steps):
-        matmul_rs.matmul_reference(lhs, rhs)
-    elapsed = time.perf_counter() - started
-    value = 2.0 * rows * K * N * steps / elapsed / 1e12
-    sample = f"{rows} of {M} lhs rows of the {M}x{K}x{N} product per step, numpy float32 matmul on bf16-valued inputs"
+
+    def step():
+        return matmul_rs.matmul_reduce_scatter(lhs, rhs, world=world, scatter_dimension=0, transport_dtype="f32", out_dtype="bf16")
+
+    with blas_threads() as pool:
+        for _ in range(args.warmup):
+            step()
+        started = time.perf_counter()
+        for _ in range(args.steps):
+            step()
+        elapsed = time.perf_counter() - started
+    value = 2.0 * rows * K * N * args.steps / elapsed / 1e12
+    sample = (f"{rows} of {M} lhs rows of the {M}x{K}x{N} product per step: {world} split-K partial products (numpy float32 "
+              f"matmul on bf16-valued inputs), summed in rank order, sliced along M, rounded to bf16")
+    baseline = {"value": value, "unit": "TFLOP/s", "cores": pool.used, "threads_used": pool.used, "host_cores": host_threads(),
+                "kind": "port", "sample": sample}
     line = {
-        "impl": "reference", "metric": "matmul_reduce_scatter_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True,
+        "impl": "reference", "metric": "matmul_reduce_scatter_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"K-sharded bf16 matmul {M}x{K}x{N} + reduce-scatter along M", "m": M, "k": K, "n": N, "mesh": args.gpus},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": matmul_config(world, "p2p_bf16" if world > 1 else "single"),
+        "cpu_baseline": baseline,
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if not args.no_rpa:
+        # The attention objects' CPU side: the numpy oracle on a bounded sample of each configuration.
+        __graft_entry__.load_package()
+        from tpu_cake_b200 import workloads
+
+        for key, config, sequences in (("rpa_decode", workloads.DECODE_64, 32), ("rpa_decode_sharded", workloads.DECODE_SHARDED_256, 8)):
+            lengths, table = workloads.decode_metadata(config)
+            sampled = cpu_rpa_sample(lengths, table, config, sequences)
+            line[key] = {"metric": "rpa_decode_hbm_gbs" if key == "rpa_decode" else "rpa_decode_sharded_hbm_gbs",
+                         "value": sampled["value"], "unit": "GB/s", "config": {"workload": config.name}, "cpu_baseline": sampled}
     print(json.dumps(line), flush=True)
 
 
@@ -664,23 +862,21 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--strategy", choices=("p2p_bf16", "p2p_f32", "nccl"), default="p2p_bf16")
     parser.add_argument("--kv-chunk", type=int, default=0)
-    parser.add_argument("--cpu-rows", type=int, default=8192)
-    parser.add_argument("--k", type=int, default=K, help="contraction extent (experiments only; the headline uses the default)")
+    parser.add_argument("--cpu-rows", type=int, default=8192, help="lhs rows of the CPU legs' sample (the whole product by default)")
     parser.add_argument("--no-rpa", action="store_true")
     parser.add_argument("--rpa-gather", choices=("p2p", "nccl"), default="p2p", help="how the sharded decode's outputs are all-gathered")
     parser.add_argument("--no-graph", action="store_true", help="launch the attention step kernel by kernel instead of replaying a CUDA graph")
-    parser.add_argument("--only-rpa", action="store_true", help="run only the attention part (profiling aid)")
-    parser.add_argument("--only-mixed", action="store_true", help="run only the mixed prefill/decode batch (profiling aid)")
     parser.add_argument("--no-mixed", action="store_true", help="skip the mixed prefill/decode batch")
-    parser.add_argument("--mixed-prefill-only", action="store_true",
-                        help="with --only-mixed: only prefill sequences, on a small page pool (for profiler captures)")
-    parser.add_argument("--rpa-pool-pages", type=int, default=0,
-                        help="shrink the KV page pool (same sequences and lengths; for captures that must hold little memory)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--case", choices=("all", "rpa-decode", "rpa-mixed", "rpa-prefill"), default="all",
+                        help="one part of the bench alone, sized for a profiler capture: rpa-decode = the 64-sequence decode "
+                             "(with --rpa-pool-pages to shrink the page pool), rpa-mixed = the mixed batch, rpa-prefill = its "
+                             "prefill sequences on a small pool")
+    parser.add_argument("--rpa-pool-pages", type=int, default=0,
+                        help="with --case rpa-decode: shrink the KV page pool (same sequences and lengths)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    globals()["K"] = args.k
     if args.impl == "reference":
         run_reference(args)
     else:

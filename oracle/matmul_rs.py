@@ -41,6 +41,29 @@ def local_partials(lhs_q: np.ndarray, rhs_q: np.ndarray, world: int) -> list[np.
     ]
 
 
+def reduced_rows(
+    lhs_rows_q: np.ndarray,
+    rhs_q: np.ndarray,
+    *,
+    world: int,
+    transport_dtype: str = "f32",
+    out_dtype: str = "f32",
+) -> np.ndarray:
+    """Full-width rows of the reduced product for a subset of lhs rows: the ``world`` split-K
+    partials of those rows (pallas_lowering.py:446-472), rounded to the transport dtype if it is
+    bf16, summed in rank order in float32 and rounded to ``out_dtype``. What a rank's local output
+    must hold in the rows it owns; used to check large products on sampled rows."""
+    if transport_dtype not in ("f32", "bf16"):
+        raise ValueError(f"unknown transport dtype {transport_dtype}")
+    partials = local_partials(lhs_rows_q, rhs_q, world)
+    if transport_dtype == "bf16" and world > 1:
+        partials = [quantize_bf16(p) for p in partials]
+    total = np.zeros_like(partials[0])
+    for partial in partials:
+        total = total + partial
+    return quantize_bf16(total) if out_dtype == "bf16" else total
+
+
 def matmul_reduce_scatter(
     lhs_q: np.ndarray,
     rhs_q: np.ndarray,

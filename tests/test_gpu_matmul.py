@@ -325,11 +325,16 @@ def test_runner_writes_a_complete_bundle(cuda_device, tmp_path, mesh_size, strat
     from tpu_cake_b200.run_ledger import RunLedger, RunState
 
     out = tmp_path / "run"
+    with pytest.raises(ValueError, match="MESH_NOT_AVAILABLE"):
+        runner.run_distributed_matmul(out, mesh_size=mesh_size, m=128, k=1024, n=1024, warmup_iterations=1, measured_iterations=3,
+                                      collective_strategy=strategy)
+    assert not out.exists()
     result = runner.run_distributed_matmul(out, mesh_size=mesh_size, m=128, k=1024, n=1024, warmup_iterations=1,
-                                           measured_iterations=3, collective_strategy=strategy)
+                                           measured_iterations=3, collective_strategy=strategy, emulate_on_one_gpu=True)
     assert result.passed and result.median_ns > 0 and len(result.samples_ns) == 3
     assert result.execution == "emulated-on-one-gpu"
-    for name in ("invocation.json", "distributed.mlir", "physical.mlir", "lowered_cuda.py", "cost_model.json",
+    for name in ("invocation.json", "profiler_config.json", "source_state.json", "source_diff.patch", "experiment.json",
+                 "distributed.mlir", "physical.mlir", "lowered_cuda.py", "cost_model_input.json", "cost_model.json",
                  "kernel_manifest.json", "lhs.npy", "rhs.npy", "output.npy", "oracle.npy", "ledger.sqlite", "result.json"):
         assert (out / name).exists(), name
     with RunLedger(out / "ledger.sqlite") as ledger:
@@ -340,7 +345,8 @@ def test_runner_writes_a_complete_bundle(cuda_device, tmp_path, mesh_size, strat
     else:
         assert np.allclose(np.load(out / "output.npy"), np.load(out / "oracle.npy"), atol=1e-3, rtol=1e-3)
     with pytest.raises(FileExistsError):
-        runner.run_distributed_matmul(out, mesh_size=mesh_size, m=128, k=1024, n=1024, warmup_iterations=0, measured_iterations=1)
+        runner.run_distributed_matmul(out, mesh_size=mesh_size, m=128, k=1024, n=1024, warmup_iterations=0, measured_iterations=1,
+                                      emulate_on_one_gpu=True)
 
 
 def test_tile_search_through_the_runner(cuda_device, tmp_path):
@@ -350,7 +356,7 @@ def test_tile_search_through_the_runner(cuda_device, tmp_path):
 
     contract = search.MatmulSearchContract(
         mesh_size=2, m=256, k=1024, n=512, warmup_iterations=1, measured_iterations=3, rounds=5, bootstrap_samples=1000,
-        collective_strategy="p2p_fused_epilogue", scatter_dimension="N", output_dtype="f32",
+        collective_strategy="p2p_fused_epilogue", scatter_dimension="N", output_dtype="f32", execution="emulated-on-one-gpu",
         candidates=(search.MatmulSearchCandidate("tile-128x256", 128, 256), search.MatmulSearchCandidate("tile-128x64", 128, 64)),
     )
     result = search.run_matmul_search(tmp_path / "search", contract)
@@ -359,6 +365,17 @@ def test_tile_search_through_the_runner(cuda_device, tmp_path):
     assert all(row.sample_count == 15 and row.median_ns > 0 for row in result.candidates)
     assert result.winner in (None, "tile-128x64")
     assert (tmp_path / "search" / "round-04" / "tile-128x64" / "result.json").exists()
+    # Resume: the finished runs are validated and reused (same samples, nothing re-run) ...
+    resumed = search.run_matmul_search(tmp_path / "search", contract)
+    assert resumed.candidates == result.candidates and resumed.run_results == result.run_results
+    # ... a different contract in the same directory is refused, and so is a run that left no result.
+    import dataclasses
+
+    with pytest.raises(ValueError, match="SEARCH_CONTRACT_CHANGED"):
+        search.run_matmul_search(tmp_path / "search", dataclasses.replace(contract, measured_iterations=4))
+    (tmp_path / "search" / "round-02" / "tile-128x64" / "result.json").unlink()
+    with pytest.raises(ValueError, match="SEARCH_RUN_INCOMPLETE"):
+        search.run_matmul_search(tmp_path / "search", contract)
 
 
 def test_receipt_is_written_validated_and_refuses_tampering(cuda_device, tmp_path):
@@ -370,7 +387,7 @@ def test_receipt_is_written_validated_and_refuses_tampering(cuda_device, tmp_pat
 
     out = tmp_path / "run"
     runner.run_distributed_matmul(out, mesh_size=2, m=128, k=1024, n=1024, warmup_iterations=1, measured_iterations=3,
-                                  collective_strategy="p2p_fused_epilogue")
+                                  collective_strategy="p2p_fused_epilogue", emulate_on_one_gpu=True)
     header = '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"\n'
 
     def launch(index, kernel):

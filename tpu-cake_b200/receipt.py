@@ -48,6 +48,17 @@ def expected_kernels(strategy: str, mesh_size: int, tile_n: int) -> tuple[list[s
     return [main, "cake_reduce_slots_sm100"], ("ncclDevKernel_ReduceScatter",)
 
 
+def required_profile_markers(strategy: str, mesh_size: int, tile_n: int, execution: str) -> tuple[str, ...]:
+    """Kernel-name fragments a profile of the run must contain. One process per GPU launches the
+    contraction alone (its last warps are the slot reduction); only the one-GPU emulation of a mesh
+    launches the reduction as a kernel of its own."""
+    wanted, _ = expected_kernels(strategy, mesh_size, tile_n)
+    markers = [wanted[0].split("<")[0]]
+    if len(wanted) > 1 and execution == "emulated-on-one-gpu":
+        markers.append(wanted[1])
+    return tuple(markers)
+
+
 def _validate_strategy(manifest: dict, strategy: str, mesh_size: int, tile_n: int) -> None:
     wanted, _ = expected_kernels(strategy, mesh_size, tile_n)
     if list(manifest.get("kernels", ())) != wanted:
@@ -147,10 +158,11 @@ def finalize_matmul_run(root: Path, *, profile_csv: Path | None = None) -> dict:
     artifacts.append(_artifact(root, "roofline/metrics.json", "roofline_metrics"))
     profile = {"attached": False}
     if profile_csv is not None:
-        wanted, forbidden = expected_kernels(invocation["collective_strategy"], invocation["mesh_size"], plan.tile_n)
+        _, forbidden = expected_kernels(invocation["collective_strategy"], invocation["mesh_size"], plan.tile_n)
         expectation = profile_evidence.ProfileExpectation(
             name=f"matmul-{invocation['collective_strategy']}", require_tensor_core_activity=False,
-            required_timed_hlo_markers=tuple(name.split("<")[0] for name in wanted), forbidden_timed_hlo_fragments=forbidden,
+            required_timed_hlo_markers=required_profile_markers(invocation["collective_strategy"], invocation["mesh_size"], plan.tile_n, result["execution"]),
+            forbidden_timed_hlo_fragments=forbidden,
         )
         assessment = profile_evidence.assess_capture(Path(profile_csv), expectation)
         if not assessment.accepted:
@@ -218,11 +230,89 @@ def validate_receipt(root: Path) -> dict:
     if not math.isclose(float(workload["measured_time_s"]), result["median_ns"] / 1_000_000_000, rel_tol=0, abs_tol=1e-15):
         raise ValueError("ROOFLINE_TIMING_SOURCE_MISMATCH")
     if receipt["profile"]["attached"]:
-        wanted, forbidden = expected_kernels(invocation["collective_strategy"], invocation["mesh_size"], plan.tile_n)
+        _, forbidden = expected_kernels(invocation["collective_strategy"], invocation["mesh_size"], plan.tile_n)
         expectation = profile_evidence.ProfileExpectation(
             name="revalidation", require_tensor_core_activity=False,
-            required_timed_hlo_markers=tuple(name.split("<")[0] for name in wanted), forbidden_timed_hlo_fragments=forbidden,
+            required_timed_hlo_markers=required_profile_markers(invocation["collective_strategy"], invocation["mesh_size"], plan.tile_n, result["execution"]),
+            forbidden_timed_hlo_fragments=forbidden,
         )
         if not profile_evidence.assess_capture(root / "profile" / "launches.csv", expectation).accepted:
             raise ValueError("PROFILE_CAPTURE_REJECTED")
     return receipt
+
+
+# ------------------------------------------------------------------------------ three-phase bundle
+
+BUNDLE_SCHEMA = "cake-b200-run-bundle-v1"
+_PHASES = ("timing", "trace", "counters")
+_SAME_ACROSS_PHASES = ("schedule_sha256", "cuda_source_sha256", "kernel_manifest_sha256", "lhs_sha256", "rhs_sha256", "output_sha256",
+                       "collective_strategy", "device_count", "execution", "device_kind")
+
+
+def finalize_matmul_bundle(root: Path, *, trace_profile: Path, counters_profile: Path) -> dict:
+    """A run bundle is three runs of one invocation -- ``timing/``, ``trace/`` and ``counters/`` under
+    ``root`` -- that must agree on everything but the mode: the same schedule, lowered code, kernel
+    manifest, input and output hashes (src/tpu_cake/run_bundle.py:88-112). The timing run gets its
+    receipt; the trace capture (kernel durations only) must show the strategy's kernels and none of
+    the forbidden ones; the counters capture must in addition carry tensor-pipe activity and DRAM
+    byte counters. Writes ``bundle.json`` and returns it."""
+    root = Path(root)
+    loaded = {}
+    for phase in _PHASES:
+        directory = root / phase
+        if not (directory / "result.json").is_file():
+            raise ValueError(f"BUNDLE_PHASE_MISSING phase={phase}")
+        result, invocation, manifest = _load_bundle(directory)
+        if result["mode"] != phase or invocation["mode"] != phase:
+            raise ValueError(f"BUNDLE_PHASE_MODE_MISMATCH phase={phase} mode={result['mode']}")
+        if not result["passed"]:
+            raise ValueError(f"BUNDLE_PHASE_NOT_CORRECT phase={phase}")
+        _check_result_artifacts(directory, result)
+        contract = json.loads((directory / "profiler_config.json").read_text())
+        from . import run_artifacts
+
+        run_artifacts.validate_profiler_contract(contract)
+        if contract["mode"] != phase:
+            raise ValueError(f"PROFILER_CONTRACT_VIOLATION phase={phase} profiler_config is for {contract['mode']}")
+        loaded[phase] = (result, invocation, manifest)
+    reference_result, reference_invocation, _ = loaded["timing"]
+    for phase in ("trace", "counters"):
+        result, invocation, _ = loaded[phase]
+        for name in _SAME_ACROSS_PHASES:
+            if result[name] != reference_result[name]:
+                raise ValueError(f"BUNDLE_IDENTITY_MISMATCH phase={phase} field={name}")
+        if {k: v for k, v in invocation.items() if k != "mode"} != {k: v for k, v in reference_invocation.items() if k != "mode"}:
+            raise ValueError(f"BUNDLE_INVOCATION_MISMATCH phase={phase}")
+        if result["samples_ns"]:
+            raise ValueError(f"BUNDLE_PHASE_CARRIES_HOST_TIMINGS phase={phase}")
+    receipt = finalize_matmul_run(root / "timing")
+    plan = _plan_of(reference_invocation)
+    strategy, mesh_size = reference_invocation["collective_strategy"], reference_invocation["mesh_size"]
+    _, forbidden = expected_kernels(strategy, mesh_size, plan.tile_n)
+    markers = required_profile_markers(strategy, mesh_size, plan.tile_n, reference_result["execution"])
+    assessments = {}
+    for phase, capture, counters in (("trace", trace_profile, False), ("counters", counters_profile, True)):
+        expectation = profile_evidence.ProfileExpectation(
+            name=f"matmul-{strategy}-{phase}", require_tensor_core_activity=counters, require_hbm_read_counters=counters,
+            require_hbm_write_counters=counters, required_timed_hlo_markers=markers, forbidden_timed_hlo_fragments=forbidden,
+        )
+        assessment = profile_evidence.assess_capture(Path(capture), expectation)
+        if not assessment.accepted:
+            raise ValueError(f"PROFILE_CAPTURE_REJECTED phase={phase} " + ",".join(f.code for f in assessment.findings))
+        if not counters:
+            evidence = profile_evidence.read_ncu_csv(Path(capture).read_text())
+            if any(name.startswith(("dram__", "sm__")) for name in evidence.metric_names):
+                raise ValueError("PROFILER_CONTRACT_VIOLATION phase=trace capture carries hardware counters")
+        target = root / phase / "profile" / "launches.csv"
+        target.parent.mkdir(exist_ok=True)
+        target.write_bytes(Path(capture).read_bytes())
+        assessments[phase] = {"capture": _artifact(root, f"{phase}/profile/launches.csv", "profile_capture"),
+                              "marker_launches": assessment.marker_launches, "marker_time_ns": assessment.marker_time_ns}
+    bundle = {
+        "schema": BUNDLE_SCHEMA, "run_ids": {phase: loaded[phase][0]["run_id"] for phase in _PHASES},
+        "identities": {name: reference_result[name] for name in _SAME_ACROSS_PHASES}, "timing_receipt_id": receipt["receipt_id"],
+        "profiles": assessments,
+    }
+    bundle["bundle_id"] = semantic_sha256("run-bundle", json.dumps(bundle, sort_keys=True))
+    (root / "bundle.json").write_text(json.dumps(bundle, indent=2) + "\n")
+    return bundle

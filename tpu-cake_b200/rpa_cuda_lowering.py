@@ -199,6 +199,27 @@ def lower_fused_rpa_to_cuda(module, *, with_relative_bias: bool = True, kv_chunk
     )
 
 
+def lower_inkling_rpa_to_cuda(module, *, with_relative_bias: bool = True, kv_chunk_tokens: int = 0):
+    """The name the reference's callers use (``lower_inkling_rpa_to_pallas``,
+    src/tpu_cake/rpa_lowering.py:1084): fused-RPA kernel -> ``CudaFusedRpaPlan`` with ``preflight`` /
+    ``invoke`` / ``run_preflighted`` (:228-288)."""
+    return lower_fused_rpa_to_cuda(module, with_relative_bias=with_relative_bias, kv_chunk_tokens=kv_chunk_tokens)
+
+
+def lower_inkling_sharded_rpa_to_cuda(module, *, kv_chunk_tokens: int = 0) -> "ShardedCudaFusedRpaPlan":
+    """Counterpart of ``lower_inkling_sharded_rpa_to_pallas`` (src/tpu_cake/rpa_lowering.py:1139): the
+    kernel describes one mesh position's shard and names a ``data`` x ``tensor`` mesh; the result
+    places global inputs (``place_inputs``) and builds the local executable (``build_executable``)."""
+    kernel, _ = _single_op(module, "tpu_schedule.fused_ragged_paged_attention")
+    axes, sizes = tuple(kernel.properties["mesh_axis_names"]), tuple(kernel.properties["mesh_axis_sizes"])
+    if axes != ("data", "tensor"):
+        raise UnsupportedRpaLowering(f"sharded RPA runs on a data x tensor mesh, the kernel names {axes}")
+    local = lower_fused_rpa_to_cuda(module, kv_chunk_tokens=kv_chunk_tokens)
+    if not isinstance(local, CudaFusedRpaPlan):
+        raise UnsupportedRpaLowering("the sharded surface lowers decode batches (one query token per sequence)")
+    return ShardedCudaFusedRpaPlan(local_plan=local, mesh_axes=axes, mesh_shape=sizes)
+
+
 def decode_resource_contract(plan) -> dict:
     """Properties of a ``tpu_schedule.cuda_rpa_decode`` op for a decode plan: the static resources of
     the sm_100a decode kernel as built (6 worker warps, 2-stage rings of 32-token stages)."""
@@ -636,6 +657,16 @@ class ShardedCudaFusedRpaPlan:
 
     def build(self, device: torch.device | None = None) -> "RpaDecodeExecutable":
         return self.local_plan.build(device)
+
+    # The reference's names for the two steps (src/tpu_cake/rpa_lowering.py:395-571).
+    def place_inputs(self, global_inputs: tuple, rank: int, device: torch.device | None = None) -> tuple:
+        """This rank's shard of every global input as device tensors (the shard_map placement)."""
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        shards = self.shard_inputs(global_inputs, self.mesh_position(rank))
+        return tuple(None if value is None else _to_device_tensor(np.ascontiguousarray(_to_host(value)), device) for value in shards)
+
+    def build_executable(self, device: torch.device | None = None) -> "RpaDecodeExecutable":
+        return self.build(device)
 
     def run_local(self, executable: "RpaDecodeExecutable", *local_inputs):
         """Preflight (host integers) and decode of one mesh position's shard."""

@@ -10,9 +10,16 @@ in float32 (:488-525), timed calls each followed by a synchronisation (:526-531)
 a kernel manifest: library path, size and SHA-256, ABI version, kernel names.
 
 Execution models: ``mesh_size == 1`` runs on the current GPU; ``mesh_size > 1`` runs one process
-per GPU when launched under ``torch.distributed.run`` with a matching world size, and otherwise
-emulates every mesh position on the current GPU (all pushes enqueued before any reduction), which
-checks correctness but whose timing is marked ``emulated``.
+per GPU when launched under ``torch.distributed.run`` with a matching world size. Without such a
+launch a mesh larger than one is refused, unless the caller asks for ``emulate_on_one_gpu``: every
+mesh position's kernels then run on the current GPU (all pushes enqueued before any reduction),
+which checks correctness but whose timing is marked ``emulated-on-one-gpu`` and is not a multi-GPU
+number.
+
+Modes (``RunMode``, src/tpu_cake/runner.py:54-57): ``timing`` times every measured call on the host;
+``trace`` and ``counters`` run the same calls untimed for a profiler that wraps the process
+(``profiler_config.json`` names the ``ncu`` invocation; src/tpu_cake/runner.py:144-217) and end in
+TRACED / COUNTERED (:570-571).
 """
 
 from __future__ import annotations
@@ -31,9 +38,10 @@ from pathlib import Path
 import numpy as np
 import torch
 
-from . import _native, cost_model, cuda_lowering, dialects, ir, schedule_lowering, workloads
+from . import _native, cost_model, cuda_lowering, dialects, ir, run_artifacts, schedule_lowering, workloads
 from .identity import array_sha256, semantic_sha256
 from .mesh import ProcessMesh
+from .run_artifacts import RunMode
 from .run_ledger import RunLedger, RunState
 
 _IMPLEMENTATION = {
@@ -192,14 +200,23 @@ def run_distributed_matmul(
     collective_strategy: str = "nccl_reduce_scatter",
     scatter_dimension: str = "N",
     output_dtype: str = "f32",
+    mode: RunMode | str = RunMode.TIMING,
+    emulate_on_one_gpu: bool = False,
 ) -> MatmulRunResult:
     if not torch.cuda.is_available():
         raise RuntimeError("run_distributed_matmul needs a CUDA device: the CUDA backend has no CPU fallback")
     if measured_iterations <= 0 or warmup_iterations < 0:
         raise ValueError("measured_iterations must be positive and warmup_iterations non-negative")
+    mode = RunMode(mode)
     strategy = cuda_lowering.MatmulCollectiveStrategy(collective_strategy)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     distributed = mesh_size > 1 and world == mesh_size
+    if mesh_size > 1 and not distributed and not emulate_on_one_gpu:
+        raise ValueError(
+            f"MESH_NOT_AVAILABLE mesh_size={mesh_size} world_size={world}: launch one process per GPU "
+            "(python -m torch.distributed.run --nproc-per-node MESH ...), or ask for emulate_on_one_gpu "
+            "(correctness only: its timing is not a multi-GPU number)"
+        )
     mesh = ProcessMesh.from_environment() if distributed else ProcessMesh.single()
     leader = mesh.rank == 0
     output_dir = Path(output_dir)
@@ -209,7 +226,8 @@ def run_distributed_matmul(
     invocation = {
         "mesh_size": mesh_size, "m": m, "k": k, "n": n, "warmup_iterations": warmup_iterations,
         "measured_iterations": measured_iterations, "tile": None if tile is None else [tile.m, tile.n],
-        "collective_strategy": strategy.value, "scatter_dimension": scatter_dimension, "output_dtype": output_dtype, "mode": "timing",
+        "collective_strategy": strategy.value, "scatter_dimension": scatter_dimension, "output_dtype": output_dtype, "mode": mode.value,
+        "execution": "one-process-per-gpu" if distributed or mesh_size == 1 else "emulated-on-one-gpu",
     }
     run_id = semantic_sha256("distributed-matmul-run", json.dumps(invocation, sort_keys=True))
     ledger_path = output_dir / "ledger.sqlite"
@@ -223,8 +241,15 @@ def run_distributed_matmul(
             else:
                 ledger.transition(run_id, state, payload)
 
+    contract = run_artifacts.profiler_contract(mode)
+    run_artifacts.validate_profiler_contract(contract)
     if leader:
         _write(output_dir / "invocation.json", json.dumps(invocation, indent=2, sort_keys=True) + "\n", "invocation", artifacts)
+        _write(output_dir / "profiler_config.json", json.dumps({**contract, "attached": run_artifacts.profiler_attached()}, indent=2, sort_keys=True) + "\n",
+               "profiler_config", artifacts)
+        shared: list[run_artifacts.ArtifactReference] = []
+        run_artifacts.source_state(output_dir, shared)
+        artifacts.extend(ArtifactReference(a.path, a.size_bytes, a.sha256, a.role) for a in shared)
     record(RunState.CREATED, invocation)
 
     logical = workloads.distributed_matmul_schedule(mesh_size=mesh_size, m=m, k=k, n=n, scatter_dimension=scatter_dimension)
@@ -245,6 +270,28 @@ def run_distributed_matmul(
         _write(output_dir / "distributed.mlir", ir.canonical_text(logical), "schedule", artifacts)
         _write(output_dir / "physical.mlir", ir.canonical_text(physical), "physical_schedule", artifacts)
         _write(output_dir / "lowered_cuda.py", plan.render_executable_source(), "lowered_source", artifacts)
+        wanted_kernels = [name.split("<")[0] for name in manifest["kernels"][:1]]
+        experiment = run_artifacts.experiment_record(
+            workload={"name": "distributed-matmul-reduce-scatter", "identity": workloads.distributed_matmul_workload_identity(mesh_size, m, k, n),
+                      "mesh_size": mesh_size, "m": m, "k": k, "n": n, "scatter_dimension": scatter_dimension, "input_dtype": "bf16",
+                      "accumulate": "f32", "output_dtype": output_dtype, "collective_strategy": strategy.value},
+            schedule_sha256=plan.schedule_sha256, warmup_iterations=warmup_iterations, measured_iterations=measured_iterations,
+            profile_expectation={"name": f"matmul-{strategy.value}", "required_timed_hlo_markers": wanted_kernels,
+                                 "forbidden_timed_hlo_fragments": [] if strategy is cuda_lowering.MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER else ["ncclDevKernel_ReduceScatter"],
+                                 "require_tensor_core_activity": mode is RunMode.COUNTERS},
+            tolerance={"reference": "bf16(lhs).astype(f32) @ bf16(rhs).astype(f32)", "absolute_tolerance": 1e-3, "relative_tolerance": 1e-3,
+                       "bf16_rule": "relative L2 <= 1e-2 when the output or the transport is bf16"},
+        )
+        _write(output_dir / "experiment.json", json.dumps(experiment, indent=2, sort_keys=True) + "\n", "experiment", artifacts)
+        hardware = cost_model.B200_MEASURED
+        _write(output_dir / "cost_model_input.json", json.dumps({
+            "plan": {"mesh_size": plan.mesh_size, "lhs_local_shape": plan.lhs_local_shape, "rhs_local_shape": plan.rhs_local_shape,
+                     "partial_local_shape": plan.partial_local_shape, "output_local_shape": plan.output_local_shape,
+                     "scatter_dimension": plan.scatter_dimension, "tile": [plan.tile_m, plan.tile_k, plan.tile_n],
+                     "output_dtype": plan.output_dtype, "transport_dtype": plan.transport_dtype,
+                     "collective_implementation": None if plan.collective_implementation is None else plan.collective_implementation.value},
+            "hardware": asdict(hardware),
+        }, indent=2, sort_keys=True, default=str) + "\n", "cost_model_input", artifacts)
         report = cost_model.estimate_distributed_matmul(plan)
         _write(output_dir / "cost_model.json", json.dumps({**asdict(report.counts), "compute_ns": str(report.compute_ns), "memory_ns": str(report.memory_ns),
                                                           "communication_ns": str(report.communication_ns), "lower_bound_ns": str(report.lower_bound_ns),
@@ -314,12 +361,19 @@ def run_distributed_matmul(
         started = time.perf_counter_ns()
         call()
         torch.cuda.synchronize(mesh.device)
-        samples.append(time.perf_counter_ns() - started)
-    median_ns = int(statistics.median(samples))
-    p90_ns = _percentile(samples, 0.9)
+        if mode is RunMode.TIMING:  # under a profiler the host clock measures the profiler
+            samples.append(time.perf_counter_ns() - started)
+    (emulated or executable).status()
+    median_ns = int(statistics.median(samples)) if samples else None
+    p90_ns = _percentile(samples, 0.9) if samples else None
     coefficient = statistics.pstdev(samples) / statistics.mean(samples) if len(samples) > 1 and statistics.mean(samples) else None
-    record(RunState.TIMED, {"measured_iterations": measured_iterations, "warmup_iterations": warmup_iterations, "median_ns": median_ns,
-                            "p90_ns": p90_ns, "sample_count": len(samples)})
+    terminal = {RunMode.TIMING: RunState.TIMED, RunMode.TRACE: RunState.TRACED, RunMode.COUNTERS: RunState.COUNTERED}[mode]
+    payload = {"measured_iterations": measured_iterations, "warmup_iterations": warmup_iterations}
+    if mode is RunMode.TIMING:
+        payload.update(median_ns=median_ns, p90_ns=p90_ns, sample_count=len(samples))
+    else:
+        payload.update(profiler_attached=run_artifacts.profiler_attached(), capture="launches.csv, attached when the bundle is finalised")
+    record(terminal, payload)
     if leader:
         for name, array, role in (("lhs.npy", lhs32, "correctness_input"), ("rhs.npy", rhs32, "correctness_input"),
                                   ("output.npy", actual, "correctness_output"), ("oracle.npy", reference_slice, "oracle_output")):
@@ -328,7 +382,7 @@ def run_distributed_matmul(
             artifacts.append(ArtifactReference(name, path.stat().st_size, _sha256_file(path), role))
         artifacts.append(ArtifactReference(ledger_path.name, ledger_path.stat().st_size, _sha256_file(ledger_path), "execution_ledger"))
     outcome = MatmulRunResult(
-        run_id=run_id, mode="timing", backend="cuda", device_kind=torch.cuda.get_device_name(mesh.device), device_count=mesh_size,
+        run_id=run_id, mode=mode.value, backend="cuda", device_kind=torch.cuda.get_device_name(mesh.device), device_count=mesh_size,
         execution="one-process-per-gpu" if distributed or mesh_size == 1 else "emulated-on-one-gpu", collective_strategy=strategy.value,
         hostname=socket.gethostname(), schedule_sha256=plan.schedule_sha256, cuda_source_sha256=plan.source_sha256(),
         kernel_manifest_sha256=manifest_reference.sha256 if manifest_reference else "", lhs_sha256=array_sha256(lhs32),

@@ -54,8 +54,11 @@ class MatmulSearchContract:
     collective_strategy: str = "p2p_fused_epilogue_bf16_transport"
     scatter_dimension: str = "M"
     output_dtype: str = "bf16"
+    execution: str = "one-process-per-gpu"  # or "emulated-on-one-gpu": every mesh position on the current GPU (correctness, not multi-GPU timing)
 
     def __post_init__(self) -> None:
+        if self.execution not in ("one-process-per-gpu", "emulated-on-one-gpu"):
+            raise ValueError(f"execution must be one-process-per-gpu or emulated-on-one-gpu, got {self.execution}")
         if min(self.mesh_size, self.m, self.k, self.n, self.measured_iterations) <= 0 or self.warmup_iterations < 0:
             raise ValueError("mesh, shape and measured iterations must be positive; warmup non-negative")
         if self.rounds < 5:
@@ -195,7 +198,9 @@ def summarise(contract: MatmulSearchContract, runs: list[tuple[int, str, object]
 def run_matmul_search(output_dir: Path, contract: MatmulSearchContract, *, run: Callable | None = None, write_result: bool = True) -> MatmulSearchResult:
     """Runs every candidate in every round (order reversed on odd rounds) through the runner and
     writes ``contract.json`` and ``result.json``. ``run(path, contract, candidate)`` defaults to the
-    CUDA runner; a directory that holds a different contract is refused."""
+    CUDA runner. A directory that holds a different contract is refused (the contract must be
+    byte-identical on resume, src/tpu_cake/search.py:507-514); a round directory that already holds a
+    finished run is validated and reused, one without a result is refused (:461-496)."""
     output_dir = Path(output_dir)
     output_dir.mkdir(parents=True, exist_ok=True)
     contract_path = output_dir / "contract.json"
@@ -212,12 +217,59 @@ def run_matmul_search(output_dir: Path, contract: MatmulSearchContract, *, run: 
         orders.append(tuple(c.name for c in order))
         for candidate in order:
             path = output_dir / f"round-{round_index:02d}" / candidate.name
-            runs.append((round_index, candidate.name, run(path, contract, candidate)))
+            runs.append((round_index, candidate.name, _load_or_run(path, contract, candidate, run)))
             paths.append(str(path.relative_to(output_dir)))
     result = summarise(contract, runs, orders, paths)
     if write_result:
         (output_dir / "result.json").write_text(result.to_json())
     return result
+
+
+def _expected_invocation(contract: MatmulSearchContract, candidate: MatmulSearchCandidate) -> dict:
+    return {
+        "mesh_size": contract.mesh_size, "m": contract.m, "k": contract.k, "n": contract.n,
+        "warmup_iterations": contract.warmup_iterations, "measured_iterations": contract.measured_iterations,
+        "tile": [candidate.tile_m, candidate.tile_n], "collective_strategy": contract.collective_strategy,
+        "scatter_dimension": contract.scatter_dimension, "output_dtype": contract.output_dtype, "mode": "timing",
+        "execution": contract.execution if contract.mesh_size > 1 else "one-process-per-gpu",
+    }
+
+
+def validate_saved_run_evidence(path: Path, contract: MatmulSearchContract, candidate: MatmulSearchCandidate):
+    """A finished run directory as search evidence: its invocation must be the one this contract
+    and candidate would make, the run must have passed with the declared number of samples, and
+    every artifact it lists must still have the recorded size and hash
+    (src/tpu_cake/search.py:166-372). Returns the saved result."""
+    import hashlib
+
+    from . import runner
+
+    result_path, invocation_path = path / "result.json", path / "invocation.json"
+    if not result_path.is_file() or not invocation_path.is_file():
+        raise ValueError(f"SEARCH_RUN_INCOMPLETE path={path}")
+    invocation = json.loads(invocation_path.read_text())
+    expected = _expected_invocation(contract, candidate)
+    if invocation != expected:
+        changed = sorted(key for key in set(invocation) | set(expected) if invocation.get(key) != expected.get(key))
+        raise ValueError(f"SEARCH_RUN_INVOCATION_MISMATCH path={path} fields={changed}")
+    raw = json.loads(result_path.read_text())
+    if not raw.get("passed") or raw.get("mode") != "timing" or len(raw.get("samples_ns", ())) != contract.measured_iterations:
+        raise ValueError(f"SEARCH_RUN_EVIDENCE_REJECTED path={path}")
+    for artifact in raw["artifacts"]:
+        target = path / artifact["path"]
+        if not target.is_file() or target.stat().st_size != artifact["size_bytes"] or hashlib.sha256(target.read_bytes()).hexdigest() != artifact["sha256"]:
+            raise ValueError(f"SEARCH_RUN_ARTIFACT_CHANGED path={target}")
+    raw["artifacts"] = tuple(runner.ArtifactReference(**artifact) for artifact in raw["artifacts"])
+    raw["samples_ns"] = tuple(raw["samples_ns"])
+    return runner.MatmulRunResult(**raw)
+
+
+def _load_or_run(path: Path, contract: MatmulSearchContract, candidate: MatmulSearchCandidate, run: Callable):
+    """Resume rule: a directory that exists holds either a finished, valid run (reused) or the
+    remains of one that died (refused: delete it deliberately, never silently)."""
+    if path.exists() and run is _run_candidate:
+        return validate_saved_run_evidence(path, contract, candidate)
+    return run(path, contract, candidate)
 
 
 def _run_candidate(path: Path, contract: MatmulSearchContract, candidate: MatmulSearchCandidate):
@@ -228,4 +280,5 @@ def _run_candidate(path: Path, contract: MatmulSearchContract, candidate: Matmul
         path, mesh_size=contract.mesh_size, m=contract.m, k=contract.k, n=contract.n, warmup_iterations=contract.warmup_iterations,
         measured_iterations=contract.measured_iterations, tile=schedule_lowering.MatmulTile(candidate.tile_m, candidate.tile_n),
         collective_strategy=contract.collective_strategy, scatter_dimension=contract.scatter_dimension, output_dtype=contract.output_dtype,
+        emulate_on_one_gpu=contract.execution == "emulated-on-one-gpu",
     )

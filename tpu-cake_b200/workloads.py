@@ -230,7 +230,7 @@ def paged_attention_schedule(*, batch: int = 4, q_heads: int = 4, kv_heads: int 
 
 def fused_rpa_schedule(*, tokens: int, sequences: int | None = None, q_heads: int, kv_heads: int, head_dim: int, pages: int,
                        page_size: int, page_indices: int, relative_dim: int = 16, bias_extent: int = 512, softmax_scale: str | None = None,
-                       execution_authority: str | None = None, target: str = "b200"):
+                       execution_authority: str | None = None, target: str = "b200", mesh: dict[str, int] | None = None):
     """Physical kernel holding one ``tpu_schedule.fused_ragged_paged_attention`` over external HBM
     buffers, output and cache aliased to the query and cache inputs (the contract of
     src/tpu_cake/dialects/tpu_schedule.py:2107-2349). ``sequences`` below ``tokens`` describes a ragged
@@ -253,8 +253,9 @@ def fused_rpa_schedule(*, tokens: int, sequences: int | None = None, q_heads: in
         buffer((tokens, q_heads, relative_dim), "T H R".split(), "bf16", **external),
         buffer((relative_dim, bias_extent), "R E".split(), "bf16", **external),
     )
+    mesh = dict(mesh or {})
     builder = KernelBuilder("inkling_fused_rpa", target, inputs, vmem_capacity_bytes=160 << 30, smem_capacity_bytes=227 << 10,
-                            mesh={}, interconnect_bandwidth_bytes_per_second={})
+                            mesh=mesh, interconnect_bandwidth_bytes_per_second={axis: 700_000_000_000 for axis in mesh})
     if execution_authority is None:
         execution_authority = FUSED_RPA_UPSTREAM_AUTHORITY if sequences == tokens and softmax_scale is None else FUSED_RPA_CUDA_AUTHORITY
     if softmax_scale is None:
@@ -267,6 +268,53 @@ def fused_rpa_schedule(*, tokens: int, sequences: int | None = None, q_heads: in
         kv_cluster_size=kv_block, execution_authority=execution_authority,
     )
     return builder.module()
+
+
+# The toy fused-RPA experiment of the reference (src/tpu_cake/workloads/inkling_rpa.py:413-468):
+# 4 decode sequences of 1, 17, 33 and 49 tokens, 4 query heads over 2 KV heads of dimension 32
+# (padded to 128 in the cache), 32 pages of 16 tokens dealt out in this fixed order.
+FUSED_RPA_PAGE_ORDER = (7, 2, 19, 4, 25, 1, 16, 9, 30, 12, 0, 5, 8, 11, 14, 17, 20, 23, 26, 29, 3, 6, 10, 13, 15, 18, 21, 22, 24, 27, 28, 31)
+FUSED_RPA_KV_LENGTHS = (1, 17, 33, 49)
+FUSED_RPA_BENCHMARK_PROTOCOL = {"seed": 97, "warmup_iterations": 5, "measured_iterations": 50}  # rpa_runner.py:82-98
+
+
+def inkling_fused_rpa_inputs(seed: int = 0) -> tuple[np.ndarray, ...]:
+    """The 11 inputs of the toy fused-RPA experiment as host arrays (bfloat16 through ml_dtypes,
+    int32 metadata), drawn exactly as the reference draws them: one ``default_rng(seed)`` normal
+    stream in the order queries, keys, values, cache (scale 0.25), relative states and projection
+    (scale 0.4), each rounded float32 -> bfloat16."""
+    import ml_dtypes
+
+    generator = np.random.default_rng(seed)
+
+    def bf16(shape, scale=1.0):
+        return generator.normal(scale=scale, size=shape).astype(np.float32).astype(ml_dtypes.bfloat16)
+
+    queries, keys, values = bf16((4, 4, 32)), bf16((4, 2, 32)), bf16((4, 2, 32))
+    cache = bf16((32, 16, 2, 2, 128), scale=0.25)
+    lengths = np.asarray(FUSED_RPA_KV_LENGTHS, dtype=np.int32)
+    aligned = -(-lengths.astype(np.int64) // 16) * 16
+    return (
+        queries, keys, values, cache, lengths, np.asarray(FUSED_RPA_PAGE_ORDER, dtype=np.int32), np.arange(5, dtype=np.int32),
+        np.concatenate(([0], np.cumsum(aligned))).astype(np.int32), np.full((3,), 4, dtype=np.int32),
+        bf16((4, 4, 16), scale=0.4), bf16((16, 128), scale=0.4),
+    )
+
+
+def inkling_fused_rpa_schedule():
+    """The physical kernel of the toy fused-RPA experiment (strict form: scale 1/head_dim, one query
+    token per sequence)."""
+    return fused_rpa_schedule(tokens=4, q_heads=4, kv_heads=2, head_dim=32, pages=32, page_size=16, page_indices=32,
+                              relative_dim=16, bias_extent=128)
+
+
+def inkling_sharded_rpa_schedule(*, data: int = 2, tensor: int = 4):
+    """The local kernel of the data x tensor sharded fused decode, on a mesh of ``data`` x ``tensor``
+    positions: the shapes of one position's shard (src/tpu_cake/workloads/inkling_rpa.py:198-228 --
+    4 sequences, 8 / 4 local heads of dimension 128, 3712 local pages of one token, 8192 page slots,
+    relative dimension 16 over an extent of 512)."""
+    return fused_rpa_schedule(tokens=4, q_heads=8, kv_heads=4, head_dim=128, pages=3712, page_size=1, page_indices=8192,
+                              relative_dim=16, bias_extent=512, mesh={"data": data, "tensor": tensor})
 
 
 def distributed_matmul_schedule(*, mesh_size: int = 4, m: int = 16, k: int = 32, n: int = 16, scatter_dimension: str = "N"):
