@@ -517,7 +517,7 @@ def bench_rpa(mesh, args, peaks, peak_kind, config) -> dict:
         },
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-            "traffic": MEASURED_TRAFFIC_BYTES["rpa_decode_64"] if world == 1 else None,
+            "traffic": MEASURED_TRAFFIC_BYTES["rpa_decode_64"] if (world == 1 and config.num_seqs == 64) else None,
             "peak_source": f"{peak_kind}: device copy bandwidth", "kernel": "cake_rpa_decode_sm100 (+plan, combine)",
             "algorithmic_bytes": bytes_total // world,
         },

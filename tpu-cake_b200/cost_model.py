@@ -25,7 +25,7 @@ class HardwareRateModel:
     ici_bytes_per_second: int  # per direction per device
 
 
-# Denominators measured on this pool's B200s (copy bandwidth, cuBLAS bf16 burst) and the nominal
+# Denominators measured on B200 (device copy bandwidth, cuBLAS bf16 burst throughput) and the nominal
 # NVLink 5 rate per direction; the reference's TPU7x model is 1153.5 TFLOP/s, 3690 GB/s, 600 GB/s
 # (src/tpu_cake/cost_model.py:95-106).
 B200_MEASURED = HardwareRateModel("b200-measured", 1_628_900_000_000_000, 6_459_000_000_000, 900_000_000_000)

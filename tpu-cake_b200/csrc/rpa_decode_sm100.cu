@@ -1277,18 +1277,6 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
   return CAKE_OK;
 }
 
-#ifdef CAKE_PF_TIMING
-int32_t cake_debug_pf_timing(unsigned long long* host_out, int32_t reset) {
-  CAKE_CUDA_TRY(cudaDeviceSynchronize());
-  CAKE_CUDA_TRY(cudaMemcpyFromSymbol(host_out, cake::g_pf_timing, sizeof(unsigned long long) * 256 * 16));
-  if (reset) {
-    static unsigned long long zeros[256 * 16];
-    CAKE_CUDA_TRY(cudaMemcpyToSymbol(cake::g_pf_timing, zeros, sizeof(zeros)));
-  }
-  return CAKE_OK;
-}
-#endif
-
 int32_t cake_rpa_status(cake_rpa* plan, void* stream_v, cake_status* out) {
   if (!plan || !out) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_rpa_status: null argument");
   int32_t rc = plan->status.read_and_clear(static_cast<cudaStream_t>(stream_v), out);

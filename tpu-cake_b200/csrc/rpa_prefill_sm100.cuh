@@ -69,25 +69,6 @@ struct PrefillParams {
   RpaParams r;             // page table, layout, scale, status
 };
 
-#ifdef CAKE_PF_TIMING
-// Development aid (off by default): cycles each role of every CTA spends blocked in its waits.
-// Slots per CTA: 0 softmax wait S, 1 softmax wait PV, 2 softmax total, 3 softmax steps,
-// 4 MMA wait K/V, 5 MMA wait S free, 6 MMA wait P, 7 MMA total, 8 K producer wait slot, 9 K producer
-// total, 10 V producer wait slot, 11 V producer total, 12 MMA issue of S = Q K^T, 13 MMA issue of O += P V.
-__device__ unsigned long long g_pf_timing[256 * 16];
-#define PF_DECLARE() long long pf_acc_[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
-#define PF_T0() const long long pf_t0_ = clock64()
-#define PF_ADD(slot, cond) do { if (cond) pf_acc_[slot] += clock64() - pf_t0_; } while (0)
-#define PF_COUNT(slot, cond) do { if (cond) pf_acc_[slot] += 1; } while (0)
-#define PF_FLUSH() do { for (int i_ = 0; i_ < 16; ++i_) if (pf_acc_[i_]) atomicAdd(&g_pf_timing[blockIdx.x * 16 + i_], static_cast<unsigned long long>(pf_acc_[i_])); } while (0)
-#else
-#define PF_DECLARE() do {} while (0)
-#define PF_T0() do {} while (0)
-#define PF_ADD(slot, cond) do {} while (0)
-#define PF_COUNT(slot, cond) do {} while (0)
-#define PF_FLUSH() do {} while (0)
-#endif
-
 __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
@@ -244,7 +225,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  PF_DECLARE();
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
@@ -331,7 +311,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     const uint32_t pair_barrier = 2 + quarter;
     const float scale = p.scale_log2;  // positive: checked on the host
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
-      PF_T0();
       const int limit = min(it.prior + it.q0 + row, it.kv_len - 1);  // last position this row sees
       // Running maximum (log2 domain, scaled) of the row and sum of this thread's columns. The
       // maximum is allowed to lag by kPfRescale, so the exponentials are bounded by 2^kPfRescale.
@@ -340,10 +319,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       for (int j = 0; j < it.n_steps; ++j) {
         const uint32_t t = step_total;
         {
-          PF_T0();
           ok = __all_sync(0xffffffffu, pf_wait(smem_u32(s_full), t & 1u, abort_flag));
-          PF_ADD(0, threadIdx.x == 0);
-          PF_COUNT(3, threadIdx.x == 0);
         }
         if (!ok) {
           if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 500);
@@ -388,9 +364,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         // its own barriers, completing every other step, so a wait names exactly one completion
         // even though this role may run up to two steps ahead of the issuer.
         if (j >= 2) {
-          PF_T0();
           ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[t & 1u]), ((t >> 1) & 1u) ^ 1u, abort_flag));
-          PF_ADD(1, threadIdx.x == 0);
           if (!ok) {
             if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 700);
             *abort_flag = 1;
@@ -480,7 +454,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         }
         tcgen05_fence_before();  // the accumulator reads are ordered before the next item's MMAs
       }
-      PF_ADD(2, threadIdx.x == 0);
     }
   } else if (warp == 8 || warp == 10 || warp == 11) {
     // ---------------------------------------------------------------- TMA producers (K ring, V ring)
@@ -507,7 +480,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     const int reps = (boxes + 31) >> 5;
     const bool wide = p.page_size >= 8;
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
-      PF_T0();
       if (warp == 8) {
         if (lane == 0) {
           mbar_arrive_expect_tx(smem_u32(q_full), kPfQBytes);
@@ -557,9 +529,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           load_window(win_base + 128, win_nxt);
         }
         {
-          PF_T0();
           alive = __all_sync(0xffffffffu, pf_wait(smem_u32(&empty[slot]), parity ^ 1u, abort_flag));
-          PF_ADD(is_v ? 10 : 8, lane == 0 && warp != 11);
         }
         if (!alive) {
           if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, (is_v ? 150 : 100) + j);
@@ -599,7 +569,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         ++loads_issued;
         ++step_total;
       }
-      PF_ADD(is_v ? 11 : 9, lane == 0 && warp != 11);
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
@@ -620,7 +589,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     const uint32_t desc_v_lo = static_cast<uint32_t>(umma_desc_sw128(smem_u32(v_smem), v_pages ? 2048 : 1024, kPfGroupBytes));
     const uint32_t desc_hi_v = v_pages ? desc_hi_1024 : desc_hi_kv;
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
-      PF_T0();
       int where = 200;
       auto issue_qk = [&](uint32_t t) {
         const uint32_t k_lo = desc_k_lo + (t % kPfRing) * (kPfTileBytes >> 4);
@@ -634,9 +602,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         tcgen05_commit(smem_u32(&k_empty[t % kPfRing]));
       };
       auto wait_tile = [&](uint64_t* full, uint32_t t) -> bool {
-        PF_T0();
         const bool arrived = __all_sync(0xffffffffu, pf_wait(smem_u32(&full[t % kPfRing]), (t / kPfRing) & 1u, abort_flag));
-        PF_ADD(4, lane == 0);
         return arrived;
       };
       // S = Q K^T runs two steps ahead of O += P V: S(t+2) is issued as soon as the softmax warps
@@ -647,16 +613,12 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         if (!wait_tile(k_full, t_next)) return false;
         where = 350;
         {
-          PF_T0();
           const bool taken = __all_sync(0xffffffffu, pf_wait(smem_u32(s_free), t_consumed & 1u, abort_flag));
-          PF_ADD(5, lane == 0);
           if (!taken) return false;
         }
         tcgen05_fence_after();
         {
-          PF_T0();
           if (lane == 0) issue_qk(t_next);
-          PF_ADD(12, lane == 0);
         }
         __syncwarp();
         return true;
@@ -690,9 +652,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           }
           where = 400;
           {
-            PF_T0();
             ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&p_full[t & 1u]), (t >> 1) & 1u, abort_flag));
-            PF_ADD(6, lane == 0);
           }
           if (!ok) break;
           if (j + 2 < it.n_steps) {
@@ -700,7 +660,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             if (!ok) break;
           }
           tcgen05_fence_after();
-          PF_T0();
           if (lane == 0) {
             const uint32_t a_base = tmem_base + kPfTmemP + (t & 1u) * 64;  // 8 columns per 16-token K step
             const uint32_t b_base = desc_v_lo + (t % kPfRing) * (kPfTileBytes >> 4);
@@ -712,7 +671,6 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             tcgen05_commit(smem_u32(&pv_full[t & 1u]));
             tcgen05_commit(smem_u32(&v_empty[t % kPfRing]));
           }
-          PF_ADD(13, lane == 0);
           __syncwarp();
           ++step_total;
         }
@@ -722,12 +680,10 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         *abort_flag = 1;
       }
       __syncwarp();
-      PF_ADD(7, lane == 0);
     }
   }
 
   // ---- orderly exit
-  PF_FLUSH();
   __syncthreads();
   if (*abort_flag) {
     if ((warp == 8 || warp == 10 || warp == 11) && lane == 0) {

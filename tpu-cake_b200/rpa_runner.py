@@ -236,7 +236,7 @@ def run_fused_rpa(output_dir: Path, *, mode: RunMode | str = RunMode.TIMING, see
         torch.cuda.synchronize(device)
         executable.status()
         if corrupt_device_cache_for_testing:
-            flat = cache.view(torch.uint16).view(-1)
+            flat = cache.view(torch.int16).view(-1)
             flat[12345] ^= 1
         actual = (_bf16_host(output), _bf16_host(cache))
         maximum_errors = tuple(_errors(a, e) for a, e in zip(actual, expected, strict=True))
