@@ -1214,7 +1214,8 @@ int32_t cake_rpa_mixed_enqueue(cake_rpa* plan, const void* q, const void* new_k,
   pp.kv_lens = kv_lens;
   pp.cu_q_lens = cu_q_lens;
   pp.first_seq = num_decode_seqs;
-  pp.heads_items = d.q_heads;
+  pp.paired = (d.q_heads / d.kv_heads) % 2 == 0 ? 1 : 0;
+  pp.heads_items = pp.paired ? d.q_heads / 2 : d.q_heads;
   pp.work_counter = reinterpret_cast<int32_t*>(ws + 64);
   pp.entry_count = reinterpret_cast<int32_t*>(ws + 128);
   pp.entries = reinterpret_cast<int4*>(ws + plan->off_pf_entries);

@@ -13,44 +13,46 @@
 //   cake_rpa_ragged_update_sm100   writes the new K/V of EVERY query token at its position
 //   cake_rpa_prefill_plan_sm100    cuts every sequence with index >= first_seq into 128-token query
 //                                  tiles, later tiles (more visible KV) first
-//   cake_rpa_prefill_sm100         persistent, one CTA per SM; a work item is 128 query tokens of one
-//                                  query head, walked over the KV range in steps of 128 tokens.
-//       warps 0-7   softmax: two threads per query row (TMEM lane), one per 64-column half of a step,
-//                   so the row maximum needs one exchange through shared memory and no shuffles.
-//                   S comes out of TMEM with tcgen05.ld, P = exp2(S - max) goes back into TMEM
-//                   (tcgen05.st, bf16 pairs, double-buffered) where the tensor core reads it as the
-//                   A operand, so P never touches shared memory; the output row accumulates in TMEM
-//                   over all steps and is read, rescaled and written back only when its maximum has
-//                   moved by more than 2^8.
-//       warps 8, 11 TMA producers of the query tile and of the K ring (3 slots), half a tile each
-//       warp 10     TMA producer of the V ring (3 slots). K tiles are gathered page by page in boxes of
-//                   one 8-token group (both 64-element halves of the row: 2 KiB), laid out
+//   cake_rpa_prefill_sm100         persistent, one CTA per SM. A work item is 128 query tokens of TWO
+//                                  query heads of one KV group (tiles A and B), walked over the KV
+//                                  range in steps of 128 tokens: every K and V tile is loaded once for
+//                                  both heads, and while the softmax of one tile runs the tensor core
+//                                  works for the other, so neither waits for the other's latency.
+//                                  (An odd group size pairs nothing: tile B is then left out.)
+//       warps 0-3   softmax of tile A, warps 4-7 softmax of tile B: one thread per query row (= TMEM
+//                   lane), so a row's maximum and sum need no exchange. A step brings its whole score
+//                   row (128 columns) into registers with one wait, forms P = exp2(S * scale - max)
+//                   and writes it back into tensor memory as packed bf16 OVER the columns of S (the
+//                   tensor core reads it from there as the A operand of O += P V). The output row
+//                   accumulates in TMEM over all steps and is read, rescaled and written back only
+//                   when its maximum has moved by more than 2^8.
+//       warps 8, 11 TMA producers of the two query tiles and of the K ring, half a tile each
+//       warp 10     TMA producer of the V ring. K tiles are gathered page by page in boxes of one
+//                   8-token group (both 64-element halves of the row: 2 KiB), laid out
 //                   [group][lo | hi][8 rows][128 B]: groups a uniform 2 KiB apart, which is what the
 //                   tcgen05 shared-memory descriptor of a 128-token operand needs. V tiles are read
-//                   16 tokens per MMA, so their boxes are 16 tokens (4 KiB) when pages allow: half
-//                   as many copy instructions (each costs its issuing warp about 70 cycles).
+//                   16 tokens per MMA, so their boxes are 16 tokens (4 KiB) when pages allow.
 //                   Never multicast.
-//       warp 9      tcgen05.mma issuer: S = Q K^T (128x128x128, both operands K-major in shared
-//                   memory) two steps ahead of the softmax, as soon as the softmax warps have taken
-//                   the previous S into registers, and O += P V (128x128x128, P from TMEM, V consumed
-//                   in place from shared memory as an MN-major operand) when P is written.
-//     A 128-wide MMA keeps the tensor pipe busy for about 64 cycles, which is also what the issuing
-//     thread needs per instruction; 64-wide steps were issue-bound.
+//       warp 9      tcgen05.mma issuer, in the order S_A(0) S_B(0) | O_A+=P_A V(j), S_A(j+1),
+//                   O_B+=P_B V(j), S_B(j+1) | ...: the tensor pipe executes in issue order, so the
+//                   next S of a tile follows the P V that read the P it overwrites.
+//     TMEM: S_A columns 0-127 (P_A over 0-63), S_B 128-255 (P_B over 128-191), O_A 256-383, O_B 384-511.
 #pragma once
 
 namespace cake {
 
 constexpr int kPfThreads = 384;
-constexpr int kPfTileQ = 128;                    // query rows per work item (one query head)
+constexpr int kPfTileQ = 128;                    // query rows per tile (one query head)
 constexpr int kPfTileKv = 128;                   // KV tokens per step
-constexpr int kPfRing = 3;                       // slots of the K ring and of the V ring
-constexpr int kPfQBytes = kPfTileQ * 256;        // queries: [2 halves][128 rows][128 B]
+constexpr int kPfRingK = 2;                      // slots of the K ring (a third slot measured no faster)
+constexpr int kPfRingV = 2;                      // slots of the V ring
+constexpr int kPfQBytes = kPfTileQ * 256;        // one query tile: [2 halves][128 rows][128 B]
 constexpr int kPfTileBytes = kPfTileKv * 256;    // a K or V tile: [16 groups][lo | hi][8 rows][128 B]
 constexpr int kPfGroupBytes = 2048;              // one 8-token group of a K or V tile
-constexpr int kPfTailBytes = 3072;               // barriers, TMEM slot, item slots, 2 KiB row-maximum exchange
-constexpr int kPfSmemBytes = kPfQBytes + 2 * kPfRing * kPfTileBytes + kPfTailBytes;  // all a CTA may own
-constexpr uint32_t kPfTmemCols = 512;            // S @0 (128 columns), O @128 (128), P buffers @256 and @320 (64 each)
-constexpr uint32_t kPfTmemP = 256;
+constexpr int kPfTailBytes = 1024;               // barriers, TMEM slot, item slots
+constexpr int kPfSmemBytes = 2 * kPfQBytes + (kPfRingK + kPfRingV) * kPfTileBytes + kPfTailBytes;
+constexpr uint32_t kPfTmemCols = 512;
+constexpr uint32_t kPfTmemO = 256;               // first column of O_A; tile X: S at 128 X, O at 256 + 128 X
 constexpr long long kPfBarrierBudget = 2000000000ll;
 constexpr float kPfRescale = 8.f;                // log2 units the row maximum may lag before O is rescaled
 
@@ -60,7 +62,8 @@ struct PrefillParams {
   const int32_t* kv_lens;
   const int32_t* cu_q_lens;
   int32_t first_seq;       // sequences [first_seq, num_seqs) are handled here
-  int32_t heads_items;     // work items per (sequence, query tile): one per query head
+  int32_t heads_items;     // work items per (sequence, query tile): one per query head, or per pair of heads
+  int32_t paired;          // 1: an item is heads 2i and 2i+1 of one KV group (group size even)
   int32_t* work_counter;
   int32_t* entry_count;    // number of (sequence, query tile) entries
   int4* entries;           // two per tile: {sequence, first query row, q_len, kv_len}, {first query token, first page-table slot, 0, 0}
@@ -185,10 +188,54 @@ __device__ __forceinline__ uint64_t pf_desc(uint32_t lo, uint32_t hi) {
   return d;
 }
 
+// Two float32 values in one 64-bit register, for the packed (two per instruction) arithmetic of sm_100.
+__device__ __forceinline__ uint64_t pf_pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+
+__device__ __forceinline__ void pf_unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__device__ __forceinline__ uint64_t pf_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+__device__ __forceinline__ uint64_t pf_add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 __device__ __forceinline__ float pf_max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
+}
+
+// Warp-collective: lane i writes 16 consecutive 32-bit columns of TMEM lane (base lane + i).
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// Warp-collective: lane i receives 16 consecutive f32 columns of TMEM lane (base lane + i).
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
 }
 
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -196,49 +243,48 @@ __global__ void __launch_bounds__(kPfThreads, 1)
                            const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v, const PrefillParams pp) {
   const RpaParams& p = pp.r;
-  // The tiles need 1 KiB alignment (128-byte swizzle atoms) and the CTA uses every byte it may own,
-  // so there is no slack to round the base up: the alignment is requested and checked.
+  // The tiles need 1 KiB alignment (128-byte swizzle atoms): requested and checked.
   extern __shared__ __align__(1024) uint8_t pf_smem_raw[];
   uint8_t* smem = pf_smem_raw;
   if (smem_u32(smem) & 1023u) {
     if (threadIdx.x == 0) rpa_record(p.status, 5, blockIdx.x, static_cast<int>(smem_u32(smem) & 1023u), 0);
     return;
   }
-  uint8_t* q_smem = smem;                                  // [2 halves][128 rows][128 B]
-  uint8_t* k_smem = q_smem + kPfQBytes;                    // [ring][16 groups][lo | hi][8 rows][128 B]
-  uint8_t* v_smem = k_smem + kPfRing * kPfTileBytes;       // same
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + kPfRing * kPfTileBytes);
+  uint8_t* q_smem = smem;                                  // [tile A | tile B][2 halves][128 rows][128 B]
+  uint8_t* k_smem = q_smem + 2 * kPfQBytes;                // [ring][16 groups][lo | hi][8 rows][128 B]
+  uint8_t* v_smem = k_smem + kPfRingK * kPfTileBytes;      // same
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + kPfRingV * kPfTileBytes);
   uint64_t* q_full = bars;                 // [1]
-  uint64_t* k_full = bars + 1;             // [ring]
-  uint64_t* k_empty = k_full + kPfRing;    // [ring]
-  uint64_t* v_full = k_empty + kPfRing;    // [ring]
-  uint64_t* v_empty = v_full + kPfRing;    // [ring]
-  uint64_t* s_full = v_empty + kPfRing;    // [1]
-  uint64_t* s_free = s_full + 1;           // [1]
-  uint64_t* p_full = s_free + 1;           // [2 P buffers]
-  uint64_t* pv_full = p_full + 2;          // [2 P buffers]
-  uint64_t* drain_bar = pv_full + 2;       // [1]
+  uint64_t* k_full = bars + 1;             // [K ring]
+  uint64_t* k_empty = k_full + kPfRingK;   // [K ring]
+  uint64_t* v_full = k_empty + kPfRingK;   // [V ring]
+  uint64_t* v_empty = v_full + kPfRingV;   // [V ring]
+  uint64_t* s_full = v_empty + kPfRingV;   // [2 tiles] S = Q K^T of the tile's current step is complete
+  uint64_t* p_full = s_full + 2;           // [2 tiles][2 halves] 128 rows x 64 KV tokens of P are in tensor memory
+  uint64_t* pv_done = p_full + 4;          // [2 tiles] O += P V of the tile's current step is complete
+  uint64_t* drain_bar = pv_done + 2;       // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   volatile int32_t* item_slot = reinterpret_cast<volatile int32_t*>(tmem_base_slot + 2);  // [2]
-  float* xchg = reinterpret_cast<float*>(tmem_base_slot + 4);  // [2 parities][2 column halves][128 rows]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
-    for (int s = 0; s < kPfRing; ++s) {
+    for (int s = 0; s < kPfRingK; ++s) {
       mbar_init(smem_u32(&k_full[s]), 2);  // two producer warps, half a tile each
       mbar_init(smem_u32(&k_empty[s]), 1);
+    }
+    for (int s = 0; s < kPfRingV; ++s) {
       mbar_init(smem_u32(&v_full[s]), 1);
       mbar_init(smem_u32(&v_empty[s]), 1);
     }
-    mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(s_free), 256);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&p_full[b]), 256);
-      mbar_init(smem_u32(&pv_full[b]), 1);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(smem_u32(&s_full[x]), 1);
+      mbar_init(smem_u32(&p_full[2 * x]), 128);
+      mbar_init(smem_u32(&p_full[2 * x + 1]), 128);
+      mbar_init(smem_u32(&pv_done[x]), 1);
     }
     mbar_init(smem_u32(drain_bar), 1);
     *abort_flag = 0;
@@ -258,17 +304,19 @@ __global__ void __launch_bounds__(kPfThreads, 1)
   const uint32_t tmem_base = *tmem_base_slot;
   const int total_items = min(*pp.entry_count, pp.max_entries) * pp.heads_items;
 
-  // Running step count that persists across work items: every role advances it the same way. It
-  // gives the ring slot (t % ring), the P buffer (t & 1) and every barrier phase.
-  uint32_t step_total = 0;
+  // Running counts that persist across work items; every role advances them the same way.
+  // kv_total numbers the K / V tiles (ring slot kv_total % ring, phase (kv_total / ring) & 1, per ring);
+  // tile_total[x] numbers the steps tile x has taken (phase of its three barriers: tile_total & 1).
+  uint32_t kv_total = 0;
+  uint32_t tile_total[2] = {0u, 0u};
   uint32_t loads_issued = 0;  // producers: tiles issued, for the orderly exit
 
   struct Item {
-    int id, seq, q0, kv_len, head, kvh, prior, rows, kv_needed, n_steps, q_tok0, table_base;
+    int id, seq, q0, kv_len, head, kvh, two, prior, rows, kv_needed, n_steps, q_tok0, table_base;
   };
   // Hands the next work item to the whole CTA. One thread claims (an item, or -1 after an abort),
   // one item ahead, so that every thread leaves its loop in the same iteration. The barrier also
-  // separates items: when it opens, every role has finished the previous one, so the query buffer
+  // separates items: when it opens, every role has finished the previous one, so the query buffers
   // and all TMEM columns are free.
   auto next_item = [&](uint32_t iter, Item& it) -> bool {
     named_bar_sync(1, kPfThreads);
@@ -283,7 +331,8 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     it.seq = entry.x;
     it.q0 = entry.y;
     it.kv_len = entry.w;
-    it.head = id % pp.heads_items;
+    it.two = pp.paired;
+    it.head = (id % pp.heads_items) * (pp.paired ? 2 : 1);  // tile A's query head; tile B's is the next one
     it.kvh = it.head / p.group;
     it.prior = entry.w - entry.z;               // cached tokens before the first query token
     it.rows = min(kPfTileQ, entry.z - entry.y);
@@ -297,163 +346,151 @@ __global__ void __launch_bounds__(kPfThreads, 1)
 
   if (warp < 8) {
     // ---------------------------------------------------------------- softmax warps
-    // Two threads per query row: warp w and warp w + 4 read the same TMEM lanes (32 (w & 3) ...) and
-    // take the lower and upper 64 columns of S, P and O. The row maximum is combined through shared
-    // memory once per step (a 64-thread named barrier per warp pair), so both threads derive the
-    // same running maximum and the same rescale decisions; the row sums are combined at the end.
-    const int quarter = warp & 3;
-    const int half = warp >> 2;
-    const int row = quarter * 32 + lane;
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t t_s = t_lane + half * 64;
-    const uint32_t t_o = t_lane + 128 + half * 64;
-    const uint32_t t_p = t_lane + kPfTmemP + half * 32;  // this thread's 32 packed columns of P buffer 0
-    const uint32_t pair_barrier = 2 + quarter;
+    // Warps 0-3 own tile A, warps 4-7 tile B; thread = query row = TMEM lane 32 (warp & 3) + lane.
+    const int x = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t t_s = t_lane + x * 128;             // S of this tile; P is written over its first 64 columns
+    const uint32_t t_o = t_lane + kPfTmemO + x * 128;  // O of this tile
     const float scale = p.scale_log2;  // positive: checked on the host
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
+      if (x == 1 && !it.two) continue;  // nothing is paired with tile A in this batch
       const int limit = min(it.prior + it.q0 + row, it.kv_len - 1);  // last position this row sees
-      // Running maximum (log2 domain, scaled) of the row and sum of this thread's columns. The
-      // maximum is allowed to lag by kPfRescale, so the exponentials are bounded by 2^kPfRescale.
+      // Running maximum (log2 domain, scaled) and sum of the row. The maximum is allowed to lag by
+      // kPfRescale, so the exponentials are bounded by 2^kPfRescale.
       float m_run = kNegBig, l_run = 0.f;
       bool ok = true;
+      int where = 500;
       for (int j = 0; j < it.n_steps; ++j) {
-        const uint32_t t = step_total;
-        {
-          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(s_full), t & 1u, abort_flag));
-        }
-        if (!ok) {
-          if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 500);
-          *abort_flag = 1;
-          break;
-        }
+        const uint32_t t = tile_total[x];
+        ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&s_full[x]), t & 1u, abort_flag));
+        if (!ok) break;
         tcgen05_fence_after();
-        uint32_t v[64];
-        {
-          uint32_t c0[32], c1[32];
-          tmem_ld_32x32b_x32(t_s, c0);
-          tmem_ld_32x32b_x32(t_s + 32, c1);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            v[c] = c0[c];
-            v[32 + c] = c1[c];
-          }
-        }
-        tcgen05_fence_before();
-        mbar_arrive(smem_u32(s_free));  // S is in registers: the next S = Q K^T may overwrite it
-        const int pos0 = j * kPfTileKv + half * 64;
+        const int pos0 = j * kPfTileKv;
+        // The whole score row comes into registers with one wait: four loads in flight together
+        // (a load's round trip through tensor memory is several hundred cycles, and a step that
+        // waited for eight of them in turn spent most of its time there).
+        uint32_t v[128];
+        tmem_ld_32x32b_x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_ld_32x32b_x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+        tmem_ld_32x32b_x32(t_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
+        tmem_ld_32x32b_x32(t_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
+        tmem_ld_wait();
         // Only the steps that cross the row's causal limit (or the end of the sequence) mask.
-        if (__any_sync(0xffffffffu, pos0 + 63 > limit)) {
+        if (__any_sync(0xffffffffu, pos0 + kPfTileKv - 1 > limit)) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
+          for (int c = 0; c < 128; ++c)
             if (pos0 + c > limit) v[c] = 0xff800000u;  // -inf
         }
-        float mr0 = __uint_as_float(v[0]), mr1 = __uint_as_float(v[1]);
+        float mr0 = __uint_as_float(v[0]), mr1 = __uint_as_float(v[1]), mr2 = __uint_as_float(v[2]), mr3 = __uint_as_float(v[3]);
 #pragma unroll
-        for (int c = 2; c + 3 < 64; c += 4) {
+        for (int c = 4; c < 128; c += 8) {
           mr0 = pf_max3(mr0, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
           mr1 = pf_max3(mr1, __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
-        }
-        const float mine = pf_max3(mr0, mr1, fmaxf(__uint_as_float(v[62]), __uint_as_float(v[63])));
-        // Combine with the thread that holds the other 64 columns of this row.
-        float* slot = xchg + (t & 1u) * 256;
-        slot[half * 128 + row] = mine;
-        named_bar_sync(pair_barrier, 64);
-        const float mx = fmaxf(mine, slot[(half ^ 1) * 128 + row]) * scale;
-        // P is double-buffered: this step writes buffer t & 1, which PV(t-2) read. Each buffer has
-        // its own barriers, completing every other step, so a wait names exactly one completion
-        // even though this role may run up to two steps ahead of the issuer.
-        if (j >= 2) {
-          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[t & 1u]), ((t >> 1) & 1u) ^ 1u, abort_flag));
-          if (!ok) {
-            if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 700);
-            *abort_flag = 1;
-            break;
+          if (c + 4 < 128) {
+            mr2 = pf_max3(mr2, __uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
+            mr3 = pf_max3(mr3, __uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
           }
         }
+        const float mx = fmaxf(fmaxf(mr0, mr1), fmaxf(mr2, mr3)) * scale;
         float alpha = 1.f;
         if (mx > m_run + kPfRescale) {
           alpha = pf_exp2(m_run - mx);
           m_run = mx;
         }
-        // Rare: the accumulator is read and rewritten once PV(t-1) is complete; PV(t) is issued
-        // only after p_full below. Both threads of a row take the same decision.
+        // Rare: the accumulator is read and rewritten once the previous O += P V of this tile is
+        // complete; the next one is issued only after p_full below.
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[(t - 1u) & 1u]), ((t - 1u) >> 1) & 1u, abort_flag));
-          if (!ok) {
-            if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 800);
-            *abort_flag = 1;
-            break;
-          }
+          where = 800;
+          ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_done[x]), (t - 1u) & 1u, abort_flag));
+          if (!ok) break;
           tcgen05_fence_after();
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t acc[32];
-            tmem_ld_32x32b_x32(t_o + c * 32, acc);
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t acc[16];
+            tmem_ld_32x32b_x16(t_o + c * 16, acc);
             tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
-            tmem_st_32x32b_x32(t_o + c * 32, acc);
+            for (int e = 0; e < 16; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+            tmem_st_32x32b_x16(t_o + c * 16, acc);
           }
           tmem_st_wait();
+          where = 500;
         }
-        // ---- P = exp2(S * scale - max) as bf16 into tensor memory: row = lane, two values per
-        //      32-bit column, which is the form tcgen05.mma reads an A operand from TMEM in
-        const float neg_m = -m_run;
-        float sum0 = 0.f, sum1 = 0.f;
-        uint32_t w[32];
+        // ---- P = exp2(S * scale - max) as bf16 pairs, written over the columns of S (all of it is
+        //      in registers): 32 scores become 16 packed columns. The packing rounds half up with
+        //      integer adds and a byte permute, so that only the exponentials use the XU pipe,
+        //      which the conversion instruction would otherwise share with them.
+        // Scale-and-subtract and the row sum run two values per instruction (packed f32x2), the
+        // packing to bf16 is one conversion per pair: the exponentials, on the XU pipe, are the only
+        // per-element instructions left. P is announced in two halves of 64 KV tokens, so the
+        // tensor core starts O += P V on the first while the second is being formed.
+        const uint64_t scale2 = pf_pack2(scale, scale);
+        const uint64_t neg_m2 = pf_pack2(-m_run, -m_run);
+        uint64_t sum2 = pf_pack2(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float a = pf_exp2(fmaf(__uint_as_float(v[2 * c]), scale, neg_m));
-          const float b = pf_exp2(fmaf(__uint_as_float(v[2 * c + 1]), scale, neg_m));
-          sum0 += a;
-          sum1 += b;
-          w[c] = pack_bf16(a, b);
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t w[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            float x0, x1;
+            pf_unpack2(pf_fma2(pf_pack2(__uint_as_float(v[ch * 32 + 2 * c]), __uint_as_float(v[ch * 32 + 2 * c + 1])), scale2, neg_m2), x0, x1);
+            const float e0 = pf_exp2(x0);
+            const float e1 = pf_exp2(x1);
+            sum2 = pf_add2(sum2, pf_pack2(e0, e1));
+            // bf16 pair, rounded half up with integer adds and a byte permute (measured faster
+            // than the conversion instruction here).
+            w[c] = __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632);
+          }
+          tmem_st_32x32b_x16(t_s + ch * 16, w);
+          if (ch == 1) {
+            tmem_st_wait();
+            tcgen05_fence_before();
+            mbar_arrive(smem_u32(&p_full[2 * x]));
+          }
         }
-        tmem_st_32x32b_x32(t_p + (t & 1u) * 64, w);
+        float sum0, sum1;
+        pf_unpack2(sum2, sum0, sum1);
         l_run = l_run * alpha + (sum0 + sum1);
         tmem_st_wait();
         tcgen05_fence_before();     // TMEM reads and writes above are ordered before the next MMAs
-        mbar_arrive(smem_u32(&p_full[t & 1u]));
-        ++step_total;
+        mbar_arrive(smem_u32(&p_full[2 * x + 1]));
+        ++tile_total[x];
       }
       if (ok) {
-        // The last PV of the item.
-        const uint32_t last = step_total - 1u;
-        ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_full[last & 1u]), (last >> 1) & 1u, abort_flag));
-        if (!ok) {
-          if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, 600);
-          *abort_flag = 1;
-        }
+        // The last O += P V of the item.
+        where = 600;
+        ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&pv_done[x]), (tile_total[x] - 1u) & 1u, abort_flag));
       }
-      // Row sum = the two threads' partial sums, added in a fixed order. The barrier is taken on
-      // every path so that a pair never splits.
-      float* slot = xchg + (step_total & 1u) * 256;
-      slot[half * 128 + row] = l_run;
-      named_bar_sync(pair_barrier, 64);
-      if (ok) {
-        tcgen05_fence_after();
-        const float inv = 1.f / (slot[row] + slot[128 + row]);
-        __nv_bfloat16* dst = pp.out + (static_cast<size_t>(it.q_tok0 + row) * p.q_heads + it.head) * 128 + half * 64;
+      if (!ok) {
+        if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, where + x);
+        *abort_flag = 1;
+        continue;
+      }
+      tcgen05_fence_after();
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = pp.out + (static_cast<size_t>(it.q_tok0 + row) * p.q_heads + it.head + x) * 128;
+      {
+        // The whole output row with one wait, as for the scores.
+        uint32_t acc[128];
+        tmem_ld_32x32b_x32(t_o, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+        tmem_ld_32x32b_x32(t_o + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+        tmem_ld_32x32b_x32(t_o + 64, *reinterpret_cast<uint32_t(*)[32]>(&acc[64]));
+        tmem_ld_32x32b_x32(t_o + 96, *reinterpret_cast<uint32_t(*)[32]>(&acc[96]));
+        tmem_ld_wait();
+        if (row < it.rows) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t acc[32];
-          tmem_ld_32x32b_x32(t_o + c * 32, acc);
-          tmem_ld_wait();
-          if (row < it.rows) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              uint4 piece;
-              piece.x = pack_bf16(__uint_as_float(acc[e * 8 + 0]) * inv, __uint_as_float(acc[e * 8 + 1]) * inv);
-              piece.y = pack_bf16(__uint_as_float(acc[e * 8 + 2]) * inv, __uint_as_float(acc[e * 8 + 3]) * inv);
-              piece.z = pack_bf16(__uint_as_float(acc[e * 8 + 4]) * inv, __uint_as_float(acc[e * 8 + 5]) * inv);
-              piece.w = pack_bf16(__uint_as_float(acc[e * 8 + 6]) * inv, __uint_as_float(acc[e * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = piece;
-            }
+          for (int e = 0; e < 16; ++e) {
+            uint4 piece;
+            piece.x = pack_bf16(__uint_as_float(acc[e * 8 + 0]) * inv, __uint_as_float(acc[e * 8 + 1]) * inv);
+            piece.y = pack_bf16(__uint_as_float(acc[e * 8 + 2]) * inv, __uint_as_float(acc[e * 8 + 3]) * inv);
+            piece.z = pack_bf16(__uint_as_float(acc[e * 8 + 4]) * inv, __uint_as_float(acc[e * 8 + 5]) * inv);
+            piece.w = pack_bf16(__uint_as_float(acc[e * 8 + 6]) * inv, __uint_as_float(acc[e * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + e * 8) = piece;
           }
         }
-        tcgen05_fence_before();  // the accumulator reads are ordered before the next item's MMAs
       }
+      tcgen05_fence_before();  // the accumulator reads are ordered before the next item's MMAs
     }
   } else if (warp == 8 || warp == 10 || warp == 11) {
     // ---------------------------------------------------------------- TMA producers (K ring, V ring)
@@ -464,6 +501,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     uint8_t* ring = is_v ? v_smem : k_smem;
     uint64_t* full = is_v ? v_full : k_full;
     uint64_t* empty = is_v ? v_empty : k_empty;
+    const uint32_t ring_slots = is_v ? kPfRingV : kPfRingK;
     // The tensor-memory engine takes of the order of a hundred cycles per copy instruction, so the
     // number of boxes per tile matters. K tiles need a uniform 8-token group stride (the 128 tokens
     // are the N extent of one MMA), which caps a box at one group. A V tile is consumed 16 tokens per
@@ -482,10 +520,11 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
       if (warp == 8) {
         if (lane == 0) {
-          mbar_arrive_expect_tx(smem_u32(q_full), kPfQBytes);
-          for (int half = 0; half < 2; ++half)
-            tma_load_2d(smem_u32(q_smem + half * (kPfQBytes / 2)), &tmap_q, smem_u32(q_full), it.head * 128 + half * 64,
-                        it.q_tok0);
+          mbar_arrive_expect_tx(smem_u32(q_full), it.two ? 2 * kPfQBytes : kPfQBytes);
+          for (int x = 0; x < (it.two ? 2 : 1); ++x)
+            for (int half = 0; half < 2; ++half)
+              tma_load_2d(smem_u32(q_smem + x * kPfQBytes + half * (kPfQBytes / 2)), &tmap_q, smem_u32(q_full),
+                          (it.head + x) * 128 + half * 64, it.q_tok0);
         }
         __syncwarp();
       }
@@ -518,9 +557,9 @@ __global__ void __launch_bounds__(kPfThreads, 1)
       load_window(128, win_nxt);
       bool alive = true;
       for (int j = 0; j < it.n_steps && alive; ++j) {
-        const uint32_t t = step_total;
-        const uint32_t slot = t % kPfRing;
-        const uint32_t parity = (t / kPfRing) & 1u;
+        const uint32_t t = kv_total;
+        const uint32_t slot = t % ring_slots;
+        const uint32_t parity = (t / ring_slots) & 1u;
         const int first_slot = (j * kPfTileKv) >> p.log2_ps;
         if (first_slot >= win_base + 128) {  // a tile never straddles two windows
           win_base += 128;
@@ -528,9 +567,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
           for (int r = 0; r < 4; ++r) win_cur[r] = win_nxt[r];
           load_window(win_base + 128, win_nxt);
         }
-        {
-          alive = __all_sync(0xffffffffu, pf_wait(smem_u32(&empty[slot]), parity ^ 1u, abort_flag));
-        }
+        alive = __all_sync(0xffffffffu, pf_wait(smem_u32(&empty[slot]), parity ^ 1u, abort_flag));
         if (!alive) {
           if (lane == 0 && !*abort_flag) rpa_record(p.status, 1, blockIdx.x, it.id, (is_v ? 150 : 100) + j);
           *abort_flag = 1;
@@ -567,7 +604,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
         }
         __syncwarp();
         ++loads_issued;
-        ++step_total;
+        ++kv_total;
       }
     }
   } else if (warp == 9) {
@@ -590,56 +627,56 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     const uint32_t desc_hi_v = v_pages ? desc_hi_1024 : desc_hi_kv;
     for (uint32_t iter = 0; next_item(iter, it); ++iter) {
       int where = 200;
-      auto issue_qk = [&](uint32_t t) {
-        const uint32_t k_lo = desc_k_lo + (t % kPfRing) * (kPfTileBytes >> 4);
+      const int tiles = it.two ? 2 : 1;
+      // S_x = Q_x K^T of K tile `t` (one elected lane).
+      auto issue_qk = [&](int x, uint32_t t) {
+        const uint32_t k_lo = desc_k_lo + (t % kPfRingK) * (kPfTileBytes >> 4);
+        const uint32_t q_lo = desc_q_lo + x * (kPfQBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t a_lo = desc_q_lo + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+          const uint32_t a_lo = q_lo + (((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
           const uint32_t b_lo = k_lo + (((ks >> 2) * 1024 + (ks & 3) * 32) >> 4);
-          tcgen05_mma_bf16(tmem_base, pf_desc(a_lo, desc_hi_1024), pf_desc(b_lo, desc_hi_kv), idesc, ks != 0 ? 1u : 0u);
+          tcgen05_mma_bf16(tmem_base + x * 128, pf_desc(a_lo, desc_hi_1024), pf_desc(b_lo, desc_hi_kv), idesc, ks != 0 ? 1u : 0u);
         }
-        tcgen05_commit(smem_u32(s_full));
-        tcgen05_commit(smem_u32(&k_empty[t % kPfRing]));
+        tcgen05_commit(smem_u32(&s_full[x]));
       };
-      auto wait_tile = [&](uint64_t* full, uint32_t t) -> bool {
-        const bool arrived = __all_sync(0xffffffffu, pf_wait(smem_u32(&full[t % kPfRing]), (t / kPfRing) & 1u, abort_flag));
-        return arrived;
+      // One half (64 KV tokens: four 16-token K steps) of O_x += P_x V of V tile `t`; P_x is read
+      // from tensor memory, 8 columns per K step.
+      auto issue_pv_half = [&](int x, uint32_t t, int half, bool accumulate) {
+        const uint32_t a_base = tmem_base + x * 128;
+        const uint32_t b_base = desc_v_lo + (t % kPfRingV) * (kPfTileBytes >> 4);
+        const uint32_t d = tmem_base + kPfTmemO + x * 128;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const int ks = half * 4 + k4;
+          tcgen05_mma_bf16_ts(d, a_base + ks * 8, pf_desc(b_base + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_v), idesc_pv,
+                              (accumulate || ks != 0) ? 1u : 0u);
+        }
+        if (half == 1) tcgen05_commit(smem_u32(&pv_done[x]));
       };
-      // S = Q K^T runs two steps ahead of O += P V: S(t+2) is issued as soon as the softmax warps
-      // have taken S(t+1) into registers, which is right after they finish step t, and before PV(t);
-      // the softmax never waits for a score tile, and PV(t) still finishes well inside step t+1.
-      auto next_scores = [&](uint32_t t_next, uint32_t t_consumed) -> bool {
-        where = 300;
-        if (!wait_tile(k_full, t_next)) return false;
-        where = 350;
-        {
-          const bool taken = __all_sync(0xffffffffu, pf_wait(smem_u32(s_free), t_consumed & 1u, abort_flag));
-          if (!taken) return false;
-        }
-        tcgen05_fence_after();
-        {
-          if (lane == 0) issue_qk(t_next);
-        }
-        __syncwarp();
-        return true;
+      auto wait_tile = [&](uint64_t* full, uint32_t t, uint32_t ring_slots) -> bool {
+        return __all_sync(0xffffffffu, pf_wait(smem_u32(&full[t % ring_slots]), (t / ring_slots) & 1u, abort_flag));
       };
       bool ok = __all_sync(0xffffffffu, pf_wait(smem_u32(q_full), iter & 1u, abort_flag));
-      if (ok) ok = wait_tile(k_full, step_total);
+      if (ok) ok = wait_tile(k_full, kv_total, kPfRingK);
       if (ok) {
         tcgen05_fence_after();
-        if (lane == 0) issue_qk(step_total);
+        if (lane == 0) {
+          for (int x = 0; x < tiles; ++x) issue_qk(x, kv_total);
+          tcgen05_commit(smem_u32(&k_empty[kv_total % kPfRingK]));
+        }
         __syncwarp();
-        if (it.n_steps > 1) ok = next_scores(step_total + 1, step_total);
         for (int j = 0; j < it.n_steps && ok; ++j) {
-          const uint32_t t = step_total;
+          const uint32_t t = kv_total;
+          const bool more = j + 1 < it.n_steps;
           where = 380;
-          ok = wait_tile(v_full, t);
+          ok = wait_tile(v_full, t, kPfRingV);
           if (!ok) break;
           // V rows at or beyond kv_len are zeroed (page tails may hold anything; 0 * NaN would
           // poison the product) before the tensor core reads them.
           const int first_bad = max(it.kv_len - j * kPfTileKv, 0);
           if (first_bad < kPfTileKv) {
-            uint8_t* v_base = v_smem + (t % kPfRing) * kPfTileBytes;
+            uint8_t* v_base = v_smem + (t % kPfRingV) * kPfTileBytes;
             for (int e = lane; e < (kPfTileKv - first_bad) * 16; e += 32) {
               const int vrow = first_bad + (e >> 4);
               const int piece = e & 15;
@@ -650,29 +687,34 @@ __global__ void __launch_bounds__(kPfThreads, 1)
             fence_proxy_async_smem();
             __syncwarp();
           }
-          where = 400;
-          {
-            ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&p_full[t & 1u]), (t >> 1) & 1u, abort_flag));
-          }
-          if (!ok) break;
-          if (j + 2 < it.n_steps) {
-            ok = next_scores(t + 2, t + 1);
+          if (more) {
+            where = 300;
+            ok = wait_tile(k_full, t + 1, kPfRingK);
             if (!ok) break;
           }
-          tcgen05_fence_after();
-          if (lane == 0) {
-            const uint32_t a_base = tmem_base + kPfTmemP + (t & 1u) * 64;  // 8 columns per 16-token K step
-            const uint32_t b_base = desc_v_lo + (t % kPfRing) * (kPfTileBytes >> 4);
-            tcgen05_mma_bf16_ts(tmem_base + 128, a_base, pf_desc(b_base, desc_hi_v), idesc_pv, j != 0 ? 1u : 0u);
-#pragma unroll
-            for (int ks = 1; ks < 8; ++ks)
-              tcgen05_mma_bf16_ts(tmem_base + 128, a_base + ks * 8, pf_desc(b_base + ((ks * 2 * kPfGroupBytes) >> 4), desc_hi_v),
-                                  idesc_pv, 1u);
-            tcgen05_commit(smem_u32(&pv_full[t & 1u]));
-            tcgen05_commit(smem_u32(&v_empty[t % kPfRing]));
+          for (int x = 0; x < tiles && ok; ++x) {
+            for (int half = 0; half < 2 && ok; ++half) {
+              where = 400 + 2 * x + half;
+              ok = __all_sync(0xffffffffu, pf_wait(smem_u32(&p_full[2 * x + half]), tile_total[x] & 1u, abort_flag));
+              if (!ok) break;
+              tcgen05_fence_after();
+              if (lane == 0) issue_pv_half(x, t, half, j != 0);
+              __syncwarp();
+            }
+            if (!ok) break;
+            if (lane == 0) {
+              if (x == tiles - 1) tcgen05_commit(smem_u32(&v_empty[t % kPfRingV]));
+              // The next S of this tile overwrites the P that the MMAs above read: issue order
+              // is execution order on the tensor pipe.
+              if (more) {
+                issue_qk(x, t + 1);
+                if (x == tiles - 1) tcgen05_commit(smem_u32(&k_empty[(t + 1) % kPfRingK]));
+              }
+            }
+            __syncwarp();
+            ++tile_total[x];
           }
-          __syncwarp();
-          ++step_total;
+          ++kv_total;
         }
       }
       if (!ok) {
@@ -689,9 +731,10 @@ __global__ void __launch_bounds__(kPfThreads, 1)
     if ((warp == 8 || warp == 10 || warp == 11) && lane == 0) {
       // loads already issued must land before shared memory is released
       uint64_t* full = warp == 10 ? v_full : k_full;
-      for (uint32_t back = 0; back < kPfRing && back < loads_issued; ++back) {
-        const uint32_t t = step_total - 1 - back;
-        mbar_wait_bounded(smem_u32(&full[t % kPfRing]), (t / kPfRing) & 1u, 200000000ll);
+      const uint32_t ring_slots = warp == 10 ? kPfRingV : kPfRingK;
+      for (uint32_t back = 0; back < ring_slots && back < loads_issued; ++back) {
+        const uint32_t t = kv_total - 1 - back;
+        mbar_wait_bounded(smem_u32(&full[t % ring_slots]), (t / ring_slots) & 1u, 200000000ll);
       }
       if (warp == 8) mbar_wait_bounded(smem_u32(q_full), 0, 1000000ll);
     }
