@@ -386,6 +386,59 @@ def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
     }
 
 
+def bench_matmul_c1_latency(mesh, calls: int = 200) -> dict:
+    """The reference's CPU-runnable case on the GPUs it names: mesh 8, A[128,1024] x B[1024,1024]
+    (K = 128 per GPU), partials reduce-scattered along N in f32 -- 33.5 MFLOP and 458,752 bytes of
+    egress per GPU, so the step is latency: launch, one tile's contraction, the push across the
+    link, the flag round trip and the slot reduction. Median of ``calls`` device-timed calls; the
+    output is checked with the reference's allclose(1e-3, 1e-3) first."""
+    import torch
+
+    from oracle import matmul_rs
+    from tpu_cake_b200 import cuda_lowering, workloads
+
+    world = mesh.world
+    m, k, n = 128, 1024, 1024
+    plan = cuda_lowering.plan_distributed_matmul(
+        mesh_size=world, m=m, k=k, n=n, scatter_dimension=1, output_dtype="f32", tile_n=128,
+        collective_implementation=cuda_lowering.MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE,
+    )
+    executable, _ = plan.build(mesh=mesh)
+    lhs, rhs = workloads.distributed_matmul_inputs(world, m, k, n)
+    lhs_r, rhs_r = workloads.shard_matmul_inputs(lhs, rhs, world, mesh.rank)
+    lhs_d = torch.from_numpy(np.ascontiguousarray(lhs_r).view(np.uint16).copy()).view(torch.bfloat16).to(mesh.device)
+    rhs_d = torch.from_numpy(np.ascontiguousarray(rhs_r).view(np.uint16).copy()).view(torch.bfloat16).to(mesh.device)
+    out = torch.empty(plan.output_local_shape, dtype=torch.float32, device=mesh.device)
+    for _ in range(10):
+        executable(lhs_d, rhs_d, out)
+    torch.cuda.synchronize(mesh.device)
+    expected = matmul_rs.matmul_reduce_scatter(lhs.astype(np.float32), rhs.astype(np.float32), world=world, scatter_dimension=1)[mesh.rank]
+    ok = all_ranks_ok(mesh, bool(np.allclose(out.cpu().numpy(), expected, atol=1e-3, rtol=1e-3)))
+    mesh.barrier()
+    pairs = []
+    for _ in range(calls):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        executable(lhs_d, rhs_d, out)
+        stop.record()
+        pairs.append((start, stop))
+    torch.cuda.synchronize(mesh.device)
+    executable.status()
+    samples = sorted(a.elapsed_time(b) * 1e3 for a, b in pairs)
+    median_us = reduce_max(mesh, samples[len(samples) // 2])
+    p90_us = reduce_max(mesh, samples[int(len(samples) * 0.9)])
+    executable.close()
+    return {
+        "metric": "matmul_c1_latency_us", "value": median_us, "unit": "us", "higher_is_better": False, "p90_us": p90_us, "calls": calls,
+        "config": {"workload": f"run-matmul --mesh-size {world} --m {m} --k {k} --n {n}: bf16 inputs, f32 partials reduce-scattered along N",
+                   "collective": "p2p_f32", "launch": "stream, back to back"},
+        "note": "latency-bound (tens of MFLOP and a few hundred KB of link egress per GPU): a roofline fraction would be meaningless",
+        "flops_per_gpu": 2 * m * (k // world) * n, "link_egress_bytes_per_gpu": (world - 1) * m * (n // world) * 4,
+        "parity": {"checked": "the local [128, 128] output of every rank against the oracle, allclose(1e-3, 1e-3)", "ok": ok},
+        "gpu_launches": calls,
+    }
+
+
 def matmul_parity(mesh, plan, out, inputs) -> dict:
     """This rank's local output of the last timed step against the oracle: the sampled rows must
     equal the rank-ordered sum of the W split-K partials (rounded to the transport and output dtypes
@@ -764,6 +817,7 @@ def run_ours(args) -> None:
         sharded = bench_rpa(mesh, args, peaks, peak_kind, workloads.DECODE_SHARDED_256)
         sharded["metric"] = "rpa_decode_sharded_hbm_gbs"
     matmul = bench_matmul(mesh, args, peaks, peak_kind)
+    c1 = bench_matmul_c1_latency(mesh) if mesh.world == 8 else None
     line = {
         "metric": "matmul_reduce_scatter_tflops", "value": matmul["value"], "unit": "TFLOP/s", "n_gpus": mesh.world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": matmul["ms_per_step"], "higher_is_better": True,
@@ -785,7 +839,10 @@ def run_ours(args) -> None:
     if mixed is not None:
         line["rpa_mixed"] = mixed
         line["gpu_launches"] += mixed["gpu_launches"]
-    ok = line["parity"]["ok"] and all(part is None or part["parity"]["ok"] for part in (rpa, sharded))
+    if c1 is not None:
+        line["matmul_c1_latency"] = c1
+        line["gpu_launches"] += c1["gpu_launches"]
+    ok = line["parity"]["ok"] and all(part is None or part["parity"]["ok"] for part in (rpa, sharded, c1))
     if mesh.rank == 0:
         print(json.dumps(line), flush=True)
     if mesh.world > 1:
