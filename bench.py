@@ -48,9 +48,9 @@ import __graft_entry__  # noqa: E402
 M, K, N = 8192, 16384, 8192
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/: cake_matmul_rs_sm100<256> on 8192x16384x8192 (2.909 GB read + 0.134 GB written) and
-# cake_rpa_decode_sm100 on the 64-sequence decode configuration (1.090 GB read + 0.011 GB written).
-MEASURED_TRAFFIC_BYTES = {"matmul_n1": 3_043_610_488, "rpa_decode_64": 1_101_872_264}
+# profiles/: cake_matmul_rs_sm100<256> on 8192x16384x8192 (2.910 GB read + 0.130 GB written) and
+# cake_rpa_decode_sm100 on the 64-sequence decode configuration (1.090 GB read + 0.012 GB written).
+MEASURED_TRAFFIC_BYTES = {"matmul_n1": 3_039_912_056, "rpa_decode_64": 1_102_643_400}
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -760,7 +760,7 @@ def bench_rpa_mixed(mesh, args, peaks, peak_kind) -> dict:
     bound_tensor_ms = work["prefill_flops"] / (tensor_peak * 1e12) * 1e3
     ms = timings["whole"]
     timings.setdefault("prefill_only", ms)
-    timings.setdefault("decode_only", float("nan"))
+    decode_ms = timings.get("decode_only")
     return {
         "metric": "rpa_mixed_step_ms", "value": ms, "unit": "ms", "higher_is_better": False, "steps": steps,
         "config": {
@@ -778,8 +778,8 @@ def bench_rpa_mixed(mesh, args, peaks, peak_kind) -> dict:
             "peak_source": f"{peak_kind}: device copy bandwidth and cuBLAS bf16 burst",
         },
         "parts": {
-            "decode_only_ms": timings["decode_only"], "decode_only_gbs": work["decode_bytes"] / (timings["decode_only"] * 1e-3) / 1e9,
-            "decode_only_frac_of_hbm_peak": work["decode_bytes"] / (timings["decode_only"] * 1e-3) / 1e9 / hbm_peak,
+            "decode_only_ms": decode_ms, "decode_only_gbs": work["decode_bytes"] / (decode_ms * 1e-3) / 1e9 if decode_ms else None,
+            "decode_only_frac_of_hbm_peak": work["decode_bytes"] / (decode_ms * 1e-3) / 1e9 / hbm_peak if decode_ms else None,
             "prefill_only_ms": timings["prefill_only"], "prefill_only_tflops": work["prefill_flops"] / (timings["prefill_only"] * 1e-3) / 1e12,
             "prefill_only_frac_of_bf16_peak": work["prefill_flops"] / (timings["prefill_only"] * 1e-3) / 1e12 / tensor_peak,
             "kernel": "cake_rpa_prefill_sm100 (tcgen05, TMEM accumulators) for prefill; cake_rpa_decode_sm100 for decode",
