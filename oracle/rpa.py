@@ -182,17 +182,22 @@ def rpa_mixed(
     *,
     scale: float | None = None,
     update_cache: bool = True,
+    probabilities_in_bf16: bool = False,
 ) -> tuple[np.ndarray, np.ndarray]:
     """Ragged batch (decode and prefill sequences mixed) on the fused cache, causal, no bias.
 
-    PARITY UNPINNED: the reference has no oracle, test or golden vector for query lengths above one
-    (its oracle rejects them, src/tpu_cake/workloads/inkling_rpa.py:505-509). This function extends
-    ``rpa_fused`` by the semantics of the kernel the reference wraps (causal=1, new tokens appended
-    at the end of each sequence; src/tpu_cake/rpa_lowering.py:232-273): sequence s owns query
-    tokens [cu_q[s], cu_q[s+1]); query token i of a sequence with q query tokens and kv_len cached
-    tokens sits at position kv_len - q + i, its K/V are written there first, and it attends to
-    positions 0..kv_len - q + i. tests/test_oracle_golden.py ties it to the pinned decode oracle:
-    every query token equals a one-token decode at its own length.
+    The reference's own oracle rejects query lengths above one
+    (src/tpu_cake/workloads/inkling_rpa.py:505-509); this function extends ``rpa_fused`` by the
+    semantics of the kernel the reference wraps (causal=1, new tokens appended at the end of each
+    sequence; src/tpu_cake/rpa_lowering.py:232-273): sequence s owns query tokens
+    [cu_q[s], cu_q[s+1]); query token i of a sequence with q query tokens and kv_len cached tokens
+    sits at position kv_len - q + i, its K/V are written there first, and it attends to positions
+    0..kv_len - q + i. PINNED two ways: tests/test_mixed_cpu.py ties it to the pinned decode oracle
+    (every query token equals a one-token decode at its own length), and compares it with the
+    outputs of the array program shipped with that kernel
+    (ecosystem/source/jax/ragged_paged_attention.py:73-148, ``ref_ragged_paged_attention``) stored
+    in tests/golden/mixed_reference_vectors.npz. That program rounds the softmax probabilities to
+    the value dtype before multiplying by V; ``probabilities_in_bf16`` does the same here.
     Returns (output [T,Hq,D] bfloat16, updated cache bfloat16).
     """
     q = np.asarray(queries, dtype=np.float32)
@@ -237,5 +242,7 @@ def rpa_mixed(
         visible = np.arange(length)[None, :] <= (length - q_len + np.arange(q_len))[:, None]
         scores = np.where(visible[:, None, None, :], scores, -np.inf).astype(np.float32)
         weights = _softmax_rows(scores)
+        if probabilities_in_bf16:
+            weights = weights.astype(BF16).astype(np.float32)
         out[cu_q[s] : cu_q[s + 1]] = np.einsum("thgl,lhd->thgd", weights, values, dtype=np.float32).reshape(q_len, -1, dim)
     return out.astype(BF16), cache.astype(BF16)

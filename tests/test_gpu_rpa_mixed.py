@@ -1,6 +1,8 @@
 """GPU parity of the ragged (mixed prefill / decode) attention path against the CPU oracle, through
-the C ABI. The oracle for query runs longer than one token is unpinned (the reference has none); it
-is tied to the pinned decode oracle row by row in tests/test_mixed_cpu.py. Tolerance: max-abs <= 2e-2
+the C ABI. The reference has no oracle of its own for query runs longer than one token; the oracle
+used here is tied to the pinned decode oracle row by row and to the outputs of the array program
+shipped with the kernel the reference wraps (tests/test_mixed_cpu.py), and one test below compares
+the kernels with those stored outputs directly. Tolerance: max-abs <= 2e-2
 and relative-L2 <= 1e-2 on bf16 outputs; the updated cache must be bit-exact."""
 
 from __future__ import annotations
@@ -70,6 +72,20 @@ def test_mixed_batches_match_the_oracle(cuda_device, decode_kv, prefill, q_heads
     output, cache = run_mixed(mixed_plan(inputs, scale=scale), inputs, cuda_device)
     np.testing.assert_array_equal(cache.view(np.uint16), expected_cache.view(np.uint16))
     assert_close(output, expected_out)
+
+
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b"])
+def test_mixed_batches_match_the_shipped_reference_program(cuda_device, golden_dir, name):
+    """Against the stored outputs of ``ref_ragged_paged_attention``
+    (ecosystem/source/jax/ragged_paged_attention.py:73-148) on the cache after the update."""
+    vectors = np.load(golden_dir / "mixed_reference_vectors.npz")
+    bits = lambda key: vectors[f"{name}/{key}_bf16_bits"].view(BF16)  # noqa: E731
+    plain = lambda key: vectors[f"{name}/{key}"]  # noqa: E731
+    inputs = (bits("queries"), bits("keys"), bits("values"), bits("cache"), plain("kv_lengths"), plain("page_indices"),
+              plain("cu_q_lens"), plain("cu_kv_lens"), plain("distribution"), None, None)
+    scale = float(plain("softmax_scale"))
+    output, _ = run_mixed(mixed_plan(inputs, scale=scale), inputs, cuda_device)
+    assert_close(output, vectors[f"{name}/reference_output_bf16_bits"].view(BF16))
 
 
 def test_poisoned_unused_rows_are_never_read(cuda_device):

@@ -1,6 +1,7 @@
-"""CPU checks of the ragged (mixed prefill / decode) path: the unpinned mixed oracle is tied to the
-pinned decode oracle, the host preflight accepts and rejects what it should, and the seeded
-128-sequence configuration has the stated shape."""
+"""CPU checks of the ragged (mixed prefill / decode) path: the mixed oracle is tied to the pinned
+decode oracle and to the outputs of the array program shipped with the kernel the reference wraps,
+the host preflight accepts and rejects what it should, and the seeded 128-sequence configuration
+has the stated shape."""
 
 from __future__ import annotations
 
@@ -53,6 +54,33 @@ def test_cache_update_writes_every_query_token_at_its_position():
             position = int(meta.kv_lens[s]) - q_len + i
             expected[meta.page_indices[first + position // 4], position % 4] = True
     np.testing.assert_array_equal(changed, expected)
+
+
+def load_reference_case(golden_dir, name):
+    vectors = np.load(golden_dir / "mixed_reference_vectors.npz")
+    bits = lambda key: vectors[f"{name}/{key}_bf16_bits"].view(rpa.BF16)  # noqa: E731
+    plain = lambda key: vectors[f"{name}/{key}"]  # noqa: E731
+    inputs = (bits("queries"), bits("keys"), bits("values"), bits("cache"), plain("kv_lengths"), plain("page_indices"),
+              plain("cu_q_lens"), plain("cu_kv_lens"))
+    return inputs, float(plain("softmax_scale")), vectors[f"{name}/reference_output_bf16_bits"]
+
+
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b"])
+def test_mixed_oracle_against_the_shipped_reference_program(golden_dir, name):
+    """``ref_ragged_paged_attention`` (ecosystem/source/jax/ragged_paged_attention.py:73-148) rounds the
+    softmax probabilities to bf16 before the product with V. With the same rounding the oracle agrees
+    bit for bit on all but a few outputs (a different summation order of the scores flips the rounding
+    of a rare probability by one bf16 step, which moves an output by a few 1e-4); without it, in
+    float32 as the GPU tests use it, it stays within 1e-2 max-abs / 5e-3 relative L2."""
+    inputs, scale, reference_bits = load_reference_case(golden_dir, name)
+    reference = reference_bits.view(rpa.BF16).astype(np.float32)
+    rounded, _ = rpa.rpa_mixed(*inputs, scale=scale, probabilities_in_bf16=True)
+    assert (rounded.view(np.uint16) == reference_bits).mean() >= 0.999
+    np.testing.assert_allclose(rounded.astype(np.float32), reference, rtol=2**-7, atol=5e-4)
+    plain, _ = rpa.rpa_mixed(*inputs, scale=scale)
+    difference = plain.astype(np.float32) - reference
+    assert np.abs(difference).max() <= 1e-2
+    assert np.linalg.norm(difference) / np.linalg.norm(reference) <= 5e-3
 
 
 def shapes_of(inputs):
