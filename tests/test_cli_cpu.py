@@ -121,3 +121,48 @@ def test_reference_named_lowerings():
     assert sharded.mesh_axes == ("data", "tensor") and sharded.mesh_shape == (2, 4)
     assert sharded.global_input_shapes[0] == (8, 32, 128) and sharded.global_input_shapes[3] == (7424, 1, 16, 2, 128)
     assert hasattr(sharded, "place_inputs") and hasattr(sharded, "build_executable")
+
+
+def test_validate_saved_cuda_plan_replays_and_rejects(tmp_path):
+    """The saved physical IR and lowered source of a run replay to the same plan; a changed byte in
+    either, a stale hash, or a source that belongs to another workload is refused with the
+    reference's error names (src/tpu_cake/pallas_lowering.py:850-947)."""
+    import pytest
+
+    from tpu_cake_b200 import cuda_lowering, dialects, ir, schedule_lowering, workloads
+    from tpu_cake_b200.identity import text_sha256
+
+    def save(mesh_size, n, implementation, folder):
+        logical = workloads.distributed_matmul_schedule(mesh_size=mesh_size, m=128, k=1024, n=n, scatter_dimension="N")
+        physical = schedule_lowering.lower_distributed_matmul(logical, collective_implementation=implementation)
+        plan = cuda_lowering.lower_physical_matmul_to_cuda(physical)
+        folder.mkdir()
+        (folder / "physical.mlir").write_text(ir.canonical_text(physical))
+        (folder / "lowered_cuda.py").write_text(plan.render_executable_source())
+        return plan, folder / "physical.mlir", folder / "lowered_cuda.py"
+
+    plan, physical_path, source_path = save(8, 1024, dialects.CollectiveImplementation.P2P_OWNER_PUSH_BF16, tmp_path / "a")
+    hashes = {"schedule_sha256": plan.schedule_sha256, "source_sha256": plan.source_sha256()}
+    assert cuda_lowering.validate_saved_cuda_plan(physical_path, source_path, **hashes) == plan
+    with pytest.raises(ValueError, match="SAVED_PHYSICAL_IR_HASH_MISMATCH"):
+        cuda_lowering.validate_saved_cuda_plan(physical_path, source_path, schedule_sha256="0" * 64, source_sha256=hashes["source_sha256"])
+    with pytest.raises(ValueError, match="SAVED_CUDA_SOURCE_HASH_MISMATCH"):
+        cuda_lowering.validate_saved_cuda_plan(physical_path, source_path, schedule_sha256=hashes["schedule_sha256"], source_sha256="0" * 64)
+    # A physical IR edited after the run (hash re-recorded by the forger) no longer regenerates.
+    forged = tmp_path / "forged.mlir"
+    forged.write_text(physical_path.read_text().replace('reducer = "sum"', 'reducer = "max"'))
+    with pytest.raises(ValueError, match="SAVED_PHYSICAL_IR_INVALID"):
+        cuda_lowering.validate_saved_cuda_plan(forged, source_path, schedule_sha256=text_sha256(forged.read_text()), source_sha256=hashes["source_sha256"])
+    # A source edited after the run: another tile than the plan of the saved IR gives.
+    edited = tmp_path / "edited.py"
+    edited.write_text(source_path.read_text().replace("tile = (128, 128, 256)", "tile = (128, 128, 128)"))
+    with pytest.raises(ValueError, match="SAVED_CUDA_SOURCE_PLAN_MISMATCH"):
+        cuda_lowering.validate_saved_cuda_plan(physical_path, edited, schedule_sha256=hashes["schedule_sha256"], source_sha256=text_sha256(edited.read_text()))
+    commented = tmp_path / "commented.py"
+    commented.write_text(source_path.read_text() + "# appended\n")
+    with pytest.raises(ValueError, match="SAVED_CUDA_RENDERING_MISMATCH"):
+        cuda_lowering.validate_saved_cuda_plan(physical_path, commented, schedule_sha256=hashes["schedule_sha256"], source_sha256=text_sha256(commented.read_text()))
+    # The source of another workload beside this IR.
+    _, _, other_source = save(8, 2048, dialects.CollectiveImplementation.P2P_OWNER_PUSH_BF16, tmp_path / "b")
+    with pytest.raises(ValueError, match="SAVED_PHYSICAL_IR_INVALID|SAVED_CUDA_SOURCE_PLAN_MISMATCH"):
+        cuda_lowering.validate_saved_cuda_plan(physical_path, other_source, schedule_sha256=hashes["schedule_sha256"], source_sha256=text_sha256(other_source.read_text()))
