@@ -183,6 +183,12 @@ def make_rpa_fixtures() -> None:
                     np.array_equal(_as_u16(np.asarray(mutated_cache)), arrays["fused/seed0/updated_cache_bf16_bits"])
                 )
     np.savez_compressed(HERE / "rpa_reference_vectors.npz", **arrays)
+    # The 2 x 4 sharded surface: its global inputs are 60 MB per seed, so only their hashes are kept
+    # (the contract's first correctness seed and a small one).
+    identity = importlib.import_module("tpu_cake.identity")
+    hashes = {str(seed): [identity.array_sha256(np.asarray(value)) for value in rpa.inkling_sharded_fused_rpa_inputs(seed)]
+              for seed in (9423267841700844256, 3)}
+    (HERE / "sharded_surface_input_hashes.json").write_text(json.dumps(hashes, indent=2, sort_keys=True) + "\n")
 
 
 def main() -> None:

@@ -166,3 +166,28 @@ def test_validate_saved_cuda_plan_replays_and_rejects(tmp_path):
     _, _, other_source = save(8, 2048, dialects.CollectiveImplementation.P2P_OWNER_PUSH_BF16, tmp_path / "b")
     with pytest.raises(ValueError, match="SAVED_PHYSICAL_IR_INVALID|SAVED_CUDA_SOURCE_PLAN_MISMATCH"):
         cuda_lowering.validate_saved_cuda_plan(physical_path, other_source, schedule_sha256=hashes["schedule_sha256"], source_sha256=text_sha256(other_source.read_text()))
+
+
+def test_sharded_surface_inputs_and_host_definition(golden_dir):
+    """The surface's global inputs are the reference's (hashes of all eleven arrays for the contract's
+    first correctness seed and a small seed), and the host definition of the result assembles the
+    eight positions' shards into the global shapes."""
+    import numpy as np
+
+    from tpu_cake_b200 import identity, rpa_cuda_lowering, rpa_surface_runner, workloads
+
+    wanted = json.loads((golden_dir / "sharded_surface_input_hashes.json").read_text())
+    for seed, hashes in wanted.items():
+        inputs = workloads.inkling_sharded_fused_rpa_inputs(int(seed))
+        assert [identity.array_sha256(np.asarray(value)) for value in inputs] == hashes
+    plan = rpa_cuda_lowering.lower_inkling_sharded_rpa_to_cuda(workloads.inkling_sharded_rpa_schedule())
+    assert [tuple(np.asarray(v).shape) for v in inputs] == [tuple(shape) for shape in plan.global_input_shapes]
+    output, cache = rpa_surface_runner.expected_surface(plan, inputs)
+    assert output.shape == (8, 32, 128) and cache.shape == (7424, 1, 16, 2, 128)
+    # Position (1, 2) alone: its shard through the single-position definition equals its block of the assembly.
+    shard = tuple(np.ascontiguousarray(v) for v in plan.shard_inputs(inputs, (1, 2)))
+    local_output, _ = rpa_surface_runner.expected_fused_rpa(shard, softmax_scale=plan.local_plan.softmax_scale)
+    np.testing.assert_array_equal(local_output.view(np.uint16), output[4:8, 16:24].view(np.uint16))
+    assert rpa_surface_runner.SURFACE_PROTOCOL["repeat_executions"] == 2 and len(rpa_surface_runner.SURFACE_PROTOCOL["correctness_seeds"]) == 5
+    maximum, relative = rpa_surface_runner.surface_error_metrics(output, output)
+    assert maximum == 0.0 and relative == 0.0

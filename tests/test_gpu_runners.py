@@ -112,3 +112,20 @@ def test_three_phase_matmul_bundle(cuda_device, tmp_path):
     runner.run_distributed_matmul(other / "counters", mode="counters", **{**common, "n": 512})
     with pytest.raises(ValueError, match="BUNDLE_IDENTITY_MISMATCH phase=counters"):
         receipt.finalize_matmul_bundle(other, trace_profile=trace, counters_profile=counters)
+
+
+def test_sharded_surface_protocol_emulated_on_one_gpu(cuda_device, tmp_path):
+    """The 2 x 4 surface protocol with the eight positions run one after the other on this GPU: five
+    seeds, two executions each, exact repeats, exact cache, output within 1e-3 / 6e-3 of the host
+    definition; two chained timing rounds instead of sixteen. A single process must ask for the
+    emulation explicitly."""
+    from tpu_cake_b200 import rpa_surface_runner
+
+    with pytest.raises(ValueError, match="MESH_NOT_AVAILABLE"):
+        rpa_surface_runner.run_inkling_sharded_rpa_surface(tmp_path / "refused")
+    result = rpa_surface_runner.run_inkling_sharded_rpa_surface(tmp_path / "surface", emulate_on_one_gpu=True, protocol={"timing_rounds": 2})
+    assert result["passed"] and result["execution"] == "emulated" and len(result["correctness"]) == 5
+    for observation in result["correctness"]:
+        assert observation["repeated_output_exact"] and observation["repeated_cache_exact"] and observation["cache_exact"]
+        assert observation["maximum_absolute_error"] <= 1e-3 and observation["relative_l2_error"] <= 6e-3
+    assert len(result["round_medians_ns"]) == 2 and (tmp_path / "surface" / "correctness.json").is_file()

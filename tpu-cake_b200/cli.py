@@ -50,6 +50,10 @@ def main(argv: list[str] | None = None) -> int:
     run_rpa.add_argument("output_dir", type=Path)
     run_rpa.add_argument("--mode", choices=("timing", "trace", "counters"), default="timing")
     run_rpa.add_argument("--kv-chunk-tokens", type=int, default=0)
+    surface = commands.add_parser("run-rpa-surface", help="run the 2 x 4 sharded RPA surface protocol (five seeds, two executions each, exact repeats and cache; chained timing rounds)")
+    surface.add_argument("output_dir", type=Path)
+    surface.add_argument("--emulate-on-one-gpu", action="store_true", help="run the eight mesh positions one after the other on this GPU (they exchange nothing); recorded as emulated")
+    surface.add_argument("--timing-rounds", type=int, default=None, help="fewer timing rounds than the contract's 16 (the record says so)")
     verify_rpa = commands.add_parser("verify-rpa-bundle", help="re-check a finished RPA run bundle from its files")
     verify_rpa.add_argument("root", type=Path)
     experiment = commands.add_parser("experiment", help="print (or write) the experiment record of a workload")
@@ -92,6 +96,17 @@ def main(argv: list[str] | None = None) -> int:
         from . import rpa_runner
 
         return rpa_runner.rpa_device_main([str(args.output_dir), "--mode", args.mode, "--kv-chunk-tokens", str(args.kv_chunk_tokens)])
+    if args.command == "run-rpa-surface":
+        from . import rpa_surface_runner
+        from .mesh import ProcessMesh
+
+        mesh = ProcessMesh.from_environment()  # one process per GPU under torch.distributed.run, else a single position
+        protocol = {"timing_rounds": args.timing_rounds} if args.timing_rounds else None
+        result = rpa_surface_runner.run_inkling_sharded_rpa_surface(args.output_dir, emulate_on_one_gpu=args.emulate_on_one_gpu, protocol=protocol)
+        if mesh.rank == 0:
+            print(f"INKLING_SHARDED_RPA_SURFACE_{'PASSED' if result['passed'] else 'FAILED'} run_id={result['run_id']} "
+                  f"execution={result['execution']} median_ns={result['median_ns']:.0f}")
+        return 0
     if args.command == "verify-rpa-bundle":
         from . import rpa_runner
 

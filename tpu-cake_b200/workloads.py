@@ -317,6 +317,38 @@ def inkling_sharded_rpa_schedule(*, data: int = 2, tensor: int = 4):
                               relative_dim=16, bias_extent=512, mesh={"data": data, "tensor": tensor})
 
 
+INKLING_SHARDED_RPA_LOCAL_CONTEXTS = (128, 512, 1024, 2048)
+
+
+def inkling_sharded_fused_rpa_inputs(seed: int) -> tuple[np.ndarray, ...]:
+    """The 11 GLOBAL inputs of the 2 x 4 sharded surface as host arrays, drawn as the reference draws
+    them (src/tpu_cake/workloads/inkling_rpa.py:595-637): one ``default_rng(seed)`` normal stream in
+    the order queries [8, 32, 128], keys and values [8, 16, 128], cache [7424, 1, 16, 2, 128]
+    (scale 0.25), relative states [8, 32, 16] and projection [16, 512] (scale 0.4), each rounded
+    float32 -> bfloat16; per data block four sequences of 128 / 512 / 1024 / 2048 tokens on pages of
+    one token numbered inside the block, 8192 page slots."""
+    import ml_dtypes
+
+    generator = np.random.default_rng(seed)
+    data, tensor, local_tokens, local_q, local_kv = 2, 4, 4, 8, 4
+    contexts = INKLING_SHARDED_RPA_LOCAL_CONTEXTS
+    local_pages = sum(contexts)
+
+    def bf16(shape, scale=1.0):
+        return generator.normal(scale=scale, size=shape).astype(np.float32).astype(ml_dtypes.bfloat16)
+
+    page_indices = np.zeros((local_tokens * max(contexts),), dtype=np.int32)
+    page_indices[:local_pages] = np.arange(local_pages, dtype=np.int32)
+    cumulative_kv = np.concatenate((np.zeros((1,), dtype=np.int32), np.cumsum(contexts, dtype=np.int32)))
+    return (
+        bf16((data * local_tokens, tensor * local_q, 128)), bf16((data * local_tokens, tensor * local_kv, 128)),
+        bf16((data * local_tokens, tensor * local_kv, 128)), bf16((data * local_pages, 1, tensor * local_kv, 2, 128), scale=0.25),
+        np.tile(np.asarray(contexts, dtype=np.int32), data), np.tile(page_indices, data), np.tile(np.arange(local_tokens + 1, dtype=np.int32), data),
+        np.tile(cumulative_kv, data), np.tile(np.full((3,), local_tokens, dtype=np.int32), data),
+        bf16((data * local_tokens, tensor * local_q, 16), scale=0.4), bf16((16, 512), scale=0.4),
+    )
+
+
 def distributed_matmul_schedule(*, mesh_size: int = 4, m: int = 16, k: int = 32, n: int = 16, scatter_dimension: str = "N"):
     """The logical program ``einsum_local(lhs[M, K@t], rhs[K@t, N]) -> f32[M, N]{pending t:sum}``
     followed by ``reduce_scatter(axes=t, dim=scatter_dimension)``
