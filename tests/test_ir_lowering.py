@@ -198,3 +198,37 @@ def test_cuda_decode_resource_contract_op():
                                {"stage": 2, "attention": attention.name, "backend": "cake-b200/sm_100a", **{**contract, "shared_memory_bytes": 4096}})
     with pytest.raises(ir.VerifyException, match="shared_memory_bytes must be"):
         dialects.verify_operation(wrong_bytes)
+
+
+def _gather_kernel(*, source_sharding=("", "t", ""), destination_shape=(256, 64, 128), destination_sharding=("", "", ""), reducer=None,
+                   implementation=dialects.CollectiveImplementation.P2P_PEER_STORE):
+    """The sharded decode's collective on its own: every rank's [256, 8, 128] output rows gathered
+    along the head dimension over an 8-way axis."""
+    builder = dialects.KernelBuilder("gather", "b200", (), vmem_capacity_bytes=1 << 30, smem_capacity_bytes=232448, mesh={"t": 8},
+                                     interconnect_bandwidth_bytes_per_second={"t": 900_000_000_000})
+    local = builder.alloc(dialects.buffer((256, 8, 128), ("B", "H", "D"), "bf16", memory="vmem", sharding=source_sharding, lifetime=(0, 1)), "local_output")
+    gathered = builder.alloc(dialects.buffer(destination_shape, ("B", "H", "D"), "bf16", memory="vmem", sharding=destination_sharding, lifetime=(0, 1)), "gathered_output")
+    op = builder.collective_all_gather(local, gathered, stage=0, mesh_axis="t", group_size=8, concat_dimension=1, implementation=implementation)
+    if reducer is not None:
+        op.properties["reducer"] = reducer
+    return builder
+
+
+def test_all_gather_collective_rules():
+    """The all-gather the KV-head-sharded decode ends with is expressible, carried by peer stores or
+    NCCL, with the reference's rules (src/tpu_cake/dialects/tpu_schedule.py:1914-1923): one concat
+    dimension, no reducer, the mesh axis leaves the gathered dimension, the extent grows by the group."""
+    module = _gather_kernel().module()
+    collective = module.ops[0].body.ops[2]
+    assert collective.properties["kind"] == "all_gather" and collective.properties["implementation"] == "p2p_peer_store"
+    assert '"tpu_schedule.collective"' in ir.canonical_text(module)
+    _gather_kernel(implementation=dialects.CollectiveImplementation.NCCL).module()
+    for kwargs, message in (
+        ({"source_sharding": ("", "", "")}, "must remove its mesh axis"),
+        ({"destination_shape": (256, 8, 128)}, "destination must be"),
+        ({"destination_sharding": ("", "t", "")}, "must be sharded over"),
+        ({"reducer": "sum"}, "no reducer"),
+        ({"implementation": dialects.CollectiveImplementation.P2P_OWNER_PUSH}, "NCCL or by peer stores"),
+    ):
+        with pytest.raises(ir.VerifyException, match=message):
+            _gather_kernel(**kwargs).module()

@@ -29,6 +29,7 @@ class CollectiveImplementation(StrEnum):
     NCCL = "nccl"
     P2P_OWNER_PUSH = "p2p_owner_push"
     P2P_OWNER_PUSH_BF16 = "p2p_owner_push_bf16"
+    P2P_PEER_STORE = "p2p_peer_store"  # all-gather: the producing kernel stores its rows into every rank's buffer
 
 
 DMA_TOKEN = OpaqueType("tpu_schedule.dma_token")
@@ -149,6 +150,18 @@ class KernelBuilder:
         properties = {
             "kind": "reduce_scatter", "stage": stage, "mesh_axis": mesh_axis, "group_size": group_size,
             "split_dimension": scatter_dimension, "concat_dimension": -1, "reducer": "sum", "collective_plan": f"axis:{mesh_axis}",
+        }
+        if implementation is not None:
+            properties["implementation"] = CollectiveImplementation(implementation).value
+        return self._append(Operation("tpu_schedule.collective", [source, destination], [], properties))
+
+    def collective_all_gather(self, source: Value, destination: Value, *, stage: int, mesh_axis: str, group_size: int,
+                              concat_dimension: int, implementation: CollectiveImplementation | None = None) -> Operation:
+        """All-gather along ``concat_dimension`` (tpu_schedule.py:1914-1923): the collective of the
+        decode sharded by KV head, whose per-rank outputs are gathered along the head dimension."""
+        properties = {
+            "kind": "all_gather", "stage": stage, "mesh_axis": mesh_axis, "group_size": group_size,
+            "split_dimension": -1, "concat_dimension": concat_dimension, "reducer": "none", "collective_plan": f"axis:{mesh_axis}",
         }
         if implementation is not None:
             properties["implementation"] = CollectiveImplementation(implementation).value
@@ -305,28 +318,50 @@ def _verify_matmul(op: Operation) -> None:
 
 
 def _verify_collective(op: Operation) -> None:
-    if op.properties["kind"] != "reduce_scatter":
-        raise _fail(op, "only reduce_scatter is lowered by this backend")
+    """Rules of the reference's collective (tpu_schedule.py:1867-1960) for the two kinds this backend
+    lowers: reduce-scatter (the matmul's) and all-gather (the sharded decode's)."""
+    kind = op.properties["kind"]
+    if kind not in ("reduce_scatter", "all_gather"):
+        raise _fail(op, "only reduce_scatter and all_gather are lowered by this backend")
     source, destination = _buffer(op, op.operands[0], "source"), _buffer(op, op.operands[1], "destination")
-    group, split = op.properties["group_size"], op.properties["split_dimension"]
+    group, split, concat = op.properties["group_size"], op.properties["split_dimension"], op.properties["concat_dimension"]
     if group <= 1:
         raise _fail(op, "group_size must exceed 1")
-    if not 0 <= split < len(source.shape) or source.shape[split] % group:
-        raise _fail(op, "split dimension must exist and be divisible by the group size")
-    expected = list(source.shape)
-    expected[split] //= group
-    if tuple(expected) != destination.shape or destination.element_type != source.element_type:
-        raise _fail(op, f"destination must be {tuple(expected)} {source.element_type}")
+    if len(source.shape) != len(destination.shape):
+        raise _fail(op, "collectives cannot change rank")
     axis = op.properties["mesh_axis"]
-    previous = source.sharding[split]
-    wanted = f"{previous}/{axis}" if previous else axis
-    if destination.sharding[split] != wanted:
-        raise _fail(op, f"destination dimension {split} must be sharded over {wanted}")
     implementation = op.properties.get("implementation")
     if implementation is not None:
-        CollectiveImplementation(implementation)
-        if op.properties["reducer"] != "sum" or source.element_type != "f32":
+        implementation = CollectiveImplementation(implementation)
+    expected = list(source.shape)
+    if kind == "reduce_scatter":
+        if concat != -1 or op.properties["reducer"] == "none":
+            raise _fail(op, "reduce-scatter needs a reducer and one split dimension")
+        if not 0 <= split < len(source.shape) or source.shape[split] % group:
+            raise _fail(op, "split dimension must exist and be divisible by the group size")
+        expected[split] //= group
+        previous = source.sharding[split]
+        dimension, wanted = split, (f"{previous}/{axis}" if previous else axis)
+        if implementation is CollectiveImplementation.P2P_PEER_STORE:
+            raise _fail(op, "peer stores carry an all-gather, not a reduction")
+        if implementation is not None and (op.properties["reducer"] != "sum" or source.element_type != "f32"):
             raise _fail(op, "owned collective implementations reduce f32 sums")
+    else:
+        if split != -1 or op.properties["reducer"] != "none":
+            raise _fail(op, "all-gather needs one concat dimension and no reducer")
+        if not 0 <= concat < len(source.shape):
+            raise _fail(op, "collective dimension is out of range")
+        parts = source.sharding[concat].split("/") if source.sharding[concat] else []
+        if not parts or parts[-1] != axis:
+            raise _fail(op, "all-gather must remove its mesh axis from the gathered dimension")
+        expected[concat] *= group
+        dimension, wanted = concat, "/".join(parts[:-1])
+        if implementation not in (None, CollectiveImplementation.NCCL, CollectiveImplementation.P2P_PEER_STORE):
+            raise _fail(op, "an all-gather is carried by NCCL or by peer stores")
+    if tuple(expected) != destination.shape or destination.element_type != source.element_type:
+        raise _fail(op, f"destination must be {tuple(expected)} {source.element_type}")
+    if destination.sharding[dimension] != wanted:
+        raise _fail(op, f"destination dimension {dimension} must be sharded over {wanted!r}")
 
 
 def _verify_kernel(op: Operation) -> None:
