@@ -220,12 +220,19 @@ def lower_inkling_sharded_rpa_to_cuda(module, *, kv_chunk_tokens: int = 0) -> "S
     return ShardedCudaFusedRpaPlan(local_plan=local, mesh_axes=axes, mesh_shape=sizes)
 
 
+def default_kv_chunk_tokens(kv_heads: int) -> int:
+    """The library's split-KV chunk when a plan asks for none: 512 tokens, 1024 with one or two KV
+    heads on the GPU (the chunk search on the KV-head-sharded decode's per-rank shapes)."""
+    return 1024 if kv_heads <= 2 else 512
+
+
 def decode_resource_contract(plan) -> dict:
     """Properties of a ``tpu_schedule.cuda_rpa_decode`` op for a decode plan: the static resources of
     the sm_100a decode kernel as built (6 worker warps, 2-stage rings of 32-token stages)."""
     warps, stages, stage_tokens, row_bytes = 6, 2, 32, 256
     batch, q_heads = plan.query_shape[0], plan.query_shape[1]
-    chunk = plan.kv_chunk_tokens or 512
+    kv_heads = plan.key_shape[1] if hasattr(plan, "key_shape") else plan.cache_shape[2]
+    chunk = plan.kv_chunk_tokens or default_kv_chunk_tokens(kv_heads)
     shared = warps * (stages * stage_tokens * 2 * row_bytes + 8 * row_bytes) + 1024 + 256
     return {"kv_chunk_tokens": chunk, "warps_per_cta": warps, "ring_stages": stages, "stage_tokens": stage_tokens,
             "shared_memory_bytes": shared, "workspace_bytes": max(1, batch * q_heads * 130 * 4)}
