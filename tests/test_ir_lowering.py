@@ -232,3 +232,39 @@ def test_all_gather_collective_rules():
     ):
         with pytest.raises(ir.VerifyException, match=message):
             _gather_kernel(**kwargs).module()
+
+
+def test_generic_physical_cost_model():
+    """The static report of a physical kernel: for the matmul kernel it reproduces the closed-form
+    counts (the reference's known integers for mesh 8, 128 x 1024 x 1024: ring-equivalent bytes
+    917,504, 2 * 128 * 128 * 1024 FLOP), for the attention kernels it prices the declared capacity,
+    and an over-full on-chip budget or an unknown operation is refused."""
+    from decimal import Decimal
+
+    from tpu_cake_b200 import physical_cost_model
+
+    module = physical(collective_implementation=dialects.CollectiveImplementation.P2P_OWNER_PUSH_BF16)
+    report = physical_cost_model.analyze_physical_kernel(module)
+    plan = cuda_lowering.lower_physical_matmul_to_cuda(module)
+    closed_form = cost_model.estimate_distributed_matmul(plan)
+    region = report.mxu_regions[0]
+    assert (region.m, region.k, region.n, region.flops) == (128, 128, 1024, 2 * 128 * 128 * 1024) == (128, 128, 1024, closed_form.counts.operations_per_device)
+    collective = report.collectives[0]
+    assert collective.ring_equivalent_bidirectional_bytes_per_device == Decimal(closed_form.counts.ici_bidirectional_bytes_per_device) == Decimal(917504)
+    assert collective.switch_egress_bytes_per_device == Decimal(closed_form.counts.link_egress_bytes_per_device)
+    assert report.priced_compute_time_floor_ns == closed_form.compute_ns and report.priced_ici_time_floor_ns == closed_form.communication_ns
+    assert report.memory.explicit_hbm_dma_read_bytes_per_device == 2 * (128 * 128 + 128 * 1024)
+    assert report.memory.peak_live_vmem_bytes_per_device <= report.resource_peaks[0].capacity and report.device_count == 8
+    assert dict(report.canonical_operation_inventory)["tpu_schedule.dma_start"] == 3 and len(report.stages) == 6
+    sharded = physical_cost_model.analyze_physical_kernel(workloads.inkling_sharded_rpa_schedule())
+    work = sharded.attention[0]
+    assert (work.sequences, work.q_heads, work.kv_heads, work.token_capacity) == (4, 8, 4, 3712)
+    assert sharded.predicted_limiting_priced_resource == "hbm" and "upper bound" in " ".join(sharded.assumptions)
+    assert isinstance(sharded.to_json()["priced_hbm_time_floor_ns"], str)
+    gather = _gather_kernel().module()
+    traffic = physical_cost_model.analyze_physical_kernel(gather).collectives[0]
+    assert traffic.kind == "all_gather" and traffic.payload_bytes_per_device == 256 * 64 * 128 * 2
+    bad = physical()
+    bad.ops[0].body.ops[11].name = "tpu_schedule.vector_compute"
+    with pytest.raises((physical_cost_model.UnsupportedPhysicalCostModelError, ir.VerifyException)):
+        physical_cost_model.analyze_physical_kernel(bad)

@@ -86,6 +86,8 @@ def main(argv: list[str] | None = None) -> int:
     estimate = commands.add_parser("estimate", help="cost model of the lowered plan")
     _add_shape(estimate)
     estimate.add_argument("--collective-strategy", choices=[s.value for s in cuda_lowering.MatmulCollectiveStrategy], default="p2p_fused_epilogue_bf16_transport")
+    estimate.add_argument("--physical-kernel", choices=("matmul", "inkling-rpa", "inkling-fused-rpa", "inkling-sharded-rpa"), default=None,
+                          help="print the static resource report of this workload's physical kernel instead of the matmul plan's counts")
     args = parser.parse_args(argv)
 
     if args.command == "experiment":
@@ -168,6 +170,17 @@ def main(argv: list[str] | None = None) -> int:
         print(json.dumps({"distributed_sha256": ir.schedule_sha256(logical), "physical_sha256": ir.schedule_sha256(physical)}))
         return 0
     strategy = cuda_lowering.MatmulCollectiveStrategy(args.collective_strategy)
+    if args.physical_kernel is not None:
+        from . import physical_cost_model
+        from .runner import _IMPLEMENTATION
+
+        kernel = {
+            "matmul": lambda: schedule_lowering.lower_distributed_matmul(logical, collective_implementation=_IMPLEMENTATION[strategy] if args.mesh_size > 1 else None),
+            "inkling-rpa": workloads.paged_attention_schedule, "inkling-fused-rpa": workloads.inkling_fused_rpa_schedule,
+            "inkling-sharded-rpa": workloads.inkling_sharded_rpa_schedule,
+        }[args.physical_kernel]()
+        print(json.dumps(physical_cost_model.analyze_physical_kernel(kernel).to_json(), indent=2))
+        return 0
     plan = cuda_lowering.plan_distributed_matmul(
         mesh_size=args.mesh_size, m=args.m, k=args.k, n=args.n, scatter_dimension=0 if args.scatter_dimension == "M" else 1,
         collective_implementation=strategy if args.mesh_size > 1 else None,
