@@ -195,10 +195,13 @@ def test_p2p_owner_push_all_ranks_on_one_gpu(cuda_device, scatter_dimension, tra
     ((96, 96, 40), 3, 0, "bf16"),   # a mesh size the vector reduction does not cover
     ((256, 192, 520), 4, 0, "f32"), # rows aligned, 520 columns: vector pieces, ragged last chunk
     ((384, 128, 768), 2, 1, "bf16"),
+    ((512, 8192, 1024), 2, 0, "bf16"),   # K per rank 4096: deep enough that a rank's own tiles come last
+    ((256, 16384, 512), 4, 1, "bf16"),   # the same owner order on four positions, scattering N
 ])
 def test_p2p_owner_push_odd_shapes(cuda_device, shape, world, scatter_dimension, transport):
     """Shapes whose local output is not a whole number of 16-byte pieces, 128-byte chunks or
-    128-row tiles go through the element-wise push and reduction; all must match the oracle."""
+    128-row tiles go through the element-wise push and reduction; the last two are deep enough in K
+    that the kernel walks its peers' tiles first and its own last. All must match the oracle."""
     m, k, n = shape
     generator = np.random.default_rng(m * 131 + n)
     lhs = generator.normal(size=(m, k)).astype(np.float32).astype(BF16)

@@ -100,6 +100,8 @@ struct MatmulParams {
   int32_t tma_store;           // epilogue chunks leave shared memory as TMA tensor stores
   int32_t region_order;        // consecutive tiles go to consecutive owners, starting at rank+1
   int32_t owner_rotation;      // tile groups after which the owner sequence shifts by one
+  int32_t own_last;            // the rank's own tiles come after all tiles of its peers
+  int32_t region_tiles;        // tiles of one owner's region
   int32_t publish;             // kPublish*
   int32_t reduce_in_kernel;    // the slot reduction runs in this kernel
   uint32_t epoch;              // value written to the flags
@@ -163,9 +165,27 @@ __device__ __forceinline__ void tile_coords(const MatmulParams& p, int t, int& m
   owner = 0;
   region_tile = 0;
   if (p.region_order) {
-    const int group = t / p.world;
-    const int j = (t - group * p.world + group / p.owner_rotation) % p.world;
-    owner = (p.rank + 1 + j) % p.world;
+    int group;
+    if (p.own_last) {
+      // Peers first, own region last: while the last 1 / W of the tiles is contracted nothing
+      // crosses the link, so the pushes of the last peer tiles, their arrival at the owners and
+      // most of the reduction (which needs this rank's own partial of every tile) happen under that
+      // contraction instead of after the kernel's last MMA.
+      const int peers = p.world - 1;
+      const int peer_tiles = peers * p.region_tiles;
+      if (t < peer_tiles) {
+        group = t / peers;
+        const int j = (t - group * peers + group / p.owner_rotation) % peers;
+        owner = (p.rank + 1 + j) % p.world;
+      } else {
+        group = t - peer_tiles;
+        owner = p.rank;
+      }
+    } else {
+      group = t / p.world;
+      const int j = (t - group * p.world + group / p.owner_rotation) % p.world;
+      owner = (p.rank + 1 + j) % p.world;
+    }
     int mi, ni;
     if (p.scatter_dim == 0) {
       const int m_tiles_r = p.out_rows / kTileM;
@@ -1099,6 +1119,15 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
       p.region_order = aligned ? 1 : 0;
       // One wave of the grid covers grid / W tile groups: shift the owner sequence once per wave.
       p.owner_rotation = grid / d.world > 0 ? grid / d.world : 1;
+      p.region_tiles = num_tiles / d.world;
+      // Own tiles last when the link has slack for it: all pushes then fall into the first
+      // (W - 1) / W of the contraction, which must still cover their time on the link (estimated at
+      // 600 GB/s per GPU with every GPU pushing, against 1.6 PFLOP/s of contraction). 8192 x 16384 x
+      // 8192 in bf16: on 2 and 4 GPUs yes (4 GPUs measured 0.422 against 0.451 ms); at K / W = 2048
+      // (8 GPUs, or K = 8192 on 4) the link is the bound and concentrating the pushes costs 4-7 %.
+      const double push_phase_s = (d.world - 1.0) / d.world * 2.0 * d.m * d.n * d.k_local / 1.6e15;
+      const double link_s = (d.world - 1.0) / d.world * static_cast<double>(d.m) * d.n * plan->tsize / 600e9;
+      p.own_last = (p2p && p.region_order && link_s <= 0.8 * push_phase_s) ? 1 : 0;
       if (p2p) p.publish = (p.region_order && p.tma_store) ? cake::kPublishPerTile : cake::kPublishAtEnd;
     }
     const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
