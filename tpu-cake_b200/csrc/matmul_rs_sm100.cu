@@ -44,7 +44,8 @@ constexpr int kGemmThreads = 384;
 constexpr uint32_t kABytes = kTileM * kBlockK * 2;
 // Chunks (32 rows x 128 bytes) an epilogue warp can have staged for stores still reading shared
 // memory, and the depth of the 256-wide configuration's operand ring: the two compete for the
-// CTA's shared memory (4 stages + 2 chunks, or 3 stages + up to 6 chunks, fit).
+// CTA's shared memory (4 stages + 2 chunks, or 3 stages + up to 5 chunks, fit; 3 + 4 measured
+// 9 % slower in the contraction and no faster in the pushes).
 #ifndef CAKE_MM_STAGING_CHUNKS
 #define CAKE_MM_STAGING_CHUNKS 2
 #endif
@@ -63,7 +64,7 @@ struct GemmCfg {
   static constexpr int kStages = BN == 256 ? CAKE_MM_STAGES_256 : (BN == 128 ? 6 : 8);
   static constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
   static constexpr uint32_t kSmemBytes =
-      kStages * kStageBytes + 4 * kStagingBytesPerWarp + 256 /*barriers*/ + 1024 /*alignment*/;
+      kStages * kStageBytes + 4 * kStagingBytesPerWarp + 512 /*barriers, mailbox*/ + 1024 /*alignment*/;
 };
 
 // What the slot reduction needs: this rank's receive slots of the current parity (source s at
@@ -88,6 +89,11 @@ struct ReduceParams {
 
 // MatmulParams::publish: 0 = destinations are not receive slots, nothing to announce.
 constexpr int kPublishPerTile = 1;  // every epilogue warp announces its quarter, one tile late
+// Announcements an epilogue warp may have handed to the publisher warp without their having been
+// sent yet, and the bit of the hand-over counter that says the epilogue warp has finished.
+constexpr uint32_t kMailDepth = 4;
+constexpr uint32_t kMailDone = 0x80000000u;
+constexpr int kPublisherWarp = 11;
 constexpr int kPublishAtEnd = 2;    // the last block to finish announces everything (tiles may straddle owners)
 
 struct MatmulParams {
@@ -100,9 +106,10 @@ struct MatmulParams {
   int32_t tma_store;           // epilogue chunks leave shared memory as TMA tensor stores
   int32_t region_order;        // consecutive tiles go to consecutive owners, starting at rank+1
   int32_t owner_rotation;      // tile groups after which the owner sequence shifts by one
-  int32_t own_last;            // the rank's own tiles come after all tiles of its peers
+  int32_t own_tail;            // this many of the rank's own tiles (the last of its region) come after everything else
   int32_t region_tiles;        // tiles of one owner's region
   int32_t publish;             // kPublish*
+  int32_t mailbox;             // kPublishPerTile: the release stores are issued by the publisher warp
   int32_t reduce_in_kernel;    // the slot reduction runs in this kernel
   uint32_t epoch;              // value written to the flags
   int32_t region_n_tiles;      // tile columns of one owner's region (flag indexing)
@@ -165,26 +172,29 @@ __device__ __forceinline__ void tile_coords(const MatmulParams& p, int t, int& m
   owner = 0;
   region_tile = 0;
   if (p.region_order) {
+    // The walk has three parts: groups of W tiles (the same region tile of every owner, this rank's
+    // included), then groups of W - 1 tiles (peers only), then the `own_tail` own tiles that were
+    // left out of those groups. While the own tail is contracted nothing crosses the link, so the
+    // last pushes, their arrival at the owners and the reduction that waits for this rank's own
+    // partial run under that contraction instead of after the kernel's last MMA.
+    const int peers = p.world - 1;
+    const int mixed_groups = p.region_tiles - p.own_tail;
+    const int mixed_tiles = mixed_groups * p.world;
+    const int peer_tiles = p.own_tail * peers;
     int group;
-    if (p.own_last) {
-      // Peers first, own region last: while the last 1 / W of the tiles is contracted nothing
-      // crosses the link, so the pushes of the last peer tiles, their arrival at the owners and
-      // most of the reduction (which needs this rank's own partial of every tile) happen under that
-      // contraction instead of after the kernel's last MMA.
-      const int peers = p.world - 1;
-      const int peer_tiles = peers * p.region_tiles;
-      if (t < peer_tiles) {
-        group = t / peers;
-        const int j = (t - group * peers + group / p.owner_rotation) % peers;
-        owner = (p.rank + 1 + j) % p.world;
-      } else {
-        group = t - peer_tiles;
-        owner = p.rank;
-      }
-    } else {
+    if (t < mixed_tiles) {
       group = t / p.world;
       const int j = (t - group * p.world + group / p.owner_rotation) % p.world;
       owner = (p.rank + 1 + j) % p.world;
+    } else if (t < mixed_tiles + peer_tiles) {
+      const int u = t - mixed_tiles;
+      const int g = u / peers;
+      const int j = (u - g * peers + g / p.owner_rotation) % peers;
+      owner = (p.rank + 1 + j) % p.world;
+      group = mixed_groups + g;
+    } else {
+      group = mixed_groups + (t - mixed_tiles - peer_tiles);
+      owner = p.rank;
     }
     int mi, ni;
     if (p.scatter_dim == 0) {
@@ -235,6 +245,20 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
 
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* addr, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* addr, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_cta_shared_u32(const volatile uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(const_cast<const uint32_t*>(addr))) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_cta_shared_u32(volatile uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(addr))), "r"(v) : "memory");
 }
 
 // Slot data is read once, after its flag has been seen: straight from L2, no L1 allocation.
@@ -455,6 +479,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   volatile uint32_t* epilogue_done = tmem_base_slot + 2;  // epilogue warps whose stores have completed
+  // Mailbox between the epilogue warps and the publisher warp: what epilogue warp i has handed over
+  // so far (with kMailDone once it has finished), what the publisher has sent of it, and the ring of
+  // announcements in between, each packed as owner << 24 | flag index.
+  volatile uint32_t* mail_seq = tmem_base_slot + 4;     // [4]
+  volatile uint32_t* mail_taken = mail_seq + 4;         // [4]
+  volatile uint32_t* mail_ring = mail_taken + 4;        // [4][kMailDepth]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -472,6 +502,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     mbar_init(smem_u32(drain_bar), 1);
     *abort_flag = 0;
     *epilogue_done = 0;
+    for (int i = 0; i < 4; ++i) {
+      mail_seq[i] = 0;
+      mail_taken[i] = 0;
+    }
     fence_mbar_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
@@ -588,6 +622,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint8_t* my_stage_base = staging + (warp - 2) * kStagingBytesPerWarp;
     int chunk_count = 0;  // chunks this warp has staged so far (selects the staging half)
     uint32_t* pending_flag = nullptr;  // lane 0: the flag of the quarter sent last, not yet announced
+    uint32_t pending_packed = 0;       // the same flag as owner << 24 | index, for the mailbox
+    uint32_t handed = 0;               // announcements handed to the publisher warp so far
+    // A release store at system scope holds its thread until the SM's earlier writes have been
+    // acknowledged from across the link; issued here once per tile it cost a fifth of the push rate
+    // (4 GPUs pushing 4 KiB tensor stores from 4 warps per SM: 644 GB/s per GPU, 502 with the release
+    // store, 644 again with a relaxed one). So the epilogue warp only waits for its stores, fences
+    // the proxy and hands the flag over through shared memory; the publisher warp issues the release.
+    auto announce = [&](bool last) {
+      if (!p.mailbox) {
+        if (pending_flag != nullptr) st_release_sys_u32(pending_flag, p.epoch);
+        return;
+      }
+      const int w = warp - 2;
+      if (pending_flag != nullptr) {
+        if (handed - ld_acquire_cta_shared_u32(mail_taken + w) >= kMailDepth) {
+          const long long start = clock64();
+          while (handed - ld_acquire_cta_shared_u32(mail_taken + w) >= kMailDepth) {
+            if (*abort_flag || clock64() - start > kBarrierBudgetCycles) {
+              if (!*abort_flag) record_status(p.status, 1, blockIdx.x, static_cast<int>(handed), 500 + w);
+              *abort_flag = 1;
+              return;
+            }
+          }
+        }
+        mail_ring[w * kMailDepth + handed % kMailDepth] = pending_packed;
+        ++handed;
+      }
+      st_release_cta_shared_u32(mail_seq + w, handed | (last ? kMailDone : 0u));
+    };
     const int elem_bytes = p.store_f32 ? 4 : 2;
     const int cols_per_chunk = p.store_f32 ? 32 : 64;  // 128 bytes per row per chunk
     const int epp = 16 / elem_bytes;                   // elements per 16-byte piece
@@ -714,15 +777,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (pending_flag != nullptr) {
           bulk_wait_group_at_most(num_chunks);
           asm volatile("fence.proxy.async.global;" ::: "memory");
-          st_release_sys_u32(pending_flag, p.epoch);
+          announce(false);
         }
         pending_flag = p.flags_at[owner] + region_tile * 4 + (warp - 2);
+        pending_packed = (static_cast<uint32_t>(owner) << 24) | static_cast<uint32_t>(region_tile * 4 + (warp - 2));
       }
     }
-    if (p.publish == kPublishPerTile && lane == 0 && pending_flag != nullptr && ok) {
-      bulk_wait_group_at_most(0);
-      asm volatile("fence.proxy.async.global;" ::: "memory");
-      st_release_sys_u32(pending_flag, p.epoch);
+    if (p.publish == kPublishPerTile && lane == 0) {
+      // The last quarter, and the word that lets the publisher warp leave (also when this warp gave up).
+      if (!ok) pending_flag = nullptr;
+      if (pending_flag != nullptr) {
+        bulk_wait_group_at_most(0);
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+      }
+      announce(true);
     }
     if (p.publish == kPublishAtEnd && ok) {
       // Tiles may straddle owners here, so nothing is announced per tile: every epilogue warp
@@ -747,6 +815,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int o = 0; o < p.world; ++o)
           for (int idx = lane; idx < p.quarters; idx += 32) st_release_sys_u32(p.flags_at[o] + idx, p.epoch);
         if (lane == 0) *p.push_done = 0;
+      }
+    }
+  }
+  else if (warp == kPublisherWarp && p.publish == kPublishPerTile && p.mailbox) {
+    // ------------------------------------------------------------------ publisher
+    // Lane i < 4 serves epilogue warp i: whatever it has handed over since the last look is
+    // announced behind one system-scope fence (fence + relaxed stores form the release), so the
+    // wait for the acknowledgements is spent by a warp that has nothing else to do.
+    uint32_t taken = 0;
+    long long start = clock64();
+    while (true) {
+      const uint32_t word = lane < 4 ? ld_acquire_cta_shared_u32(mail_seq + lane) : kMailDone;
+      const uint32_t avail = word & ~kMailDone;
+      const bool have = lane < 4 && avail != taken;
+      if (have) {
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        while (taken != avail) {
+          const uint32_t packed = mail_ring[lane * kMailDepth + taken % kMailDepth];
+          st_relaxed_sys_u32(p.flags_at[packed >> 24] + (packed & 0xFFFFFFu), p.epoch);
+          ++taken;
+        }
+        st_release_cta_shared_u32(mail_taken + lane, taken);
+      }
+      if (__all_sync(0xffffffffu, (word & kMailDone) != 0 && !have)) break;
+      if (*abort_flag) break;
+      if (__any_sync(0xffffffffu, have)) {
+        start = clock64();
+      } else if (clock64() - start > kBarrierBudgetCycles) {
+        if (lane == 0 && !*abort_flag) record_status(p.status, 1, blockIdx.x, static_cast<int>(taken), 600);
+        *abort_flag = 1;
+        break;
+      } else {
+        __nanosleep(64);
       }
     }
   }
@@ -1120,15 +1221,19 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
       // One wave of the grid covers grid / W tile groups: shift the owner sequence once per wave.
       p.owner_rotation = grid / d.world > 0 ? grid / d.world : 1;
       p.region_tiles = num_tiles / d.world;
-      // Own tiles last when the link has slack for it: all pushes then fall into the first
-      // (W - 1) / W of the contraction, which must still cover their time on the link (estimated at
-      // 600 GB/s per GPU with every GPU pushing, against 1.6 PFLOP/s of contraction). 8192 x 16384 x
-      // 8192 in bf16: on 2 and 4 GPUs yes (4 GPUs measured 0.422 against 0.451 ms); at K / W = 2048
-      // (8 GPUs, or K = 8192 on 4) the link is the bound and concentrating the pushes costs 4-7 %.
+      // How many of this rank's own tiles close the walk. With slack on the link, all of them: the
+      // pushes then fall into the first (W - 1) / W of the contraction, which must still cover their
+      // time on the link (estimated at 600 GB/s per GPU with every GPU pushing, against 1.6 PFLOP/s
+      // of contraction). 8192 x 16384 x 8192 in bf16: on 2 and 4 GPUs yes (4 GPUs measured 0.432
+      // against 0.445 ms with own tiles spread over the walk); at K / W = 2048 (8 GPUs, or K = 8192
+      // on 4) the pushes need most of the link for the whole kernel and concentrating them costs
+      // 2-12 %, also when only one or two waves of own tiles close the walk (K = 8192 on 4 GPUs:
+      // 0.243 ms spread, 0.248 with a tail of two waves, 0.274 with all own tiles last).
       const double push_phase_s = (d.world - 1.0) / d.world * 2.0 * d.m * d.n * d.k_local / 1.6e15;
       const double link_s = (d.world - 1.0) / d.world * static_cast<double>(d.m) * d.n * plan->tsize / 600e9;
-      p.own_last = (p2p && p.region_order && link_s <= 0.8 * push_phase_s) ? 1 : 0;
+      p.own_tail = (p2p && p.region_order && link_s <= 0.8 * push_phase_s) ? p.region_tiles : 0;
       if (p2p) p.publish = (p.region_order && p.tma_store) ? cake::kPublishPerTile : cake::kPublishAtEnd;
+      p.mailbox = (p.publish == cake::kPublishPerTile && p.quarters < (1 << 24)) ? 1 : 0;
     }
     const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
     int32_t rc;
