@@ -110,6 +110,7 @@ struct MatmulParams {
   int32_t region_tiles;        // tiles of one owner's region
   int32_t publish;             // kPublish*
   int32_t mailbox;             // kPublishPerTile: the release stores are issued by the publisher warp
+  int32_t own_now;             // kPublishPerTile: quarters of the rank's own region are announced without the one-tile delay
   int32_t reduce_in_kernel;    // the slot reduction runs in this kernel
   uint32_t epoch;              // value written to the flags
   int32_t region_n_tiles;      // tile columns of one owner's region (flag indexing)
@@ -774,13 +775,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // Announce the quarter sent one tile ago: its stores were issued a whole main loop ago, so
         // waiting for all but this tile's groups costs nothing. Completion of a bulk group makes
         // its writes visible to this thread; the proxy fence orders them before the release store.
-        if (pending_flag != nullptr) {
-          bulk_wait_group_at_most(num_chunks);
+        // A quarter of the rank's own region is announced at once: its stores are local and complete
+        // in about a microsecond, and the reduction of that tile need not wait a whole main loop.
+        const bool now = p.own_now && owner == p.rank;
+        if (pending_flag != nullptr || now) {
+          bulk_wait_group_at_most(now ? 0 : num_chunks);
           asm volatile("fence.proxy.async.global;" ::: "memory");
-          announce(false);
+          if (pending_flag != nullptr) announce(false);
         }
         pending_flag = p.flags_at[owner] + region_tile * 4 + (warp - 2);
         pending_packed = (static_cast<uint32_t>(owner) << 24) | static_cast<uint32_t>(region_tile * 4 + (warp - 2));
+        if (now) {
+          announce(false);
+          pending_flag = nullptr;
+        }
       }
     }
     if (p.publish == kPublishPerTile && lane == 0) {
@@ -1234,6 +1242,7 @@ int32_t enqueue_impl(cake_matmul_rs* plan, const void* lhs, const void* rhs, voi
       p.own_tail = (p2p && p.region_order && link_s <= 0.8 * push_phase_s) ? p.region_tiles : 0;
       if (p2p) p.publish = (p.region_order && p.tma_store) ? cake::kPublishPerTile : cake::kPublishAtEnd;
       p.mailbox = (p.publish == cake::kPublishPerTile && p.quarters < (1 << 24)) ? 1 : 0;
+      p.own_now = 1;  // 4 GPUs, 8192 x K x 8192: K = 16384 0.4356 -> 0.4306 ms, K = 12288 0.344 -> 0.339, K = 8192 unchanged
     }
     const bool kmajor = d.rhs_layout == 1 || plan->rhs_via_transpose;
     int32_t rc;
