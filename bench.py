@@ -351,6 +351,14 @@ def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
             "exposed_communication": max(0.0, (ms_per_step - only_ms) / ms_per_step),
             "link_egress_bytes_per_gpu": plan.collective_resources.remote_payload_bytes,
         }
+        # Roofline of the fused step: the slower of the contraction at the measured bf16 burst and the
+        # link egress at the measured peer-copy rate of one direction (770 GB/s).
+        tensor_ms = flops_total / world / (peak * 1e12) * 1e3
+        link_ms = phases["link_egress_bytes_per_gpu"] / 770e9 * 1e3
+        phases["fused_target"] = {
+            "tensor_ms": tensor_ms, "link_ms": link_ms, "link_peak_gbs": 770.0, "bound": "tensor" if tensor_ms >= link_ms else "link",
+            "frac": max(tensor_ms, link_ms) / ms_per_step,
+        }
 
     # End to end through the C ABI with host buffers (pinned): H2D of both operands, the kernels,
     # D2H of the local output, inside the timed region.

@@ -69,6 +69,23 @@ def build(*, force: bool = False, verbose: bool = False) -> Path:
     return LIBRARY
 
 
+PUSH_RATE_PROGRAM = LIB_DIR / "peer_push_rate"
+
+
+def build_push_rate_program(*, force: bool = False) -> Path:
+    """Compiles ``csrc/peer_push_rate.cu``, the stand-alone measurement of the all-to-all push rate
+    between the GPUs of a node (the link-side denominator of the fused matmul + reduce-scatter)."""
+    LIB_DIR.mkdir(exist_ok=True)
+    source = CSRC / "peer_push_rate.cu"
+    if force or _stale(PUSH_RATE_PROGRAM, [source]):
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", str(PUSH_RATE_PROGRAM), str(source)]
+        result = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if result.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {source.name}:\n{result.stdout}")
+    return PUSH_RATE_PROGRAM
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv or bool(os.environ.get("CAKE_VERBOSE")))
     print(path)
+    print(build_push_rate_program(force="--force" in sys.argv))
