@@ -38,7 +38,8 @@ namespace cake {
 constexpr int kTileM = 128;
 constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;
-// Producer, issuer, 4 epilogue warps, 6 reduction warps. Twelve warps are three per scheduler, whose
+// Producer, issuer, 4 epilogue warps, 6 reduction warps (the last of them first publishes the
+// arrival flags, for as long as the epilogue warps run). Twelve warps are three per scheduler, whose
 // register file (16 K) then allows 168 registers per thread -- the same as ten warps would get.
 constexpr int kGemmThreads = 384;
 constexpr uint32_t kABytes = kTileM * kBlockK * 2;
@@ -860,7 +861,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
   // ------------------------------------------------------------------ slot reduction
-  // Warps 6..11 do nothing else; the others join when their own role is done (unless the block has
+  // Warps 6..10 do nothing else; the publisher and the others join when their own role is done (unless the block has
   // given up on one of its barriers), so the chunks that arrive last find every warp free.
   __syncwarp();
   if (p.reduce_in_kernel && !*abort_flag) reduce_worker(p.red, lane);
