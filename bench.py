@@ -379,7 +379,12 @@ def bench_matmul(mesh, args, peaks, peak_kind) -> dict:
         elapsed = reduce_max(mesh, time.perf_counter() - started)
         mesh.barrier()
         executable.status()
+        # The host-buffer call may cut the matrix into blocks of rows; its bits must not differ.
+        same = bool(np.array_equal(out_host, out.cpu().view(torch.uint16).numpy()))
+        if not all_ranks_ok(mesh, same):
+            raise SystemExit("PARITY_FAILED: cake_matmul_rs_run_host and the device-buffer call disagree")
         e2e = {
+            "bit_identical_to_device_call": True,
             "value": flops_total / (elapsed / e2e_steps) / 1e12, "unit": "TFLOP/s",
             "h2d_bytes_per_step": int(lhs_host.nbytes + rhs_host.nbytes), "d2h_bytes_per_step": int(out_host.nbytes),
             "ms_per_step": elapsed / e2e_steps * 1e3, "steps": e2e_steps, "api": "cake_matmul_rs_run_host",

@@ -141,7 +141,11 @@ int32_t cake_matmul_rs_enqueue_push(cake_matmul_rs* plan, const void* lhs, const
 int32_t cake_matmul_rs_enqueue_reduce(cake_matmul_rs* plan, void* out, void* stream);
 
 /* Same computation with HOST buffers: copies lhs and rhs to device staging buffers owned by the
- * plan, enqueues, copies the local output back and synchronises the stream. world == 1 or P2P. */
+ * plan, enqueues, copies the local output back and synchronises the stream. world == 1 or P2P.
+ * At world == 1, when lhs is large enough (blocks of whole tiles and at least 8 MiB each), the
+ * matrix goes through in up to 8 blocks of rows on two copy streams of the plan's own, so that a
+ * block is contracted while the next one arrives and the previous one leaves; the output bits are
+ * those of one enqueue. Pinned host buffers are needed for that overlap, not for correctness. */
 int32_t cake_matmul_rs_run_host(cake_matmul_rs* plan, const void* lhs_host, const void* rhs_host,
                                 void* out_host, void* stream);
 

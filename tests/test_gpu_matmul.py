@@ -419,3 +419,36 @@ def test_receipt_is_written_validated_and_refuses_tampering(cuda_device, tmp_pat
         handle.write(b"\x01")
     with pytest.raises(ValueError, match="ARTIFACT_CHANGED path=output.npy"):
         receipt.validate_receipt(out)
+
+
+@pytest.mark.parametrize(
+    "shape, output_dtype",
+    [((384, 1000, 520), "f32"), ((2048, 4096, 512), "bf16"), ((4096, 8192, 256), "f32")],
+    ids=["one-enqueue", "two-row-blocks", "eight-row-blocks"],
+)
+def test_host_buffers_in_host_buffer_out(cuda_device, shape, output_dtype):
+    """cake_matmul_rs_run_host: the same bits as the device-buffer call, whether the matrix goes
+    through in one enqueue (small operands) or in blocks of rows that overlap the copies with the
+    contraction (lhs blocks of at least 8 MiB), twice in a row on the same plan."""
+    m, k, n = shape
+    generator = np.random.default_rng(m + k + n)
+    lhs = generator.normal(scale=k**-0.5, size=(m, k)).astype(np.float32).astype(BF16)
+    rhs = generator.normal(scale=k**-0.5, size=(k, n)).astype(np.float32).astype(BF16)
+    plan = cuda_lowering.plan_distributed_matmul(mesh_size=1, m=m, k=k, n=n, tile_n=256, output_dtype=output_dtype)
+    executable, _ = plan.build()
+    try:
+        torch_dtype = torch.float32 if output_dtype == "f32" else torch.bfloat16
+        device_out = torch.full(plan.output_local_shape, float("nan"), dtype=torch_dtype, device=cuda_device)
+        executable(bf16_to_torch(lhs, cuda_device), bf16_to_torch(rhs, cuda_device), device_out)
+        expected_bits = device_out.cpu().view(torch.int32 if output_dtype == "f32" else torch.int16).numpy()
+        host_dtype = np.float32 if output_dtype == "f32" else np.uint16
+        for _ in range(2):
+            out = np.zeros(plan.output_local_shape, dtype=host_dtype)
+            executable.run_host(lhs.view(np.uint16), rhs.view(np.uint16), out)
+            np.testing.assert_array_equal(out.view(expected_bits.dtype), expected_bits)
+        assert executable.status() == (0, 0, 0, 0)
+        reference = oracle.matmul_reference(lhs.astype(np.float32), rhs.astype(np.float32))
+        actual = out if output_dtype == "f32" else bits_to_bf16(out).astype(np.float32)
+        assert oracle.relative_l2_error(actual, reference) <= (1e-5 if output_dtype == "f32" else 1e-2)
+    finally:
+        executable.close()

@@ -924,6 +924,13 @@ struct cake_matmul_rs {
   void* h_lhs = nullptr;
   void* h_rhs = nullptr;
   void* h_out = nullptr;
+  // run_host at world 1: a plan for one block of rows, and what overlaps the copies with it
+  static constexpr int kHostBlocks = 8;
+  cake_matmul_rs* row_block_plan = nullptr;
+  int host_blocks = 0;  // 0 = not decided yet, 1 = one enqueue for the whole matrix
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t host_begin = nullptr, host_end = nullptr;
+  cudaEvent_t block_in[kHostBlocks] = {}, block_done[kHostBlocks] = {};
   int launches = 0;
 };
 
@@ -1060,6 +1067,15 @@ int32_t cake_matmul_rs_destroy(cake_matmul_rs* plan) {
   if (plan->h_lhs) cudaFree(plan->h_lhs);
   if (plan->h_rhs) cudaFree(plan->h_rhs);
   if (plan->h_out) cudaFree(plan->h_out);
+  if (plan->row_block_plan) cake_matmul_rs_destroy(plan->row_block_plan);
+  if (plan->copy_in) cudaStreamDestroy(plan->copy_in);
+  if (plan->copy_out) cudaStreamDestroy(plan->copy_out);
+  if (plan->host_begin) cudaEventDestroy(plan->host_begin);
+  if (plan->host_end) cudaEventDestroy(plan->host_end);
+  for (int i = 0; i < cake_matmul_rs::kHostBlocks; ++i) {
+    if (plan->block_in[i]) cudaEventDestroy(plan->block_in[i]);
+    if (plan->block_done[i]) cudaEventDestroy(plan->block_done[i]);
+  }
   delete plan;
   return CAKE_OK;
 }
@@ -1287,6 +1303,85 @@ int32_t cake_matmul_rs_enqueue_reduce(cake_matmul_rs* plan, void* out, void* str
   return enqueue_impl(plan, nullptr, nullptr, out, stream, kPhaseReduce);
 }
 
+}  // extern "C"
+
+namespace {
+
+// run_host at world 1 is bound by the host link: 2 (M + N) K bytes in, then the kernel, then M N
+// elements out, one after the other. The rows of lhs are independent, so the matrix is cut into
+// blocks of rows: once rhs is on the device, block i is contracted while block i + 1 arrives and
+// block i - 1 leaves (the link carries both directions at once). Every output element is still
+// accumulated over K in the same order, so the result does not depend on the cut. The cut is used
+// when the blocks are whole tiles and at least 8 MiB of lhs each.
+int32_t prepare_row_blocks(cake_matmul_rs* plan) {
+  if (plan->host_blocks != 0) return CAKE_OK;
+  const cake_matmul_rs_desc& d = plan->d;
+  plan->host_blocks = 1;
+  if (plan->rhs_via_transpose) return CAKE_OK;
+  int blocks = 0;
+  for (int candidate = cake_matmul_rs::kHostBlocks; candidate >= 2; candidate /= 2) {
+    const int64_t rows = d.m / candidate;
+    if (d.m % candidate == 0 && rows % cake::kTileM == 0 && rows * d.k_local * 2 >= (8ll << 20)) {
+      blocks = candidate;
+      break;
+    }
+  }
+  if (blocks == 0) return CAKE_OK;
+  cake_matmul_rs_desc block_desc = d;
+  block_desc.m = d.m / blocks;
+  int32_t rc = cake_matmul_rs_create(&block_desc, &plan->row_block_plan);
+  if (rc) return rc;
+  CAKE_CUDA_TRY(cudaStreamCreateWithFlags(&plan->copy_in, cudaStreamNonBlocking));
+  CAKE_CUDA_TRY(cudaStreamCreateWithFlags(&plan->copy_out, cudaStreamNonBlocking));
+  CAKE_CUDA_TRY(cudaEventCreateWithFlags(&plan->host_begin, cudaEventDisableTiming));
+  CAKE_CUDA_TRY(cudaEventCreateWithFlags(&plan->host_end, cudaEventDisableTiming));
+  for (int i = 0; i < blocks; ++i) {
+    CAKE_CUDA_TRY(cudaEventCreateWithFlags(&plan->block_in[i], cudaEventDisableTiming));
+    CAKE_CUDA_TRY(cudaEventCreateWithFlags(&plan->block_done[i], cudaEventDisableTiming));
+  }
+  plan->host_blocks = blocks;
+  return CAKE_OK;
+}
+
+int32_t run_host_row_blocks(cake_matmul_rs* plan, const void* lhs_host, const void* rhs_host, void* out_host,
+                            cudaStream_t stream) {
+  const cake_matmul_rs_desc& d = plan->d;
+  const int blocks = plan->host_blocks;
+  const size_t lhs_block = static_cast<size_t>(d.m / blocks) * d.k_local * 2;
+  const size_t out_block = static_cast<size_t>(d.m / blocks) * d.n * plan->osize;
+  const size_t rhs_bytes = static_cast<size_t>(d.n) * d.k_local * 2;
+  // The copies start after whatever the caller has already queued on its stream.
+  CAKE_CUDA_TRY(cudaEventRecord(plan->host_begin, stream));
+  CAKE_CUDA_TRY(cudaStreamWaitEvent(plan->copy_in, plan->host_begin, 0));
+  CAKE_CUDA_TRY(cudaStreamWaitEvent(plan->copy_out, plan->host_begin, 0));
+  CAKE_CUDA_TRY(cudaMemcpyAsync(plan->h_rhs, rhs_host, rhs_bytes, cudaMemcpyHostToDevice, plan->copy_in));
+  for (int i = 0; i < blocks; ++i) {
+    CAKE_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(plan->h_lhs) + i * lhs_block, static_cast<const char*>(lhs_host) + i * lhs_block,
+                                  lhs_block, cudaMemcpyHostToDevice, plan->copy_in));
+    CAKE_CUDA_TRY(cudaEventRecord(plan->block_in[i], plan->copy_in));
+  }
+  for (int i = 0; i < blocks; ++i) {
+    CAKE_CUDA_TRY(cudaStreamWaitEvent(stream, plan->block_in[i], 0));
+    int32_t rc = cake_matmul_rs_enqueue(plan->row_block_plan, static_cast<char*>(plan->h_lhs) + i * lhs_block, plan->h_rhs,
+                                        static_cast<char*>(plan->h_out) + i * out_block, stream);
+    if (rc) return rc;
+    CAKE_CUDA_TRY(cudaEventRecord(plan->block_done[i], stream));
+    CAKE_CUDA_TRY(cudaStreamWaitEvent(plan->copy_out, plan->block_done[i], 0));
+    CAKE_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(out_host) + i * out_block, static_cast<char*>(plan->h_out) + i * out_block,
+                                  out_block, cudaMemcpyDeviceToHost, plan->copy_out));
+  }
+  CAKE_CUDA_TRY(cudaEventRecord(plan->host_end, plan->copy_out));
+  CAKE_CUDA_TRY(cudaStreamWaitEvent(stream, plan->host_end, 0));
+  CAKE_CUDA_TRY(cudaStreamSynchronize(stream));
+  // A barrier of a row block's kernel that gave up is reported like one of the whole matrix's.
+  cake_status block_status;
+  return cake_matmul_rs_status(plan->row_block_plan, stream, &block_status);
+}
+
+}  // namespace
+
+extern "C" {
+
 int32_t cake_matmul_rs_run_host(cake_matmul_rs* plan, const void* lhs_host, const void* rhs_host,
                                 void* out_host, void* stream_v) {
   if (!plan || !lhs_host || !rhs_host || !out_host) return fail(CAKE_ERR_INVALID_ARGUMENT, "cake_matmul_rs_run_host: null argument");
@@ -1300,6 +1395,11 @@ int32_t cake_matmul_rs_run_host(cake_matmul_rs* plan, const void* lhs_host, cons
   if (!plan->h_lhs) CAKE_CUDA_TRY(cudaMalloc(&plan->h_lhs, lhs_bytes));
   if (!plan->h_rhs) CAKE_CUDA_TRY(cudaMalloc(&plan->h_rhs, rhs_bytes));
   if (!plan->h_out) CAKE_CUDA_TRY(cudaMalloc(&plan->h_out, out_bytes));
+  if (d.world == 1) {
+    int32_t prc = prepare_row_blocks(plan);
+    if (prc) return prc;
+    if (plan->host_blocks > 1) return run_host_row_blocks(plan, lhs_host, rhs_host, out_host, stream);
+  }
   CAKE_CUDA_TRY(cudaMemcpyAsync(plan->h_lhs, lhs_host, lhs_bytes, cudaMemcpyHostToDevice, stream));
   CAKE_CUDA_TRY(cudaMemcpyAsync(plan->h_rhs, rhs_host, rhs_bytes, cudaMemcpyHostToDevice, stream));
   int32_t rc = cake_matmul_rs_enqueue(plan, plan->h_lhs, plan->h_rhs, plan->h_out, stream_v);
