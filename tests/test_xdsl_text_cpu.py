@@ -1,0 +1,212 @@
+"""The canonical text of physical kernels is the reference's, byte for byte.
+
+Known answers: the schedule hashes the reference pins in its own tests and sources for programs
+that can be rebuilt here from their definitions. xDSL is not installed, so these SHA-256 values are
+the only witness of the exact bytes -- and a sufficient one.
+"""
+
+from __future__ import annotations
+
+import pytest
+
+from tpu_cake_b200 import ir, schedule_lowering, workloads, xdsl_text
+from tpu_cake_b200.dialects import KernelBuilder, buffer
+from tpu_cake_b200.ir import Operation
+
+TPU7X = schedule_lowering.LoweringTarget("tpu7x", 64 << 20, 16 << 20, 600_000_000_000)  # src/tpu_cake/lowering.py:47-52
+EXTERNAL = {"memory": "hbm", "ownership": "external", "lifetime": (0, 0)}
+
+
+def rpa_kernel(name, inputs, mesh=None, **properties):
+    """KernelBuilder with the capacities of the reference's RPA schedules (96 MiB / 1 MiB)."""
+    mesh = dict(mesh or {})
+    builder = KernelBuilder(name, "tpu7x", inputs, vmem_capacity_bytes=96 << 20, smem_capacity_bytes=1 << 20, mesh=mesh,
+                            interconnect_bandwidth_bytes_per_second={axis: 600_000_000_000 for axis in mesh})
+    builder.kernel.properties.update(properties)
+    return builder
+
+
+def test_default_distributed_matmul_kernel_has_the_pinned_hash():
+    """tests/test_pallas_lowering.py:54-60: mesh 4, 16 x 32 x 16, whole-shard tiles."""
+    physical = schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(), target=TPU7X)
+    assert ir.schedule_sha256(physical) == "395c5e60a6ae43e2c86b61b06271666010d79d103175cb43a4c01c9fb22a8819"
+    text = ir.canonical_text(physical)
+    assert text.startswith('"builtin.module"() ({\n  "tpu_schedule.kernel"() <{dma_engine_count = #builtin.int<2>, ')
+    assert text.endswith('    "tpu_schedule.yield"() : () -> ()\n  }) : () -> ()\n}) : () -> ()\n')
+
+
+@pytest.mark.parametrize(
+    "implementation, expected",
+    [(None, "9593beb3ad1607b65f12ac02cfe4bf2adbf6279405aa307f46c155e430d40990"),
+     ("pallas_bidirectional_ring", "23917a172499112cebd52bb26333f11b367f1b67190546e90af847ec8b71fe97")],
+)
+def test_mesh8_matmul_kernels_have_the_confirmation_hashes(implementation, expected):
+    """src/tpu_cake/matmul_collective_confirmation.py:42-48,87,108: mesh 8, 1024 x 65536 x 1024,
+    tiles 128 x 128, with the compiler's reduce-scatter and with the ring named as implementation."""
+    logical = workloads.distributed_matmul_schedule(mesh_size=8, m=1024, k=65536, n=1024)
+    physical = schedule_lowering.lower_distributed_matmul(logical, target=TPU7X, tile=schedule_lowering.MatmulTile(128, 128))
+    if implementation is not None:
+        collective = next(op for op in physical.walk() if op.name == "tpu_schedule.collective")
+        collective.properties["implementation"] = implementation
+    assert ir.schedule_sha256(physical) == expected
+
+
+def fused_inputs():
+    return (
+        buffer((4, 4, 32), "T Hq D".split(), "bf16", **EXTERNAL),
+        buffer((4, 2, 32), "T Hkv D".split(), "bf16", **EXTERNAL),
+        buffer((4, 2, 32), "T Hkv D".split(), "bf16", **EXTERNAL),
+        buffer((32, 16, 2, 2, 128), "P S Hkv2p Pack Dpad".split(), "bf16", **EXTERNAL),
+        buffer((4,), ("N",), "i32", **EXTERNAL),
+        buffer((32,), ("PI",), "i32", **EXTERNAL),
+        buffer((5,), ("N1",), "i32", **EXTERNAL),
+        buffer((5,), ("N1",), "i32", **EXTERNAL),
+        buffer((3,), ("R3",), "i32", **EXTERNAL),
+        buffer((4, 4, 16), "T Hq R".split(), "bf16", **EXTERNAL),
+        buffer((16, 128), "R E".split(), "bf16", **EXTERNAL),
+    )
+
+
+def test_fused_rpa_kernel_has_the_pinned_hash():
+    """tests/test_rpa_lowering.py:140-146 over src/tpu_cake/workloads/inkling_rpa.py:145-195: a
+    kernel without a mesh (one device, no links) around the fused attention operation."""
+    builder = rpa_kernel("inkling_fused_rpa_decode", fused_inputs())
+    builder.fused_ragged_paged_attention((*builder.inputs, builder.inputs[0], builder.inputs[3]), stage=0, softmax_scale="0.03125",
+                                         vmem_limit_bytes=96 << 20)
+    assert ir.schedule_sha256(builder.module()) == "e1de39a3dfa8f4c930207fbe5218aa1f956b19b0b933e993fe35ae916e8ecad7"
+
+
+def test_sharded_rpa_surface_kernel_has_the_contract_hash():
+    """contracts/inkling-sharded-rpa-surface.json plan.schedule_sha256 over
+    src/tpu_cake/workloads/inkling_rpa.py:198-262: a 2 x 4 mesh, so the topology has two axes."""
+    inputs = (
+        buffer((4, 8, 128), "T Hq D".split(), "bf16", sharding=("data", "tensor", ""), **EXTERNAL),
+        buffer((4, 4, 128), "T Hkv D".split(), "bf16", sharding=("data", "tensor", ""), **EXTERNAL),
+        buffer((4, 4, 128), "T Hkv D".split(), "bf16", sharding=("data", "tensor", ""), **EXTERNAL),
+        buffer((3712, 1, 4, 2, 128), "P S Hkv2p Pack Dpad".split(), "bf16", sharding=("data", "", "tensor", "", ""), **EXTERNAL),
+        buffer((4,), ("N",), "i32", sharding=("data",), **EXTERNAL),
+        buffer((8192,), ("PI",), "i32", sharding=("data",), **EXTERNAL),
+        buffer((5,), ("N1",), "i32", sharding=("data",), **EXTERNAL),
+        buffer((5,), ("N1",), "i32", sharding=("data",), **EXTERNAL),
+        buffer((3,), ("R3",), "i32", sharding=("data",), **EXTERNAL),
+        buffer((4, 8, 16), "T Hq R".split(), "bf16", sharding=("data", "tensor", ""), **EXTERNAL),
+        buffer((16, 512), "R E".split(), "bf16", **EXTERNAL),
+    )
+    builder = rpa_kernel("inkling_sharded_fused_rpa_decode", inputs, mesh={"data": 2, "tensor": 4})
+    builder.fused_ragged_paged_attention((*builder.inputs, builder.inputs[0], builder.inputs[3]), stage=0, softmax_scale="0.0078125",
+                                         vmem_limit_bytes=96 << 20)
+    assert ir.schedule_sha256(builder.module()) == "12007604b3b6305899bd2f13d311aa77889199fc0398a3615c142f7966572b13"
+
+
+def decode_core_module():
+    """src/tpu_cake/workloads/inkling_rpa.py:265-401: argument modes on the kernel, scratch in both
+    on-chip spaces, a ten-slot semaphore and an operation with 26 operands and 22 properties."""
+    inputs = (
+        buffer((4, 4, 1, 2, 128), "Hkv T Hqp Pack Dpad".split(), "bf16", **EXTERNAL),
+        buffer((4, 4, 2, 128), "T Hkv2p Pack Dpad".split(), "bf16", **EXTERNAL),
+        buffer((3712, 1, 4, 2, 128), "P S Hkv2p Pack Dpad".split(), "bf16", **EXTERNAL),
+        buffer((4,), ("N",), "i32", **EXTERNAL),
+        buffer((8192,), ("PI",), "i32", **EXTERNAL),
+        buffer((5,), ("N1",), "i32", **EXTERNAL),
+        buffer((5,), ("N1",), "i32", **EXTERNAL),
+        buffer((3,), ("R3",), "i32", **EXTERNAL),
+        buffer((4, 4, 2, 128), "Hkv T Hqpk Rpad".split(), "bf16", **EXTERNAL),
+        buffer((128, 4608), "Rpad Epad".split(), "bf16", **EXTERNAL),
+    )
+    builder = rpa_kernel("inkling_owned_rpa_decode_core", inputs, argument_modes=("inout", "input", "inout", *("input",) * 7))
+    vmem = {"memory": "vmem", "lifetime": (0, 0)}
+    smem = {"memory": "smem", "lifetime": (0, 0)}
+    scratch = [
+        builder.alloc(buffer((4, 4, 2, 128), "Hkv T Hqpk Rpad".split(), "bf16", **vmem), "relative_states_resident"),
+        builder.alloc(buffer((128, 4608), "Rpad Epad".split(), "bf16", **vmem), "relative_projection_resident"),
+        builder.alloc(buffer((2, 128, 5, 2, 128), "Slot Bkv Hkv2pPad Pack Dpad".split(), "bf16", **vmem), "paged_kv_double_buffer"),
+        builder.alloc(buffer((2, 4, 8, 1, 2, 128), "Slot Hkv Bq Hqp Pack Dpad".split(), "bf16", **vmem), "query_double_buffer"),
+        builder.alloc(buffer((2, 4, 8, 1, 2, 128), "Slot Hkv Bq Hqp Pack Dpad".split(), "bf16", **vmem), "output_double_buffer"),
+        builder.alloc(buffer((4, 16, 128), "Hkv QH Lane".split(), "bf16", **vmem), "online_softmax_l"),
+        builder.alloc(buffer((4, 16, 128), "Hkv QH Lane".split(), "bf16", **vmem), "online_softmax_m"),
+        builder.alloc(buffer((4, 16, 128), "Hkv QH Dpad".split(), "bf16", **vmem), "attention_accumulator"),
+        builder.alloc(buffer((4, 8, 2, 256, 4), "Hkv Bq Hq KVD Work".split(), "f32", **vmem), "compiler_attention_intermediates"),
+        builder.alloc(buffer((1,), ("One",), "i32", **smem), "cumulative_mask_lengths"),
+        builder.alloc(buffer((3,), ("SemId",), "i32", **smem), "semaphore_ids"),
+        builder.alloc(buffer((4,), ("OutputId",), "i32", **smem), "output_ids"),
+        builder.alloc(buffer((6,), ("UpdateId",), "i32", **smem), "cache_update_ids"),
+    ]
+    semaphores = builder.semaphore()
+    semaphores.owner.properties["slots"] = 10
+    properties = {
+        "stage": 0, "query_fetch_size": 8, "kv_fetch_size": 128, "query_compute_size": 8, "kv_compute_size": 128, "buffer_slots": 2,
+        "dma_channels": 5, "prefetch_distance": 1, "relative_extent": 512, "softmax_scale": "0.0078125", "softmax_dtype": "float32",
+        "execution_authority": "tpu-cake-owned-pallas-decode-core-v1", "attention_case": "decode",
+        "masking_authority": "decode-kv-length-no-custom-mask-v1", "relative_dimension": 16, "cumulative_mask_initial": (0,),
+        "semaphore_ids_initial": (0, 0, 0), "output_ids_initial": (-1,) * 4, "cache_update_ids_initial": (-1,) * 6,
+        # src/tpu_cake/rpa_lowering.py:54-58
+        "backend_repository_revision": "9e1a7d39ccdcf9f396e024bfc45935f4f50f70c7",
+        "backend_file_revision": "ac88a2ecfa905965b43edbbb5e6510eb272d09e5",
+        "backend_sha256": "12c6aeeade66538d3bb638f048850c3d69095ade4ec42559cd8b3566bfc68897",
+    }
+    builder.block.ops.append(Operation("tpu_schedule.rpa_decode_core", [*builder.inputs, builder.inputs[0], builder.inputs[2], *scratch, semaphores],
+                                       [], properties))
+    return builder.module()
+
+
+def test_owned_decode_core_kernel_has_the_pinned_hash():
+    """tests/test_rpa_lowering.py:223-228 and :342-344."""
+    assert ir.schedule_sha256(decode_core_module()) == "41946eb01074fd2ecd2831190321631f09d9c25fb7c3ee68a28ebc272f6d576a"
+
+
+def every_kernel():
+    yield schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(), target=TPU7X)
+    yield schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(mesh_size=8, m=8192, k=16384, n=8192, scatter_dimension="M"),
+                                                     tile=schedule_lowering.MatmulTile(128, 256), collective_implementation="p2p_owner_push_bf16")
+    yield workloads.inkling_fused_rpa_schedule()
+    yield workloads.inkling_sharded_rpa_schedule()
+    yield workloads.paged_attention_schedule()
+    yield decode_core_module()
+
+
+def test_saved_text_parses_back_to_the_same_bytes_and_verifies():
+    for module in every_kernel():
+        text = ir.canonical_text(module)
+        parsed = xdsl_text.parse_reference_physical_kernel(text)
+        assert ir.canonical_text(parsed) == text
+        parsed.verify()
+        assert [op.name for op in parsed.walk()] == [op.name for op in module.walk()]
+
+
+def test_text_that_would_not_print_back_is_refused():
+    text = ir.canonical_text(schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(), target=TPU7X))
+    with pytest.raises(ValueError, match="XDSL_TEXT_NOT_CANONICAL"):
+        # properties out of order: xDSL would accept it, the canonical form does not contain it
+        xdsl_text.parse_reference_physical_kernel(text.replace("dma_engine_count = #builtin.int<2>, ici_link_count = #builtin.int<1>",
+                                                               "ici_link_count = #builtin.int<1>, dma_engine_count = #builtin.int<2>"))
+    with pytest.raises(ValueError, match="XDSL_TEXT_UNSUPPORTED_ENGINE_COUNT property=mxu_count"):
+        xdsl_text.parse_reference_physical_kernel(text.replace("mxu_count = #builtin.int<1>", "mxu_count = #builtin.int<2>"))
+    with pytest.raises(ValueError, match="XDSL_TEXT_UNSUPPORTED_LAYOUT"):
+        xdsl_text.parse_reference_physical_kernel(text.replace("#tpu_schedule.layout<[#builtin.int<0>, #builtin.int<1>]>",
+                                                               "#tpu_schedule.layout<[#builtin.int<1>, #builtin.int<0>]>", 1))
+    with pytest.raises(ValueError, match="XDSL_TEXT_UNDEFINED_VALUE value=%99"):
+        xdsl_text.parse_reference_physical_kernel(text.replace('"tpu_schedule.dma_wait"(%10)', '"tpu_schedule.dma_wait"(%99)'))
+    with pytest.raises(ValueError, match="XDSL_TEXT_PARSE_ERROR line=1"):
+        xdsl_text.parse_reference_physical_kernel("module {}\n")
+    with pytest.raises(ValueError, match="XDSL_TEXT_UNSUPPORTED_OPERATION operation=tpu_schedule.vector_compute"):
+        xdsl_text.parse_reference_physical_kernel(text.replace('"tpu_schedule.dma_wait"(%10)', '"tpu_schedule.vector_compute"(%10)'))
+
+
+def test_a_parsed_kernel_that_breaks_a_dialect_rule_fails_verification():
+    text = ir.canonical_text(schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(), target=TPU7X))
+    broken = text.replace("tile_k = #builtin.int<8>", "tile_k = #builtin.int<4>")
+    module = xdsl_text.parse_reference_physical_kernel(broken)
+    with pytest.raises(ir.VerifyException):
+        module.verify()
+
+
+def test_verify_schedule_command_accepts_a_saved_physical_text(tmp_path, capsys):
+    from tpu_cake_b200 import cli
+
+    physical = schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(), target=TPU7X)
+    path = tmp_path / "physical.xdsl"
+    path.write_text(ir.canonical_text(physical))
+    assert cli.main(["verify-schedule", str(path)]) == 0
+    assert capsys.readouterr().out.strip() == (
+        f"SCHEDULE_ACCEPTED path={path} schedule_sha256=395c5e60a6ae43e2c86b61b06271666010d79d103175cb43a4c01c9fb22a8819"
+    )

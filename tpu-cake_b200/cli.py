@@ -70,7 +70,8 @@ def main(argv: list[str] | None = None) -> int:
     render = commands.add_parser("render-workload", help="print the canonical text of the logical or physical schedule")
     _add_shape(render)
     render.add_argument("--physical", action="store_true")
-    verify = commands.add_parser("verify-schedule", help="build, verify and hash the schedules")
+    verify = commands.add_parser("verify-schedule", help="verify a saved physical schedule (the reference's physical.xdsl text), or build, verify and hash the matmul schedules")
+    verify.add_argument("schedule", type=Path, nargs="?", help="canonical text of a physical kernel; without it the schedules of the shape options are built")
     _add_shape(verify)
     search = commands.add_parser("search-matmul", help="tile search: run every candidate of a contract in alternating rounds and pick a winner")
     search.add_argument("contract", type=Path)
@@ -127,6 +128,14 @@ def main(argv: list[str] | None = None) -> int:
         document = (receipt_module.finalize_matmul_run(args.root, profile_csv=args.profile) if args.command == "finalize-matmul-run"
                     else receipt_module.validate_receipt(args.root))
         print(json.dumps({"receipt_id": document["receipt_id"], "run_id": document["run_id"], **document["metrics"]}))
+        return 0
+    if args.command == "verify-schedule" and args.schedule is not None:
+        # The reference's command (src/tpu_cake/cli.py:432-436): parse the file, verify, accept.
+        from . import xdsl_text
+
+        module = xdsl_text.parse_reference_physical_kernel(args.schedule.read_text())
+        module.verify()
+        print(f"SCHEDULE_ACCEPTED path={args.schedule} schedule_sha256={ir.schedule_sha256(module)}")
         return 0
     if args.command == "search-rpa":
         from . import rpa_search

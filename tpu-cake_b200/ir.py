@@ -175,7 +175,14 @@ _NORMALISED_SYMBOLS = {"tpu_schedule.kernel": "kernel", "dtensor.program": "prog
 def canonical_text(module: Module) -> str:
     """Generic-format text with the reference's normalisations: properties sorted by key, the
     kernel / program symbol replaced by a fixed name, alloc roles renamed alloc0.. in definition
-    order, SSA names numbered in definition order, locations omitted."""
+    order, SSA names numbered in definition order, locations omitted. A physical kernel made only
+    of operations the reference's dialect has is printed exactly as the reference prints it
+    (``xdsl_text``), so its text and hash are the ones the reference assigns to the same kernel;
+    logical programs and kernels with this backend's own operations use the compact form below."""
+    from . import xdsl_text
+
+    if xdsl_text.is_reference_physical_kernel(module):
+        return xdsl_text.reference_canonical_text(module)
     names: dict[int, str] = {}
     alloc_roles: dict[str, str] = {}
     lines: list[str] = []
