@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import ast
 import ctypes
-import re
 from dataclasses import dataclass, field, replace
 from enum import StrEnum
 from pathlib import Path
@@ -463,14 +462,6 @@ def lower_physical_matmul_to_cuda(module, *, output_dtype: str = "f32") -> CudaM
     )
 
 
-_SAVED_TILE = re.compile(r'"tpu_schedule\.mxu_matmul"\(.*?tile_m = #builtin\.int<(\d+)>, tile_n = #builtin\.int<(\d+)>')
-_STRATEGY_TO_IMPLEMENTATION = {
-    MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER: "NCCL",
-    MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE: "P2P_OWNER_PUSH",
-    MatmulCollectiveStrategy.P2P_FUSED_EPILOGUE_BF16_TRANSPORT: "P2P_OWNER_PUSH_BF16",
-}
-
-
 def _saved_source_constants(source_path: Path) -> dict[str, object]:
     try:
         tree = ast.parse(source_path.read_text(), filename=str(source_path))
@@ -488,16 +479,14 @@ def _saved_source_constants(source_path: Path) -> dict[str, object]:
 
 def validate_saved_cuda_plan(physical_path: Path, source_path: Path, *, schedule_sha256: str, source_sha256: str) -> CudaMatmulRsPlan:
     """Replays a saved run's lowering: the counterpart of ``validate_saved_pallas_plan``
-    (src/tpu_cake/pallas_lowering.py:850-947), with its error names.
+    (src/tpu_cake/pallas_lowering.py:850-947), with its error names and its order of checks.
 
-    Both files must have the recorded hashes. The saved source's constants (mesh, local shapes,
-    shardings, scatter dimension, collective) name a workload; the logical schedule of that workload
-    is built again, lowered with the schedule tile the saved IR carries, and its canonical text must
-    be the saved physical IR byte for byte (this backend's IR core has a printer and no parser, so
-    the saved text is checked by regeneration instead of by parsing it). The plan lowered from it
-    must then agree with every constant of the saved source and render that source again exactly.
-    Returns the replayed plan."""
-    from . import dialects, ir, schedule_lowering, workloads
+    Both files must have the recorded hashes. The saved physical IR is parsed (it is the reference's
+    canonical text; only text that prints back to the same bytes parses), verified and lowered to a
+    plan again; that plan must agree with every constant of the saved source and render that source
+    again exactly. The output dtype is the one thing the IR does not carry (the dialect's matmul
+    accumulates and stores f32): it is read from the saved source. Returns the replayed plan."""
+    from . import xdsl_text
 
     physical_text = physical_path.read_text()
     if text_sha256(physical_text) != schedule_sha256:
@@ -506,29 +495,17 @@ def validate_saved_cuda_plan(physical_path: Path, source_path: Path, *, schedule
     if text_sha256(source_text) != source_sha256:
         raise ValueError("SAVED_CUDA_SOURCE_HASH_MISMATCH")
     constants = _saved_source_constants(source_path)
+    output_line = next((line for line in source_text.splitlines() if line.startswith("output_local")), "")
     try:
-        mesh_axis, mesh_size = constants["mesh"]
-        m, k_local = constants["lhs_local"]
-        _, n = constants["rhs_local"]
-        scatter = int(constants["scatter_dimension"])
-        strategy = None if constants["collective"] is None else MatmulCollectiveStrategy(constants["collective"])
-        output_dtype = "bf16" if "# bf16" in next(line for line in source_text.splitlines() if line.startswith("output_local")) else "f32"
-    except (KeyError, TypeError, ValueError, StopIteration) as error:
-        raise ValueError("SAVED_CUDA_SOURCE_PLAN_MISMATCH") from error
-    tile = _SAVED_TILE.search(physical_text)
-    if tile is None:
-        raise ValueError("SAVED_PHYSICAL_IR_INVALID")
-    try:
-        logical = workloads.distributed_matmul_schedule(mesh_size=mesh_size, m=m, k=k_local * mesh_size, n=n, scatter_dimension="MN"[scatter])
-        physical = schedule_lowering.lower_distributed_matmul(
-            logical, tile=schedule_lowering.MatmulTile(int(tile.group(1)), int(tile.group(2))),
-            collective_implementation=None if strategy is None or mesh_size == 1 else getattr(dialects.CollectiveImplementation, _STRATEGY_TO_IMPLEMENTATION[strategy]),
-        )
-        if ir.canonical_text(physical) != physical_text:
-            raise ValueError("regenerated physical IR differs from the saved text")
-        plan = lower_physical_matmul_to_cuda(physical, output_dtype=output_dtype)
+        physical = xdsl_text.parse_reference_physical_kernel(physical_text)
+        physical.verify()
+        plan = lower_physical_matmul_to_cuda(physical, output_dtype="bf16" if "# bf16" in output_line else "f32")
     except Exception as error:
         raise ValueError("SAVED_PHYSICAL_IR_INVALID") from error
+    try:
+        mesh_axis, _ = constants["mesh"]
+    except (KeyError, TypeError, ValueError) as error:
+        raise ValueError("SAVED_CUDA_SOURCE_PLAN_MISMATCH") from error
     if plan.schedule_sha256 != schedule_sha256 or mesh_axis != plan.mesh_axis:
         raise ValueError("SAVED_CUDA_SOURCE_PLAN_MISMATCH")
     expected = {
