@@ -210,3 +210,26 @@ def test_verify_schedule_command_accepts_a_saved_physical_text(tmp_path, capsys)
     assert capsys.readouterr().out.strip() == (
         f"SCHEDULE_ACCEPTED path={path} schedule_sha256=395c5e60a6ae43e2c86b61b06271666010d79d103175cb43a4c01c9fb22a8819"
     )
+
+
+def test_physical_cost_commands_work_from_a_saved_kernel(tmp_path, capsys):
+    """estimate-physical-cost / verify-physical-cost (src/tpu_cake/cli.py:439-469): the report is
+    derived from the saved text alone, and a report that was edited is refused."""
+    import json
+
+    from tpu_cake_b200 import cli
+
+    physical = schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(mesh_size=8, m=128, k=1024, n=1024))
+    schedule = tmp_path / "physical.mlir"
+    schedule.write_text(ir.canonical_text(physical))
+    report = tmp_path / "cost.json"
+    assert cli.main(["estimate-physical-cost", str(schedule), "--output", str(report)]) == 0
+    derived = capsys.readouterr().out
+    assert derived.startswith(f"PHYSICAL_COST_DERIVED schedule_sha256={ir.schedule_sha256(physical)} mxu_regions=1 ")
+    assert cli.main(["verify-physical-cost", str(report), "--schedule", str(schedule)]) == 0
+    assert capsys.readouterr().out == derived.replace("PHYSICAL_COST_DERIVED", "PHYSICAL_COST_REPLAYED")
+    document = json.loads(report.read_text())
+    document["device_count"] += 1
+    report.write_text(json.dumps(document))
+    with pytest.raises(ValueError, match="PHYSICAL_COST_REPORT_MISMATCH"):
+        cli.main(["verify-physical-cost", str(report), "--schedule", str(schedule)])

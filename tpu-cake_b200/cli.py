@@ -73,6 +73,12 @@ def main(argv: list[str] | None = None) -> int:
     verify = commands.add_parser("verify-schedule", help="verify a saved physical schedule (the reference's physical.xdsl text), or build, verify and hash the matmul schedules")
     verify.add_argument("schedule", type=Path, nargs="?", help="canonical text of a physical kernel; without it the schedules of the shape options are built")
     _add_shape(verify)
+    estimate_cost = commands.add_parser("estimate-physical-cost", help="static resource report of a saved physical kernel, written as JSON")
+    estimate_cost.add_argument("schedule", type=Path)
+    estimate_cost.add_argument("--output", required=True, type=Path)
+    verify_cost = commands.add_parser("verify-physical-cost", help="derive the report of a saved physical kernel again and compare it with a saved report")
+    verify_cost.add_argument("report", type=Path)
+    verify_cost.add_argument("--schedule", required=True, type=Path)
     search = commands.add_parser("search-matmul", help="tile search: run every candidate of a contract in alternating rounds and pick a winner")
     search.add_argument("contract", type=Path)
     search.add_argument("output_dir", type=Path)
@@ -136,6 +142,24 @@ def main(argv: list[str] | None = None) -> int:
         module = xdsl_text.parse_reference_physical_kernel(args.schedule.read_text())
         module.verify()
         print(f"SCHEDULE_ACCEPTED path={args.schedule} schedule_sha256={ir.schedule_sha256(module)}")
+        return 0
+    if args.command in ("estimate-physical-cost", "verify-physical-cost"):
+        # The reference's commands (src/tpu_cake/cli.py:439-469) on this backend's rate model.
+        from . import physical_cost_model, xdsl_text
+
+        module = xdsl_text.parse_reference_physical_kernel(args.schedule.read_text())
+        module.verify()
+        report = physical_cost_model.analyze_physical_kernel(module)
+        document = json.dumps(report.to_json(), indent=2, sort_keys=True) + "\n"
+        if args.command == "estimate-physical-cost":
+            args.output.write_text(document)
+            word = "PHYSICAL_COST_DERIVED"
+        else:
+            if json.loads(args.report.read_text()) != json.loads(document):
+                raise ValueError("PHYSICAL_COST_REPORT_MISMATCH the saved report is not what the schedule derives")
+            word = "PHYSICAL_COST_REPLAYED"
+        print(f"{word} schedule_sha256={report.physical_schedule_sha256} mxu_regions={len(report.mxu_regions)} "
+              f"limiting_priced_resource={report.predicted_limiting_priced_resource}")
         return 0
     if args.command == "search-rpa":
         from . import rpa_search
