@@ -137,9 +137,9 @@ def test_validate_saved_cuda_plan_replays_and_rejects(tmp_path):
         physical = schedule_lowering.lower_distributed_matmul(logical, collective_implementation=implementation)
         plan = cuda_lowering.lower_physical_matmul_to_cuda(physical)
         folder.mkdir()
-        (folder / "physical.mlir").write_text(ir.canonical_text(physical))
+        (folder / "physical.xdsl").write_text(ir.canonical_text(physical))
         (folder / "lowered_cuda.py").write_text(plan.render_executable_source())
-        return plan, folder / "physical.mlir", folder / "lowered_cuda.py"
+        return plan, folder / "physical.xdsl", folder / "lowered_cuda.py"
 
     plan, physical_path, source_path = save(8, 1024, dialects.CollectiveImplementation.P2P_OWNER_PUSH_BF16, tmp_path / "a")
     hashes = {"schedule_sha256": plan.schedule_sha256, "source_sha256": plan.source_sha256()}

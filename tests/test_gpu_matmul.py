@@ -337,7 +337,7 @@ def test_runner_writes_a_complete_bundle(cuda_device, tmp_path, mesh_size, strat
     assert result.passed and result.median_ns > 0 and len(result.samples_ns) == 3
     assert result.execution == "emulated-on-one-gpu"
     for name in ("invocation.json", "profiler_config.json", "source_state.json", "source_diff.patch", "experiment.json",
-                 "distributed.mlir", "physical.mlir", "lowered_cuda.py", "cost_model_input.json", "cost_model.json",
+                 "distributed.xdsl", "physical.xdsl", "lowered_cuda.py", "cost_model_input.json", "cost_model.json",
                  "kernel_manifest.json", "lhs.npy", "rhs.npy", "output.npy", "oracle.npy", "ledger.sqlite", "result.json"):
         assert (out / name).exists(), name
     with RunLedger(out / "ledger.sqlite") as ledger:

@@ -31,7 +31,7 @@ def test_fused_rpa_run_writes_a_bundle_that_verifies(cuda_device, tmp_path):
     result = rpa_runner.run_fused_rpa(out)
     assert result.passed and result.preflight_passed and len(result.samples_ns) == 50 and result.median_ns > 0
     assert result.maximum_absolute_errors[0] <= 0.02 and result.maximum_absolute_errors[1] == 0.0
-    for name in ("invocation.json", "profiler_config.json", "source_state.json", "source_diff.patch", "experiment.json", "physical.mlir",
+    for name in ("invocation.json", "profiler_config.json", "source_state.json", "source_diff.patch", "experiment.json", "physical.xdsl",
                  "lowered_cuda.py", "preflight.json", "kernel_manifest.json", "inputs/03-fused_cache.npy", "outputs/00-output.npy",
                  "outputs/01-updated_cache.npy", "oracle/01-updated_cache.npy", "ledger.sqlite", "result.json"):
         assert (out / name).exists(), name

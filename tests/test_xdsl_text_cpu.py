@@ -220,7 +220,7 @@ def test_physical_cost_commands_work_from_a_saved_kernel(tmp_path, capsys):
     from tpu_cake_b200 import cli
 
     physical = schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule(mesh_size=8, m=128, k=1024, n=1024))
-    schedule = tmp_path / "physical.mlir"
+    schedule = tmp_path / "physical.xdsl"
     schedule.write_text(ir.canonical_text(physical))
     report = tmp_path / "cost.json"
     assert cli.main(["estimate-physical-cost", str(schedule), "--output", str(report)]) == 0

@@ -137,7 +137,7 @@ def finalize_matmul_run(root: Path, *, profile_csv: Path | None = None) -> dict:
     if plan.schedule_sha256 != result["schedule_sha256"] or plan.source_sha256() != result["cuda_source_sha256"]:
         raise ValueError("LOWERED_CODE_IDENTITY_DOES_NOT_REPLAY")
     # The saved IR text and lowered source themselves, not only their recorded hashes.
-    saved_plan = cuda_lowering.validate_saved_cuda_plan(root / "physical.mlir", root / "lowered_cuda.py", schedule_sha256=result["schedule_sha256"],
+    saved_plan = cuda_lowering.validate_saved_cuda_plan(root / "physical.xdsl", root / "lowered_cuda.py", schedule_sha256=result["schedule_sha256"],
                                                         source_sha256=result["cuda_source_sha256"])
     if saved_plan != plan:
         raise ValueError("LOWERED_CODE_IDENTITY_DOES_NOT_REPLAY")
@@ -218,7 +218,7 @@ def validate_receipt(root: Path) -> dict:
     if plan.schedule_sha256 != receipt["schedule_sha256"] or plan.source_sha256() != receipt["cuda_source_sha256"]:
         raise ValueError("LOWERED_CODE_IDENTITY_DOES_NOT_REPLAY")
     # The saved IR text and lowered source themselves, not only their recorded hashes.
-    saved_plan = cuda_lowering.validate_saved_cuda_plan(root / "physical.mlir", root / "lowered_cuda.py", schedule_sha256=receipt["schedule_sha256"],
+    saved_plan = cuda_lowering.validate_saved_cuda_plan(root / "physical.xdsl", root / "lowered_cuda.py", schedule_sha256=receipt["schedule_sha256"],
                                                         source_sha256=receipt["cuda_source_sha256"])
     if saved_plan != plan:
         raise ValueError("LOWERED_CODE_IDENTITY_DOES_NOT_REPLAY")

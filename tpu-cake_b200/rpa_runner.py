@@ -207,7 +207,7 @@ def run_fused_rpa(output_dir: Path, *, mode: RunMode | str = RunMode.TIMING, see
                    "cache": "bit-exact"},
     )
     run_artifacts.write_json(output_dir, output_dir / "experiment.json", experiment, "experiment", artifacts)
-    run_artifacts.write_text(output_dir, output_dir / "physical.mlir", physical_text, "physical_schedule", artifacts)
+    run_artifacts.write_text(output_dir, output_dir / "physical.xdsl", physical_text, "physical_schedule", artifacts)
     run_artifacts.write_text(output_dir, output_dir / "lowered_cuda.py", plan.render_executable_source(), "lowered_source", artifacts)
     record(RunState.LOWERED, {"schedule_sha256": plan.schedule_sha256, "cuda_source_sha256": plan.source_sha256(),
                               "execution_scope": plan.execution_scope})

@@ -172,7 +172,7 @@ def run_inkling_sharded_rpa_surface(output_dir: Path, *, emulate_on_one_gpu: boo
                                                                                 "global_input_shapes": [None if s is None else list(s) for s in plan.global_input_shapes],
                                                                                 "execution": executor.execution}, "contract", artifacts)
             run_artifacts.source_state(output_dir, artifacts)
-            run_artifacts.write_text(output_dir, output_dir / "physical.mlir", ir.canonical_text(schedule), "physical_schedule", artifacts)
+            run_artifacts.write_text(output_dir, output_dir / "physical.xdsl", ir.canonical_text(schedule), "physical_schedule", artifacts)
         record(RunState.CREATED, {"run_id": run_id, "execution": executor.execution})
         schedule.verify()
         record(RunState.VERIFIED, {"physical_ir_sha256": ir.schedule_sha256(schedule)})

@@ -267,8 +267,8 @@ def run_distributed_matmul(
         "kernels": [f"cake_matmul_rs_sm100<{plan.tile_n}>"] + (["cake_reduce_slots_sm100"] if mesh_size > 1 and strategy is not cuda_lowering.MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER else []),
     }
     if leader:
-        _write(output_dir / "distributed.mlir", ir.canonical_text(logical), "schedule", artifacts)
-        _write(output_dir / "physical.mlir", ir.canonical_text(physical), "physical_schedule", artifacts)
+        _write(output_dir / "distributed.xdsl", ir.canonical_text(logical), "schedule", artifacts)
+        _write(output_dir / "physical.xdsl", ir.canonical_text(physical), "physical_schedule", artifacts)
         _write(output_dir / "lowered_cuda.py", plan.render_executable_source(), "lowered_source", artifacts)
         wanted_kernels = [name.split("<")[0] for name in manifest["kernels"][:1]]
         experiment = run_artifacts.experiment_record(
