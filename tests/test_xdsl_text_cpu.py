@@ -233,3 +233,20 @@ def test_physical_cost_commands_work_from_a_saved_kernel(tmp_path, capsys):
     report.write_text(json.dumps(document))
     with pytest.raises(ValueError, match="PHYSICAL_COST_REPORT_MISMATCH"):
         cli.main(["verify-physical-cost", str(report), "--schedule", str(schedule)])
+
+
+def test_logical_program_prints_in_the_reference_syntax():
+    """No hash of a logical program is pinned by the reference, so this checks the shape the
+    dialect definitions prescribe (src/tpu_cake/dialects/distributed_tensor.py:55-160,1020-1043,
+    1202-1226,1437-1447): one mesh property, structured tensor types, sorted properties."""
+    text = ir.canonical_text(workloads.distributed_matmul_schedule(mesh_size=8, m=128, k=1024, n=1024))
+    lines = text.splitlines()
+    assert lines[1] == '  "dtensor.program"() <{mesh = #dtensor.mesh<["t"], [#builtin.int<8>]>, sym_name = "program"}> ({'
+    lhs = ('!dtensor.tensor<bf16, [#dtensor.dimension<"M", #builtin.int<128>>, #dtensor.dimension<"K", #builtin.int<1024>>], '
+           '#dtensor.sharding<[#dtensor.axis_list<[]>, #dtensor.axis_list<["t"]>]>, #dtensor.pending_reductions<[], []>>')
+    assert lines[2].startswith(f"  ^bb0(%0: {lhs}, %1: !dtensor.tensor<bf16, ")
+    assert lines[3].startswith('    %2 = "dtensor.einsum_local"(%0, %1) <{accumulation_type = f32, contracting_dimension = "K"}> : (')
+    assert lines[3].endswith('#dtensor.pending_reductions<["t"], ["sum"]>>')
+    assert lines[4].startswith('    %3 = "dtensor.reduce_scatter"(%2) <{axes = ["t"], reducer = "sum", scatter_dimensions = ["N"]}> : (')
+    assert lines[5].startswith('    "dtensor.return"(%3) : (') and lines[5].endswith(") -> ()")
+    assert lines[6:] == ["  }) : () -> ()", "}) : () -> ()"]

@@ -177,12 +177,15 @@ def canonical_text(module: Module) -> str:
     kernel / program symbol replaced by a fixed name, alloc roles renamed alloc0.. in definition
     order, SSA names numbered in definition order, locations omitted. A physical kernel made only
     of operations the reference's dialect has is printed exactly as the reference prints it
-    (``xdsl_text``), so its text and hash are the ones the reference assigns to the same kernel;
-    logical programs and kernels with this backend's own operations use the compact form below."""
+    (``xdsl_text``), so its text and hash are the ones the reference assigns to the same kernel; a
+    distributed matmul program is printed in the reference's syntax as well; kernels with this
+    backend's own operations use the compact form below."""
     from . import xdsl_text
 
     if xdsl_text.is_reference_physical_kernel(module):
         return xdsl_text.reference_canonical_text(module)
+    if xdsl_text.is_reference_logical_program(module):
+        return xdsl_text.reference_logical_text(module)
     names: dict[int, str] = {}
     alloc_roles: dict[str, str] = {}
     lines: list[str] = []
