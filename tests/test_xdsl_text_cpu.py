@@ -250,3 +250,24 @@ def test_logical_program_prints_in_the_reference_syntax():
     assert lines[4].startswith('    %3 = "dtensor.reduce_scatter"(%2) <{axes = ["t"], reducer = "sum", scatter_dimensions = ["N"]}> : (')
     assert lines[5].startswith('    "dtensor.return"(%3) : (') and lines[5].endswith(") -> ()")
     assert lines[6:] == ["  }) : () -> ()", "}) : () -> ()"]
+
+
+def test_logical_program_parses_back_and_lowers_to_the_same_kernel(tmp_path, capsys):
+    from tpu_cake_b200 import cli
+
+    logical = workloads.distributed_matmul_schedule(mesh_size=8, m=8192, k=16384, n=8192, scatter_dimension="M")
+    text = ir.canonical_text(logical)
+    parsed = xdsl_text.parse_reference_module(text)
+    parsed.verify()
+    assert ir.canonical_text(parsed) == text
+    assert ir.schedule_sha256(schedule_lowering.lower_distributed_matmul(parsed)) == ir.schedule_sha256(schedule_lowering.lower_distributed_matmul(logical))
+    path = tmp_path / "distributed.xdsl"
+    path.write_text(text)
+    assert cli.main(["verify-schedule", str(path)]) == 0
+    assert capsys.readouterr().out.startswith(f"SCHEDULE_ACCEPTED path={path} schedule_sha256={ir.schedule_sha256(logical)}")
+    with pytest.raises(ValueError, match="XDSL_TEXT_UNSUPPORTED_ACCUMULATION accumulation_type=bf16"):
+        xdsl_text.parse_reference_module(text.replace("accumulation_type = f32", "accumulation_type = bf16"))
+    # a sharding the mesh does not have: well-formed text, refused by the dialect's verifier
+    broken = xdsl_text.parse_reference_module(text.replace('#dtensor.mesh<["t"]', '#dtensor.mesh<["u"]'))
+    with pytest.raises(ir.VerifyException):
+        broken.verify()

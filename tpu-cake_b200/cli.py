@@ -139,7 +139,7 @@ def main(argv: list[str] | None = None) -> int:
         # The reference's command (src/tpu_cake/cli.py:432-436): parse the file, verify, accept.
         from . import xdsl_text
 
-        module = xdsl_text.parse_reference_physical_kernel(args.schedule.read_text())
+        module = xdsl_text.parse_reference_module(args.schedule.read_text())
         module.verify()
         print(f"SCHEDULE_ACCEPTED path={args.schedule} schedule_sha256={ir.schedule_sha256(module)}")
         return 0

@@ -560,3 +560,103 @@ def _property(reader: _Reader) -> tuple[str, object]:
     key = reader.word()
     reader.expect("=")
     return key, reader.attribute()
+
+
+def _dtensor_from(reader: _Reader) -> DTensorType:
+    reader.expect("!dtensor.tensor<")
+    element = reader.word()
+    reader.expect(",")
+    dimensions = reader.attribute()
+    reader.expect(",")
+    sharding = reader.attribute()
+    reader.expect(",")
+    pending = reader.attribute()
+    reader.expect(">")
+    try:
+        axes = _single(sharding, "dtensor.sharding", reader)
+        if not isinstance(pending, _Param) or pending.name != "dtensor.pending_reductions" or len(pending.parameters) != 2:
+            raise reader.fail("#dtensor.pending_reductions<axes, reducers>")
+        return DTensorType(
+            element_type=element,
+            dimensions=tuple((d.parameters[0], int(d.parameters[1])) for d in dimensions),
+            sharding=tuple(tuple(_single(a, "dtensor.axis_list", reader)) for a in axes),
+            pending_reductions=tuple(zip(pending.parameters[0], pending.parameters[1], strict=True)),
+        )
+    except (AttributeError, IndexError, TypeError) as malformed:
+        raise reader.fail("a !dtensor.tensor type") from malformed
+
+
+def parse_reference_logical_program(text: str) -> Module:
+    """Reads a distributed matmul program in the syntax ``reference_logical_text`` prints; as for
+    kernels, only text that prints back to the same bytes is accepted."""
+    reader = _Reader(text)
+    reader.expect('"builtin.module"() ({')
+    reader.expect('"dtensor.program"()')
+    reader.expect("<{")
+    raw = dict(reader.list_of(lambda: _property(reader), "}>"))
+    mesh = raw.get("mesh")
+    if not isinstance(mesh, _Param) or mesh.name != "dtensor.mesh" or len(mesh.parameters) != 2 or "sym_name" not in raw:
+        raise reader.fail("the mesh and sym_name properties of dtensor.program")
+    properties = {"sym_name": raw["sym_name"], "mesh_axis_names": tuple(mesh.parameters[0]), "mesh_axis_sizes": tuple(mesh.parameters[1])}
+    reader.expect("({")
+    values: dict[str, Value] = {}
+    block = Block()
+    if reader.take("^bb0("):
+        def argument():
+            name = reader.value_name()
+            reader.expect(":")
+            value = Value(_dtensor_from(reader), block, len(block.args))
+            block.args.append(value)
+            values[name] = value
+        reader.list_of(argument, ")")
+        reader.expect(":")
+    while not reader.peek("})"):
+        results = reader.list_of(reader.value_name, "=") if reader.peek("%") else []
+        name = reader.string()
+        reader.expect("(")
+        operand_names = reader.list_of(reader.value_name, ")")
+        op_properties = {}
+        if reader.take("<{"):
+            def logical_property():
+                key = reader.word()
+                reader.expect("=")
+                return key, (reader.word() if key == "accumulation_type" else reader.attribute())
+            op_properties = dict(reader.list_of(logical_property, "}>"))
+        reader.expect(":")
+        reader.expect("(")
+        reader.list_of(lambda: _dtensor_from(reader), ")")
+        reader.expect("->")
+        result_types = reader.list_of(lambda: _dtensor_from(reader), ")") if reader.take("(") else [_dtensor_from(reader)]
+        accumulation = op_properties.pop("accumulation_type", None)
+        if accumulation is not None and (not result_types or accumulation != result_types[0].element_type):
+            raise ValueError(f"XDSL_TEXT_UNSUPPORTED_ACCUMULATION accumulation_type={accumulation}")
+        try:
+            operands = [values[n] for n in operand_names]
+        except KeyError as unknown:
+            raise ValueError(f"XDSL_TEXT_UNDEFINED_VALUE value={unknown.args[0]}") from None
+        op = Operation(name, operands, result_types, op_properties)
+        if len(results) != len(op.results):
+            raise reader.fail("as many result names as result types")
+        for result_name, result in zip(results, op.results):
+            values[result_name] = result
+        block.ops.append(op)
+    reader.expect("}) : () -> ()")
+    reader.expect("}) : () -> ()")
+    reader.spaces()
+    if reader.at != len(text):
+        raise reader.fail("the end of the text")
+    module = Module([Operation("dtensor.program", properties=properties, body=block)])
+    if not is_reference_logical_program(module):
+        unknown = next(op.name for op in block.ops if op.name not in _LOGICAL_OPS)
+        raise ValueError(f"XDSL_TEXT_UNSUPPORTED_OPERATION operation={unknown}")
+    if reference_logical_text(module) != text:
+        raise ValueError("XDSL_TEXT_NOT_CANONICAL the text does not print back to the same bytes")
+    return module
+
+
+def parse_reference_module(text: str) -> Module:
+    """A saved schedule of either level (the reference's ``_parse_schedule``, src/tpu_cake/cli.py:419-429)."""
+    lines = text.split("\n", 2)
+    if len(lines) > 1 and lines[1].lstrip().startswith('"dtensor.program"'):
+        return parse_reference_logical_program(text)
+    return parse_reference_physical_kernel(text)
