@@ -271,3 +271,22 @@ def test_logical_program_parses_back_and_lowers_to_the_same_kernel(tmp_path, cap
     broken = xdsl_text.parse_reference_module(text.replace('#dtensor.mesh<["t"]', '#dtensor.mesh<["u"]'))
     with pytest.raises(ir.VerifyException):
         broken.verify()
+
+
+def test_damaged_text_is_refused_or_is_another_canonical_schedule():
+    """A truncation, a deleted character or a stray bracket or quote in a saved schedule either ends
+    in ValueError (never in another exception) or -- when it only changed a name or a number -- gives
+    a text that is itself canonical, i.e. prints back to exactly those bytes."""
+    refused = accepted = 0
+    for text in (ir.canonical_text(schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule())),
+                 ir.canonical_text(workloads.distributed_matmul_schedule())):
+        for cut in range(0, len(text) - 1, 11):
+            for damaged in (text[:cut], text[:cut] + text[cut + 1:], text[:cut] + "<" + text[cut:], text[:cut] + '"' + text[cut:]):
+                try:
+                    module = xdsl_text.parse_reference_module(damaged)
+                except ValueError:
+                    refused += 1
+                    continue
+                accepted += 1
+                assert ir.canonical_text(module) == damaged
+    assert refused > 20 * accepted > 0

@@ -476,7 +476,7 @@ def _axis_bandwidths(topology, mesh: dict[str, int], reader: _Reader) -> dict[st
     return bandwidth
 
 
-def parse_reference_physical_kernel(text: str) -> Module:
+def _parse_physical_kernel(text: str) -> Module:
     """Reads the canonical text of a physical kernel -- as the reference writes it to
     ``physical.xdsl`` -- into this package's IR. Only what prints back to the same bytes is
     accepted: rectilinear topologies, default engine counts, identity layouts; anything else is
@@ -586,7 +586,7 @@ def _dtensor_from(reader: _Reader) -> DTensorType:
         raise reader.fail("a !dtensor.tensor type") from malformed
 
 
-def parse_reference_logical_program(text: str) -> Module:
+def _parse_logical_program(text: str) -> Module:
     """Reads a distributed matmul program in the syntax ``reference_logical_text`` prints; as for
     kernels, only text that prints back to the same bytes is accepted."""
     reader = _Reader(text)
@@ -652,6 +652,29 @@ def parse_reference_logical_program(text: str) -> Module:
     if reference_logical_text(module) != text:
         raise ValueError("XDSL_TEXT_NOT_CANONICAL the text does not print back to the same bytes")
     return module
+
+
+def _guarded(parse, text: str) -> Module:
+    """Text that is cut short or has an attribute of the wrong kind where a number, a name or a list
+    is due ends in the same kind of error as any other text that is not a canonical schedule."""
+    try:
+        return parse(text)
+    except ValueError:
+        raise
+    except (AttributeError, IndexError, KeyError, TypeError) as malformed:
+        raise ValueError(f"XDSL_TEXT_MALFORMED {type(malformed).__name__}: {malformed}") from malformed
+
+
+def parse_reference_physical_kernel(text: str) -> Module:
+    return _guarded(_parse_physical_kernel, text)
+
+
+def parse_reference_logical_program(text: str) -> Module:
+    return _guarded(_parse_logical_program, text)
+
+
+parse_reference_physical_kernel.__doc__ = _parse_physical_kernel.__doc__
+parse_reference_logical_program.__doc__ = _parse_logical_program.__doc__
 
 
 def parse_reference_module(text: str) -> Module:
