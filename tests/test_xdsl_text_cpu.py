@@ -290,3 +290,59 @@ def test_damaged_text_is_refused_or_is_another_canonical_schedule():
                 accepted += 1
                 assert ir.canonical_text(module) == damaged
     assert refused > 20 * accepted > 0
+
+
+def test_schedules_written_by_the_reference_lower_to_cuda_plans_with_its_hashes():
+    """The drop-in in one step: the text the reference writes for its own tpu7x kernels (the pinned
+    hashes above say these are those bytes) is parsed, verified and lowered by this backend, and the
+    plan carries the schedule hash the reference computed."""
+    from tpu_cake_b200 import cuda_lowering, rpa_cuda_lowering
+
+    logical = workloads.distributed_matmul_schedule(mesh_size=8, m=1024, k=65536, n=1024)
+    kernel = schedule_lowering.lower_distributed_matmul(logical, target=TPU7X, tile=schedule_lowering.MatmulTile(128, 128))
+    parsed = xdsl_text.parse_reference_module(ir.canonical_text(kernel))
+    parsed.verify()
+    plan = cuda_lowering.lower_physical_matmul_to_cuda(parsed)
+    assert plan.schedule_sha256 == "9593beb3ad1607b65f12ac02cfe4bf2adbf6279405aa307f46c155e430d40990"
+    assert (plan.mesh_size, plan.lhs_local_shape, plan.rhs_local_shape, plan.output_local_shape) == (8, (1024, 8192), (8192, 1024), (1024, 128))
+    assert (plan.tile_m, plan.tile_k, plan.tile_n, plan.scatter_dimension) == (128, 8192, 128, 1)
+    assert plan.collective_link_bandwidths == (("t", 600_000_000_000),)
+
+    builder = rpa_kernel("inkling_fused_rpa_decode", fused_inputs())
+    builder.fused_ragged_paged_attention((*builder.inputs, builder.inputs[0], builder.inputs[3]), stage=0, softmax_scale="0.03125",
+                                         vmem_limit_bytes=96 << 20)
+    parsed = xdsl_text.parse_reference_module(ir.canonical_text(builder.module()))
+    parsed.verify()
+    rpa_plan = rpa_cuda_lowering.lower_inkling_rpa_to_cuda(parsed)
+    assert rpa_plan.schedule_sha256 == "e1de39a3dfa8f4c930207fbe5218aa1f956b19b0b933e993fe35ae916e8ecad7"
+    assert rpa_plan.query_shape == (4, 4, 32)
+
+
+def test_a_saved_schedule_names_the_run_that_reproduces_it():
+    """run-matmul --from-physical: the arguments read from a saved kernel regenerate that kernel
+    byte for byte, for a kernel of this backend (b200 target, an implementation named) and for one
+    the reference wrote (tpu7x target, none named); the invocation record replays the same plan."""
+    from tpu_cake_b200 import runner
+
+    own = schedule_lowering.lower_distributed_matmul(
+        workloads.distributed_matmul_schedule(mesh_size=8, m=8192, k=16384, n=8192, scatter_dimension="M"),
+        tile=schedule_lowering.MatmulTile(128, 256), collective_implementation="p2p_owner_push_bf16")
+    theirs = schedule_lowering.lower_distributed_matmul(
+        workloads.distributed_matmul_schedule(mesh_size=8, m=1024, k=65536, n=1024), target=TPU7X, tile=schedule_lowering.MatmulTile(128, 128))
+    for kernel, strategy, declared in ((own, "p2p_fused_epilogue_bf16_transport", True), (theirs, "nccl_reduce_scatter", False)):
+        import tempfile
+        from pathlib import Path
+
+        with tempfile.TemporaryDirectory() as folder:
+            path = Path(folder) / "physical.xdsl"
+            path.write_text(ir.canonical_text(kernel))
+            what = runner.invocation_of_saved_schedule(path)
+        assert what["collective_strategy"] == strategy and what["declare_implementation"] is declared
+        assert what["expected_schedule_sha256"] == ir.schedule_sha256(kernel)
+        invocation = {**what, "tile": [what["tile"].m, what["tile"].n], "output_dtype": "f32"}
+        _, physical, plan = runner.lower_invocation(invocation)
+        assert ir.canonical_text(physical) == ir.canonical_text(kernel)
+        assert plan.schedule_sha256 == what["expected_schedule_sha256"]
+    assert what["target"] == {"name": "tpu7x", "vmem_capacity_bytes": 64 << 20, "smem_capacity_bytes": 16 << 20,
+                              "ici_bandwidth_bytes_per_second": 600_000_000_000}
+    assert (what["mesh_size"], what["m"], what["k"], what["n"], what["scatter_dimension"]) == (8, 1024, 65536, 1024, "N")

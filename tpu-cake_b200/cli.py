@@ -44,6 +44,9 @@ def main(argv: list[str] | None = None) -> int:
     run.add_argument("--output-dtype", choices=("f32", "bf16"), default="f32")
     run.add_argument("--mode", choices=("timing", "trace", "counters"), default="timing",
                      help="trace / counters: run the measured calls untimed for the ncu invocation profiler_config.json names")
+    run.add_argument("--from-physical", type=Path, metavar="PHYSICAL.XDSL",
+                     help="run the kernel a saved physical schedule holds (one this backend or the reference wrote): mesh, shapes, tile, "
+                          "scatter dimension, target and collective come from the file and the shape options are ignored")
     run.add_argument("--emulate-on-one-gpu", action="store_true",
                      help="without one process per GPU: run every mesh position on this GPU (correctness only, not a multi-GPU timing)")
     run_rpa = commands.add_parser("run-rpa", help="run the fused Inkling RPA experiment (seed 97, 5 warm-up, 50 measured) and write a run bundle")
@@ -184,11 +187,13 @@ def main(argv: list[str] | None = None) -> int:
         if (args.tile_m is None) != (args.tile_n is None):
             parser.error("--tile-m and --tile-n come together")
         tile = schedule_lowering.MatmulTile(args.tile_m, args.tile_n) if args.tile_m is not None else None
+        what = dict(mesh_size=args.mesh_size, m=args.m, k=args.k, n=args.n, tile=tile, collective_strategy=args.collective_strategy,
+                    scatter_dimension=args.scatter_dimension)
+        if args.from_physical is not None:
+            what = runner.invocation_of_saved_schedule(args.from_physical)
         result = runner.run_distributed_matmul(
-            args.output_dir, mesh_size=args.mesh_size, m=args.m, k=args.k, n=args.n, warmup_iterations=args.warmup_iterations,
-            measured_iterations=args.measured_iterations, tile=tile, collective_strategy=args.collective_strategy,
-            scatter_dimension=args.scatter_dimension, output_dtype=args.output_dtype, mode=args.mode,
-            emulate_on_one_gpu=args.emulate_on_one_gpu,
+            args.output_dir, warmup_iterations=args.warmup_iterations, measured_iterations=args.measured_iterations,
+            output_dtype=args.output_dtype, mode=args.mode, emulate_on_one_gpu=args.emulate_on_one_gpu, **what,
         )
         print(f"run {result.run_id[:12]} mode={result.mode} passed={result.passed} median_ns={result.median_ns} execution={result.execution}")
         return 0

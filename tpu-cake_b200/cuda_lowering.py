@@ -378,15 +378,18 @@ _PHYSICAL_MATMUL_OPS = (
 )
 
 
-def _hardware_tile(schedule_tile: int, supported: tuple[int, ...], op, reject) -> int:
+def _hardware_tile(schedule_tile: int, supported: tuple[int, ...], op, reject, extent: int) -> int:
     """The schedule's tile is the block of the output one step produces; the reference's default is
     the whole local operand (src/tpu_cake/dialects/tpu_schedule.py:982-984). A schedule tile that is
     a hardware tile is used as is; a larger one is covered by the largest hardware tile (the CTA
-    walks it in sub-tiles); a smaller one that is not a hardware tile cannot be expressed."""
+    walks it in sub-tiles); the whole of an operand smaller than every hardware tile is one partial
+    hardware tile; any other smaller tile cannot be expressed."""
     if schedule_tile in supported:
         return schedule_tile
     if schedule_tile > max(supported):
         return max(supported)
+    if schedule_tile == extent:
+        return min(supported)
     raise reject(f"sm_100a matmul tiles are {supported}, the schedule asks for {schedule_tile}", op)
 
 
@@ -453,9 +456,9 @@ def lower_physical_matmul_to_cuda(module, *, output_dtype: str = "f32") -> CudaM
         rhs_sharding=tuple(rhs_type.sharding),
         output_sharding=tuple(out_type.sharding),
         scatter_dimension=collective.properties["split_dimension"],
-        tile_m=_hardware_tile(matmul.properties["tile_m"], SUPPORTED_TILE_M, matmul, reject),
+        tile_m=_hardware_tile(matmul.properties["tile_m"], SUPPORTED_TILE_M, matmul, reject, lhs_type.shape[0]),
         tile_k=matmul.properties["tile_k"],
-        tile_n=_hardware_tile(matmul.properties["tile_n"], SUPPORTED_TILE_N, matmul, reject),
+        tile_n=_hardware_tile(matmul.properties["tile_n"], SUPPORTED_TILE_N, matmul, reject, rhs_type.shape[1]),
         collective_link_bandwidths=tuple((t.split(":")[0], int(t.split(":")[1])) for t in kernel.properties["topology"]),
         collective_implementation=_IMPLEMENTATION_TO_STRATEGY[implementation] if mesh_size > 1 else None,
         output_dtype=output_dtype,

@@ -66,18 +66,9 @@ def _validate_strategy(manifest: dict, strategy: str, mesh_size: int, tile_n: in
 
 
 def _plan_of(invocation: dict):
-    logical = workloads.distributed_matmul_schedule(
-        mesh_size=invocation["mesh_size"], m=invocation["m"], k=invocation["k"], n=invocation["n"],
-        scatter_dimension=invocation["scatter_dimension"],
-    )
-    tile = schedule_lowering.MatmulTile(*invocation["tile"]) if invocation.get("tile") else None
-    strategy = cuda_lowering.MatmulCollectiveStrategy(invocation["collective_strategy"])
-    from .runner import _IMPLEMENTATION
+    from .runner import lower_invocation
 
-    physical = schedule_lowering.lower_distributed_matmul(
-        logical, tile=tile, collective_implementation=_IMPLEMENTATION[strategy] if invocation["mesh_size"] > 1 else None
-    )
-    return cuda_lowering.lower_physical_matmul_to_cuda(physical, output_dtype=invocation["output_dtype"])
+    return lower_invocation(invocation)[2]
 
 
 def _cost_payload(report: cost_model.CostModelReport) -> dict:

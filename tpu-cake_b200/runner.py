@@ -187,6 +187,50 @@ class _EmulatedMesh:
         self.handles, self.slots, self.flags = [], [], []
 
 
+def lower_invocation(invocation: dict):
+    """The logical schedule, the physical kernel and the CUDA plan an invocation record names. The
+    runner and the receipt both go through here, so a bundle replays exactly what ran -- also when
+    the run was started from a saved physical schedule, whose target description and whether its
+    collective names an implementation are then part of the record."""
+    logical = workloads.distributed_matmul_schedule(
+        mesh_size=invocation["mesh_size"], m=invocation["m"], k=invocation["k"], n=invocation["n"],
+        scatter_dimension=invocation["scatter_dimension"],
+    )
+    tile = schedule_lowering.MatmulTile(*invocation["tile"]) if invocation.get("tile") else None
+    strategy = cuda_lowering.MatmulCollectiveStrategy(invocation["collective_strategy"])
+    target = schedule_lowering.LoweringTarget(**invocation["target"]) if invocation.get("target") else schedule_lowering.B200_TARGET
+    declare = invocation.get("declare_implementation", True) and invocation["mesh_size"] > 1
+    physical = schedule_lowering.lower_distributed_matmul(
+        logical, target=target, tile=tile, collective_implementation=_IMPLEMENTATION[strategy] if declare else None
+    )
+    return logical, physical, cuda_lowering.lower_physical_matmul_to_cuda(physical, output_dtype=invocation["output_dtype"])
+
+
+def invocation_of_saved_schedule(path: Path) -> dict:
+    """What ``run_distributed_matmul`` needs to run the kernel a saved ``physical.xdsl`` holds: the
+    file is parsed, verified and lowered once to read mesh, shapes, tile, scatter dimension, target
+    and collective from it. The run regenerates the kernel from these and refuses to start if the
+    text it gets is not the saved one (``SAVED_PHYSICAL_IR_NOT_REPRODUCED``)."""
+    from . import xdsl_text
+
+    module = xdsl_text.parse_reference_physical_kernel(Path(path).read_text())
+    module.verify()
+    plan = cuda_lowering.lower_physical_matmul_to_cuda(module)
+    kernel = module.ops[0]
+    matmul = next(op for op in kernel.body.ops if op.name == "tpu_schedule.mxu_matmul")
+    collective = next(op for op in kernel.body.ops if op.name == "tpu_schedule.collective")
+    bandwidth = dict(plan.collective_link_bandwidths)[plan.mesh_axis]
+    strategy = plan.collective_implementation or cuda_lowering.MatmulCollectiveStrategy.NCCL_REDUCE_SCATTER
+    target = {"name": kernel.properties["target"], "vmem_capacity_bytes": kernel.properties["vmem_capacity_bytes"],
+              "smem_capacity_bytes": kernel.properties["smem_capacity_bytes"], "ici_bandwidth_bytes_per_second": bandwidth}
+    return {
+        "mesh_size": plan.mesh_size, "m": plan.lhs_local_shape[0], "k": plan.lhs_local_shape[1] * plan.mesh_size, "n": plan.rhs_local_shape[1],
+        "tile": schedule_lowering.MatmulTile(matmul.properties["tile_m"], matmul.properties["tile_n"]),
+        "scatter_dimension": "MN"[plan.scatter_dimension], "collective_strategy": strategy.value, "target": target,
+        "declare_implementation": "implementation" in collective.properties, "expected_schedule_sha256": plan.schedule_sha256,
+    }
+
+
 def run_distributed_matmul(
     output_dir: Path,
     *,
@@ -202,6 +246,9 @@ def run_distributed_matmul(
     output_dtype: str = "f32",
     mode: RunMode | str = RunMode.TIMING,
     emulate_on_one_gpu: bool = False,
+    target: dict | None = None,
+    declare_implementation: bool = True,
+    expected_schedule_sha256: str | None = None,
 ) -> MatmulRunResult:
     if not torch.cuda.is_available():
         raise RuntimeError("run_distributed_matmul needs a CUDA device: the CUDA backend has no CPU fallback")
@@ -229,6 +276,9 @@ def run_distributed_matmul(
         "collective_strategy": strategy.value, "scatter_dimension": scatter_dimension, "output_dtype": output_dtype, "mode": mode.value,
         "execution": "one-process-per-gpu" if distributed or mesh_size == 1 else "emulated-on-one-gpu",
     }
+    if target is not None:  # a run started from a saved physical schedule
+        invocation["target"] = dict(target)
+        invocation["declare_implementation"] = bool(declare_implementation)
     run_id = semantic_sha256("distributed-matmul-run", json.dumps(invocation, sort_keys=True))
     ledger_path = output_dir / "ledger.sqlite"
 
@@ -252,13 +302,11 @@ def run_distributed_matmul(
         artifacts.extend(ArtifactReference(a.path, a.size_bytes, a.sha256, a.role) for a in shared)
     record(RunState.CREATED, invocation)
 
-    logical = workloads.distributed_matmul_schedule(mesh_size=mesh_size, m=m, k=k, n=n, scatter_dimension=scatter_dimension)
+    logical, physical, plan = lower_invocation(invocation)
     logical.verify()
     record(RunState.VERIFIED, {"distributed_sha256": ir.schedule_sha256(logical)})
-    physical = schedule_lowering.lower_distributed_matmul(
-        logical, tile=tile, collective_implementation=_IMPLEMENTATION[strategy] if mesh_size > 1 else None
-    )
-    plan = cuda_lowering.lower_physical_matmul_to_cuda(physical, output_dtype=output_dtype)
+    if expected_schedule_sha256 is not None and plan.schedule_sha256 != expected_schedule_sha256:
+        raise ValueError(f"SAVED_PHYSICAL_IR_NOT_REPRODUCED expected={expected_schedule_sha256} regenerated={plan.schedule_sha256}")
     record(RunState.LOWERED, {"schedule_sha256": plan.schedule_sha256, "cuda_source_sha256": plan.source_sha256()})
     library = _native.library_path()
     manifest = {
