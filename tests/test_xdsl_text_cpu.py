@@ -346,3 +346,64 @@ def test_a_saved_schedule_names_the_run_that_reproduces_it():
     assert what["target"] == {"name": "tpu7x", "vmem_capacity_bytes": 64 << 20, "smem_capacity_bytes": 16 << 20,
                               "ici_bandwidth_bytes_per_second": 600_000_000_000}
     assert (what["mesh_size"], what["m"], what["k"], what["n"], what["scatter_dimension"]) == (8, 1024, 65536, 1024, "N")
+
+
+def fabricate_rpa_bundle(root, schedule, outputs_from):
+    """A bundle with the files ``validate_fused_rpa_bundle`` reads, its outputs taken from
+    ``outputs_from(inputs, scale)`` instead of a device."""
+    import json
+
+    import numpy as np
+
+    from tpu_cake_b200 import rpa_cuda_lowering, rpa_runner
+
+    plan = rpa_cuda_lowering.lower_inkling_rpa_to_cuda(schedule)
+    inputs = workloads.inkling_fused_rpa_inputs(97)
+    expectation = rpa_runner.expected_fused_rpa(inputs, softmax_scale=plan.softmax_scale)
+    outputs = outputs_from(inputs, plan.softmax_scale)
+    for folder, names, arrays in (("inputs", rpa_cuda_lowering.FUSED_INPUT_NAMES, inputs), ("outputs", ("output", "updated_cache"), outputs),
+                                  ("oracle", ("output", "updated_cache"), expectation)):
+        (root / folder).mkdir()
+        for index, (name, array) in enumerate(zip(names, arrays, strict=True)):
+            np.save(root / folder / f"{index:02d}-{name}.npy", array.view(np.uint16) if array.dtype.itemsize == 2 else array)
+    (root / "physical.xdsl").write_text(ir.canonical_text(schedule))
+    (root / "lowered_cuda.py").write_text(plan.render_executable_source())
+    (root / "invocation.json").write_text(json.dumps({"kv_chunk_tokens": 0}))
+    (root / "result.json").write_text(json.dumps({"artifacts": [], "schedule_sha256": plan.schedule_sha256, "cuda_source_sha256": plan.source_sha256()}))
+    return plan
+
+
+def test_rpa_bundle_replays_from_its_saved_kernel(tmp_path):
+    """validate_fused_rpa_bundle lowers the kernel saved in the bundle again -- this backend's own
+    schedule of the experiment, or the reference's (tpu7x target, other dimension names, the pinned
+    hash) when the run was started from its file -- and refuses a bundle whose kernel was swapped."""
+    from tpu_cake_b200 import rpa_runner
+
+    def oracle(inputs, scale):
+        return rpa_runner.expected_fused_rpa(inputs, softmax_scale=scale)
+
+    own = tmp_path / "own"
+    own.mkdir()
+    fabricate_rpa_bundle(own, workloads.inkling_fused_rpa_schedule(), oracle)
+    rpa_runner.validate_fused_rpa_bundle(own)
+
+    builder = rpa_kernel("inkling_fused_rpa_decode", fused_inputs())
+    builder.fused_ragged_paged_attention((*builder.inputs, builder.inputs[0], builder.inputs[3]), stage=0, softmax_scale="0.03125",
+                                         vmem_limit_bytes=96 << 20)
+    saved = tmp_path / "reference.xdsl"
+    saved.write_text(ir.canonical_text(builder.module()))
+    theirs = tmp_path / "theirs"
+    theirs.mkdir()
+    plan = fabricate_rpa_bundle(theirs, rpa_runner.fused_rpa_schedule_of(saved), oracle)
+    assert plan.schedule_sha256 == "e1de39a3dfa8f4c930207fbe5218aa1f956b19b0b933e993fe35ae916e8ecad7"
+    rpa_runner.validate_fused_rpa_bundle(theirs)
+
+    (theirs / "physical.xdsl").write_text((own / "physical.xdsl").read_text())
+    with pytest.raises(ValueError, match="LOWERED_CODE_IDENTITY_DOES_NOT_REPLAY"):
+        rpa_runner.validate_fused_rpa_bundle(theirs)
+
+    other = schedule_lowering.lower_distributed_matmul(workloads.distributed_matmul_schedule())
+    wrong = tmp_path / "matmul.xdsl"
+    wrong.write_text(ir.canonical_text(other))
+    with pytest.raises(ValueError, match="FUSED_RPA_SCHEDULE_SHAPE_MISMATCH"):
+        rpa_runner.fused_rpa_schedule_of(wrong)

@@ -53,6 +53,8 @@ def main(argv: list[str] | None = None) -> int:
     run_rpa.add_argument("output_dir", type=Path)
     run_rpa.add_argument("--mode", choices=("timing", "trace", "counters"), default="timing")
     run_rpa.add_argument("--kv-chunk-tokens", type=int, default=0)
+    run_rpa.add_argument("--from-physical", type=Path, metavar="PHYSICAL.XDSL",
+                         help="run the kernel a saved physical schedule holds instead of this backend's own schedule of the experiment")
     surface = commands.add_parser("run-rpa-surface", help="run the 2 x 4 sharded RPA surface protocol (five seeds, two executions each, exact repeats and cache; chained timing rounds)")
     surface.add_argument("output_dir", type=Path)
     surface.add_argument("--emulate-on-one-gpu", action="store_true", help="run the eight mesh positions one after the other on this GPU (they exchange nothing); recorded as emulated")
@@ -107,7 +109,8 @@ def main(argv: list[str] | None = None) -> int:
     if args.command == "run-rpa":
         from . import rpa_runner
 
-        return rpa_runner.rpa_device_main([str(args.output_dir), "--mode", args.mode, "--kv-chunk-tokens", str(args.kv_chunk_tokens)])
+        saved = [] if args.from_physical is None else ["--from-physical", str(args.from_physical)]
+        return rpa_runner.rpa_device_main([str(args.output_dir), "--mode", args.mode, "--kv-chunk-tokens", str(args.kv_chunk_tokens), *saved])
     if args.command == "run-rpa-surface":
         from . import rpa_surface_runner
         from .mesh import ProcessMesh

@@ -22,10 +22,11 @@ from __future__ import annotations
 
 import json
 import math
+import re
 import socket
 import statistics
 import time
-from dataclasses import asdict, dataclass
+from dataclasses import asdict, dataclass, replace
 from pathlib import Path
 
 import numpy as np
@@ -155,11 +156,32 @@ def _percentile(samples: list[int], fraction: float) -> int:
     return ordered[min(len(ordered) - 1, int(round(fraction * (len(ordered) - 1))))]
 
 
+def fused_rpa_schedule_of(physical_schedule: Path | None):
+    """The kernel the toy experiment runs: this backend's own schedule of it, or the one a saved
+    ``physical.xdsl`` holds (this backend's or the reference's ``inkling_fused_rpa_schedule``,
+    src/tpu_cake/workloads/inkling_rpa.py:145-195). A saved kernel must have the experiment's eleven
+    input shapes, since the inputs are drawn for those (``FUSED_RPA_SCHEDULE_SHAPE_MISMATCH``)."""
+    own = workloads.inkling_fused_rpa_schedule()
+    if physical_schedule is None:
+        return own
+    from . import xdsl_text
+
+    saved = xdsl_text.parse_reference_physical_kernel(Path(physical_schedule).read_text())
+    saved.verify()
+    expected = [tuple(value.type.shape) for value in own.ops[0].body.args]
+    found = [tuple(value.type.shape) for value in saved.ops[0].body.args]
+    if found != expected:
+        raise ValueError(f"FUSED_RPA_SCHEDULE_SHAPE_MISMATCH expected={expected} found={found}")
+    return saved
+
+
 def run_fused_rpa(output_dir: Path, *, mode: RunMode | str = RunMode.TIMING, seed: int = 97, warmup_iterations: int = 5,
-                  measured_iterations: int = 50, kv_chunk_tokens: int = 0, corrupt_device_cache_for_testing: bool = False) -> FusedRpaRunResult:
+                  measured_iterations: int = 50, kv_chunk_tokens: int = 0, corrupt_device_cache_for_testing: bool = False,
+                  physical_schedule: Path | None = None) -> FusedRpaRunResult:
     """Runs the toy fused-RPA experiment on the current GPU and writes its bundle.
     ``corrupt_device_cache_for_testing`` flips one cache element after the device call and before the
-    check, to show that a single forged cache byte is refused."""
+    check, to show that a single forged cache byte is refused. ``physical_schedule`` names a saved
+    kernel to run instead of this backend's own schedule of the experiment."""
     if not torch.cuda.is_available():
         raise RuntimeError("run_fused_rpa needs a CUDA device: the CUDA backend has no CPU fallback")
     mode = RunMode(mode)
@@ -167,7 +189,7 @@ def run_fused_rpa(output_dir: Path, *, mode: RunMode | str = RunMode.TIMING, see
     output_dir = Path(output_dir)
     output_dir.mkdir(parents=True, exist_ok=False)
     device = torch.device("cuda", torch.cuda.current_device())
-    schedule = workloads.inkling_fused_rpa_schedule()
+    schedule = fused_rpa_schedule_of(physical_schedule)
     plan = rpa_cuda_lowering.lower_inkling_rpa_to_cuda(schedule, kv_chunk_tokens=kv_chunk_tokens)
     run_id = semantic_sha256("inkling-fused-rpa-run", mode.value, str(seed), str(warmup_iterations), str(measured_iterations),
                              plan.schedule_sha256, plan.source_sha256())
@@ -333,7 +355,14 @@ def validate_fused_rpa_bundle(root: Path) -> dict:
     actual = tuple(load("outputs", i, name, True) for i, name in enumerate(("output", "updated_cache")))
     saved_expectation = tuple(load("oracle", i, name, True) for i, name in enumerate(("output", "updated_cache")))
     invocation = json.loads((root / "invocation.json").read_text())
-    plan = rpa_cuda_lowering.lower_inkling_rpa_to_cuda(workloads.inkling_fused_rpa_schedule(), kv_chunk_tokens=invocation["kv_chunk_tokens"])
+    # The kernel that ran is the one saved in the bundle (its bytes were checked above): parse it,
+    # verify it and lower it again.
+    plan = rpa_cuda_lowering.lower_inkling_rpa_to_cuda(fused_rpa_schedule_of(root / "physical.xdsl"), kv_chunk_tokens=invocation["kv_chunk_tokens"])
+    # The canonical text carries the fixed symbol ``kernel``; the name the run used is in its source.
+    named = re.match(r"# [^\n]*\nname = '([^'\n]*)'\n", (root / "lowered_cuda.py").read_text())
+    if named is None:
+        raise ValueError("LOWERED_CODE_IDENTITY_DOES_NOT_REPLAY")
+    plan = replace(plan, name=named.group(1))
     if plan.schedule_sha256 != result["schedule_sha256"] or plan.source_sha256() != result["cuda_source_sha256"]:
         raise ValueError("LOWERED_CODE_IDENTITY_DOES_NOT_REPLAY")
     recomputed = expected_fused_rpa(inputs, softmax_scale=plan.softmax_scale)
@@ -353,9 +382,11 @@ def rpa_device_main(argv: list[str] | None = None) -> int:
     parser.add_argument("output_dir", type=Path)
     parser.add_argument("--mode", choices=[m.value for m in RunMode], default=RunMode.TIMING.value)
     parser.add_argument("--kv-chunk-tokens", type=int, default=0)
+    parser.add_argument("--from-physical", type=Path, default=None)
     args = parser.parse_args(argv)
     protocol = workloads.FUSED_RPA_BENCHMARK_PROTOCOL
     result = run_fused_rpa(args.output_dir, mode=args.mode, seed=protocol["seed"], warmup_iterations=protocol["warmup_iterations"],
-                           measured_iterations=protocol["measured_iterations"], kv_chunk_tokens=args.kv_chunk_tokens)
+                           measured_iterations=protocol["measured_iterations"], kv_chunk_tokens=args.kv_chunk_tokens,
+                           physical_schedule=args.from_physical)
     print(f"FUSED_RPA_RUN run_id={result.run_id} mode={result.mode} passed={result.passed} median_ns={result.median_ns}")
     return 0
