@@ -159,3 +159,21 @@ def test_rpa_search_protocol_with_injected_runs(tmp_path):
     assert result.execution_orders[1] == ("chunk-256", "chunk-512")
     rows = {row.name: row for row in result.candidates}
     assert rows["chunk-256"].tile_n == 256 and 0.03 < rows["chunk-256"].improvement_over_baseline < 0.06
+
+
+def test_the_reference_tile_search_contract_is_read_as_it_is():
+    """The reference's own contract document (contracts/matmul-tile-search-tpu7x.json: mesh 8,
+    1024 x 65536 x 1024, 20 + 200 calls, five rounds, square tiles of 128 / 256 / 512) has no field
+    this backend does not know and needs none it lacks; what it does not say gets this backend's
+    defaults. Tiles above the hardware tile are walked in hardware sub-tiles."""
+    import json
+
+    document = {
+        "mesh_size": 8, "m": 1024, "k": 65536, "n": 1024, "warmup_iterations": 20, "measured_iterations": 200, "rounds": 5,
+        "bootstrap_samples": 10000, "minimum_practical_improvement": 0.01,
+        "candidates": [{"name": f"tile-{size}", "tile_m": size, "tile_n": size} for size in (128, 256, 512)],
+    }
+    contract = search.MatmulSearchContract.from_json(json.dumps(document))
+    assert (contract.mesh_size, contract.m, contract.k, contract.n, contract.rounds) == (8, 1024, 65536, 1024, 5)
+    assert [(c.name, c.tile_m, c.tile_n) for c in contract.candidates] == [("tile-128", 128, 128), ("tile-256", 256, 256), ("tile-512", 512, 512)]
+    assert contract.collective_strategy == "p2p_fused_epilogue_bf16_transport" and contract.execution == "one-process-per-gpu"
